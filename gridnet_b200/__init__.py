@@ -1,0 +1,27 @@
+"""gridnet_b200 — B200-native kernels for gridnet's block-local recurrent grid
+update, behind the reference's own op surface.
+
+``GridnetCudaOp`` / ``GatedGridnetCudaOp`` are drop-ins for the classes of the same
+name in the reference's ``gridnet/backend_cuda.py``; ``gridnet_cuda`` mirrors its
+native extension module. Everything runs through ``libgridnet_b200.so`` (C ABI in
+``include/gridnet_b200.h``); there is no CPU or PyTorch fallback.
+"""
+from . import gridnet_cuda
+from ._lib import LIB_PATH, GridnetB200Error
+from .backend_cuda import (GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, fused_step, norm_apply,
+                           norm_finalize, outer_forward, outer_forward_workspace, step_stats_partials)
+
+__all__ = [
+    "GridnetCudaOp",
+    "GatedGridnetCudaOp",
+    "GridNormOp",
+    "outer_forward",
+    "outer_forward_workspace",
+    "fused_step",
+    "norm_finalize",
+    "norm_apply",
+    "step_stats_partials",
+    "gridnet_cuda",
+    "GridnetB200Error",
+    "LIB_PATH",
+]

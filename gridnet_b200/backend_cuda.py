@@ -1,0 +1,233 @@
+"""Autograd ops with the reference's op surface (gridnet/backend_cuda.py:5-190).
+
+``GridnetCudaOp.apply(weight, bias, residual_scale, init_activations, inner_iters,
+block_size, eps, normalize, activation)`` and ``GatedGridnetCudaOp.apply(weight,
+bias, init_activations, inner_iters, block_size, activation)`` take the same
+arguments, make the same shape/dtype/device assertions (AssertionError), return a
+clone for an empty batch and hand back the same gradient tuples as the reference
+classes, so ``gridnet/__init__.py:14-18`` can import them in place of the originals.
+
+Added on top of that surface, for the whole-grid normalisation the reference's
+models run between steps (gridnet/scripts/train_mnist.py:54,62-64):
+``GridNormOp`` (LayerNorm over [M,N,K] per sample, forward and backward) and
+``outer_forward`` (the fused inference loop).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import gridnet_cuda
+from ._lib import activation_id, check, lib
+
+
+def _assert_step_args(weight, bias, residual_scale, init_activations, block_size, gated):
+    batch_size, m, n, k = init_activations.shape
+    assert m % block_size == 0 and n % block_size == 0 and k % block_size == 0, (
+        f"{block_size=} incompatible with {init_activations.shape=}")
+    want = (27, 2, m, n, k) if gated else (27, m, n, k)
+    assert tuple(weight.shape) == want, f"{weight.shape=} invalid for {init_activations.shape=}"
+    assert bias.shape == weight.shape[1:], f"{bias.shape=} invalid for {weight.shape=}"
+    others = [("bias", bias), ("init_activations", init_activations)]
+    if not gated:
+        assert bias.shape == residual_scale.shape, f"{bias.shape=} invalid for {residual_scale.shape=}"
+        others.insert(1, ("residual_scale", residual_scale))
+    for name, t in others:
+        assert weight.dtype == t.dtype, f"mismatching dtypes: {weight.dtype=} {name}.dtype={t.dtype}"
+    for name, t in others:
+        assert weight.device == t.device, f"mismatching devices: {weight.device=} {name}.device={t.device}"
+    return batch_size
+
+
+class GridnetCudaOp(torch.autograd.Function):
+    """One outer-loop step of the plain gridnet (gridnet/backend_cuda.py:5-108)."""
+
+    @staticmethod
+    def forward(ctx, weight, bias, residual_scale, init_activations, inner_iters: int, block_size: int,
+                eps: float, normalize: bool, activation: str):
+        batch_size = _assert_step_args(weight, bias, residual_scale, init_activations, block_size, False)
+        if not batch_size:
+            return init_activations.clone()
+        ctx.save_for_backward(weight, bias, residual_scale, init_activations)
+        ctx.cfg = (inner_iters, block_size, eps, normalize, activation)
+        outputs = torch.empty_like(init_activations)
+        gridnet_cuda.forward(weight, bias, residual_scale, init_activations, outputs, inner_iters, block_size,
+                             eps, normalize, activation)
+        return outputs
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        weight, bias, residual_scale, init_activations = ctx.saved_tensors
+        inner_iters, block_size, eps, normalize, activation = ctx.cfg
+        # every gradient buffer is written in full by the library: no zero fill
+        weight_grad = torch.empty_like(weight)
+        bias_grad = torch.empty_like(bias)
+        scale_grad = torch.empty_like(residual_scale)
+        act_grad = torch.empty_like(init_activations)
+        gridnet_cuda.backward(weight, bias, residual_scale, init_activations, grad_output.contiguous(),
+                              weight_grad, bias_grad, scale_grad, act_grad, inner_iters, block_size, eps,
+                              normalize, activation)
+        return weight_grad, bias_grad, scale_grad, act_grad, None, None, None, None, None
+
+
+class GatedGridnetCudaOp(torch.autograd.Function):
+    """One outer-loop step of the gated gridnet (gridnet/backend_cuda.py:111-190)."""
+
+    @staticmethod
+    def forward(ctx, weight, bias, init_activations, inner_iters: int, block_size: int, activation: str):
+        batch_size = _assert_step_args(weight, bias, None, init_activations, block_size, True)
+        if not batch_size:
+            return init_activations.clone()
+        ctx.save_for_backward(weight, bias, init_activations)
+        ctx.cfg = (inner_iters, block_size, activation)
+        outputs = torch.empty_like(init_activations)
+        gridnet_cuda.forward_gated(weight, bias, init_activations, outputs, inner_iters, block_size, activation)
+        return outputs
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        weight, bias, init_activations = ctx.saved_tensors
+        inner_iters, block_size, activation = ctx.cfg
+        weight_grad = torch.empty_like(weight)
+        bias_grad = torch.empty_like(bias)
+        act_grad = torch.empty_like(init_activations)
+        gridnet_cuda.backward_gated(weight, bias, init_activations, grad_output.contiguous(), weight_grad,
+                                    bias_grad, act_grad, inner_iters, block_size, activation)
+        return weight_grad, bias_grad, act_grad, None, None, None
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _require_f32_cuda(**tensors):
+    for name, t in tensors.items():
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor")
+        if t.dtype != torch.float32:
+            raise RuntimeError(f"{name} must be float32")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+
+
+class GridNormOp(torch.autograd.Function):
+    """``torch.nn.LayerNorm`` over the whole grid of each sample, float32.
+
+    ``GridNormOp.apply(x, gamma, beta, eps)`` with x [B, M, N, K] and gamma, beta
+    [M, N, K] equals ``F.layer_norm(x, x.shape[1:], gamma, beta, eps)``.
+    """
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps: float = 1e-5):
+        assert x.shape[1:] == gamma.shape == beta.shape, f"{gamma.shape=} {beta.shape=} invalid for {x.shape=}"
+        if not x.shape[0]:
+            return x.clone()
+        _require_f32_cuda(x=x, gamma=gamma, beta=beta)
+        B, P = x.shape[0], x[0].numel()
+        y = torch.empty_like(x)
+        ws = _workspace(lib.gn_norm_workspace_bytes(B, P), x.device)
+        with torch.cuda.device(x.device):
+            check(lib.gn_norm_forward_f32(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), None, B,
+                                          P, float(eps), ws.data_ptr(), ws.numel(),
+                                          torch.cuda.current_stream().cuda_stream))
+        ctx.save_for_backward(x, gamma)
+        ctx.eps = float(eps)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, gamma = ctx.saved_tensors
+        grad_y = grad_y.contiguous()
+        B, P = x.shape[0], x[0].numel()
+        gx, gg, gb = torch.empty_like(x), torch.empty_like(gamma), torch.empty_like(gamma)
+        ws = _workspace(lib.gn_norm_workspace_bytes(B, P), x.device)
+        with torch.cuda.device(x.device):
+            check(lib.gn_norm_backward_f32(x.data_ptr(), gamma.data_ptr(), grad_y.data_ptr(), gx.data_ptr(),
+                                           gg.data_ptr(), gb.data_ptr(), B, P, ctx.eps, ws.data_ptr(), ws.numel(),
+                                           torch.cuda.current_stream().cuda_stream))
+        return gx, gg, gb, None
+
+
+def outer_forward_workspace(batch: int, shape, block_size: int, device) -> torch.Tensor:
+    """Scratch buffer for :func:`outer_forward`; reusable across calls of the same size."""
+    m, n, k = shape
+    return _workspace(lib.gn_outer_forward_workspace_bytes(batch, m, n, k, block_size), device)
+
+
+@torch.no_grad()
+def outer_forward(weight, bias, residual_scale, norm_weight, norm_bias, init_activations, inner_iters: int,
+                  outer_iters: int, block_size: int, activation: str = "silu", ln_eps: float = 1e-5,
+                  out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Inference loop of the reference's models, fused:
+
+        h = init_activations
+        for _ in range(outer_iters):
+            h = gridnet_step(weight, bias, residual_scale, h, inner_iters, block_size, normalize=False, ...)
+            h = layer_norm(h, (M, N, K), norm_weight, norm_bias, ln_eps)
+
+    (gridnet/scripts/train_mnist.py:62-64). float32, no autograd.
+    """
+    batch_size = _assert_step_args(weight, bias, residual_scale, init_activations, block_size, False)
+    assert norm_weight.shape == bias.shape == norm_bias.shape, f"{norm_weight.shape=} invalid for {bias.shape=}"
+    if not batch_size:
+        return init_activations.clone()
+    _require_f32_cuda(weight=weight, bias=bias, residual_scale=residual_scale, norm_weight=norm_weight,
+                      norm_bias=norm_bias, init_activations=init_activations)
+    B, M, N, K = init_activations.shape
+    y = torch.empty_like(init_activations) if out is None else out
+    need = lib.gn_outer_forward_workspace_bytes(B, M, N, K, block_size)
+    ws = workspace if workspace is not None else _workspace(need, weight.device)
+    with torch.cuda.device(weight.device):
+        check(lib.gn_outer_forward_f32(weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(),
+                                       norm_weight.data_ptr(), norm_bias.data_ptr(),
+                                       init_activations.data_ptr(), y.data_ptr(), B, M, N, K, int(inner_iters),
+                                       int(outer_iters), int(block_size), float(ln_eps),
+                                       activation_id(activation), ws.data_ptr(), ws.numel(),
+                                       torch.cuda.current_stream().cuda_stream))
+    return y
+
+
+def step_stats_partials(shape, block_size: int) -> int:
+    """Number of (sum, sum of squares) pairs per sample that :func:`fused_step` writes."""
+    m, n, k = shape
+    return int(lib.gn_step_stats_partials(m, n, k, block_size))
+
+
+@torch.no_grad()
+def fused_step(weight, bias, residual_scale, x, out, inner_iters: int, block_size: int, activation: str = "silu",
+               norm_weight=None, norm_bias=None, in_mean_rstd=None, out_partials=None) -> torch.Tensor:
+    """One step of the fused loop (``gn_step_forward_fused_f32``): ``x`` may be the raw
+    output of the previous step, normalised on load with ``in_mean_rstd`` [B, 2] and
+    ``norm_weight`` / ``norm_bias``; ``out_partials`` [B, nparts, 2] float64 receives the
+    statistics partials of ``out``. Block size 8, float32."""
+    _require_f32_cuda(weight=weight, bias=bias, residual_scale=residual_scale, x=x, out=out)
+    B, M, N, K = x.shape
+    ptr = lambda t: None if t is None else t.data_ptr()
+    with torch.cuda.device(weight.device):
+        check(lib.gn_step_forward_fused_f32(weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(),
+                                            x.data_ptr(), out.data_ptr(), ptr(norm_weight), ptr(norm_bias),
+                                            ptr(in_mean_rstd), ptr(out_partials), B, M, N, K, int(inner_iters),
+                                            int(block_size), activation_id(activation),
+                                            torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+@torch.no_grad()
+def norm_finalize(partials, mean_rstd, P: int, eps: float = 1e-5) -> torch.Tensor:
+    """[B, nparts, 2] float64 partial sums -> [B, 2] float32 (mean, 1/sqrt(var + eps))."""
+    B, nparts = partials.shape[0], partials.shape[1]
+    with torch.cuda.device(partials.device):
+        check(lib.gn_norm_finalize_f32(partials.data_ptr(), nparts, mean_rstd.data_ptr(), B, int(P), float(eps),
+                                       torch.cuda.current_stream().cuda_stream))
+    return mean_rstd
+
+
+@torch.no_grad()
+def norm_apply(x, norm_weight, norm_bias, mean_rstd, out) -> torch.Tensor:
+    """out = (x - mean) * rstd * norm_weight + norm_bias per sample."""
+    _require_f32_cuda(x=x, norm_weight=norm_weight, norm_bias=norm_bias, out=out)
+    B, P = x.shape[0], x[0].numel()
+    with torch.cuda.device(x.device):
+        check(lib.gn_norm_apply_f32(x.data_ptr(), norm_weight.data_ptr(), norm_bias.data_ptr(),
+                                    mean_rstd.data_ptr(), out.data_ptr(), B, P,
+                                    torch.cuda.current_stream().cuda_stream))
+    return out

@@ -1,0 +1,475 @@
+// extern "C" entry points declared in include/gridnet_b200.h: argument checks,
+// kernel selection, and the fused model loop.
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace gn {
+
+static thread_local char g_cuda_error[256] = "";
+
+void record_cuda_error(cudaError_t e, const char *where)
+{
+    snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", where, cudaGetErrorString(e));
+}
+
+int check_launch(const char *where)
+{
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        record_cuda_error(e, where);
+        (void)cudaGetLastError();  // clear a non-sticky launch error
+        return GN_ERR_CUDA;
+    }
+    return GN_OK;
+}
+
+static int check_geometry(int B, int M, int N, int K, int inner, int block, int act)
+{
+    if (B < 0 || M <= 0 || N <= 0 || K <= 0) return GN_ERR_BAD_SHAPE;
+    if (B > 65535 * 64) return GN_ERR_BAD_SHAPE;
+    if (block != 4 && block != 8) return GN_ERR_BAD_BLOCK;
+    if (M % block || N % block || K % block) return GN_ERR_BAD_BLOCK;
+    if (inner < 0) return GN_ERR_BAD_INNER;
+    if (act < GN_ACT_RELU || act > GN_ACT_TANH) return GN_ERR_BAD_ACTIVATION;
+    const long long nb = (long long)(M / block) * (N / block) * (K / block);
+    if (nb > 0x7fffffffLL) return GN_ERR_BAD_SHAPE;
+    return GN_OK;
+}
+
+template <typename R>
+static int copy_through(const R *x, R *y, int B, int M, int N, int K, cudaStream_t st)
+{
+    if (x == y) return GN_OK;
+    const cudaError_t e =
+        cudaMemcpyAsync(y, x, sizeof(R) * (size_t)B * M * N * K, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "cudaMemcpyAsync");
+        return GN_ERR_CUDA;
+    }
+    return GN_OK;
+}
+
+template <typename R>
+static int step_forward(const R *w, const R *b, const R *s, const R *x, R *y, int B, int M, int N, int K,
+                        int inner, int block, R eps, int normalize, int act, cudaStream_t st);
+
+template <>
+int step_forward<double>(const double *w, const double *b, const double *s, const double *x, double *y, int B,
+                         int M, int N, int K, int inner, int block, double eps, int normalize, int act,
+                         cudaStream_t st)
+{
+    return launch_step_fwd_generic<double>(w, b, s, x, y, B, M, N, K, inner, block, eps, normalize, act, st);
+}
+
+template <>
+int step_forward<float>(const float *w, const float *b, const float *s, const float *x, float *y, int B, int M,
+                        int N, int K, int inner, int block, float eps, int normalize, int act, cudaStream_t st)
+{
+    FastFwdParams p{};
+    p.w = w; p.b = b; p.s = s; p.x = x; p.y = y;
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
+    if (fast8_applicable(p, block, normalize)) return launch_step_fwd_fast8(p, act, st);
+    return launch_step_fwd_generic<float>(w, b, s, x, y, B, M, N, K, inner, block, eps, normalize, act, st);
+}
+
+template <typename R>
+static int api_step_forward(const R *w, const R *b, const R *s, const R *x, R *y, int B, int M, int N, int K,
+                            int inner, int block, R eps, int normalize, int act, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (B == 0) return GN_OK;
+    if (!w || !b || !s || !x || !y) return GN_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (inner == 0) return copy_through(x, y, B, M, N, K, st);
+    return step_forward<R>(w, b, s, x, y, B, M, N, K, inner, block, eps, normalize, act, st);
+}
+
+template <typename R>
+static int api_step_backward(const R *w, const R *b, const R *s, const R *x, const R *gy, R *gw, R *gb, R *gs,
+                             R *gx, int B, int M, int N, int K, int inner, int block, R eps, int normalize,
+                             int act, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (!w || !b || !s || !gw || !gb || !gs) return GN_ERR_NULL_POINTER;
+    if (B > 0 && (!x || !gy || !gx)) return GN_ERR_NULL_POINTER;
+    if (inner > step_backward_max_inner(block, (int)sizeof(R))) return GN_ERR_BAD_INNER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (B == 0) {
+        const size_t P = (size_t)M * N * K;
+        cudaError_t e = cudaMemsetAsync(gw, 0, sizeof(R) * 27 * P, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gb, 0, sizeof(R) * P, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gs, 0, sizeof(R) * P, st);
+        if (e != cudaSuccess) {
+            record_cuda_error(e, "cudaMemsetAsync");
+            return GN_ERR_CUDA;
+        }
+        return GN_OK;
+    }
+    return launch_step_bwd_generic<R>(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, eps, normalize,
+                                      act, st);
+}
+
+template <typename R>
+static int api_gated_forward(const R *w, const R *b, const R *x, R *y, int B, int M, int N, int K, int inner,
+                             int block, int act, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (B == 0) return GN_OK;
+    if (!w || !b || !x || !y) return GN_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (inner == 0) return copy_through(x, y, B, M, N, K, st);
+    return launch_gated_fwd_generic<R>(w, b, x, y, B, M, N, K, inner, block, act, st);
+}
+
+template <typename R>
+static int api_gated_backward(const R *w, const R *b, const R *x, const R *gy, R *gw, R *gb, R *gx, int B, int M,
+                              int N, int K, int inner, int block, int act, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (!w || !b || !gw || !gb) return GN_ERR_NULL_POINTER;
+    if (B > 0 && (!x || !gy || !gx)) return GN_ERR_NULL_POINTER;
+    if (inner > step_backward_max_inner(block, (int)sizeof(R))) return GN_ERR_BAD_INNER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (B == 0) {
+        const size_t P = (size_t)M * N * K;
+        cudaError_t e = cudaMemsetAsync(gw, 0, sizeof(R) * 54 * P, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gb, 0, sizeof(R) * 2 * P, st);
+        if (e != cudaSuccess) {
+            record_cuda_error(e, "cudaMemsetAsync");
+            return GN_ERR_CUDA;
+        }
+        return GN_OK;
+    }
+    return launch_gated_bwd_generic<R>(w, b, x, gy, gw, gb, gx, B, M, N, K, inner, block, act, st);
+}
+
+// ---- workspace carving ------------------------------------------------------
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct NormWs {
+    double2 *partials;  // [B][kNormMaxParts]
+    float2 *stats;      // [B]
+    float2 *ac;         // [B]
+    size_t bytes;
+};
+
+static NormWs carve_norm(void *base, int B)
+{
+    NormWs w;
+    size_t off = 0;
+    unsigned char *p = (unsigned char *)base;
+    w.partials = (double2 *)(p + off);
+    off = align_up(off + sizeof(double2) * (size_t)B * kNormMaxParts, 256);
+    w.stats = (float2 *)(p + off);
+    off = align_up(off + sizeof(float2) * (size_t)B, 256);
+    w.ac = (float2 *)(p + off);
+    off = align_up(off + sizeof(float2) * (size_t)B, 256);
+    w.bytes = off;
+    return w;
+}
+
+struct OuterWs {
+    float *buf[2];      // [B,M,N,K] each
+    double2 *partials;  // [B][blocks * 4]
+    float2 *stats;      // [B]
+    size_t bytes;
+};
+
+static OuterWs carve_outer(void *base, int B, int M, int N, int K, int block)
+{
+    OuterWs w;
+    const size_t P = (size_t)M * N * K;
+    const size_t nb = (size_t)(M / block) * (N / block) * (K / block);
+    size_t off = 0;
+    unsigned char *p = (unsigned char *)base;
+    for (int i = 0; i < 2; ++i) {
+        w.buf[i] = (float *)(p + off);
+        off = align_up(off + sizeof(float) * (size_t)B * P, 256);
+    }
+    w.partials = (double2 *)(p + off);
+    off = align_up(off + sizeof(double2) * (size_t)B * nb * 4, 256);
+    w.stats = (float2 *)(p + off);
+    off = align_up(off + sizeof(float2) * (size_t)B, 256);
+    w.bytes = off;
+    return w;
+}
+
+static int check_ws(const void *ws, size_t have, size_t need)
+{
+    if (!ws) return GN_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(ws) % 16) return GN_ERR_WORKSPACE;
+    if (have < need) return GN_ERR_WORKSPACE;
+    return GN_OK;
+}
+
+}  // namespace gn
+
+using namespace gn;
+
+extern "C" {
+
+GN_API const char *gn_status_string(int status)
+{
+    switch (status) {
+    case GN_OK: return "ok";
+    case GN_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case GN_ERR_BAD_BLOCK: return "block size must be 4 or 8 and divide M, N and K";
+    case GN_ERR_BAD_SHAPE: return "invalid or unsupported tensor shape";
+    case GN_ERR_BAD_ACTIVATION: return "unknown activation function";
+    case GN_ERR_BAD_INNER: return "invalid inner iteration count (negative, or too many for the backward stash)";
+    case GN_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case GN_ERR_CUDA: return "CUDA error (see gn_last_cuda_error)";
+    case GN_ERR_UNSUPPORTED: return "combination not supported by this entry point";
+    case GN_ERR_TOO_LARGE: return "size exceeds a fixed built-in limit";
+    default: return "unknown status";
+    }
+}
+
+GN_API const char *gn_last_cuda_error(void) { return g_cuda_error; }
+
+GN_API int gn_activation_from_name(const char *name)
+{
+    if (!name) return -1;
+    if (!strcmp(name, "relu")) return GN_ACT_RELU;
+    if (!strcmp(name, "leaky_relu")) return GN_ACT_LEAKY_RELU;
+    if (!strcmp(name, "silu")) return GN_ACT_SILU;
+    if (!strcmp(name, "tanh")) return GN_ACT_TANH;
+    return -1;
+}
+
+GN_API int gn_version(void) { return 1; }
+
+GN_API int gn_step_forward_f32(const float *w, const float *b, const float *s, const float *x, float *y, int B, int M,
+                        int N, int K, int inner, int block, float eps, int normalize, int act, void *stream)
+{
+    return api_step_forward<float>(w, b, s, x, y, B, M, N, K, inner, block, eps, normalize, act, stream);
+}
+GN_API int gn_step_forward_f64(const double *w, const double *b, const double *s, const double *x, double *y, int B,
+                        int M, int N, int K, int inner, int block, double eps, int normalize, int act,
+                        void *stream)
+{
+    return api_step_forward<double>(w, b, s, x, y, B, M, N, K, inner, block, eps, normalize, act, stream);
+}
+GN_API int gn_step_backward_f32(const float *w, const float *b, const float *s, const float *x, const float *gy,
+                         float *gw, float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner,
+                         int block, float eps, int normalize, int act, void *stream)
+{
+    return api_step_backward<float>(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, eps, normalize, act,
+                                    stream);
+}
+GN_API int gn_step_backward_f64(const double *w, const double *b, const double *s, const double *x, const double *gy,
+                         double *gw, double *gb, double *gs, double *gx, int B, int M, int N, int K, int inner,
+                         int block, double eps, int normalize, int act, void *stream)
+{
+    return api_step_backward<double>(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, eps, normalize,
+                                     act, stream);
+}
+GN_API int gn_step_backward_max_inner(int block, int elem_size) { return step_backward_max_inner(block, elem_size); }
+
+GN_API int gn_gated_forward_f32(const float *w, const float *b, const float *x, float *y, int B, int M, int N, int K,
+                         int inner, int block, int act, void *stream)
+{
+    return api_gated_forward<float>(w, b, x, y, B, M, N, K, inner, block, act, stream);
+}
+GN_API int gn_gated_forward_f64(const double *w, const double *b, const double *x, double *y, int B, int M, int N,
+                         int K, int inner, int block, int act, void *stream)
+{
+    return api_gated_forward<double>(w, b, x, y, B, M, N, K, inner, block, act, stream);
+}
+GN_API int gn_gated_backward_f32(const float *w, const float *b, const float *x, const float *gy, float *gw, float *gb,
+                          float *gx, int B, int M, int N, int K, int inner, int block, int act, void *stream)
+{
+    return api_gated_backward<float>(w, b, x, gy, gw, gb, gx, B, M, N, K, inner, block, act, stream);
+}
+GN_API int gn_gated_backward_f64(const double *w, const double *b, const double *x, const double *gy, double *gw,
+                          double *gb, double *gx, int B, int M, int N, int K, int inner, int block, int act,
+                          void *stream)
+{
+    return api_gated_backward<double>(w, b, x, gy, gw, gb, gx, B, M, N, K, inner, block, act, stream);
+}
+
+GN_API size_t gn_norm_workspace_bytes(int B, long long P)
+{
+    (void)P;
+    if (B <= 0) return 256;
+    return carve_norm(nullptr, B).bytes;
+}
+
+GN_API int gn_norm_forward_f32(const float *x, const float *gamma, const float *beta, float *y, float *mean_rstd, int B,
+                        long long P, float eps, void *workspace, size_t workspace_bytes, void *stream)
+{
+    if (B < 0 || P <= 0 || B > 65535) return GN_ERR_BAD_SHAPE;
+    if (B == 0) return GN_OK;
+    if (!x || !gamma || !beta || !y) return GN_ERR_NULL_POINTER;
+    int rc = check_ws(workspace, workspace_bytes, gn_norm_workspace_bytes(B, P));
+    if (rc != GN_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const NormWs ws = carve_norm(workspace, B);
+    const int parts = norm_pick_parts(P);
+    rc = launch_norm_partial_stats(x, ws.partials, B, P, parts, st);
+    if (rc != GN_OK) return rc;
+    rc = launch_norm_finalize(ws.partials, parts, ws.stats, B, P, eps, st);
+    if (rc != GN_OK) return rc;
+    rc = launch_norm_apply(x, gamma, beta, ws.stats, y, B, P, st);
+    if (rc != GN_OK) return rc;
+    if (mean_rstd) {
+        const cudaError_t e =
+            cudaMemcpyAsync(mean_rstd, ws.stats, sizeof(float2) * (size_t)B, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) {
+            record_cuda_error(e, "cudaMemcpyAsync");
+            return GN_ERR_CUDA;
+        }
+    }
+    return GN_OK;
+}
+
+GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float *gy, float *gx, float *ggamma,
+                         float *gbeta, int B, long long P, float eps, void *workspace, size_t workspace_bytes,
+                         void *stream)
+{
+    if (B < 0 || P <= 0 || B > 65535) return GN_ERR_BAD_SHAPE;
+    if (!gamma || !ggamma || !gbeta) return GN_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (B == 0) {
+        cudaError_t e = cudaMemsetAsync(ggamma, 0, sizeof(float) * (size_t)P, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gbeta, 0, sizeof(float) * (size_t)P, st);
+        if (e != cudaSuccess) {
+            record_cuda_error(e, "cudaMemsetAsync");
+            return GN_ERR_CUDA;
+        }
+        return GN_OK;
+    }
+    if (!x || !gy || !gx) return GN_ERR_NULL_POINTER;
+    int rc = check_ws(workspace, workspace_bytes, gn_norm_workspace_bytes(B, P));
+    if (rc != GN_OK) return rc;
+    const NormWs ws = carve_norm(workspace, B);
+    const int parts = norm_pick_parts(P);
+    rc = launch_norm_partial_stats(x, ws.partials, B, P, parts, st);
+    if (rc != GN_OK) return rc;
+    rc = launch_norm_finalize(ws.partials, parts, ws.stats, B, P, eps, st);
+    if (rc != GN_OK) return rc;
+    return launch_norm_backward(x, gamma, gy, ws.stats, ws.partials, ws.ac, gx, ggamma, gbeta, B, P, parts, st);
+}
+
+GN_API int gn_step_stats_partials(int M, int N, int K, int block)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || block != 8 || M % 8 || N % 8 || K % 8) return 0;
+    const long long n = (long long)(M / 8) * (N / 8) * (K / 8) * 4;
+    return n > 0x7fffffffLL ? 0 : (int)n;
+}
+
+GN_API int gn_step_forward_fused_f32(const float *w, const float *b, const float *s, const float *x, float *y,
+                              const float *gamma, const float *beta, const float *in_mean_rstd,
+                              double *out_partials, int B, int M, int N, int K, int inner, int block, int act,
+                              void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (B == 0) return GN_OK;
+    if (!w || !b || !s || !x || !y) return GN_ERR_NULL_POINTER;
+    if (in_mean_rstd && (!gamma || !beta)) return GN_ERR_NULL_POINTER;
+    FastFwdParams p{};
+    p.w = w; p.b = b; p.s = s; p.x = x; p.y = y; p.gamma = gamma; p.beta = beta;
+    p.in_stats = reinterpret_cast<const float2 *>(in_mean_rstd);
+    p.out_partials = reinterpret_cast<double2 *>(out_partials);
+    p.nparts = gn_step_stats_partials(M, N, K, block);
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
+    if (!fast8_applicable(p, block, 0)) return GN_ERR_UNSUPPORTED;
+    if ((in_mean_rstd && reinterpret_cast<uintptr_t>(in_mean_rstd) % 8) ||
+        (out_partials && reinterpret_cast<uintptr_t>(out_partials) % 16))
+        return GN_ERR_UNSUPPORTED;
+    return launch_step_fwd_fast8(p, act, (cudaStream_t)stream);
+}
+
+GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_rstd, int B, long long P, float eps,
+                         void *stream)
+{
+    if (B < 0 || P <= 0 || nparts <= 0) return GN_ERR_BAD_SHAPE;
+    if (B == 0) return GN_OK;
+    if (!partials || !mean_rstd) return GN_ERR_NULL_POINTER;
+    return launch_norm_finalize(reinterpret_cast<const double2 *>(partials), nparts,
+                                reinterpret_cast<float2 *>(mean_rstd), B, P, eps, (cudaStream_t)stream);
+}
+
+GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *beta, const float *mean_rstd, float *y,
+                      int B, long long P, void *stream)
+{
+    if (B < 0 || P <= 0 || B > 65535) return GN_ERR_BAD_SHAPE;
+    if (B == 0) return GN_OK;
+    if (!x || !gamma || !beta || !mean_rstd || !y) return GN_ERR_NULL_POINTER;
+    return launch_norm_apply(x, gamma, beta, reinterpret_cast<const float2 *>(mean_rstd), y, B, P,
+                             (cudaStream_t)stream);
+}
+
+GN_API size_t gn_outer_forward_workspace_bytes(int B, int M, int N, int K, int block)
+{
+    if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || (block != 4 && block != 8)) return 256;
+    return carve_outer(nullptr, B, M, N, K, block).bytes;
+}
+
+GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, const float *gamma, const float *beta,
+                         const float *x, float *y, int B, int M, int N, int K, int inner, int outer, int block,
+                         float ln_eps, int act, void *workspace, size_t workspace_bytes, void *stream)
+{
+    int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (outer < 0) return GN_ERR_BAD_SHAPE;
+    if (B > 65535) return GN_ERR_BAD_SHAPE;
+    if (B == 0) return GN_OK;
+    if (!w || !b || !s || !gamma || !beta || !x || !y) return GN_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (outer == 0) return copy_through(x, y, B, M, N, K, st);
+    rc = check_ws(workspace, workspace_bytes, gn_outer_forward_workspace_bytes(B, M, N, K, block));
+    if (rc != GN_OK) return rc;
+    const OuterWs ws = carve_outer(workspace, B, M, N, K, block);
+    const long long P = (long long)M * N * K;
+
+    FastFwdParams p{};
+    p.w = w; p.b = b; p.s = s; p.gamma = gamma; p.beta = beta;
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
+    p.x = x; p.y = ws.buf[0];
+    const bool fused = fast8_applicable(p, block, 0);
+    const int nparts_fused = (int)((long long)(M / 8) * (N / 8) * (K / 8) * 4);
+
+    const float *src = x;
+    for (int o = 0; o < outer; ++o) {
+        float *dst = ws.buf[o & 1];
+        if (fused) {
+            p.x = src;
+            p.y = dst;
+            p.in_stats = o > 0 ? ws.stats : nullptr;  // raw output of the previous step: normalise on load
+            p.out_partials = ws.partials;
+            p.nparts = nparts_fused;
+            rc = launch_step_fwd_fast8(p, act, st);
+            if (rc != GN_OK) return rc;
+            rc = launch_norm_finalize(ws.partials, nparts_fused, ws.stats, B, P, ln_eps, st);
+            if (rc != GN_OK) return rc;
+            src = dst;
+        } else {
+            // unfused composition: step, statistics, normalise in place
+            if (inner == 0) rc = copy_through(src, dst, B, M, N, K, st);
+            else rc = launch_step_fwd_generic<float>(w, b, s, src, dst, B, M, N, K, inner, block, 0.0f, 0, act, st);
+            if (rc != GN_OK) return rc;
+            const int parts = norm_pick_parts(P);
+            rc = launch_norm_partial_stats(dst, ws.partials, B, P, parts, st);
+            if (rc != GN_OK) return rc;
+            rc = launch_norm_finalize(ws.partials, parts, ws.stats, B, P, ln_eps, st);
+            if (rc != GN_OK) return rc;
+            float *out = (o + 1 == outer) ? y : dst;
+            rc = launch_norm_apply(dst, gamma, beta, ws.stats, out, B, P, st);
+            if (rc != GN_OK) return rc;
+            src = out;
+        }
+    }
+    if (fused) return launch_norm_apply(src, gamma, beta, ws.stats, y, B, P, st);
+    return GN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,52 @@
+// Internal launcher declarations shared by the .cu files and api.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace gn {
+
+// ---- step_generic.cu
+template <typename R>
+int launch_step_fwd_generic(const R *w, const R *b, const R *s, const R *x, R *y, int B, int M, int N,
+                            int K, int inner, int bs, R eps, int normalize, int act, cudaStream_t st);
+template <typename R>
+int launch_step_bwd_generic(const R *w, const R *b, const R *s, const R *x, const R *gy, R *gw, R *gb,
+                            R *gs, R *gx, int B, int M, int N, int K, int inner, int bs, R eps,
+                            int normalize, int act, cudaStream_t st);
+template <typename R>
+int launch_gated_fwd_generic(const R *w, const R *b, const R *x, R *y, int B, int M, int N, int K,
+                             int inner, int bs, int act, cudaStream_t st);
+template <typename R>
+int launch_gated_bwd_generic(const R *w, const R *b, const R *x, const R *gy, R *gw, R *gb, R *gx, int B,
+                             int M, int N, int K, int inner, int bs, int act, cudaStream_t st);
+int step_backward_max_inner(int block, int elem_size);
+
+// ---- step_fast.cu
+struct FastFwdParams {
+    const float *w, *b, *s, *x;
+    float *y;
+    const float *gamma, *beta;  // used when in_stats != nullptr
+    const float2 *in_stats;     // [B] (mean, rstd) of x: normalise while loading; nullptr = x is used as is
+    double2 *out_partials;      // [B][nparts] (sum, sum of squares) of y per warp; nullptr = not wanted
+    int nparts;                 // partial slots per sample (= blocks * 4)
+    int B, M, N, K, inner;
+    int spc;                    // samples per CTA; <= 0 picks a default
+};
+bool fast8_applicable(const FastFwdParams &p, int block, int normalize);
+int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st);
+
+// ---- norm.cu
+constexpr int kNormMaxParts = 64;
+// per-sample (sum, sum of squares) of x in double, `parts` slices per sample
+int launch_norm_partial_stats(const float *x, double2 *partials, int B, long long P, int parts, cudaStream_t st);
+// partials [B][nparts] -> stats [B] = (mean, 1/sqrt(var + eps))
+int launch_norm_finalize(const double2 *partials, int nparts, float2 *stats, int B, long long P, float eps,
+                         cudaStream_t st);
+int launch_norm_apply(const float *x, const float *gamma, const float *beta, const float2 *stats, float *y,
+                      int B, long long P, cudaStream_t st);
+int launch_norm_backward(const float *x, const float *gamma, const float *gy, const float2 *stats,
+                         double2 *partials, float2 *ac, float *gx, float *ggamma, float *gbeta, int B,
+                         long long P, int parts, cudaStream_t st);
+int norm_pick_parts(long long P);
+
+}  // namespace gn

@@ -1,0 +1,290 @@
+// Tuned float forward kernel for the block-local grid update with per-block
+// normalisation off (the configuration every reference model trains with,
+// gridnet/scripts/train_mnist.py:51) and block size 8.
+//
+// Mapping. One CTA of 128 threads owns one 8x8x8 block and a range of samples.
+// A thread owns a 1x2x2 patch of neurons (z; y = 2*yp, 2*yp+1; x = 2*xp, 2*xp+1)
+// and keeps their 4 x 27 weights in registers for the CTA's whole life, so the
+// weights cross HBM/L2 once per CTA and are reused over all its samples and all
+// inner iterations. The 10x10x10 activation tile of a sample (block + stale
+// one-voxel halo) sits in shared memory with a row stride of 12 floats: with that
+// stride the 64-bit row loads of a half-warp touch all 32 banks exactly once.
+// Per inner iteration a thread reads a 3x4x4 window (48 floats) for its
+// 4 x 27 = 108 FMAs, 2.25 FMAs per shared-memory float.
+//
+// Pipeline. Tiles are fetched two samples at a time with cp.async into a
+// double-buffered stage, so the global->shared traffic of the next stage
+// overlaps the inner iterations of the current one. New activations stay in
+// registers until every thread has finished reading the old ones (one barrier
+// pair per inner iteration per stage); the last inner iteration goes straight to
+// global memory.
+//
+// Fusion with the whole-grid normalisation (gridnet/scripts/train_mnist.py:62-64):
+//   FUSE_IN   the input is the previous step's raw output; (x - mean) * rstd *
+//             gamma + beta is applied to each tile cell as it arrives in shared
+//             memory, so the normalised tensor never exists in HBM.
+//   STATS_OUT per-sample sum and sum of squares of what this step writes are
+//             reduced in double precision per warp and stored as partials for
+//             norm_finalize_partials (norm.cu).
+//
+// Reference semantics: gridnet/backend_torch.py:61-142; the kernel it stands in
+// for is gridnet_cuda_forward_kernel, src/gridnet_cuda_kernels.cu:101-200.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace gn {
+
+namespace fast8 {
+constexpr int RS = 12;          // row stride (floats)
+constexpr int PS = 10 * RS;     // plane stride
+constexpr int TS = 10 * PS;     // one tile
+constexpr int THREADS = 128;
+constexpr int SPS = 2;          // samples per pipeline stage
+constexpr int SLOTS = 8;        // tile cells handled per thread when loading (8 * 128 >= 1000)
+}  // namespace fast8
+
+__device__ __forceinline__ void cp_async4(float *dst_smem, const float *src)
+{
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int ACT, bool FUSE_IN, bool STATS_OUT>
+__global__ void __launch_bounds__(fast8::THREADS, 3) step_fwd_fast8(const FastFwdParams p)
+{
+    using namespace fast8;
+    __shared__ __align__(16) float tiles[2][SPS][TS];
+    __shared__ int2 cell[SLOTS * THREADS];                      // (global offset | -1, tile offset)
+    __shared__ float2 gbtab[FUSE_IN ? SLOTS * THREADS : 1];     // (gamma, beta) per tile cell
+
+    const int tid = threadIdx.x;
+    const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
+    const int nbx = p.K >> 3, nby = p.N >> 3;
+    const unsigned blk = blockIdx.x;
+    const int bx = blk % nbx, by = (blk / nbx) % nby, bz = blk / nbx / nby;
+    const size_t P = (size_t)p.M * p.N * p.K;
+    const int K = p.K;
+    const size_t g00 = ((size_t)(bz * 8 + z) * p.N + (by * 8 + 2 * yp)) * K + (bx * 8 + 2 * xp);
+
+    // ---- tables: where each tile cell lives in global memory (or that it is outside the grid)
+    for (int i = tid; i < SLOTS * THREADS; i += THREADS) {
+        int goff = -1, soff = 0;
+        if (i < 1000) {
+            const int cx = i % 10, cy = (i / 10) % 10, cz = i / 100;
+            const int gz = bz * 8 + cz - 1, gy = by * 8 + cy - 1, gx = bx * 8 + cx - 1;
+            soff = cz * PS + cy * RS + cx;
+            if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K)
+                goff = (gz * p.N + gy) * K + gx;
+            else {
+                // cells outside the grid stay zero for the CTA's whole life
+#pragma unroll
+                for (int q = 0; q < 2 * SPS; ++q) (&tiles[0][0][0])[q * TS + soff] = 0.0f;
+            }
+        }
+        cell[i] = make_int2(goff, soff);
+        if (FUSE_IN) {
+            float2 gb = make_float2(0.0f, 0.0f);
+            if (goff >= 0) gb = make_float2(p.gamma[goff], p.beta[goff]);
+            gbtab[i] = gb;
+        }
+    }
+
+    // ---- this thread's parameters: 4 neurons x (27 weights, bias, scale)
+    float w[27][2][2];
+#pragma unroll
+    for (int t = 0; t < 27; ++t)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float2 v = *reinterpret_cast<const float2 *>(p.w + (size_t)t * P + g00 + (size_t)j * K);
+            w[t][j][0] = v.x;
+            w[t][j][1] = v.y;
+        }
+    float bias[2][2], scl[2][2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const float2 vb = *reinterpret_cast<const float2 *>(p.b + g00 + (size_t)j * K);
+        const float2 vs = *reinterpret_cast<const float2 *>(p.s + g00 + (size_t)j * K);
+        bias[j][0] = vb.x;
+        bias[j][1] = vb.y;
+        scl[j][0] = vs.x;
+        scl[j][1] = vs.y;
+    }
+
+    const int s0 = blockIdx.y * p.spc;
+    const int s1 = min(p.B, s0 + p.spc);
+    const int nstages = (s1 - s0 + SPS - 1) / SPS;
+    const int toff = z * PS + 2 * yp * RS + 2 * xp;  // window origin of this thread inside a tile
+
+    __syncthreads();  // tables are complete
+
+    auto issue_stage = [&](int st) {
+        const int buf = st & 1;
+#pragma unroll
+        for (int s = 0; s < SPS; ++s) {
+            const int smp = s0 + st * SPS + s;
+            if (smp < s1) {
+                const float *xs = p.x + (size_t)smp * P;
+                float *tl = tiles[buf][s];
+#pragma unroll
+                for (int j = 0; j < SLOTS; ++j) {
+                    const int2 c = cell[tid + j * THREADS];
+                    if (c.x >= 0) cp_async4(tl + c.y, xs + c.x);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+
+    if (nstages > 0) issue_stage(0);
+
+    for (int st = 0; st < nstages; ++st) {
+        const int buf = st & 1;
+        const int smp0 = s0 + st * SPS;
+        cp_async_wait_all();
+        if (FUSE_IN) {
+            // normalise-on-load: each thread fixes up exactly the cells it fetched itself
+#pragma unroll
+            for (int s = 0; s < SPS; ++s) {
+                if (smp0 + s < s1) {
+                    const float2 mr = p.in_stats[smp0 + s];
+                    float *tl = tiles[buf][s];
+#pragma unroll
+                    for (int j = 0; j < SLOTS; ++j) {
+                        const int2 c = cell[tid + j * THREADS];
+                        if (c.x >= 0) {
+                            const float2 gb = gbtab[tid + j * THREADS];
+                            tl[c.y] = fmaf((tl[c.y] - mr.x) * mr.y, gb.x, gb.y);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();  // stage st is complete; nobody still reads the other buffer
+        if (st + 1 < nstages) issue_stage(st + 1);
+
+        for (int it = 0; it < p.inner; ++it) {
+            float nv[SPS][2][2];
+#pragma unroll
+            for (int s = 0; s < SPS; ++s) {
+                if (smp0 + s < s1) {
+                    const float *tl = tiles[buf][s] + toff;
+                    float acc[2][2] = {{bias[0][0], bias[0][1]}, {bias[1][0], bias[1][1]}};
+                    float old[2][2];
+#pragma unroll
+                    for (int a = 0; a < 3; ++a)
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            const float2 v01 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS);
+                            const float2 v23 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS + 2);
+                            const float v[4] = {v01.x, v01.y, v23.x, v23.y};
+                            if (a == 1 && (r == 1 || r == 2)) {
+                                old[r - 1][0] = v[1];
+                                old[r - 1][1] = v[2];
+                            }
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const int bb = r - j;
+                                if (bb >= 0 && bb <= 2) {
+#pragma unroll
+                                    for (int c = 0; c < 3; ++c) {
+                                        acc[j][0] = fmaf(w[a * 9 + bb * 3 + c][j][0], v[c], acc[j][0]);
+                                        acc[j][1] = fmaf(w[a * 9 + bb * 3 + c][j][1], v[c + 1], acc[j][1]);
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int i = 0; i < 2; ++i)
+                            nv[s][j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
+                }
+            }
+            if (it + 1 < p.inner) {
+                __syncthreads();  // every thread has read the old activations
+#pragma unroll
+                for (int s = 0; s < SPS; ++s) {
+                    if (smp0 + s < s1) {
+                        float *tl = tiles[buf][s] + toff + PS + RS + 1;
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            tl[j * RS] = nv[s][j][0];
+                            tl[j * RS + 1] = nv[s][j][1];
+                        }
+                    }
+                }
+                __syncthreads();
+            } else {
+#pragma unroll
+                for (int s = 0; s < SPS; ++s) {
+                    if (smp0 + s < s1) {
+                        float *ys = p.y + (size_t)(smp0 + s) * P + g00;
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            *reinterpret_cast<float2 *>(ys + (size_t)j * K) = make_float2(nv[s][j][0], nv[s][j][1]);
+                        if (STATS_OUT) {
+                            double sm = 0.0, sq = 0.0;
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                                for (int i = 0; i < 2; ++i) {
+                                    const double v = (double)nv[s][j][i];
+                                    sm += v;
+                                    sq = fma(v, v, sq);
+                                }
+                            sm = warp_sum(sm);
+                            sq = warp_sum(sq);
+                            if ((tid & 31) == 0)
+                                p.out_partials[(size_t)(smp0 + s) * p.nparts + (size_t)blk * 4 + (tid >> 5)] =
+                                    make_double2(sm, sq);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ launcher
+bool fast8_applicable(const FastFwdParams &p, int block, int normalize)
+{
+    if (block != 8 || normalize || p.inner < 1) return false;
+    if ((long long)p.M * p.N * p.K >= (1LL << 31)) return false;
+    auto al = [](const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; };
+    return al(p.w, 8) && al(p.b, 8) && al(p.s, 8) && al(p.x, 4) && al(p.y, 8);
+}
+
+int fast8_default_spc(int B, long long nbricks)
+{
+    // enough CTAs for several waves of 3 CTAs per SM, but at least 8 samples per
+    // CTA (when the batch allows) so that the weight fetch is amortised
+    const int chunks = pick_batch_chunks(nbricks, B, 3 * 4, 8);
+    return (B + chunks - 1) / chunks;
+}
+
+int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
+{
+    const long long nb = (long long)(p.M / 8) * (p.N / 8) * (p.K / 8);
+    if (p.spc <= 0) p.spc = fast8_default_spc(p.B, nb);
+    dim3 grid((unsigned)nb, (unsigned)((p.B + p.spc - 1) / p.spc));
+    const bool fin = p.in_stats != nullptr, sout = p.out_partials != nullptr;
+#define LAUNCH_(A)                                                                          \
+    do {                                                                                    \
+        if (fin && sout) step_fwd_fast8<A, true, true><<<grid, fast8::THREADS, 0, st>>>(p);  \
+        else if (fin) step_fwd_fast8<A, true, false><<<grid, fast8::THREADS, 0, st>>>(p);    \
+        else if (sout) step_fwd_fast8<A, false, true><<<grid, fast8::THREADS, 0, st>>>(p);   \
+        else step_fwd_fast8<A, false, false><<<grid, fast8::THREADS, 0, st>>>(p);            \
+    } while (0)
+    switch (act) {
+    case GN_ACT_RELU: LAUNCH_(GN_ACT_RELU); break;
+    case GN_ACT_LEAKY_RELU: LAUNCH_(GN_ACT_LEAKY_RELU); break;
+    case GN_ACT_SILU: LAUNCH_(GN_ACT_SILU); break;
+    default: LAUNCH_(GN_ACT_TANH); break;
+    }
+#undef LAUNCH_
+    return check_launch("step_fwd_fast8");
+}
+
+}  // namespace gn

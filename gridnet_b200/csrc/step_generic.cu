@@ -1,0 +1,622 @@
+// General kernels for the block-local grid update: every activation, per-block
+// normalisation on or off, block 4 or 8, float or double, plain and gated,
+// forward and backward. One CTA owns one bs^3 block of the grid and walks over a
+// range of samples; one thread owns one neuron and keeps that neuron's 27 (or 54)
+// weights in registers for the CTA's whole life, so weights are read from HBM
+// once per CTA instead of once per sample.
+//
+// Semantics follow gridnet/backend_torch.py:61-142 (plain) and :241-265 (gated);
+// the launch surface they replace is src/gridnet_cuda_kernels.cu:736-930.
+//
+// The tuned float path for normalize = 0 lives in step_fast.cu; this file is the
+// reference-complete fallback and the double-precision implementation.
+#include "common.cuh"
+
+namespace gn {
+
+template <int BS>
+struct Geo {
+    static constexpr int E = BS + 2;
+    static constexpr int T = E * E * E;
+    static constexpr int NT = BS * BS * BS;
+};
+
+struct BlockPos {
+    int bx, by, bz;
+    int tx, ty, tz;
+    size_t g;  // offset of this thread's neuron inside one [M,N,K] grid
+    int own;   // this thread's cell inside the padded tile
+};
+
+template <int BS>
+__device__ __forceinline__ BlockPos block_pos(int N, int K)
+{
+    constexpr int E = Geo<BS>::E;
+    BlockPos p;
+    const int tid = threadIdx.x;
+    p.tx = tid % BS;
+    p.ty = (tid / BS) % BS;
+    p.tz = tid / (BS * BS);
+    const int nbx = K / BS, nby = N / BS;
+    const unsigned blk = blockIdx.x;
+    p.bx = blk % nbx;
+    p.by = (blk / nbx) % nby;
+    p.bz = blk / nbx / nby;
+    p.g = ((size_t)(p.bz * BS + p.tz) * N + (p.by * BS + p.ty)) * K + (p.bx * BS + p.tx);
+    p.own = ((p.tz + 1) * E + p.ty + 1) * E + p.tx + 1;
+    return p;
+}
+
+// Gather the (bs+2)^3 tile of one sample; cells outside the grid read as zero.
+template <typename R, int BS>
+__device__ __forceinline__ void load_tile(R *tile, const R *xs, const BlockPos &p, int M, int N, int K)
+{
+    constexpr int E = Geo<BS>::E, T = Geo<BS>::T, NT = Geo<BS>::NT;
+    for (int i = threadIdx.x; i < T; i += NT) {
+        const int px = i % E, py = (i / E) % E, pz = i / (E * E);
+        const int gz = p.bz * BS + pz - 1, gy = p.by * BS + py - 1, gx = p.bx * BS + px - 1;
+        R v = R(0);
+        if (gz >= 0 && gz < M && gy >= 0 && gy < N && gx >= 0 && gx < K)
+            v = xs[((size_t)gz * N + gy) * K + gx];
+        tile[i] = v;
+    }
+}
+
+// mean and 1/(std + eps) over all tile cells, zero padding included
+// (gridnet/backend_torch.py:126-129); two passes, like torch's std.
+template <typename R, int BS>
+__device__ __forceinline__ void tile_stats(const R *tile, R *red, R eps, R &mu, R &sd)
+{
+    constexpr int T = Geo<BS>::T, NT = Geo<BS>::NT;
+    R s = R(0);
+    for (int i = threadIdx.x; i < T; i += NT) s += tile[i];
+    mu = block_sum(s, red) / R(T);
+    R q = R(0);
+    for (int i = threadIdx.x; i < T; i += NT) {
+        const R d = tile[i] - mu;
+        q += d * d;
+    }
+    sd = sqrt_<R>(block_sum(q, red) / R(T));
+    (void)eps;
+}
+
+// ============================================================== plain forward
+template <typename R, int BS, int ACT, bool NORM>
+__global__ void __launch_bounds__(BS *BS *BS)
+    step_fwd_generic(const R *__restrict__ w, const R *__restrict__ b, const R *__restrict__ s,
+                     const R *__restrict__ x, R *__restrict__ y, int B, int M, int N, int K,
+                     int inner, R eps, int spc)
+{
+    constexpr int E = Geo<BS>::E, T = Geo<BS>::T;
+    __shared__ R tile[T];
+    __shared__ R red[33];
+    const BlockPos p = block_pos<BS>(N, K);
+    const size_t P = (size_t)M * N * K;
+    R wr[27];
+#pragma unroll
+    for (int t = 0; t < 27; ++t) wr[t] = w[(size_t)t * P + p.g];
+    const R br = b[p.g], sr = s[p.g];
+    const int s0 = blockIdx.y * spc, s1 = min(B, s0 + spc);
+    for (int smp = s0; smp < s1; ++smp) {
+        __syncthreads();
+        load_tile<R, BS>(tile, x + (size_t)smp * P, p, M, N, K);
+        __syncthreads();
+        for (int it = 0; it < inner; ++it) {
+            R mu = R(0), inv = R(1);
+            if (NORM) {
+                R sd;
+                tile_stats<R, BS>(tile, red, eps, mu, sd);
+                inv = R(1) / (sd + eps);
+            }
+            R acc = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        if (NORM) v = (v - mu) * inv;
+                        acc = fma(v, wr[a * 9 + bb * 3 + c], acc);
+                    }
+            const R nv = fma(Act<ACT, R>::fwd(acc + br), sr, tile[p.own]);
+            __syncthreads();
+            tile[p.own] = nv;
+            __syncthreads();
+        }
+        y[(size_t)smp * P + p.g] = tile[p.own];
+    }
+}
+
+// ============================================================= plain backward
+// Dynamic shared memory: tile[T] | G[T] | Gin[T] | red[40] | stash[inner][NT]
+// Recomputes the inner iterations (stashing each neuron's own activation per
+// iteration), then walks them in reverse. The 27 contributions of a neuron to the
+// gradient tile are scattered with shared-memory atomics, so the float summation
+// order (and the last bits of the result) can vary from run to run.
+template <typename R, int BS, int ACT, bool NORM>
+__global__ void __launch_bounds__(BS *BS *BS)
+    step_bwd_generic(const R *__restrict__ w, const R *__restrict__ b, const R *__restrict__ s,
+                     const R *__restrict__ x, const R *__restrict__ gy, R *__restrict__ gw,
+                     R *__restrict__ gb, R *__restrict__ gs, R *__restrict__ gx, int B, int M,
+                     int N, int K, int inner, R eps, int spc, int atomic_params)
+{
+    constexpr int E = Geo<BS>::E, T = Geo<BS>::T, NT = Geo<BS>::NT;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    R *tile = reinterpret_cast<R *>(smem_raw);
+    R *G = tile + T;
+    R *Gin = G + T;
+    R *red = Gin + T;
+    R *stash = red + 40;
+    const BlockPos p = block_pos<BS>(N, K);
+    const size_t P = (size_t)M * N * K;
+    const int tid = threadIdx.x;
+    R wr[27], dw[27];
+#pragma unroll
+    for (int t = 0; t < 27; ++t) {
+        wr[t] = w[(size_t)t * P + p.g];
+        dw[t] = R(0);
+    }
+    const R br = b[p.g], sr = s[p.g];
+    R db = R(0), ds = R(0);
+    const int s0 = blockIdx.y * spc, s1 = min(B, s0 + spc);
+    for (int smp = s0; smp < s1; ++smp) {
+        __syncthreads();
+        load_tile<R, BS>(tile, x + (size_t)smp * P, p, M, N, K);
+        for (int i = tid; i < T; i += NT) {
+            G[i] = R(0);
+            Gin[i] = R(0);
+        }
+        __syncthreads();
+        // forward replay
+        for (int it = 0; it < inner; ++it) {
+            stash[it * NT + tid] = tile[p.own];
+            R mu = R(0), inv = R(1);
+            if (NORM) {
+                R sd;
+                tile_stats<R, BS>(tile, red, eps, mu, sd);
+                inv = R(1) / (sd + eps);
+            }
+            R acc = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        if (NORM) v = (v - mu) * inv;
+                        acc = fma(v, wr[a * 9 + bb * 3 + c], acc);
+                    }
+            const R nv = fma(Act<ACT, R>::fwd(acc + br), sr, tile[p.own]);
+            __syncthreads();
+            tile[p.own] = nv;
+            __syncthreads();
+        }
+        G[p.own] = gy[(size_t)smp * P + p.g];
+        // reverse sweep
+        for (int it = inner - 1; it >= 0; --it) {
+            tile[p.own] = stash[it * NT + tid];
+            const R go = G[p.own];  // dL/d(output of this iteration) for this neuron
+            __syncthreads();
+            R mu = R(0), inv = R(1), sd = R(1);
+            if (NORM) {
+                tile_stats<R, BS>(tile, red, eps, mu, sd);
+                inv = R(1) / (sd + eps);
+            }
+            R xv[27];
+            R acc = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        if (NORM) v = (v - mu) * inv;
+                        xv[a * 9 + bb * 3 + c] = v;
+                        acc = fma(v, wr[a * 9 + bb * 3 + c], acc);
+                    }
+            R f, d;
+            Act<ACT, R>::both(acc + br, f, d);
+            ds = fma(f, go, ds);
+            const R dl = d * go * sr;
+            db += dl;
+            R *dst = NORM ? Gin : G;
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const int t = a * 9 + bb * 3 + c;
+                        dw[t] = fma(xv[t], dl, dw[t]);
+                        atomicAdd(&dst[((p.tz + a) * E + p.ty + bb) * E + p.tx + c], wr[t] * dl);
+                    }
+            __syncthreads();
+            if (NORM) {
+                // inputs were (cur - mu) * inv with inv = 1/(sd + eps): chain rule through mu, sd
+                R sg = R(0), sgc = R(0);
+                for (int i = tid; i < T; i += NT) {
+                    sg += Gin[i];
+                    sgc += Gin[i] * (tile[i] - mu);
+                }
+                sg = block_sum(sg, red);
+                sgc = block_sum(sgc, red);
+                const R dsd = -sgc * inv * inv;
+                for (int i = tid; i < T; i += NT) {
+                    R v = Gin[i] * inv - sg * inv / R(T);
+                    v += dsd * (tile[i] - mu) / (R(T) * sd);
+                    G[i] += v;
+                    Gin[i] = R(0);
+                }
+                __syncthreads();
+            }
+        }
+        __syncthreads();
+        // the tile gradient lands on the input grid; halo cells belong to neighbour blocks
+        R *gxs = gx + (size_t)smp * P;
+        for (int i = tid; i < T; i += NT) {
+            const int px = i % E, py = (i / E) % E, pz = i / (E * E);
+            const int gz = p.bz * BS + pz - 1, gyy = p.by * BS + py - 1, gxx = p.bx * BS + px - 1;
+            if (gz >= 0 && gz < M && gyy >= 0 && gyy < N && gxx >= 0 && gxx < K)
+                atomicAdd(&gxs[((size_t)gz * N + gyy) * K + gxx], G[i]);
+        }
+    }
+    if (atomic_params) {
+#pragma unroll
+        for (int t = 0; t < 27; ++t) atomicAdd(&gw[(size_t)t * P + p.g], dw[t]);
+        atomicAdd(&gb[p.g], db);
+        atomicAdd(&gs[p.g], ds);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 27; ++t) gw[(size_t)t * P + p.g] = dw[t];
+        gb[p.g] = db;
+        gs[p.g] = ds;
+    }
+}
+
+// ============================================================== gated forward
+template <typename R, int BS, int ACT>
+__global__ void __launch_bounds__(BS *BS *BS)
+    gated_fwd_generic(const R *__restrict__ w, const R *__restrict__ b, const R *__restrict__ x,
+                      R *__restrict__ y, int B, int M, int N, int K, int inner, int spc)
+{
+    constexpr int E = Geo<BS>::E, T = Geo<BS>::T;
+    __shared__ R tile[T];
+    const BlockPos p = block_pos<BS>(N, K);
+    const size_t P = (size_t)M * N * K;
+    R wv[27], wg[27];
+#pragma unroll
+    for (int t = 0; t < 27; ++t) {
+        wv[t] = w[(size_t)(2 * t) * P + p.g];
+        wg[t] = w[(size_t)(2 * t + 1) * P + p.g];
+    }
+    const R bv = b[p.g], bg = b[P + p.g];
+    const int s0 = blockIdx.y * spc, s1 = min(B, s0 + spc);
+    for (int smp = s0; smp < s1; ++smp) {
+        __syncthreads();
+        load_tile<R, BS>(tile, x + (size_t)smp * P, p, M, N, K);
+        __syncthreads();
+        for (int it = 0; it < inner; ++it) {
+            R av = R(0), ag = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        av = fma(v, wv[a * 9 + bb * 3 + c], av);
+                        ag = fma(v, wg[a * 9 + bb * 3 + c], ag);
+                    }
+            const R gate = sigmoid_(ag + bg);
+            const R nv = gate * tile[p.own] + (R(1) - gate) * Act<ACT, R>::fwd(av + bv);
+            __syncthreads();
+            tile[p.own] = nv;
+            __syncthreads();
+        }
+        y[(size_t)smp * P + p.g] = tile[p.own];
+    }
+}
+
+// ============================================================= gated backward
+// Dynamic shared memory: tile[T] | G[T] | stash[inner][NT]
+template <typename R, int BS, int ACT>
+__global__ void __launch_bounds__(BS *BS *BS)
+    gated_bwd_generic(const R *__restrict__ w, const R *__restrict__ b, const R *__restrict__ x,
+                      const R *__restrict__ gy, R *__restrict__ gw, R *__restrict__ gb,
+                      R *__restrict__ gx, int B, int M, int N, int K, int inner, int spc,
+                      int atomic_params)
+{
+    constexpr int E = Geo<BS>::E, T = Geo<BS>::T, NT = Geo<BS>::NT;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    R *tile = reinterpret_cast<R *>(smem_raw);
+    R *G = tile + T;
+    R *stash = G + T;
+    const BlockPos p = block_pos<BS>(N, K);
+    const size_t P = (size_t)M * N * K;
+    const int tid = threadIdx.x;
+    R wv[27], wg[27], dwv[27], dwg[27];
+#pragma unroll
+    for (int t = 0; t < 27; ++t) {
+        wv[t] = w[(size_t)(2 * t) * P + p.g];
+        wg[t] = w[(size_t)(2 * t + 1) * P + p.g];
+        dwv[t] = R(0);
+        dwg[t] = R(0);
+    }
+    const R bv = b[p.g], bg = b[P + p.g];
+    R dbv = R(0), dbg = R(0);
+    const int s0 = blockIdx.y * spc, s1 = min(B, s0 + spc);
+    for (int smp = s0; smp < s1; ++smp) {
+        __syncthreads();
+        load_tile<R, BS>(tile, x + (size_t)smp * P, p, M, N, K);
+        for (int i = tid; i < T; i += NT) G[i] = R(0);
+        __syncthreads();
+        for (int it = 0; it < inner; ++it) {
+            stash[it * NT + tid] = tile[p.own];
+            R av = R(0), ag = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        av = fma(v, wv[a * 9 + bb * 3 + c], av);
+                        ag = fma(v, wg[a * 9 + bb * 3 + c], ag);
+                    }
+            const R gate = sigmoid_(ag + bg);
+            const R nv = gate * tile[p.own] + (R(1) - gate) * Act<ACT, R>::fwd(av + bv);
+            __syncthreads();
+            tile[p.own] = nv;
+            __syncthreads();
+        }
+        G[p.own] = gy[(size_t)smp * P + p.g];
+        for (int it = inner - 1; it >= 0; --it) {
+            const R xo = stash[it * NT + tid];
+            tile[p.own] = xo;
+            const R go = G[p.own];
+            __syncthreads();
+            R av = R(0), ag = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        av = fma(v, wv[a * 9 + bb * 3 + c], av);
+                        ag = fma(v, wg[a * 9 + bb * 3 + c], ag);
+                    }
+            const R gate = sigmoid_(ag + bg);
+            R f, d;
+            Act<ACT, R>::both(av + bv, f, d);
+            const R dv = go * (R(1) - gate) * d;
+            const R dg = go * gate * (R(1) - gate) * (xo - f);
+            dbv += dv;
+            dbg += dg;
+            // the interior gradient is rebuilt from the gate path; the halo keeps accumulating
+            G[p.own] = gate * go;
+            __syncthreads();
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const int t = a * 9 + bb * 3 + c;
+                        const int ci = ((p.tz + a) * E + p.ty + bb) * E + p.tx + c;
+                        const R v = tile[ci];
+                        dwv[t] = fma(v, dv, dwv[t]);
+                        dwg[t] = fma(v, dg, dwg[t]);
+                        atomicAdd(&G[ci], fma(wv[t], dv, wg[t] * dg));
+                    }
+            __syncthreads();
+        }
+        R *gxs = gx + (size_t)smp * P;
+        for (int i = tid; i < T; i += NT) {
+            const int px = i % E, py = (i / E) % E, pz = i / (E * E);
+            const int gz = p.bz * BS + pz - 1, gyy = p.by * BS + py - 1, gxx = p.bx * BS + px - 1;
+            if (gz >= 0 && gz < M && gyy >= 0 && gyy < N && gxx >= 0 && gxx < K)
+                atomicAdd(&gxs[((size_t)gz * N + gyy) * K + gxx], G[i]);
+        }
+    }
+    if (atomic_params) {
+#pragma unroll
+        for (int t = 0; t < 27; ++t) {
+            atomicAdd(&gw[(size_t)(2 * t) * P + p.g], dwv[t]);
+            atomicAdd(&gw[(size_t)(2 * t + 1) * P + p.g], dwg[t]);
+        }
+        atomicAdd(&gb[p.g], dbv);
+        atomicAdd(&gb[P + p.g], dbg);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 27; ++t) {
+            gw[(size_t)(2 * t) * P + p.g] = dwv[t];
+            gw[(size_t)(2 * t + 1) * P + p.g] = dwg[t];
+        }
+        gb[p.g] = dbv;
+        gb[P + p.g] = dbg;
+    }
+}
+
+// ================================================================== launchers
+static constexpr size_t kMaxDynSmem = 227 * 1024;
+
+template <typename R>
+static size_t bwd_smem_bytes(int bs, int inner, bool gated)
+{
+    const size_t T = (size_t)(bs + 2) * (bs + 2) * (bs + 2), NT = (size_t)bs * bs * bs;
+    const size_t fixed = gated ? 2 * T : 3 * T + 40;
+    return (fixed + (size_t)inner * NT) * sizeof(R);
+}
+
+int step_backward_max_inner(int block, int elem_size)
+{
+    if ((block != 4 && block != 8) || (elem_size != 4 && elem_size != 8)) return -1;
+    const size_t T = (size_t)(block + 2) * (block + 2) * (block + 2), NT = (size_t)block * block * block;
+    const size_t fixed = (3 * T + 40) * elem_size;
+    return (int)((kMaxDynSmem - fixed) / (NT * elem_size));
+}
+
+#define GN_ACT_SWITCH(act, MACRO)                    \
+    switch (act) {                                   \
+    case GN_ACT_RELU: MACRO(GN_ACT_RELU); break;     \
+    case GN_ACT_LEAKY_RELU: MACRO(GN_ACT_LEAKY_RELU); break; \
+    case GN_ACT_SILU: MACRO(GN_ACT_SILU); break;     \
+    default: MACRO(GN_ACT_TANH); break;              \
+    }
+
+template <typename R>
+int launch_step_fwd_generic(const R *w, const R *b, const R *s, const R *x, R *y, int B, int M, int N,
+                            int K, int inner, int bs, R eps, int normalize, int act, cudaStream_t st)
+{
+    const long long nb = (long long)(M / bs) * (N / bs) * (K / bs);
+    const int chunks = pick_batch_chunks(nb, B, bs == 8 ? 2 : 16);
+    const int spc = (B + chunks - 1) / chunks;
+    dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
+#define LAUNCH_(A)                                                                                      \
+    do {                                                                                                \
+        if (bs == 8) {                                                                                  \
+            if (normalize) step_fwd_generic<R, 8, A, true><<<grid, 512, 0, st>>>(w, b, s, x, y, B, M, N, K, inner, eps, spc); \
+            else step_fwd_generic<R, 8, A, false><<<grid, 512, 0, st>>>(w, b, s, x, y, B, M, N, K, inner, eps, spc);          \
+        } else {                                                                                        \
+            if (normalize) step_fwd_generic<R, 4, A, true><<<grid, 64, 0, st>>>(w, b, s, x, y, B, M, N, K, inner, eps, spc);  \
+            else step_fwd_generic<R, 4, A, false><<<grid, 64, 0, st>>>(w, b, s, x, y, B, M, N, K, inner, eps, spc);           \
+        }                                                                                               \
+    } while (0)
+    GN_ACT_SWITCH(act, LAUNCH_)
+#undef LAUNCH_
+    return check_launch("step_fwd_generic");
+}
+
+template <typename K_>
+static int opt_in_smem(K_ kernel, size_t bytes)
+{
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) {
+            record_cuda_error(e, "cudaFuncSetAttribute");
+            return GN_ERR_CUDA;
+        }
+    }
+    return GN_OK;
+}
+
+template <typename R>
+int launch_step_bwd_generic(const R *w, const R *b, const R *s, const R *x, const R *gy, R *gw, R *gb,
+                            R *gs, R *gx, int B, int M, int N, int K, int inner, int bs, R eps,
+                            int normalize, int act, cudaStream_t st)
+{
+    const size_t P = (size_t)M * N * K;
+    const long long nb = (long long)(M / bs) * (N / bs) * (K / bs);
+    const int chunks = pick_batch_chunks(nb, B, bs == 8 ? 1 : 8);
+    const int spc = (B + chunks - 1) / chunks;
+    dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
+    const int atomic_params = grid.y > 1;
+    const size_t smem = bwd_smem_bytes<R>(bs, inner, false);
+    if (smem > kMaxDynSmem) return GN_ERR_BAD_INNER;
+    cudaError_t e = cudaMemsetAsync(gx, 0, sizeof(R) * B * P, st);
+    if (e == cudaSuccess && atomic_params) {
+        e = cudaMemsetAsync(gw, 0, sizeof(R) * 27 * P, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gb, 0, sizeof(R) * P, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gs, 0, sizeof(R) * P, st);
+    }
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "cudaMemsetAsync");
+        return GN_ERR_CUDA;
+    }
+#define ONE_(BSV, A, NRM)                                                                      \
+    do {                                                                                       \
+        auto kern = step_bwd_generic<R, BSV, A, NRM>;                                          \
+        int rc = opt_in_smem(kern, smem);                                                      \
+        if (rc != GN_OK) return rc;                                                            \
+        kern<<<grid, BSV * BSV * BSV, smem, st>>>(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, \
+                                                  inner, eps, spc, atomic_params);             \
+    } while (0)
+#define LAUNCH_(A)                          \
+    do {                                    \
+        if (bs == 8) {                      \
+            if (normalize) ONE_(8, A, true); \
+            else ONE_(8, A, false);         \
+        } else {                            \
+            if (normalize) ONE_(4, A, true); \
+            else ONE_(4, A, false);         \
+        }                                   \
+    } while (0)
+    GN_ACT_SWITCH(act, LAUNCH_)
+#undef LAUNCH_
+#undef ONE_
+    return check_launch("step_bwd_generic");
+}
+
+template <typename R>
+int launch_gated_fwd_generic(const R *w, const R *b, const R *x, R *y, int B, int M, int N, int K,
+                             int inner, int bs, int act, cudaStream_t st)
+{
+    const long long nb = (long long)(M / bs) * (N / bs) * (K / bs);
+    const int chunks = pick_batch_chunks(nb, B, bs == 8 ? 1 : 8);
+    const int spc = (B + chunks - 1) / chunks;
+    dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
+#define LAUNCH_(A)                                                                                  \
+    do {                                                                                            \
+        if (bs == 8) gated_fwd_generic<R, 8, A><<<grid, 512, 0, st>>>(w, b, x, y, B, M, N, K, inner, spc); \
+        else gated_fwd_generic<R, 4, A><<<grid, 64, 0, st>>>(w, b, x, y, B, M, N, K, inner, spc);   \
+    } while (0)
+    GN_ACT_SWITCH(act, LAUNCH_)
+#undef LAUNCH_
+    return check_launch("gated_fwd_generic");
+}
+
+template <typename R>
+int launch_gated_bwd_generic(const R *w, const R *b, const R *x, const R *gy, R *gw, R *gb, R *gx, int B,
+                             int M, int N, int K, int inner, int bs, int act, cudaStream_t st)
+{
+    const size_t P = (size_t)M * N * K;
+    const long long nb = (long long)(M / bs) * (N / bs) * (K / bs);
+    const int chunks = pick_batch_chunks(nb, B, bs == 8 ? 1 : 8);
+    const int spc = (B + chunks - 1) / chunks;
+    dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
+    const int atomic_params = grid.y > 1;
+    const size_t smem = bwd_smem_bytes<R>(bs, inner, true);
+    if (smem > kMaxDynSmem) return GN_ERR_BAD_INNER;
+    cudaError_t e = cudaMemsetAsync(gx, 0, sizeof(R) * B * P, st);
+    if (e == cudaSuccess && atomic_params) {
+        e = cudaMemsetAsync(gw, 0, sizeof(R) * 54 * P, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gb, 0, sizeof(R) * 2 * P, st);
+    }
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "cudaMemsetAsync");
+        return GN_ERR_CUDA;
+    }
+#define ONE_(BSV, A)                                                                          \
+    do {                                                                                      \
+        auto kern = gated_bwd_generic<R, BSV, A>;                                             \
+        int rc = opt_in_smem(kern, smem);                                                     \
+        if (rc != GN_OK) return rc;                                                           \
+        kern<<<grid, BSV * BSV * BSV, smem, st>>>(w, b, x, gy, gw, gb, gx, B, M, N, K, inner, \
+                                                  spc, atomic_params);                        \
+    } while (0)
+#define LAUNCH_(A)               \
+    do {                         \
+        if (bs == 8) ONE_(8, A); \
+        else ONE_(4, A);         \
+    } while (0)
+    GN_ACT_SWITCH(act, LAUNCH_)
+#undef LAUNCH_
+#undef ONE_
+    return check_launch("gated_bwd_generic");
+}
+
+// explicit instantiations used by api.cu
+template int launch_step_fwd_generic<float>(const float *, const float *, const float *, const float *, float *, int, int, int, int, int, int, float, int, int, cudaStream_t);
+template int launch_step_fwd_generic<double>(const double *, const double *, const double *, const double *, double *, int, int, int, int, int, int, double, int, int, cudaStream_t);
+template int launch_step_bwd_generic<float>(const float *, const float *, const float *, const float *, const float *, float *, float *, float *, float *, int, int, int, int, int, int, float, int, int, cudaStream_t);
+template int launch_step_bwd_generic<double>(const double *, const double *, const double *, const double *, const double *, double *, double *, double *, double *, int, int, int, int, int, int, double, int, int, cudaStream_t);
+template int launch_gated_fwd_generic<float>(const float *, const float *, const float *, float *, int, int, int, int, int, int, int, cudaStream_t);
+template int launch_gated_fwd_generic<double>(const double *, const double *, const double *, double *, int, int, int, int, int, int, int, cudaStream_t);
+template int launch_gated_bwd_generic<float>(const float *, const float *, const float *, const float *, float *, float *, float *, int, int, int, int, int, int, int, cudaStream_t);
+template int launch_gated_bwd_generic<double>(const double *, const double *, const double *, const double *, double *, double *, double *, int, int, int, int, int, int, int, cudaStream_t);
+
+}  // namespace gn

@@ -1,0 +1,95 @@
+"""Module-shaped stand-in for the reference's native extension ``gridnet_cuda``.
+
+Same four functions, same positional arguments and the same contract as the
+pybind11 module in src/gridnet_cuda.cpp:188-194: tensors must be CUDA and
+contiguous (RuntimeError otherwise), outputs are caller-allocated, nothing is
+returned. Work is queued on torch's current stream (the reference launches on
+the legacy default stream, src/gridnet_cuda_kernels.cu:761).
+
+The gradient outputs are overwritten; the reference accumulates into tensors its
+caller zeroes first (gridnet/backend_cuda.py:78-81), which gives the same values.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import GridnetB200Error, activation_id, check, lib
+
+
+def _check_input(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise GridnetB200Error(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise GridnetB200Error(f"{name} must be contiguous")
+
+
+def _suffix(t: torch.Tensor) -> str:
+    if t.dtype == torch.float32:
+        return "f32"
+    if t.dtype == torch.float64:
+        return "f64"
+    raise GridnetB200Error(f"unsupported dtype {t.dtype}: float32 and float64 only")
+
+
+def _same(ts, names):
+    for t, n in zip(ts, names):
+        _check_input(t, n)
+        if t.dtype != ts[0].dtype or t.device != ts[0].device:
+            raise GridnetB200Error(f"{n}: dtype/device differs from {names[0]}")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def forward(weight, bias, scale, initActivations, outActivations, innerIterations, blockSize, eps,
+            normalize, activation) -> None:
+    _same((weight, bias, scale, initActivations, outActivations),
+          ("weight", "bias", "scale", "initActivations", "outActivations"))
+    B, M, N, K = initActivations.shape
+    fn = getattr(lib, "gn_step_forward_" + _suffix(weight))
+    with torch.cuda.device(weight.device):
+        check(fn(weight.data_ptr(), bias.data_ptr(), scale.data_ptr(), initActivations.data_ptr(),
+                 outActivations.data_ptr(), B, M, N, K, int(innerIterations), int(blockSize), float(eps),
+                 int(bool(normalize)), activation_id(activation), _stream(weight)))
+
+
+def backward(weight, bias, scale, initActivations, outGrads, weightGradOut, biasGradOut, scaleGradOut,
+             activationsGradOut, innerIterations, blockSize, eps, normalize, activation) -> None:
+    _same((weight, bias, scale, initActivations, outGrads, weightGradOut, biasGradOut, scaleGradOut,
+           activationsGradOut),
+          ("weight", "bias", "scale", "initActivations", "outGrads", "weightGradOut", "biasGradOut",
+           "scaleGradOut", "activationsGradOut"))
+    B, M, N, K = initActivations.shape
+    fn = getattr(lib, "gn_step_backward_" + _suffix(weight))
+    with torch.cuda.device(weight.device):
+        check(fn(weight.data_ptr(), bias.data_ptr(), scale.data_ptr(), initActivations.data_ptr(),
+                 outGrads.data_ptr(), weightGradOut.data_ptr(), biasGradOut.data_ptr(),
+                 scaleGradOut.data_ptr(), activationsGradOut.data_ptr(), B, M, N, K, int(innerIterations),
+                 int(blockSize), float(eps), int(bool(normalize)), activation_id(activation),
+                 _stream(weight)))
+
+
+def forward_gated(weight, bias, initActivations, outActivations, innerIterations, blockSize,
+                  activation) -> None:
+    _same((weight, bias, initActivations, outActivations),
+          ("weight", "bias", "initActivations", "outActivations"))
+    B, M, N, K = initActivations.shape
+    fn = getattr(lib, "gn_gated_forward_" + _suffix(weight))
+    with torch.cuda.device(weight.device):
+        check(fn(weight.data_ptr(), bias.data_ptr(), initActivations.data_ptr(), outActivations.data_ptr(),
+                 B, M, N, K, int(innerIterations), int(blockSize), activation_id(activation),
+                 _stream(weight)))
+
+
+def backward_gated(weight, bias, initActivations, outGrads, weightGradOut, biasGradOut, activationsGradOut,
+                   innerIterations, blockSize, activation) -> None:
+    _same((weight, bias, initActivations, outGrads, weightGradOut, biasGradOut, activationsGradOut),
+          ("weight", "bias", "initActivations", "outGrads", "weightGradOut", "biasGradOut",
+           "activationsGradOut"))
+    B, M, N, K = initActivations.shape
+    fn = getattr(lib, "gn_gated_backward_" + _suffix(weight))
+    with torch.cuda.device(weight.device):
+        check(fn(weight.data_ptr(), bias.data_ptr(), initActivations.data_ptr(), outGrads.data_ptr(),
+                 weightGradOut.data_ptr(), biasGradOut.data_ptr(), activationsGradOut.data_ptr(), B, M, N, K,
+                 int(innerIterations), int(blockSize), activation_id(activation), _stream(weight)))

@@ -1,0 +1,174 @@
+/*
+ * gridnet_b200 — C ABI of the B200 (sm_100a) kernels for gridnet's block-local
+ * recurrent grid update and the whole-grid normalisation between outer steps.
+ *
+ * This header is the drop-in boundary: it carries what the reference's native
+ * extension `gridnet_cuda` exposes through pybind11 (src/gridnet_cuda.cpp:188-194),
+ * as plain `extern "C"` entry points with raw device pointers, sizes and a CUDA
+ * stream handle. No torch types appear in any signature.
+ *
+ * Conventions (same as the reference, src/gridnet_cuda.cpp:6-10,
+ * gridnet/backend_cuda.py:19-50):
+ *   - every pointer is a DEVICE pointer to a dense row-major array;
+ *   - activations are [B, M, N, K]; K is the fastest dimension;
+ *   - weight is [27, M, N, K] with tap = a*9 + b*3 + c reading the neighbour at
+ *     offset (a-1, b-1, c-1) along (M, N, K); gated weight is [27, 2, M, N, K]
+ *     (0 = value, 1 = gate), gated bias [2, M, N, K];
+ *   - block must be 4 or 8 and divide M, N and K;
+ *   - the caller owns every buffer; the library never allocates or frees device
+ *     memory, never synchronises, and launches only on the stream it is given;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - every function returns GN_OK (0) or a negative gn_status; gn_status_string()
+ *     turns it into text. A launch error is reported as GN_ERR_CUDA and the CUDA
+ *     error text is available from gn_last_cuda_error().
+ *
+ * Gradient outputs are OVERWRITTEN (the reference accumulates into tensors the
+ * caller zeroed, gridnet/backend_cuda.py:78-81; with zeroed tensors the two are
+ * the same thing).
+ */
+#ifndef GRIDNET_B200_H
+#define GRIDNET_B200_H
+
+#include <stddef.h>
+
+#if defined(__GNUC__)
+#define GN_API __attribute__((visibility("default")))
+#else
+#define GN_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum gn_status {
+    GN_OK = 0,
+    GN_ERR_NULL_POINTER = -1,
+    GN_ERR_BAD_BLOCK = -2,      /* block not in {4, 8} or not dividing M, N, K */
+    GN_ERR_BAD_SHAPE = -3,      /* non-positive or too large dimension */
+    GN_ERR_BAD_ACTIVATION = -4, /* activation id outside gn_activation */
+    GN_ERR_BAD_INNER = -5,      /* negative, or too many inner iterations for the backward stash */
+    GN_ERR_WORKSPACE = -6,      /* workspace missing, misaligned or too small */
+    GN_ERR_CUDA = -7,           /* CUDA reported an error; see gn_last_cuda_error() */
+    GN_ERR_UNSUPPORTED = -8,    /* combination not available in this entry point */
+    GN_ERR_TOO_LARGE = -9       /* size beyond a fixed built-in limit */
+} gn_status;
+
+/* The strings the reference accepts (src/activations.h:6-17) map to these ids. */
+typedef enum gn_activation {
+    GN_ACT_RELU = 0,
+    GN_ACT_LEAKY_RELU = 1, /* slope 0.01 */
+    GN_ACT_SILU = 2,
+    GN_ACT_TANH = 3
+} gn_activation;
+
+GN_API const char *gn_status_string(int status);
+GN_API const char *gn_last_cuda_error(void);
+/* -1 for an unknown name */
+GN_API int gn_activation_from_name(const char *name);
+GN_API int gn_version(void);
+
+/* ------------------------------------------------------------------ plain step
+ * Replaces gridnet_cuda.forward (src/gridnet_cuda.cpp:61-89 ->
+ * src/gridnet_cuda_kernels.cu:736-784): y = one outer-loop step of x.
+ * inner == 0 copies x to y. */
+GN_API int gn_step_forward_f32(const float *weight, const float *bias, const float *scale,
+                        const float *x, float *y, int B, int M, int N, int K, int inner,
+                        int block, float eps, int normalize, int activation, void *stream);
+GN_API int gn_step_forward_f64(const double *weight, const double *bias, const double *scale,
+                        const double *x, double *y, int B, int M, int N, int K, int inner,
+                        int block, double eps, int normalize, int activation, void *stream);
+
+/* Replaces gridnet_cuda.backward (src/gridnet_cuda.cpp:91-131 ->
+ * src/gridnet_cuda_kernels.cu:786-851). Writes grad_weight [27,M,N,K],
+ * grad_bias, grad_scale [M,N,K] and grad_x [B,M,N,K]. */
+GN_API int gn_step_backward_f32(const float *weight, const float *bias, const float *scale,
+                         const float *x, const float *grad_y, float *grad_weight,
+                         float *grad_bias, float *grad_scale, float *grad_x, int B, int M,
+                         int N, int K, int inner, int block, float eps, int normalize,
+                         int activation, void *stream);
+GN_API int gn_step_backward_f64(const double *weight, const double *bias, const double *scale,
+                         const double *x, const double *grad_y, double *grad_weight,
+                         double *grad_bias, double *grad_scale, double *grad_x, int B, int M,
+                         int N, int K, int inner, int block, double eps, int normalize,
+                         int activation, void *stream);
+/* Largest `inner` the backward entry points accept for this block size and
+ * element size (the per-iteration stash lives in shared memory). */
+GN_API int gn_step_backward_max_inner(int block, int elem_size);
+
+/* ------------------------------------------------------------------ gated step
+ * Replace gridnet_cuda.forward_gated / backward_gated
+ * (src/gridnet_cuda.cpp:133-186 -> src/gridnet_cuda_kernels.cu:853-930). */
+GN_API int gn_gated_forward_f32(const float *weight, const float *bias, const float *x, float *y,
+                         int B, int M, int N, int K, int inner, int block, int activation,
+                         void *stream);
+GN_API int gn_gated_forward_f64(const double *weight, const double *bias, const double *x, double *y,
+                         int B, int M, int N, int K, int inner, int block, int activation,
+                         void *stream);
+GN_API int gn_gated_backward_f32(const float *weight, const float *bias, const float *x,
+                          const float *grad_y, float *grad_weight, float *grad_bias,
+                          float *grad_x, int B, int M, int N, int K, int inner, int block,
+                          int activation, void *stream);
+GN_API int gn_gated_backward_f64(const double *weight, const double *bias, const double *x,
+                          const double *grad_y, double *grad_weight, double *grad_bias,
+                          double *grad_x, int B, int M, int N, int K, int inner, int block,
+                          int activation, void *stream);
+
+/* ------------------------------------------------- whole-grid normalisation
+ * The reference's models apply torch.nn.LayerNorm over the full [M,N,K] grid
+ * after every step (gridnet/scripts/train_mnist.py:54,62-64;
+ * gridnet/scripts/train_imagenet.py:67,85-86). Per sample over P = M*N*K values:
+ * y = (x - mean) / sqrt(var + eps) * gamma + beta with the biased variance.
+ * `workspace` holds the per-sample partial sums between the two kernels.
+ * mean_rstd (optional, may be NULL) receives [B][2] floats (mean, 1/std). */
+GN_API size_t gn_norm_workspace_bytes(int B, long long P);
+GN_API int gn_norm_forward_f32(const float *x, const float *gamma, const float *beta, float *y,
+                        float *mean_rstd, int B, long long P, float eps, void *workspace,
+                        size_t workspace_bytes, void *stream);
+/* grad_x [B,P], grad_gamma [P], grad_beta [P] are overwritten. */
+GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float *grad_y, float *grad_x,
+                         float *grad_gamma, float *grad_beta, int B, long long P, float eps,
+                         void *workspace, size_t workspace_bytes, void *stream);
+
+/* Building blocks of the fused loop below, for callers that drive the outer loop
+ * themselves (a slab-sharded grid exchanges halos and statistics between steps).
+ *
+ * gn_step_forward_fused_f32: one plain step with normalize = 0 whose input may be
+ * the RAW output of the previous step: with in_mean_rstd != NULL every tile cell is
+ * turned into (x - mean) * rstd * gamma + beta while it is loaded (in_mean_rstd is
+ * [B][2] floats; gamma, beta [M,N,K]); with out_partials != NULL the per-sample
+ * sum and sum of squares of y are written as gn_step_stats_partials() pairs of
+ * doubles per sample ([B][nparts][2]) for gn_norm_finalize_f32. Block size 8 and
+ * inner >= 1 only (GN_ERR_UNSUPPORTED otherwise). No counterpart in the
+ * reference, whose LayerNorm is a separate torch module.
+ * gn_norm_finalize_f32: partials -> [B][2] (mean, 1/sqrt(var + eps)).
+ * gn_norm_apply_f32: y = (x - mean) * rstd * gamma + beta. */
+GN_API int gn_step_stats_partials(int M, int N, int K, int block);
+GN_API int gn_step_forward_fused_f32(const float *weight, const float *bias, const float *scale,
+                              const float *x, float *y, const float *gamma, const float *beta,
+                              const float *in_mean_rstd, double *out_partials, int B, int M,
+                              int N, int K, int inner, int block, int activation, void *stream);
+GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_rstd, int B,
+                         long long P, float eps, void *stream);
+GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *beta,
+                      const float *mean_rstd, float *y, int B, long long P, void *stream);
+
+/* ------------------------------------------------------ fused model loop
+ * `outer` repetitions of (plain step with normalize = 0, whole-grid LayerNorm):
+ * the loop of gridnet/scripts/train_mnist.py:62-64 as one call. The
+ * normalisation is never a pass of its own: each step kernel reduces the
+ * per-sample statistics of what it writes, and the next step applies
+ * (x - mean) * rstd * gamma + beta while it loads its tiles; only the last
+ * step's output is normalised by a separate kernel into y.
+ * workspace: two [B,M,N,K] float buffers plus the statistics partials. */
+GN_API size_t gn_outer_forward_workspace_bytes(int B, int M, int N, int K, int block);
+GN_API int gn_outer_forward_f32(const float *weight, const float *bias, const float *scale,
+                         const float *gamma, const float *beta, const float *x, float *y,
+                         int B, int M, int N, int K, int inner, int outer, int block,
+                         float ln_eps, int activation, void *workspace,
+                         size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRIDNET_B200_H */

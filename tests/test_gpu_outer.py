@@ -1,0 +1,157 @@
+"""GPU parity of the whole-grid normalisation and of the fused model loop
+(step + LayerNorm, gridnet/scripts/train_mnist.py:62-64) against the CPU oracle, the
+golden vectors, and — at the benchmark's full size — against size-independent
+properties (fused == unfused composition, batch independence, determinism)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gridnet_oracle as orc
+
+from conftest import GOLDEN
+from util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def model_params(seed, shape):
+    """Model-style parameters: weights N(0, 1/27) (gridnet/__init__.py:42-45); bias, residual
+    scale, gamma, beta perturbed around their initial values so that every term is exercised."""
+    r = np.random.default_rng(seed)
+    f = np.float32
+    w = (r.standard_normal((27, *shape)) / np.sqrt(27)).astype(f)
+    b = (0.1 * r.standard_normal(shape)).astype(f)
+    s = (1 + 0.1 * r.standard_normal(shape)).astype(f)
+    gamma = (1 + 0.1 * r.standard_normal(shape)).astype(f)
+    beta = (0.1 * r.standard_normal(shape)).astype(f)
+    return w, b, s, gamma, beta
+
+
+def face_input(seed, B, shape):
+    x = np.zeros((B, *shape), np.float32)
+    x[..., 0] = np.random.default_rng(seed).standard_normal((B, *shape[:2]))
+    return x
+
+
+@pytest.mark.parametrize("B,shape", [(3, (16, 16, 16)), (2, (8, 24, 40)), (5, (4, 4, 4)), (1, (32, 32, 32))])
+def test_grid_norm_forward_backward(B, shape):
+    from gridnet_b200 import GridNormOp
+
+    r = np.random.default_rng(20)
+    x = (3 * r.standard_normal((B, *shape)) + 1.5).astype(np.float32)
+    gamma = (1 + 0.2 * r.standard_normal(shape)).astype(np.float32)
+    beta = (0.3 * r.standard_normal(shape)).astype(np.float32)
+    gy = r.standard_normal(x.shape).astype(np.float32)
+    y64 = orc.layernorm_forward(x.astype(np.float64), gamma.astype(np.float64), beta.astype(np.float64))
+    gx64, gg64, gb64 = orc.layernorm_backward(x.astype(np.float64), gamma.astype(np.float64), gy.astype(np.float64))
+    tx, tg, tb = (dev(a).requires_grad_(True) for a in (x, gamma, beta))
+    y = GridNormOp.apply(tx, tg, tb, 1e-5)
+    assert_close(y.detach().cpu().numpy(), y64, None, "norm forward")
+    gx, gg, gb = torch.autograd.grad(y, (tx, tg, tb), dev(gy))
+    assert_close(gx.cpu().numpy(), gx64, None, "norm gx")
+    assert_close(gg.cpu().numpy(), gg64, None, "norm ggamma")
+    assert_close(gb.cpu().numpy(), gb64, None, "norm gbeta")
+    # and against torch's own LayerNorm on the device (what the reference's models call)
+    ty = torch.nn.functional.layer_norm(tx, shape, tg, tb, 1e-5)
+    assert torch.allclose(y, ty, rtol=1e-4, atol=1e-5)
+
+
+def test_golden_outer_loop():
+    from gridnet_b200 import outer_forward
+
+    z = np.load(os.path.join(GOLDEN, "outer_loop.npz"))
+    bs, inner, outer = (int(v) for v in z["meta"])
+    args = [dev(z[k]) for k in ("w", "b", "s", "gamma", "beta", "x")]
+    got = outer_forward(*args, inner, outer, bs).cpu().numpy()
+    assert_close(got, z["y64"], z["y32"], "golden outer loop")
+
+
+@pytest.mark.parametrize(
+    "name,B,shape,bs,inner,outer",
+    [
+        ("C1 MNIST-shaped, full", 8, (32, 32, 32), 8, 2, 8),
+        ("C2 shape, reduced batch", 2, (64, 64, 64), 8, 4, 12),
+        ("C4 shape (block 4), reduced", 2, (32, 32, 32), 4, 8, 4),
+        ("non-cubic", 3, (8, 16, 24), 8, 3, 5),
+        ("single block", 2, (8, 8, 8), 8, 2, 3),
+        ("odd batch, one sample per CTA", 1, (16, 16, 16), 8, 1, 2),
+    ],
+)
+def test_outer_forward_matches_oracle(name, B, shape, bs, inner, outer):
+    from gridnet_b200 import outer_forward
+
+    w, b, s, gamma, beta = model_params(21, shape)
+    if name.startswith("C1"):
+        # MNIST-style input: 28x28 pixels in [0,1] zero-padded onto the [..., 0] face
+        # (gridnet/scripts/train_mnist.py:59-60)
+        x = np.zeros((B, *shape), np.float32)
+        x[:, 2:30, 2:30, 0] = np.random.default_rng(22).random((B, 28, 28))
+    else:
+        x = face_input(22, B, shape)
+    a64 = [a.astype(np.float64) for a in (w, b, s, gamma, beta, x)]
+    ref64 = orc.outer_forward(*a64, inner, outer, bs)
+    ref32 = orc.outer_forward(w, b, s, gamma, beta, x, inner, outer, bs)
+    got = outer_forward(*(dev(a) for a in (w, b, s, gamma, beta, x)), inner, outer, bs).cpu().numpy()
+    assert_close(got, ref64, ref32, name)
+
+
+def test_outer_forward_edge_cases():
+    from gridnet_b200 import outer_forward
+
+    shape = (8, 8, 8)
+    w, b, s, gamma, beta = (dev(a) for a in model_params(23, shape))
+    x = dev(face_input(24, 2, shape))
+    assert torch.equal(outer_forward(w, b, s, gamma, beta, x, 2, 0, 8), x)  # no outer steps
+    e = torch.empty(0, *shape, device="cuda")
+    assert outer_forward(w, b, s, gamma, beta, e, 2, 3, 8).shape == e.shape
+    # zero inner iterations: the loop is LayerNorm applied `outer` times
+    got = outer_forward(w, b, s, gamma, beta, x, 0, 2, 8)
+    want = x
+    for _ in range(2):
+        want = torch.nn.functional.layer_norm(want, shape, gamma, beta, 1e-5)
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-5)
+    with pytest.raises(AssertionError):
+        outer_forward(w, b, s, gamma[:4], beta, x, 2, 2, 8)
+
+
+def test_full_size_properties_c2():
+    """BASELINE config 2 at full size (64^3, block 8, 4 inner x 12 outer, batch 64): too slow
+    for the scalar oracle in float64 at full batch, so parity is carried by properties."""
+    from gridnet_b200 import GridnetCudaOp, GridNormOp, outer_forward
+
+    shape, B, bs, inner, outer = (64, 64, 64), 64, 8, 4, 12
+    w, b, s, gamma, beta = (dev(a) for a in model_params(25, shape))
+    x = dev(face_input(26, B, shape))
+    y = outer_forward(w, b, s, gamma, beta, x, inner, outer, bs)
+    assert torch.isfinite(y).all()
+    # (1) deterministic: a second run is bit-identical
+    assert torch.equal(y, outer_forward(w, b, s, gamma, beta, x, inner, outer, bs))
+    # (2) the fused loop equals the unfused composition of the two public ops
+    h = x
+    for _ in range(outer):
+        h = GridnetCudaOp.apply(w, b, s, h, inner, bs, 1e-5, False, "silu")
+        h = GridNormOp.apply(h, gamma, beta, 1e-5)
+    assert torch.allclose(y, h, rtol=1e-4, atol=1e-5), (y - h).abs().max().item()
+    # (3) samples are independent: any sub-batch gives the same rows
+    sub = outer_forward(w, b, s, gamma, beta, x[5:8].contiguous(), inner, outer, bs)
+    assert torch.allclose(y[5:8], sub, rtol=1e-5, atol=1e-6)
+    # (4) every sample is normalised: mean beta-ish, variance gamma-ish (gamma, beta near 1, 0)
+    flat = ((y - beta) / gamma).flatten(1)
+    assert flat.mean(1).abs().max() < 1e-3
+    assert (flat.var(1, unbiased=False) - 1).abs().max() < 1e-2
+    # (5) three samples against the float64 oracle
+    a64 = [t.cpu().numpy().astype(np.float64) for t in (w, b, s, gamma, beta)]
+    idx = [0, 31, 63]
+    x64 = x[idx].cpu().numpy().astype(np.float64)
+    ref64 = orc.outer_forward(*a64, x64, inner, outer, bs)
+    ref32 = orc.outer_forward(*(a.astype(np.float32) for a in a64), x64.astype(np.float32), inner, outer, bs)
+    assert_close(y[idx].cpu().numpy(), ref64, ref32, "C2 full size, sampled rows")

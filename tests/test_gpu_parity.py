@@ -1,0 +1,306 @@
+"""GPU parity: the CUDA path (through the C ABI, via the reference-shaped op
+surface) against the CPU oracle and the committed golden vectors.
+
+Layout follows the reference's own GPU tests (gridnet/backend_cuda_test.py): same
+shapes, both block sizes, both normalize values, float32 forward and float64
+gradients, plus the edge cases listed in each test."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gridnet_oracle as orc
+
+from conftest import GOLDEN
+from util import assert_close, rng_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def ops():
+    from gridnet_b200 import GatedGridnetCudaOp, GridnetCudaOp
+
+    return GridnetCudaOp, GatedGridnetCudaOp
+
+
+# ------------------------------------------------------------------ plain forward
+@pytest.mark.parametrize(
+    "shape,block_size,normalize",
+    [
+        ((16, 16, 16), 8, True),
+        ((32, 64, 128), 8, True),
+        ((32, 64, 128), 4, True),
+        ((32, 16, 8), 4, False),
+        ((32, 16, 8), 8, False),
+        ((32, 64, 128), 8, False),
+        ((8, 8, 8), 8, False),
+        ((8, 24, 40), 8, False),
+        ((4, 4, 4), 4, True),
+    ],
+)
+def test_forward_equivalence(shape, block_size, normalize):
+    # gridnet/backend_cuda_test.py:9-36 (all-randn parameters, B = 2, 2 inner iterations, silu)
+    Op, _ = ops()
+    w, b, s, x = rng_inputs(1, 2, shape)
+    ref64 = orc.step_forward(*(a.astype(np.float64) for a in (w, b, s, x)), 2, block_size, 1e-5, normalize, "silu")
+    ref32 = orc.step_forward(w, b, s, x, 2, block_size, 1e-5, normalize, "silu")
+    got = Op.apply(dev(w), dev(b), dev(s), dev(x), 2, block_size, 1e-5, normalize, "silu").cpu().numpy()
+    assert np.abs(got - ref64).max() < 2e-4  # the reference's own bar
+    assert_close(got, ref64, ref32, f"forward {shape}/{block_size}/{normalize}")
+
+
+@pytest.mark.parametrize("activation", ["relu", "leaky_relu", "silu", "tanh"])
+@pytest.mark.parametrize("block_size,normalize", [(8, False), (4, False), (8, True)])
+def test_forward_activations(activation, block_size, normalize):
+    Op, _ = ops()
+    shape = (16, 8, 24)
+    w, b, s, x = rng_inputs(2, 3, shape)
+    ref64 = orc.step_forward(*(a.astype(np.float64) for a in (w, b, s, x)), 3, block_size, 1e-5, normalize, activation)
+    ref32 = orc.step_forward(w, b, s, x, 3, block_size, 1e-5, normalize, activation)
+    got = Op.apply(dev(w), dev(b), dev(s), dev(x), 3, block_size, 1e-5, normalize, activation).cpu().numpy()
+    assert_close(got, ref64, ref32, f"{activation}/{block_size}/{normalize}")
+
+
+@pytest.mark.parametrize("inner", [1, 2, 8, 9, 32])
+@pytest.mark.parametrize("batch", [1, 5])
+def test_forward_inner_depth_and_odd_batches(inner, batch):
+    # model-like parameters (weights N(0, 1/27), unit scale) so that deep inner loops stay finite
+    Op, _ = ops()
+    shape = (16, 16, 8)
+    w, b, s, x = rng_inputs(3, batch, shape, unit_scale=True)
+    ref64 = orc.step_forward(*(a.astype(np.float64) for a in (w, b, s, x)), inner, 8, 1e-5, False, "silu")
+    ref32 = orc.step_forward(w, b, s, x, inner, 8, 1e-5, False, "silu")
+    got = Op.apply(dev(w), dev(b), dev(s), dev(x), inner, 8, 1e-5, False, "silu").cpu().numpy()
+    assert_close(got, ref64, ref32, f"inner={inner} B={batch}")
+
+
+def test_forward_float64_matches_oracle_tightly():
+    Op, _ = ops()
+    for bs, norm in ((8, True), (4, False), (8, False), (4, True)):
+        w, b, s, x = rng_inputs(4, 2, (8, 16, 8), dtype=np.float64)
+        ref = orc.step_forward(w, b, s, x, 2, bs, 1e-5, norm, "silu")
+        got = Op.apply(dev(w), dev(b), dev(s), dev(x), 2, bs, 1e-5, norm, "silu").cpu().numpy()
+        assert np.abs(got - ref).max() < 1e-10 * (1 + np.abs(ref).max())
+
+
+def test_known_answers():
+    # gridnet/backend_torch_test.py:10-60
+    Op, _ = ops()
+    shape = (16, 16, 16)
+    w, b, s, x = rng_inputs(5, 2, shape)
+    out = Op.apply(dev(w), dev(b), dev(np.ones_like(s)), dev(x), 0, 8, 1e-5, True, "silu")
+    assert torch.equal(out.cpu(), torch.from_numpy(x))
+    zw = np.zeros_like(w)
+    sc = np.full(shape, 0.31, np.float32)
+    for norm in (True, False):
+        out = Op.apply(dev(zw), dev(b), dev(sc), dev(x), 10, 8, 1e-5, norm, "silu").cpu().numpy()
+        want = x + 10 * (b / (1 + np.exp(-b.astype(np.float64)))) * 0.31
+        np.testing.assert_allclose(out, want, rtol=1e-5, atol=1e-5)
+
+
+def test_boundary_and_interior_blocks_see_the_right_halo():
+    # one hot voxel per sample placed at a block corner: its influence must cross into every
+    # neighbouring block through the halo, and stop at the grid boundary
+    Op, _ = ops()
+    shape = (24, 24, 24)
+    w, b, s, _ = rng_inputs(6, 1, shape, unit_scale=True)
+    x = np.zeros((4, *shape), np.float32)
+    x[0, 8, 8, 8] = 1.0   # interior corner shared by 8 blocks
+    x[1, 0, 0, 0] = 1.0   # grid corner
+    x[2, 23, 15, 16] = 1.0
+    x[3, 7, 23, 0] = 1.0
+    ref = orc.step_forward(*(a.astype(np.float64) for a in (w, b, s, x)), 2, 8, 1e-5, False, "silu")
+    got = Op.apply(dev(w), dev(b), dev(s), dev(x), 2, 8, 1e-5, False, "silu").cpu().numpy()
+    assert_close(got, ref, None, "hot voxel")
+
+
+def test_golden_forward_vectors():
+    Op, _ = ops()
+    z = np.load(os.path.join(GOLDEN, "step_forward.npz"))
+    for c in sorted({k.split("_")[0] for k in z.files if k.endswith("_meta")}):
+        bs, inner, norm = (int(v) for v in z[f"{c}_meta"])
+        act = str(z[f"{c}_act"])
+        w, b, s, x = (z[f"{c}_{k}"] for k in ("w", "b", "s", "x"))
+        got = Op.apply(dev(w), dev(b), dev(s), dev(x), inner, bs, 1e-5, bool(norm), act).cpu().numpy()
+        assert_close(got, z[f"{c}_y64"], z[f"{c}_y32"], f"golden forward {c}")
+
+
+# ----------------------------------------------------------------- plain backward
+def _grads(Op, w, b, s, x, gy, inner, bs, norm, act, dtype):
+    tw, tb, ts, tx = (dev(a, dtype).requires_grad_(True) for a in (w, b, s, x))
+    out = Op.apply(tw, tb, ts, tx, inner, bs, 1e-5, norm, act)
+    gs, gb, gw, gx = torch.autograd.grad(out, (ts, tb, tw, tx), dev(gy, dtype))
+    return [g.cpu().numpy() for g in (gw, gb, gs, gx)]
+
+
+@pytest.mark.parametrize(
+    "shape,inner_iters,block_size,normalize",
+    [
+        ((16, 16, 16), 1, 8, True),
+        ((16, 16, 16), 2, 8, True),
+        ((32, 64, 128), 2, 8, True),
+        ((32, 64, 128), 2, 4, True),
+        ((32, 16, 8), 2, 4, False),
+        ((32, 16, 8), 2, 8, False),
+    ],
+)
+def test_grad_equivalence_float64(shape, inner_iters, block_size, normalize):
+    # gridnet/backend_cuda_test.py:61-110: float64, grads w.r.t. scales, biases, weights, inputs
+    Op, _ = ops()
+    w, b, s, x = rng_inputs(7, 2, shape, dtype=np.float64)
+    gy = np.random.default_rng(8).standard_normal(x.shape)
+    want = orc.step_backward(w, b, s, x, gy, inner_iters, block_size, 1e-5, normalize, "silu")
+    got = _grads(Op, w, b, s, x, gy, inner_iters, block_size, normalize, "silu", torch.float64)
+    for name, g, r in zip(("weights", "biases", "scales", "inputs"), got, want):
+        err = np.abs(g - r).max()
+        assert err < 3e-4, f"MAE in {name}: {err}"  # the reference's bar
+        assert err < 1e-9 * (1 + np.abs(r).max()), f"{name}: {err}"
+
+
+@pytest.mark.parametrize("activation", ["relu", "leaky_relu", "silu", "tanh"])
+@pytest.mark.parametrize("block_size,normalize,inner", [(8, False, 2), (4, False, 3), (8, True, 2), (4, True, 1)])
+def test_grad_float32(activation, block_size, normalize, inner):
+    Op, _ = ops()
+    shape = (8, 16, 16)
+    w, b, s, x = rng_inputs(9, 3, shape, unit_scale=not normalize)
+    if not normalize:
+        b = (0.1 * np.random.default_rng(10).standard_normal(shape)).astype(np.float32)
+    gy = np.random.default_rng(11).standard_normal(x.shape).astype(np.float32)
+    a64 = [a.astype(np.float64) for a in (w, b, s, x, gy)]
+    want = orc.step_backward(*a64, inner, block_size, 1e-5, normalize, activation)
+    noise = orc.step_backward(w, b, s, x, gy, inner, block_size, 1e-5, normalize, activation)
+    got = _grads(Op, w, b, s, x, gy, inner, block_size, normalize, activation, torch.float32)
+    for name, g, r, n in zip(("gw", "gb", "gs", "gx"), got, want, noise):
+        assert_close(g, r, n, f"{name} {activation}/{block_size}/{normalize}")
+
+
+@pytest.mark.parametrize("inner", [8, 9, 32])
+def test_grad_deep_inner(inner):
+    # stash boundaries of the reference kernel (8 / 16 / 32, src/gridnet_cuda_kernels.cu:829-836)
+    Op, _ = ops()
+    shape = (8, 8, 16)
+    w, b, s, x = rng_inputs(12, 2, shape, unit_scale=True, dtype=np.float64)
+    w *= 0.5
+    gy = np.random.default_rng(13).standard_normal(x.shape)
+    want = orc.step_backward(w, b, s, x, gy, inner, 8, 1e-5, False, "silu")
+    got = _grads(Op, w, b, s, x, gy, inner, 8, False, "silu", torch.float64)
+    for name, g, r in zip(("gw", "gb", "gs", "gx"), got, want):
+        assert np.abs(g - r).max() < 1e-9 * (1 + np.abs(r).max()), name
+
+
+def test_golden_backward_vectors():
+    Op, _ = ops()
+    z = np.load(os.path.join(GOLDEN, "step_backward.npz"))
+    for c in sorted({k.split("_")[0] for k in z.files if k.endswith("_meta")}):
+        bs, inner, norm = (int(v) for v in z[f"{c}_meta"])
+        act = str(z[f"{c}_act"])
+        w, b, s, x, gy = (z[f"{c}_{k}"].astype(np.float64) for k in ("w", "b", "s", "x", "gy"))
+        got = _grads(Op, w, b, s, x, gy, inner, bs, bool(norm), act, torch.float64)
+        for name, g in zip(("gw", "gb", "gs", "gx"), got):
+            r = z[f"{c}_{name}"]
+            assert np.abs(g - r).max() < 1e-9 * (1 + np.abs(r).max()), (c, name)
+
+
+def test_backward_overwrites_its_outputs():
+    # gradient buffers handed to the extension may hold garbage: every element is written
+    from gridnet_b200 import gridnet_cuda
+
+    shape = (8, 8, 8)
+    w, b, s, x = rng_inputs(14, 2, shape, dtype=np.float64)
+    gy = np.random.default_rng(15).standard_normal(x.shape)
+    want = orc.step_backward(w, b, s, x, gy, 2, 8, 1e-5, False, "silu")
+    bufs = [torch.full(a.shape, 7.0, dtype=torch.float64, device="cuda") for a in (w, b, s, x)]
+    gridnet_cuda.backward(dev(w), dev(b), dev(s), dev(x), dev(gy), *bufs, 2, 8, 1e-5, False, "silu")
+    for g, r in zip(bufs, want):
+        assert np.abs(g.cpu().numpy() - r).max() < 1e-9 * (1 + np.abs(r).max())
+
+
+# -------------------------------------------------------------------------- gated
+@pytest.mark.parametrize("shape,block_size", [((16, 16, 16), 8), ((32, 64, 128), 8), ((32, 64, 128), 4)])
+def test_forward_equivalence_gated(shape, block_size):
+    # gridnet/backend_cuda_test.py:39-58
+    _, Gated = ops()
+    w, b, x = rng_inputs(16, 2, shape, gated=True)
+    ref64 = orc.gated_forward(*(a.astype(np.float64) for a in (w, b, x)), 2, block_size, "tanh")
+    ref32 = orc.gated_forward(w, b, x, 2, block_size, "tanh")
+    got = Gated.apply(dev(w), dev(b), dev(x), 2, block_size, "tanh").cpu().numpy()
+    assert np.abs(got - ref64).max() < 2e-4
+    assert_close(got, ref64, ref32, f"gated {shape}/{block_size}")
+
+
+@pytest.mark.parametrize(
+    "shape,inner_iters,block_size",
+    [((16, 16, 16), 1, 8), ((16, 16, 16), 2, 8), ((32, 64, 128), 2, 8), ((32, 64, 128), 2, 4)],
+)
+def test_grad_equivalence_gated(shape, inner_iters, block_size):
+    # gridnet/backend_cuda_test.py:113-152
+    _, Gated = ops()
+    w, b, x = rng_inputs(17, 2, shape, gated=True, dtype=np.float64)
+    gy = np.random.default_rng(18).standard_normal(x.shape)
+    want = orc.gated_backward(w, b, x, gy, inner_iters, block_size, "tanh")
+    tw, tb, tx = (dev(a).requires_grad_(True) for a in (w, b, x))
+    out = Gated.apply(tw, tb, tx, inner_iters, block_size, "tanh")
+    gb, gw, gx = torch.autograd.grad(out, (tb, tw, tx), dev(gy))
+    for name, g, r in zip(("weights", "biases", "inputs"), (gw, gb, gx), want):
+        g = g.cpu().numpy()
+        assert np.isfinite(g).all()
+        err = np.abs(g - r).max()
+        assert err < 3e-4, f"MAE in {name}: {err}"
+        assert err < 1e-9 * (1 + np.abs(r).max()), name
+
+
+def test_golden_gated_vectors():
+    _, Gated = ops()
+    z = np.load(os.path.join(GOLDEN, "gated.npz"))
+    for c in sorted({k.split("_")[0] for k in z.files if k.endswith("_meta")}):
+        bs, inner = (int(v) for v in z[f"{c}_meta"])
+        act = str(z[f"{c}_act"])
+        w, b, x, gy = (z[f"{c}_{k}"] for k in ("w", "b", "x", "gy"))
+        got = Gated.apply(dev(w), dev(b), dev(x), inner, bs, act).cpu().numpy()
+        assert_close(got, z[f"{c}_y64"], z[f"{c}_y32"], f"golden gated {c}")
+        tw, tb, tx = (dev(a, torch.float64).requires_grad_(True) for a in (w, b, x))
+        out = Gated.apply(tw, tb, tx, inner, bs, act)
+        gw, gb, gx = torch.autograd.grad(out, (tw, tb, tx), dev(gy, torch.float64))
+        for name, g in zip(("gw", "gb", "gx"), (gw, gb, gx)):
+            r = z[f"{c}_{name}"]
+            assert np.abs(g.cpu().numpy() - r).max() < 1e-9 * (1 + np.abs(r).max()), (c, name)
+
+
+# ------------------------------------------------------------------- error paths
+def test_extension_layer_errors():
+    # RuntimeError for non-contiguous tensors and unknown activations, as the reference's
+    # C++ layer raises (src/gridnet_cuda.cpp:6-10, src/activations.h:15-16)
+    from gridnet_b200 import gridnet_cuda
+
+    Op, _ = ops()
+    shape = (8, 8, 8)
+    w, b, s, x = (dev(a) for a in rng_inputs(19, 2, shape))
+    with pytest.raises(RuntimeError, match="unknown activation"):
+        Op.apply(w, b, s, x, 1, 8, 1e-5, False, "gelu")
+    y = torch.empty_like(x)
+    xt = x.transpose(1, 2)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        gridnet_cuda.forward(w, b, s, xt, y, 1, 8, 1e-5, False, "silu")
+    from gridnet_b200._lib import lib
+
+    big = lib.gn_step_backward_max_inner(8, 4) + 1
+    tw = w.clone().requires_grad_(True)
+    out = Op.apply(tw, b, s, x, big, 8, 1e-5, False, "relu")
+    with pytest.raises(RuntimeError, match="inner"):
+        out.sum().backward()
+    # an empty batch returns a clone without launching anything
+    e = torch.empty(0, *shape, device="cuda")
+    assert Op.apply(w, b, s, e, 1, 8, 1e-5, False, "silu").shape == e.shape
+    # a non-contiguous upstream gradient is accepted (made contiguous by the op)
+    tx = x.clone().requires_grad_(True)
+    out = Op.apply(w, b, s, tx, 1, 8, 1e-5, False, "silu")
+    out.transpose(1, 2).contiguous().transpose(1, 2).backward(torch.ones_like(out))
+    assert torch.isfinite(tx.grad).all()
