@@ -31,8 +31,9 @@ __device__ __forceinline__ float exp_f32(float x)
 
 __device__ __forceinline__ float sigmoid_(float x)
 {
-    // 1 / (1 + exp(-x)); exp overflow gives 1/inf = 0, which is the right limit
-    return __fdividef(1.0f, 1.0f + exp_f32(-x));
+    // 1 / (1 + exp(-x)). The exponent is capped at 87 so that exp stays finite (an overflowed
+    // ex2 would turn the error-feedback term of exp_f32 into inf - inf); sigmoid(-87) = 1.6e-38.
+    return __fdividef(1.0f, 1.0f + exp_f32(fminf(-x, 87.0f)));
 }
 __device__ __forceinline__ double sigmoid_(double x) { return 1.0 / (1.0 + exp(-x)); }
 

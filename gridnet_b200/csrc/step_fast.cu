@@ -10,22 +10,26 @@
 // one-voxel halo) sits in shared memory with a row stride of 12 floats: with that
 // stride the 64-bit row loads of a half-warp touch all 32 banks exactly once.
 // Per inner iteration a thread reads a 3x4x4 window (48 floats) for its
-// 4 x 27 = 108 FMAs, 2.25 FMAs per shared-memory float.
+// 4 x 27 = 108 FMAs, 2.25 FMAs per shared-memory float. Shared-memory wavefronts,
+// not HBM and not the FMA pipe, are what this kernel runs out of first, so
+// everything around the stencil is arranged to cost as few of them as possible.
 //
-// Pipeline. Tiles are fetched two samples at a time with cp.async into a
-// double-buffered stage, so the global->shared traffic of the next stage
-// overlaps the inner iterations of the current one. New activations stay in
-// registers until every thread has finished reading the old ones (one barrier
-// pair per inner iteration per stage); the last inner iteration goes straight to
-// global memory.
+// Pipeline. Each sample has two tiles; inner iteration i reads one and writes the
+// block interior of the other (the halo is stored in both when the tile is
+// loaded), so one barrier per iteration is enough and new values never wait in
+// registers. Tile cells are fetched global -> registers one stage (one sample)
+// ahead, so those loads are in flight while the current stage iterates; they are
+// written to shared memory when the stage starts. The last inner iteration goes
+// straight to global memory.
 //
 // Fusion with the whole-grid normalisation (gridnet/scripts/train_mnist.py:62-64):
 //   FUSE_IN   the input is the previous step's raw output; (x - mean) * rstd *
-//             gamma + beta is applied to each tile cell as it arrives in shared
-//             memory, so the normalised tensor never exists in HBM.
+//             gamma + beta is applied to each tile cell on its way from the
+//             prefetch register into shared memory, so the normalised tensor never
+//             exists in HBM.
 //   STATS_OUT per-sample sum and sum of squares of what this step writes are
 //             reduced in double precision per warp and stored as partials for
-//             norm_finalize_partials (norm.cu).
+//             norm_finalize_k (norm.cu).
 //
 // Reference semantics: gridnet/backend_torch.py:61-142; the kernel it stands in
 // for is gridnet_cuda_forward_kernel, src/gridnet_cuda_kernels.cu:101-200.
@@ -39,25 +43,28 @@ constexpr int RS = 12;          // row stride (floats)
 constexpr int PS = 10 * RS;     // plane stride
 constexpr int TS = 10 * PS;     // one tile
 constexpr int THREADS = 128;
-constexpr int SPS = 2;          // samples per pipeline stage
+#ifndef GN_F8_SPS
+#define GN_F8_SPS 1
+#endif
+#ifndef GN_F8_MINB
+#define GN_F8_MINB 3
+#endif
+constexpr int SPS = GN_F8_SPS;  // samples per pipeline stage
 constexpr int SLOTS = 8;        // tile cells handled per thread when loading (8 * 128 >= 1000)
+// Per-slot descriptor, one register: bits 0..10 tile offset, bit 11 = halo cell (kept in both
+// ping-pong tiles), bits 12..31 global offset relative to the tile's origin cell.
+constexpr unsigned kSkip = 0xffffffffu;     // slot beyond the 1000 tile cells
+constexpr unsigned kOutside = 0xfffffffeu;  // cell outside the grid: reads as zero
+constexpr unsigned kFirstSpecial = kOutside;
+constexpr long long kMaxRel = 1LL << 20;
 }  // namespace fast8
 
-__device__ __forceinline__ void cp_async4(float *dst_smem, const float *src)
-{
-    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
 template <int ACT, bool FUSE_IN, bool STATS_OUT>
-__global__ void __launch_bounds__(fast8::THREADS, 3) step_fwd_fast8(const FastFwdParams p)
+__global__ void __launch_bounds__(fast8::THREADS, GN_F8_MINB) step_fwd_fast8(const FastFwdParams p)
 {
     using namespace fast8;
     __shared__ __align__(16) float tiles[2][SPS][TS];
-    __shared__ int2 cell[SLOTS * THREADS];                      // (global offset | -1, tile offset)
-    __shared__ float2 gbtab[FUSE_IN ? SLOTS * THREADS : 1];     // (gamma, beta) per tile cell
+    __shared__ float2 gbtab[FUSE_IN ? SLOTS * THREADS : 1];  // (gamma, beta) per tile cell
 
     const int tid = threadIdx.x;
     const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
@@ -67,28 +74,34 @@ __global__ void __launch_bounds__(fast8::THREADS, 3) step_fwd_fast8(const FastFw
     const size_t P = (size_t)p.M * p.N * p.K;
     const int K = p.K;
     const size_t g00 = ((size_t)(bz * 8 + z) * p.N + (by * 8 + 2 * yp)) * K + (bx * 8 + 2 * xp);
+    // offset of the tile's origin cell (block corner minus one voxel; may lie outside the grid)
+    const long long origin = ((long long)(bz * 8 - 1) * p.N + (by * 8 - 1)) * K + (bx * 8 - 1);
 
-    // ---- tables: where each tile cell lives in global memory (or that it is outside the grid)
-    for (int i = tid; i < SLOTS * THREADS; i += THREADS) {
-        int goff = -1, soff = 0;
+    // ---- which tile cells this thread fetches for every sample, and where they go
+    unsigned cinfo[SLOTS];
+#pragma unroll
+    for (int j = 0; j < SLOTS; ++j) {
+        const int i = tid + j * THREADS;
+        unsigned ci = kSkip;
+        float2 gb = make_float2(0.0f, 0.0f);
         if (i < 1000) {
             const int cx = i % 10, cy = (i / 10) % 10, cz = i / 100;
             const int gz = bz * 8 + cz - 1, gy = by * 8 + cy - 1, gx = bx * 8 + cx - 1;
-            soff = cz * PS + cy * RS + cx;
-            if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K)
-                goff = (gz * p.N + gy) * K + gx;
-            else {
+            const int soff = cz * PS + cy * RS + cx;
+            const bool halo = cx == 0 || cx == 9 || cy == 0 || cy == 9 || cz == 0 || cz == 9;
+            if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K) {
+                const int rel = (cz * p.N + cy) * K + cx;
+                ci = (unsigned)soff | (halo ? 0x800u : 0u) | ((unsigned)rel << 12);
+                if (FUSE_IN) gb = make_float2(p.gamma[origin + rel], p.beta[origin + rel]);
+            } else {
+                ci = kOutside;
                 // cells outside the grid stay zero for the CTA's whole life
 #pragma unroll
                 for (int q = 0; q < 2 * SPS; ++q) (&tiles[0][0][0])[q * TS + soff] = 0.0f;
             }
         }
-        cell[i] = make_int2(goff, soff);
-        if (FUSE_IN) {
-            float2 gb = make_float2(0.0f, 0.0f);
-            if (goff >= 0) gb = make_float2(p.gamma[goff], p.beta[goff]);
-            gbtab[i] = gb;
-        }
+        cinfo[j] = ci;
+        if (FUSE_IN) gbtab[i] = gb;
     }
 
     // ---- this thread's parameters: 4 neurons x (27 weights, bias, scale)
@@ -117,59 +130,61 @@ __global__ void __launch_bounds__(fast8::THREADS, 3) step_fwd_fast8(const FastFw
     const int nstages = (s1 - s0 + SPS - 1) / SPS;
     const int toff = z * PS + 2 * yp * RS + 2 * xp;  // window origin of this thread inside a tile
 
-    __syncthreads();  // tables are complete
-
-    auto issue_stage = [&](int st) {
-        const int buf = st & 1;
+    // global -> registers for one stage; consumed by commit() one stage later
+    float pf[SPS][SLOTS];
+    auto prefetch = [&](int st) {
 #pragma unroll
         for (int s = 0; s < SPS; ++s) {
             const int smp = s0 + st * SPS + s;
             if (smp < s1) {
-                const float *xs = p.x + (size_t)smp * P;
-                float *tl = tiles[buf][s];
+                const float *xs = p.x + (size_t)smp * P + origin;
 #pragma unroll
-                for (int j = 0; j < SLOTS; ++j) {
-                    const int2 c = cell[tid + j * THREADS];
-                    if (c.x >= 0) cp_async4(tl + c.y, xs + c.x);
-                }
+                for (int j = 0; j < SLOTS; ++j)
+                    if (cinfo[j] < kFirstSpecial) pf[s][j] = __ldg(xs + (cinfo[j] >> 12));
             }
         }
-        cp_async_commit();
     };
-
-    if (nstages > 0) issue_stage(0);
-
-    for (int st = 0; st < nstages; ++st) {
-        const int buf = st & 1;
-        const int smp0 = s0 + st * SPS;
-        cp_async_wait_all();
-        if (FUSE_IN) {
-            // normalise-on-load: each thread fixes up exactly the cells it fetched itself
+    // registers -> tiles, normalising on the way when the input is a raw step output
+    auto commit = [&](int st) {
 #pragma unroll
-            for (int s = 0; s < SPS; ++s) {
-                if (smp0 + s < s1) {
-                    const float2 mr = p.in_stats[smp0 + s];
-                    float *tl = tiles[buf][s];
+        for (int s = 0; s < SPS; ++s) {
+            const int smp = s0 + st * SPS + s;
+            if (smp < s1) {
+                float2 mr = make_float2(0.0f, 1.0f);
+                if (FUSE_IN) mr = p.in_stats[smp];
 #pragma unroll
-                    for (int j = 0; j < SLOTS; ++j) {
-                        const int2 c = cell[tid + j * THREADS];
-                        if (c.x >= 0) {
+                for (int j = 0; j < SLOTS; ++j) {
+                    const unsigned ci = cinfo[j];
+                    if (ci < kFirstSpecial) {
+                        float v = pf[s][j];
+                        if (FUSE_IN) {
                             const float2 gb = gbtab[tid + j * THREADS];
-                            tl[c.y] = fmaf((tl[c.y] - mr.x) * mr.y, gb.x, gb.y);
+                            v = fmaf((v - mr.x) * mr.y, gb.x, gb.y);
                         }
+                        tiles[0][s][ci & 0x7ff] = v;
+                        if (ci & 0x800) tiles[1][s][ci & 0x7ff] = v;
                     }
                 }
             }
         }
-        __syncthreads();  // stage st is complete; nobody still reads the other buffer
-        if (st + 1 < nstages) issue_stage(st + 1);
+    };
 
+    if (nstages > 0) prefetch(0);
+
+    for (int st = 0; st < nstages; ++st) {
+        const int smp0 = s0 + st * SPS;
+        __syncthreads();  // the previous stage no longer reads the tiles (and the zero fill is done)
+        commit(st);
+        __syncthreads();
+        if (st + 1 < nstages) prefetch(st + 1);
+
+        int cur = 0;
         for (int it = 0; it < p.inner; ++it) {
-            float nv[SPS][2][2];
+            const bool last = it + 1 == p.inner;
 #pragma unroll
             for (int s = 0; s < SPS; ++s) {
                 if (smp0 + s < s1) {
-                    const float *tl = tiles[buf][s] + toff;
+                    const float *tl = tiles[cur][s] + toff;
                     float acc[2][2] = {{bias[0][0], bias[0][1]}, {bias[1][0], bias[1][1]}};
                     float old[2][2];
 #pragma unroll
@@ -195,42 +210,31 @@ __global__ void __launch_bounds__(fast8::THREADS, 3) step_fwd_fast8(const FastFw
                                 }
                             }
                         }
+                    float nv[2][2];
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
                         for (int i = 0; i < 2; ++i)
-                            nv[s][j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
-                }
-            }
-            if (it + 1 < p.inner) {
-                __syncthreads();  // every thread has read the old activations
-#pragma unroll
-                for (int s = 0; s < SPS; ++s) {
-                    if (smp0 + s < s1) {
-                        float *tl = tiles[buf][s] + toff + PS + RS + 1;
+                            nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
+                    if (!last) {
+                        float *to = tiles[cur ^ 1][s] + toff + PS + RS + 1;
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            tl[j * RS] = nv[s][j][0];
-                            tl[j * RS + 1] = nv[s][j][1];
+                            to[j * RS] = nv[j][0];
+                            to[j * RS + 1] = nv[j][1];
                         }
-                    }
-                }
-                __syncthreads();
-            } else {
-#pragma unroll
-                for (int s = 0; s < SPS; ++s) {
-                    if (smp0 + s < s1) {
+                    } else {
                         float *ys = p.y + (size_t)(smp0 + s) * P + g00;
 #pragma unroll
                         for (int j = 0; j < 2; ++j)
-                            *reinterpret_cast<float2 *>(ys + (size_t)j * K) = make_float2(nv[s][j][0], nv[s][j][1]);
+                            *reinterpret_cast<float2 *>(ys + (size_t)j * K) = make_float2(nv[j][0], nv[j][1]);
                         if (STATS_OUT) {
                             double sm = 0.0, sq = 0.0;
 #pragma unroll
                             for (int j = 0; j < 2; ++j)
 #pragma unroll
                                 for (int i = 0; i < 2; ++i) {
-                                    const double v = (double)nv[s][j][i];
+                                    const double v = (double)nv[j][i];
                                     sm += v;
                                     sq = fma(v, v, sq);
                                 }
@@ -243,6 +247,10 @@ __global__ void __launch_bounds__(fast8::THREADS, 3) step_fwd_fast8(const FastFw
                     }
                 }
             }
+            if (!last) {
+                __syncthreads();  // the other tile is complete; this one may be overwritten next
+                cur ^= 1;
+            }
         }
     }
 }
@@ -252,6 +260,8 @@ bool fast8_applicable(const FastFwdParams &p, int block, int normalize)
 {
     if (block != 8 || normalize || p.inner < 1) return false;
     if ((long long)p.M * p.N * p.K >= (1LL << 31)) return false;
+    // the per-cell descriptor holds offsets relative to the tile origin in 20 bits
+    if ((9LL * p.N + 9) * p.K + 9 >= fast8::kMaxRel) return false;
     auto al = [](const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; };
     return al(p.w, 8) && al(p.b, 8) && al(p.s, 8) && al(p.x, 4) && al(p.y, 8);
 }
