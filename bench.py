@@ -50,8 +50,9 @@ UNIT = "neuron-updates/s"
 # FP32 pipe: 148 SMs x 128 FMA lanes x 2 FLOP at the maximum SM clock
 FP32_LANES = 148 * 128
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/); None until measured
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
+# from the capture summarised in profiles/step_fwd_fast8_c2_ncu_full.txt
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 173.7e6
 
 
 def neuron_updates(batch: int) -> float:

@@ -5,6 +5,10 @@
 
 #include "../../include/gridnet_b200.h"
 
+#ifndef GN_ACCURATE_SIGMOID
+#define GN_ACCURATE_SIGMOID 0
+#endif
+
 namespace gn {
 
 constexpr int kNumSMs = 148;  // B200
@@ -31,9 +35,20 @@ __device__ __forceinline__ float exp_f32(float x)
 
 __device__ __forceinline__ float sigmoid_(float x)
 {
+#if GN_ACCURATE_SIGMOID
     // 1 / (1 + exp(-x)). The exponent is capped at 87 so that exp stays finite (an overflowed
     // ex2 would turn the error-feedback term of exp_f32 into inf - inf); sigmoid(-87) = 1.6e-38.
     return __fdividef(1.0f, 1.0f + exp_f32(fminf(-x, 87.0f)));
+#else
+    // 1 / (1 + 2^(-x * log2 e)) in six instructions: FMUL, FMNMX, MUFU.EX2, FADD, MUFU.RCP
+    // (+ the caller's multiply). The exponent is capped at 126 so that 1 + 2^t stays finite.
+    // Relative error about |x| * 6e-8 from the rounded product plus 2 ulp from each MUFU.
+    const float t = fminf(x * -1.4426950408889634f, 126.0f);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return r;
+#endif
 }
 __device__ __forceinline__ double sigmoid_(double x) { return 1.0 / (1.0 + exp(-x)); }
 

@@ -43,13 +43,8 @@ constexpr int RS = 12;          // row stride (floats)
 constexpr int PS = 10 * RS;     // plane stride
 constexpr int TS = 10 * PS;     // one tile
 constexpr int THREADS = 128;
-#ifndef GN_F8_SPS
-#define GN_F8_SPS 1
-#endif
-#ifndef GN_F8_MINB
-#define GN_F8_MINB 3
-#endif
-constexpr int SPS = GN_F8_SPS;  // samples per pipeline stage
+constexpr int SPS = 1;          // samples per pipeline stage (2 measured slower: the prefetch registers crowd out the stencil)
+constexpr int MIN_CTAS = 3;     // CTAs per SM the register budget is sized for (168 registers per thread)
 constexpr int SLOTS = 8;        // tile cells handled per thread when loading (8 * 128 >= 1000)
 // Per-slot descriptor, one register: bits 0..10 tile offset, bit 11 = halo cell (kept in both
 // ping-pong tiles), bits 12..31 global offset relative to the tile's origin cell.
@@ -59,8 +54,18 @@ constexpr unsigned kFirstSpecial = kOutside;
 constexpr long long kMaxRel = 1LL << 20;
 }  // namespace fast8
 
+// A global load that stays where it is written: the compiler may sink an ordinary read-only
+// load past barriers down to its first use, which would put the whole memory latency back on
+// the critical path of the next stage.
+__device__ __forceinline__ float ld_pinned(const float *ptr)
+{
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
 template <int ACT, bool FUSE_IN, bool STATS_OUT>
-__global__ void __launch_bounds__(fast8::THREADS, GN_F8_MINB) step_fwd_fast8(const FastFwdParams p)
+__global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS) step_fwd_fast8(const FastFwdParams p)
 {
     using namespace fast8;
     __shared__ __align__(16) float tiles[2][SPS][TS];
@@ -140,7 +145,7 @@ __global__ void __launch_bounds__(fast8::THREADS, GN_F8_MINB) step_fwd_fast8(con
                 const float *xs = p.x + (size_t)smp * P + origin;
 #pragma unroll
                 for (int j = 0; j < SLOTS; ++j)
-                    if (cinfo[j] < kFirstSpecial) pf[s][j] = __ldg(xs + (cinfo[j] >> 12));
+                    if (cinfo[j] < kFirstSpecial) pf[s][j] = ld_pinned(xs + (cinfo[j] >> 12));
             }
         }
     };
@@ -178,9 +183,10 @@ __global__ void __launch_bounds__(fast8::THREADS, GN_F8_MINB) step_fwd_fast8(con
         __syncthreads();
         if (st + 1 < nstages) prefetch(st + 1);
 
-        int cur = 0;
-        for (int it = 0; it < p.inner; ++it) {
-            const bool last = it + 1 == p.inner;
+        const int inner = p.inner;
+        for (int it = 0; it < inner; ++it) {
+            const bool last = it + 1 == inner;
+            const int cur = it & 1;
 #pragma unroll
             for (int s = 0; s < SPS; ++s) {
                 if (smp0 + s < s1) {
@@ -217,11 +223,15 @@ __global__ void __launch_bounds__(fast8::THREADS, GN_F8_MINB) step_fwd_fast8(con
                         for (int i = 0; i < 2; ++i)
                             nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
                     if (!last) {
-                        float *to = tiles[cur ^ 1][s] + toff + PS + RS + 1;
+                        // The two z-planes of a warp would hit the same 16 banks with the same
+                        // element of the pair; odd planes store the pair in the other order, so
+                        // each store instruction covers all 32 banks once.
+                        float *to = tiles[cur ^ 1][s] + toff + PS + RS + 1 + (z & 1);
+                        const int step = 1 - 2 * (z & 1);
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            to[j * RS] = nv[j][0];
-                            to[j * RS + 1] = nv[j][1];
+                            to[j * RS] = (z & 1) ? nv[j][1] : nv[j][0];
+                            to[j * RS + step] = (z & 1) ? nv[j][0] : nv[j][1];
                         }
                     } else {
                         float *ys = p.y + (size_t)(smp0 + s) * P + g00;
@@ -249,7 +259,6 @@ __global__ void __launch_bounds__(fast8::THREADS, GN_F8_MINB) step_fwd_fast8(con
             }
             if (!last) {
                 __syncthreads();  // the other tile is complete; this one may be overwritten next
-                cur ^= 1;
             }
         }
     }
