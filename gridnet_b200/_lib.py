@@ -32,6 +32,8 @@ SIGNATURES = {
     "gn_norm_workspace_bytes": (c_size_t, [c_int, c_longlong]),
     "gn_norm_forward_f32": (c_int, [_P] * 5 + [c_int, c_longlong, c_float, _P, c_size_t, _P]),
     "gn_norm_backward_f32": (c_int, [_P] * 6 + [c_int, c_longlong, c_float, _P, c_size_t, _P]),
+    "gn_norm_static_max_batch": (c_int, []),
+    "gn_norm_forward_static_f32": (c_int, [_P] * 4 + [c_int, c_longlong, c_float, _P]),
     "gn_step_stats_partials": (c_int, [c_int] * 4),
     "gn_step_forward_fused_f32": (c_int, [_P] * 9 + _geom + [c_int, c_int, c_int, _P]),
     "gn_norm_finalize_f32": (c_int, [_P, c_int, _P, c_int, c_longlong, c_float, _P]),

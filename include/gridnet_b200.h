@@ -130,6 +130,25 @@ GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float 
                          float *grad_gamma, float *grad_beta, int B, long long P, float eps,
                          void *workspace, size_t workspace_bytes, void *stream);
 
+/* gn_norm_forward_static_f32: gn_norm_forward_f32 without a workspace argument and without
+ * any allocation, for callers that are not allowed to allocate device memory (a host
+ * application that has frozen its memory plan, a plug-in running inside another program's
+ * execution loop, a process under a hard memory cap). It has no counterpart in the
+ * reference. The partial sums live in a fixed array inside the library image (about
+ * 0.26 MB on every GPU that loads the library, held until the process exits), so:
+ *   - at most gn_norm_static_max_batch() (256) samples per call; a larger B returns
+ *     GN_ERR_TOO_LARGE and nothing is launched;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call before any stream capture begins;
+ *   - all calls on a device share the array: two calls whose kernels can overlap on the
+ *     GPU (different streams, no ordering between them) race on it. Calls on one stream,
+ *     or otherwise ordered, are safe; nothing needs clearing between calls.
+ * It calls no cudaMalloc / cudaFree or any allocating routine. Results are identical to
+ * gn_norm_forward_f32. */
+GN_API int gn_norm_static_max_batch(void);
+GN_API int gn_norm_forward_static_f32(const float *x, const float *gamma, const float *beta, float *y,
+                               int B, long long P, float eps, void *stream);
+
 /* Building blocks of the fused loop below, for callers that drive the outer loop
  * themselves (a slab-sharded grid exchanges halos and statistics between steps).
  *
