@@ -183,6 +183,9 @@ def pick_cpu_sample(target_seconds: float):
     also returns the number of OpenMP threads it runs on (all host cores)."""
     from oracle import gridnet_oracle as orc
 
+    # all host threads this process may use, whatever OMP_NUM_THREADS says (torch.distributed.run
+    # sets it to 1 for its children)
+    orc.set_threads(len(os.sched_getaffinity(0)))
     dt = cpu_oracle_pass(cpu_inputs(1))
     n = int(max(1, min(BATCH, target_seconds / max(dt, 1e-6))))
     return n, orc.max_threads()
@@ -258,7 +261,6 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
     launches_per_step = OUTER * 2 + 1  # per outer step: fused step kernel + statistics finalize; one final apply
     if dist is not None:
         t = torch.tensor([ms], device=device)
@@ -333,6 +335,9 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
            "ms_per_step": ems / n_e2e, "steps": n_e2e,
            "note": "full [B,M,N,K] activations in and out through outer_forward, pinned host memory, one stream"}
+
+    # clocks were sampled over all three timed regions (value, kernel-only, end to end)
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---------------- CPU baseline on rank 0 at N = 1
     cpu = None
