@@ -388,6 +388,31 @@ GN_API int gn_step_forward_fused_f32(const float *w, const float *b, const float
     return launch_step_fwd_fast8(p, act, (cudaStream_t)stream);
 }
 
+GN_API int gn_step_forward_slab_f32(const float *w, const float *b, const float *s, const float *x, float *y,
+                             const float *gamma, const float *beta, const float *in_mean_rstd,
+                             double *out_partials, int B, int M, int N, int K, int k_block_first,
+                             int k_block_count, int inner, int act, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, 8, act);
+    if (rc != GN_OK) return rc;
+    if (k_block_first < 0 || k_block_count <= 0 || k_block_first + k_block_count > K / 8) return GN_ERR_BAD_SHAPE;
+    if (B == 0) return GN_OK;
+    if (!w || !b || !s || !x || !y) return GN_ERR_NULL_POINTER;
+    if (in_mean_rstd && (!gamma || !beta)) return GN_ERR_NULL_POINTER;
+    FastFwdParams p{};
+    p.w = w; p.b = b; p.s = s; p.x = x; p.y = y; p.gamma = gamma; p.beta = beta;
+    p.in_stats = reinterpret_cast<const float2 *>(in_mean_rstd);
+    p.out_partials = reinterpret_cast<double2 *>(out_partials);
+    p.nparts = (M / 8) * (N / 8) * k_block_count * 4;
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
+    p.kb0 = k_block_first; p.kbn = k_block_count;
+    if (!fast8_applicable(p, 8, 0)) return GN_ERR_UNSUPPORTED;
+    if ((in_mean_rstd && reinterpret_cast<uintptr_t>(in_mean_rstd) % 8) ||
+        (out_partials && reinterpret_cast<uintptr_t>(out_partials) % 16))
+        return GN_ERR_UNSUPPORTED;
+    return launch_step_fwd_fast8(p, act, (cudaStream_t)stream);
+}
+
 GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_rstd, int B, long long P, float eps,
                          void *stream)
 {

@@ -31,6 +31,10 @@ struct FastFwdParams {
     int nparts;                 // partial slots per sample (= blocks * 4)
     int B, M, N, K, inner;
     int spc;                    // samples per CTA; <= 0 picks a default
+    // Slab mode: only blocks kb0 .. kb0 + kbn - 1 along K are updated (kbn == 0: all of them). Tile
+    // cells in the columns outside that range are read like any other cell, so they can carry a
+    // neighbour slab's boundary face.
+    int kb0, kbn;
 };
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize);
 int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st);

@@ -73,9 +73,9 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS) step_fwd_fast
 
     const int tid = threadIdx.x;
     const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
-    const int nbx = p.K >> 3, nby = p.N >> 3;
+    const int nbx = p.kbn, nby = p.N >> 3;  // blocks along K that this launch updates
     const unsigned blk = blockIdx.x;
-    const int bx = blk % nbx, by = (blk / nbx) % nby, bz = blk / nbx / nby;
+    const int bx = p.kb0 + blk % nbx, by = (blk / nbx) % nby, bz = blk / nbx / nby;
     const size_t P = (size_t)p.M * p.N * p.K;
     const int K = p.K;
     const size_t g00 = ((size_t)(bz * 8 + z) * p.N + (by * 8 + 2 * yp)) * K + (bx * 8 + 2 * xp);
@@ -285,7 +285,11 @@ int fast8_default_spc(int B, long long nbricks)
 
 int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
 {
-    const long long nb = (long long)(p.M / 8) * (p.N / 8) * (p.K / 8);
+    if (p.kbn <= 0) {
+        p.kb0 = 0;
+        p.kbn = p.K / 8;
+    }
+    const long long nb = (long long)(p.M / 8) * (p.N / 8) * p.kbn;
     if (p.spc <= 0) p.spc = fast8_default_spc(p.B, nb);
     dim3 grid((unsigned)nb, (unsigned)((p.B + p.spc - 1) / p.spc));
     const bool fin = p.in_stats != nullptr, sout = p.out_partials != nullptr;

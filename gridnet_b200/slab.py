@@ -1,0 +1,229 @@
+"""Slab-sharded inference loop: one grid split along K (the last, information-flow axis)
+across ranks, one rank per GPU.
+
+The reference is single-GPU; this is the multi-GPU form of its model loop
+(gridnet/scripts/train_mnist.py:62-64) for grids too large or too slow for one device.
+Every rank owns ``K / world`` consecutive K-columns of the activations and of every
+parameter. Per outer step there is exactly one exchange:
+
+* each rank's boundary faces ``[B, M, N]`` go to its two neighbours (send/recv), landing in
+  the receiver's OWN memory as ghost columns that the step kernel reads like any halo cell;
+* the per-sample (sum, sum of squares) of the step's raw output are all-reduced, because the
+  LayerNorm between steps spans the whole grid.
+
+Local layout: ``[..., 8 + K_loc + 8]`` — one ghost block of 8 columns on each side keeps
+block alignment; only ghost column 7 (left) and ``8 + K_loc`` (right) are ever read.
+
+The arithmetic is delegated to a backend object so that the orchestration can be exercised
+on CPU ranks (gloo) with a checker backend in the tests; :class:`CudaSlabBackend` is the
+product backend and calls the C ABI (``gn_step_forward_slab_f32`` and friends).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+GHOST = 8
+
+
+@dataclass(frozen=True)
+class SlabLayout:
+    K: int
+    world: int
+    rank: int
+
+    def __post_init__(self):
+        assert self.world >= 1 and 0 <= self.rank < self.world
+        assert self.K % (8 * self.world) == 0, f"K={self.K} must be a multiple of 8 * world={8 * self.world}"
+
+    @property
+    def k_loc(self) -> int:
+        return self.K // self.world
+
+    @property
+    def k0(self) -> int:
+        return self.rank * self.k_loc
+
+    @property
+    def k_pad(self) -> int:
+        return self.k_loc + 2 * GHOST
+
+    @property
+    def left(self):
+        return self.rank - 1 if self.rank > 0 else None
+
+    @property
+    def right(self):
+        return self.rank + 1 if self.rank + 1 < self.world else None
+
+    def shard(self, full: torch.Tensor, with_ghost_faces: bool = True) -> torch.Tensor:
+        """``[..., K]`` -> this rank's padded slab ``[..., k_pad]`` (ghost columns zero, or the
+        neighbours' adjacent columns when ``with_ghost_faces``)."""
+        out = full.new_zeros(*full.shape[:-1], self.k_pad)
+        out[..., GHOST:GHOST + self.k_loc] = full[..., self.k0:self.k0 + self.k_loc]
+        if with_ghost_faces:
+            if self.k0 > 0:
+                out[..., GHOST - 1] = full[..., self.k0 - 1]
+            if self.k0 + self.k_loc < self.K:
+                out[..., GHOST + self.k_loc] = full[..., self.k0 + self.k_loc]
+        return out.contiguous()
+
+    def real(self, padded: torch.Tensor) -> torch.Tensor:
+        return padded[..., GHOST:GHOST + self.k_loc]
+
+    # boundary faces of a padded slab (contiguous copies, ready to send)
+    def face_to_left(self, padded):
+        return padded[..., GHOST].contiguous()
+
+    def face_to_right(self, padded):
+        return padded[..., GHOST + self.k_loc - 1].contiguous()
+
+    def put_from_left(self, padded, face):
+        padded[..., GHOST - 1] = face
+
+    def put_from_right(self, padded, face):
+        padded[..., GHOST + self.k_loc] = face
+
+
+class CudaSlabBackend:
+    """Runs the local arithmetic of one rank through the C ABI (float32, block 8, normalize off)."""
+
+    def __init__(self, layout: SlabLayout, weight, bias, scale, gamma, beta, inner: int, activation: str = "silu",
+                 ln_eps: float = 1e-5):
+        from ._lib import activation_id, check, lib
+
+        self.lib, self.check = lib, check
+        self.layout = layout
+        for t in (weight, bias, scale, gamma, beta):
+            assert t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.shape[-1] == layout.k_pad
+        self.w, self.b, self.s, self.gamma, self.beta = weight, bias, scale, gamma, beta
+        self.inner, self.act, self.ln_eps = int(inner), activation_id(activation), float(ln_eps)
+        self.M, self.N = bias.shape[0], bias.shape[1]
+        self.nparts = 4 * (self.M // 8) * (self.N // 8) * (layout.k_loc // 8)
+        self._partials = None
+
+    def _stream(self):
+        return torch.cuda.current_stream().cuda_stream
+
+    def step(self, x, y, in_stats):
+        """y[real blocks] = step(x) with x normalised on load when ``in_stats`` is given; returns the
+        local per-sample (sum, sum of squares) of what was written, ``[B, 2]`` float64."""
+        B = x.shape[0]
+        if self._partials is None or self._partials.shape[0] != B:
+            self._partials = torch.empty(B, self.nparts, 2, dtype=torch.float64, device=x.device)
+        lay = self.layout
+        self.check(self.lib.gn_step_forward_slab_f32(
+            self.w.data_ptr(), self.b.data_ptr(), self.s.data_ptr(), x.data_ptr(), y.data_ptr(),
+            self.gamma.data_ptr(), self.beta.data_ptr(), None if in_stats is None else in_stats.data_ptr(),
+            self._partials.data_ptr(), B, self.M, self.N, lay.k_pad, 1, lay.k_loc // 8, self.inner, self.act,
+            self._stream()))
+        return self._partials.sum(1)
+
+    def finalize(self, sums, count: int):
+        """Global ``[B, 2]`` float64 sums over ``count`` values per sample -> ``[B, 2]`` (mean, rstd)."""
+        B = sums.shape[0]
+        stats = torch.empty(B, 2, dtype=torch.float32, device=sums.device)
+        sums = sums.contiguous()
+        self.check(self.lib.gn_norm_finalize_f32(sums.data_ptr(), 1, stats.data_ptr(), B, int(count), self.ln_eps,
+                                                 self._stream()))
+        return stats
+
+    def apply(self, x, stats, y):
+        B, P = x.shape[0], x[0].numel()
+        self.check(self.lib.gn_norm_apply_f32(x.data_ptr(), self.gamma.data_ptr(), self.beta.data_ptr(),
+                                              stats.data_ptr(), y.data_ptr(), B, P, self._stream()))
+        return y
+
+
+class SlabRunner:
+    """State machine of one rank; the communication between its calls is done by a driver
+    (:func:`run_distributed` over torch.distributed, or an in-process emulation in tests)."""
+
+    def __init__(self, layout: SlabLayout, backend, x_padded: torch.Tensor, grid_size: int):
+        self.layout, self.backend = layout, backend
+        self.grid_size = int(grid_size)  # M * N * K of the WHOLE grid
+        self.bufs = [x_padded, torch.zeros_like(x_padded), torch.zeros_like(x_padded)]
+        self.cur = 0          # index of the buffer holding the current (raw) activations
+        self.stats = None     # (mean, rstd) of the current buffer when it is a raw step output
+
+    def compute(self):
+        """One step on the current buffer; returns the local sums to be all-reduced."""
+        nxt = 1 if self.cur != 1 else 2
+        sums = self.backend.step(self.bufs[self.cur], self.bufs[nxt], self.stats)
+        self.cur = nxt
+        return sums
+
+    def faces_out(self):
+        b = self.bufs[self.cur]
+        return self.layout.face_to_left(b), self.layout.face_to_right(b)
+
+    def faces_in(self, from_left, from_right):
+        b = self.bufs[self.cur]
+        if from_left is not None:
+            self.layout.put_from_left(b, from_left)
+        if from_right is not None:
+            self.layout.put_from_right(b, from_right)
+
+    def set_global_sums(self, sums):
+        self.stats = self.backend.finalize(sums, self.grid_size)
+
+    def result(self):
+        """Normalised output of the last step, ``[B, M, N, K_loc]`` (real columns only)."""
+        src = self.bufs[self.cur]
+        out = torch.empty_like(src)
+        self.backend.apply(src, self.stats, out)
+        return self.layout.real(out).contiguous()
+
+
+def run_distributed(runner: SlabRunner, outer: int, group=None) -> torch.Tensor:
+    """Drive one rank's :class:`SlabRunner` for ``outer`` steps over torch.distributed
+    (NCCL on GPUs, gloo on CPU): grouped send/recv of the two faces, all-reduce of the sums."""
+    import torch.distributed as dist
+
+    lay = runner.layout
+    for _ in range(outer):
+        sums = runner.compute()
+        to_left, to_right = runner.faces_out()
+        from_left = torch.empty_like(to_left) if lay.left is not None else None
+        from_right = torch.empty_like(to_right) if lay.right is not None else None
+        ops = []
+        if lay.left is not None:
+            ops += [dist.P2POp(dist.isend, to_left, lay.left, group), dist.P2POp(dist.irecv, from_left, lay.left, group)]
+        if lay.right is not None:
+            ops += [dist.P2POp(dist.isend, to_right, lay.right, group),
+                    dist.P2POp(dist.irecv, from_right, lay.right, group)]
+        reqs = dist.batch_isend_irecv(ops) if ops else []
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
+        for r in reqs:
+            r.wait()
+        runner.faces_in(from_left, from_right)
+        runner.set_global_sums(sums)
+    return runner.result()
+
+
+def run_emulated(runners, outer: int):
+    """All ranks in one process, taking turns (for single-GPU tests): same data movement as
+    :func:`run_distributed`, with tensor copies in place of the collectives."""
+    world = len(runners)
+    for _ in range(outer):
+        sums = [r.compute() for r in runners]
+        faces = [r.faces_out() for r in runners]
+        total = torch.stack(sums).sum(0)
+        for i, r in enumerate(runners):
+            from_left = faces[i - 1][1] if i > 0 else None
+            from_right = faces[i + 1][0] if i + 1 < world else None
+            r.faces_in(from_left, from_right)
+            r.set_global_sums(total.clone())
+    return [r.result() for r in runners]
+
+
+def make_cuda_runner(layout: SlabLayout, weight, bias, scale, gamma, beta, x, inner: int, activation: str = "silu",
+                     ln_eps: float = 1e-5, device=None) -> SlabRunner:
+    """Shard FULL tensors (any device) for this rank and build its runner on ``device``."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    sh = lambda t, ghost: layout.shard(t, ghost).to(device)
+    backend = CudaSlabBackend(layout, sh(weight, False), sh(bias, False), sh(scale, False), sh(gamma, True),
+                              sh(beta, True), inner, activation, ln_eps)
+    M, N, K = bias.shape
+    return SlabRunner(layout, backend, sh(x, True), M * N * K)

@@ -167,6 +167,19 @@ GN_API int gn_step_forward_fused_f32(const float *weight, const float *bias, con
                               const float *x, float *y, const float *gamma, const float *beta,
                               const float *in_mean_rstd, double *out_partials, int B, int M,
                               int N, int K, int inner, int block, int activation, void *stream);
+/* Slab form of gn_step_forward_fused_f32 for a grid that is split along K across GPUs. The
+ * arrays have the usual layout with K = the local width INCLUDING one ghost block of 8 columns
+ * on each side that is not updated; only blocks k_block_first .. k_block_first + k_block_count - 1
+ * (in units of 8 columns) are computed and written. The last column of the left ghost block and the
+ * first column of the right ghost block carry the neighbours' boundary faces (zeros at the ends of
+ * the grid) and are read as ordinary halo cells. out_partials holds
+ * 4 * (M/8) * (N/8) * k_block_count pairs per sample. No counterpart in the reference (it is
+ * single-GPU). */
+GN_API int gn_step_forward_slab_f32(const float *weight, const float *bias, const float *scale,
+                             const float *x, float *y, const float *gamma, const float *beta,
+                             const float *in_mean_rstd, double *out_partials, int B, int M, int N,
+                             int K, int k_block_first, int k_block_count, int inner,
+                             int activation, void *stream);
 GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_rstd, int B,
                          long long P, float eps, void *stream);
 GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *beta,

@@ -1,0 +1,113 @@
+"""Slab sharding along K (gridnet_b200/slab.py): R ranks must reproduce the single-device
+model loop. CPU: the orchestration under gloo (world size 2) and emulated (world 4) with the
+oracle doing the local arithmetic. GPU: the CUDA backend, ranks emulated on one device."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gridnet_oracle as orc
+
+from gridnet_b200.slab import SlabLayout, SlabRunner, run_distributed, run_emulated
+from slab_checker_backend import OracleSlabBackend
+
+
+def problem(seed, B, shape):
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)
+    w = rn(27, *shape) / 27 ** 0.5
+    b = 0.1 * rn(*shape)
+    s = 1 + 0.1 * rn(*shape)
+    gamma = 1 + 0.1 * rn(*shape)
+    beta = 0.1 * rn(*shape)
+    x = torch.zeros(B, *shape, dtype=torch.float64)
+    x[..., 0] = rn(B, *shape[:2])
+    x[..., shape[2] // 2] = 0.5 * rn(B, *shape[:2])  # something on an interior slab boundary too
+    return w, b, s, gamma, beta, x
+
+
+def oracle_runner(layout, prob, inner):
+    w, b, s, gamma, beta, x = prob
+    sh = layout.shard
+    be = OracleSlabBackend(layout, sh(w, False), sh(b, False), sh(s, False), sh(gamma, True), sh(beta, True), inner)
+    return SlabRunner(layout, be, sh(x, True), b.numel())
+
+
+def test_layout_shard_and_faces():
+    full = torch.arange(2 * 3 * 32, dtype=torch.float32).reshape(2, 3, 32)
+    for world in (1, 2, 4):
+        parts = []
+        for r in range(world):
+            lay = SlabLayout(32, world, r)
+            p = lay.shard(full)
+            assert p.shape[-1] == lay.k_loc + 16
+            parts.append(lay.real(p))
+            if lay.left is not None:
+                assert torch.equal(p[..., 7], full[..., lay.k0 - 1])
+            else:
+                assert (p[..., :8] == 0).all()
+            if lay.right is not None:
+                assert torch.equal(p[..., 8 + lay.k_loc], full[..., lay.k0 + lay.k_loc])
+            assert torch.equal(lay.face_to_left(p), full[..., lay.k0])
+            assert torch.equal(lay.face_to_right(p), full[..., lay.k0 + lay.k_loc - 1])
+        assert torch.equal(torch.cat(parts, -1), full)
+    with pytest.raises(AssertionError):
+        SlabLayout(24, 2, 0)  # slabs must be whole blocks
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_emulated_ranks_match_single_grid_oracle(world):
+    shape, B, inner, outer = (8, 8, 32), 2, 2, 3
+    prob = problem(30, B, shape)
+    want = orc.outer_forward(*(t.numpy() for t in prob), inner, outer, 8)
+    runners = [oracle_runner(SlabLayout(shape[2], world, r), prob, inner) for r in range(world)]
+    got = torch.cat(run_emulated(runners, outer), -1).numpy()
+    assert np.abs(got - want).max() < 1e-10 * (1 + np.abs(want).max())
+
+
+def _gloo_worker(rank, world, port, tmpdir):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        shape, B, inner, outer = (8, 8, 32), 2, 2, 3
+        runner = oracle_runner(SlabLayout(shape[2], world, rank), problem(31, B, shape), inner)
+        out = run_distributed(runner, outer)
+        np.save(os.path.join(tmpdir, f"out{rank}.npy"), out.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_match_single_grid_oracle():
+    import torch.multiprocessing as mp
+
+    world = 2
+    port = 29600 + os.getpid() % 300
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_gloo_worker, args=(world, port, tmp), nprocs=world, join=True)
+        got = np.concatenate([np.load(os.path.join(tmp, f"out{r}.npy")) for r in range(world)], -1)
+    shape, B, inner, outer = (8, 8, 32), 2, 2, 3
+    want = orc.outer_forward(*(t.numpy() for t in problem(31, B, shape)), inner, outer, 8)
+    assert np.abs(got - want).max() < 1e-10 * (1 + np.abs(want).max())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,shape", [(2, (16, 16, 32)), (4, (8, 16, 64)), (1, (16, 8, 16))])
+def test_cuda_slabs_match_single_device(world, shape):
+    import gridnet_b200 as gb
+    from gridnet_b200.slab import make_cuda_runner
+
+    B, inner, outer = 3, 2, 4
+    prob = [t.float() for t in problem(32, B, shape)]
+    w, b, s, gamma, beta, x = prob
+    runners = [make_cuda_runner(SlabLayout(shape[2], world, r), w, b, s, gamma, beta, x, inner) for r in range(world)]
+    got = torch.cat(run_emulated(runners, outer), -1)
+    single = gb.outer_forward(*(t.cuda() for t in prob), inner, outer, 8)
+    assert torch.allclose(got, single, rtol=1e-5, atol=1e-6), (got - single).abs().max().item()
+    want = orc.outer_forward(*(t.double().numpy() for t in prob), inner, outer, 8)
+    err = np.abs(got.cpu().numpy() - want)
+    assert (err <= 1e-5 + 1e-4 * np.abs(want)).all(), err.max()
