@@ -20,6 +20,7 @@ SIGNATURES = {
     "gn_last_cuda_error": (c_char_p, []),
     "gn_activation_from_name": (c_int, [c_char_p]),
     "gn_version": (c_int, []),
+    "gn_config_set": (c_int, [c_char_p, c_int]),
     "gn_step_forward_f32": (c_int, [_P] * 5 + _geom + [c_int, c_int, c_float, c_int, c_int, _P]),
     "gn_step_forward_f64": (c_int, [_P] * 5 + _geom + [c_int, c_int, c_double, c_int, c_int, _P]),
     "gn_step_backward_f32": (c_int, [_P] * 9 + _geom + [c_int, c_int, c_float, c_int, c_int, _P]),

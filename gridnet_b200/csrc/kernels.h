@@ -39,6 +39,23 @@ struct FastFwdParams {
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize);
 int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st);
 
+// ---- step_lanes.cu ("lanes = samples" kernel of the fused loop; activations in the IL16 layout
+// [group][z][y][x][16 samples])
+struct LanesStep {
+    const float *w, *b, *s, *gamma, *beta;
+    const float *in_il16;
+    float *out_il16;
+    const float2 *in_stats;   // [G*16] or nullptr
+    double2 *out_partials;    // [G*16][blocks] or nullptr
+    int *error_flag;          // device int, set when a bounded wait gave up
+    int M, N, K, G, inner;
+};
+bool lanes16_applicable(int M, int N, int K, int block, int inner, const void *w, const void *b, const void *s);
+int launch_step_fwd_lanes16(const LanesStep &a, int act, cudaStream_t st);
+int launch_to_il16(const float *x, float *il, int B, int G, long long P, cudaStream_t st);
+int launch_norm_apply_from_il16(const float *il, const float2 *stats, const float *gamma, const float *beta, float *y,
+                                int B, int G, long long P, cudaStream_t st);
+
 // ---- norm.cu
 constexpr int kNormMaxParts = 64;
 // per-sample (sum, sum of squares) of x in double, `parts` slices per sample

@@ -44,7 +44,10 @@ constexpr int PS = 10 * RS;     // plane stride
 constexpr int TS = 10 * PS;     // one tile
 constexpr int THREADS = 128;
 constexpr int SPS = 1;          // samples per pipeline stage (2 measured slower: the prefetch registers crowd out the stencil)
-constexpr int MIN_CTAS = 3;     // CTAs per SM the register budget is sized for (168 registers per thread)
+#ifndef GN_F8_MIN_CTAS
+#define GN_F8_MIN_CTAS 3
+#endif
+constexpr int MIN_CTAS = GN_F8_MIN_CTAS;     // CTAs per SM the register budget is sized for (168 registers per thread)
 constexpr int SLOTS = 8;        // tile cells handled per thread when loading (8 * 128 >= 1000)
 // Per-slot descriptor, one register: bits 0..10 tile offset, bit 11 = halo cell (kept in both
 // ping-pong tiles), bits 12..31 global offset relative to the tile's origin cell.

@@ -67,6 +67,11 @@ GN_API const char *gn_last_cuda_error(void);
 /* -1 for an unknown name */
 GN_API int gn_activation_from_name(const char *name);
 GN_API int gn_version(void);
+/* Process-wide tuning switches (not needed for normal use). Keys:
+ *   "outer_kernel": which step kernel gn_outer_forward_f32 uses: 0 = automatic (default),
+ *                   1 = the register-patch kernel, 2 = the lanes-of-samples kernel
+ *                   (GN_ERR_UNSUPPORTED from gn_outer_forward_f32 when it does not apply). */
+GN_API int gn_config_set(const char *key, int value);
 
 /* ------------------------------------------------------------------ plain step
  * Replaces gridnet_cuda.forward (src/gridnet_cuda.cpp:61-89 ->
@@ -192,7 +197,9 @@ GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *be
  * per-sample statistics of what it writes, and the next step applies
  * (x - mean) * rstd * gamma + beta while it loads its tiles; only the last
  * step's output is normalised by a separate kernel into y.
- * workspace: two [B,M,N,K] float buffers plus the statistics partials. */
+ * workspace: two [B rounded up to 16, M,N,K] float buffers plus the statistics partials.
+ * (With the optional lanes-of-samples kernel, gn_config_set("outer_kernel", 2), the activations
+ * are kept interleaved by groups of 16 samples between steps, [group][M][N][K][16], and read by TMA.) */
 GN_API size_t gn_outer_forward_workspace_bytes(int B, int M, int N, int K, int block);
 GN_API int gn_outer_forward_f32(const float *weight, const float *bias, const float *scale,
                          const float *gamma, const float *beta, const float *x, float *y,

@@ -155,3 +155,25 @@ def test_full_size_properties_c2():
     ref64 = orc.outer_forward(*a64, x64, inner, outer, bs)
     ref32 = orc.outer_forward(*(a.astype(np.float32) for a in a64), x64.astype(np.float32), inner, outer, bs)
     assert_close(y[idx].cpu().numpy(), ref64, ref32, "C2 full size, sampled rows")
+
+
+def test_lanes_kernel_matches_patch_kernel_and_oracle():
+    """The optional lanes-of-samples step kernel (TMA tiles, activations interleaved by 16 samples)
+    must give the same fused loop as the default kernel; odd batch sizes exercise the zero-padded
+    last group."""
+    from gridnet_b200 import outer_forward
+    from gridnet_b200._lib import lib
+
+    for B, shape, inner, outer in ((5, (16, 16, 16), 2, 3), (33, (8, 16, 24), 3, 2), (16, (32, 32, 32), 1, 2)):
+        w, b, s, gamma, beta = model_params(27, shape)
+        x = face_input(28, B, shape)
+        args = [dev(a) for a in (w, b, s, gamma, beta, x)]
+        base = outer_forward(*args, inner, outer, 8)
+        try:
+            assert lib.gn_config_set(b"outer_kernel", 2) == 0
+            got = outer_forward(*args, inner, outer, 8)
+        finally:
+            lib.gn_config_set(b"outer_kernel", 0)
+        assert torch.allclose(got, base, rtol=1e-5, atol=1e-6), (got - base).abs().max().item()
+        a64 = [a.astype(np.float64) for a in (w, b, s, gamma, beta, x)]
+        assert_close(got.cpu().numpy(), orc.outer_forward(*a64, inner, outer, 8), None, f"lanes kernel B={B}")
