@@ -8,14 +8,25 @@ native extension module. Everything runs through ``libgridnet_b200.so`` (C ABI i
 """
 from . import gridnet_cuda
 from ._lib import LIB_PATH, GridnetB200Error
-from .backend_cuda import (GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, fused_step, norm_apply,
+from .backend_cuda import (GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, HostPipelinedForward, fused_step, norm_apply,
                            norm_finalize, outer_forward, outer_forward_workspace, step_stats_partials)
 
+from .modules import (GatedGridnet, Gridnet, GridnetModel, GridNorm, Readout, gated_gridnet_step,
+                      gridnet_step)
+
 __all__ = [
+    "Gridnet",
+    "GatedGridnet",
+    "GridNorm",
+    "Readout",
+    "GridnetModel",
+    "gridnet_step",
+    "gated_gridnet_step",
     "GridnetCudaOp",
     "GatedGridnetCudaOp",
     "GridNormOp",
     "outer_forward",
+    "HostPipelinedForward",
     "outer_forward_workspace",
     "fused_step",
     "norm_finalize",

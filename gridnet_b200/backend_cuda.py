@@ -231,3 +231,61 @@ def norm_apply(x, norm_weight, norm_bias, mean_rstd, out) -> torch.Tensor:
                                     mean_rstd.data_ptr(), out.data_ptr(), B, P,
                                     torch.cuda.current_stream().cuda_stream))
     return out
+
+
+class HostPipelinedForward:
+    """The fused inference loop for batches that live in (pinned) HOST memory.
+
+    ``submit(host_x, host_y)`` queues host->device copy, :func:`outer_forward` and device->host
+    copy of one batch on three streams with ``depth`` device buffer sets, so the copies of one
+    batch overlap the compute of its neighbours; ``synchronize()`` waits for everything queued.
+    ``host_x`` / ``host_y`` are ``[B, M, N, K]`` float32 CPU tensors (pinned for real overlap).
+    """
+
+    def __init__(self, weight, bias, residual_scale, norm_weight, norm_bias, batch: int, inner_iters: int,
+                 outer_iters: int, block_size: int, activation: str = "silu", ln_eps: float = 1e-5, depth: int = 2):
+        self.params = (weight, bias, residual_scale, norm_weight, norm_bias)
+        self.cfg = (int(inner_iters), int(outer_iters), int(block_size), activation, float(ln_eps))
+        dev = weight.device
+        shape = tuple(bias.shape)
+        self.device = dev
+        self.depth = depth
+        self.dx = [torch.empty(batch, *shape, device=dev) for _ in range(depth)]
+        self.dy = [torch.empty(batch, *shape, device=dev) for _ in range(depth)]
+        self.ws = outer_forward_workspace(batch, shape, block_size, dev)
+        self.s_in, self.s_compute, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        self.ev_in = [torch.cuda.Event() for _ in range(depth)]
+        self.ev_compute = [torch.cuda.Event() for _ in range(depth)]
+        self.ev_out = [torch.cuda.Event() for _ in range(depth)]
+        self.count = 0
+        torch.cuda.synchronize(dev)
+
+    def submit(self, host_x: torch.Tensor, host_y: torch.Tensor) -> None:
+        j = self.count % self.depth
+        reuse = self.count >= self.depth
+        self.count += 1
+        inner, outer, block, act, eps = self.cfg
+        if reuse:  # buffer set j is free once its previous result has left the device
+            self.s_in.wait_event(self.ev_out[j])
+            self.s_compute.wait_event(self.ev_out[j])
+        with torch.cuda.stream(self.s_in):
+            self.dx[j].copy_(host_x, non_blocking=True)
+            self.ev_in[j].record(self.s_in)
+        self.s_compute.wait_event(self.ev_in[j])
+        with torch.cuda.stream(self.s_compute):
+            outer_forward(*self.params, self.dx[j], inner, outer, block, act, eps, out=self.dy[j], workspace=self.ws)
+            self.ev_compute[j].record(self.s_compute)
+        self.s_out.wait_event(self.ev_compute[j])
+        with torch.cuda.stream(self.s_out):
+            host_y.copy_(self.dy[j], non_blocking=True)
+            self.ev_out[j].record(self.s_out)
+
+    def join(self, stream=None) -> None:
+        """Make ``stream`` (default: the current stream) wait for everything queued so far."""
+        stream = stream or torch.cuda.current_stream(self.device)
+        for ev in self.ev_out[: min(self.count, self.depth)]:
+            stream.wait_event(ev)
+
+    def synchronize(self) -> None:
+        for s in (self.s_in, self.s_compute, self.s_out):
+            s.synchronize()
