@@ -35,6 +35,7 @@ struct FastFwdParams {
     // cells in the columns outside that range are read like any other cell, so they can carry a
     // neighbour slab's boundary face.
     int kb0, kbn;
+    int *error_flag;            // optional device int, set to 1 if a bounded wait on a bulk copy gave up
 };
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize);
 int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st);

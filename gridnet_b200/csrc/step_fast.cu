@@ -33,8 +33,11 @@
 //
 // Reference semantics: gridnet/backend_torch.py:61-142; the kernel it stands in
 // for is gridnet_cuda_forward_kernel, src/gridnet_cuda_kernels.cu:101-200.
+#include <string.h>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "tma.cuh"
 
 namespace gn {
 
@@ -43,11 +46,12 @@ constexpr int RS = 12;          // row stride (floats)
 constexpr int PS = 10 * RS;     // plane stride
 constexpr int TS = 10 * PS;     // one tile
 constexpr int THREADS = 128;
-constexpr int SPS = 1;          // samples per pipeline stage (2 measured slower: the prefetch registers crowd out the stencil)
 #ifndef GN_F8_MIN_CTAS
 #define GN_F8_MIN_CTAS 3
 #endif
 constexpr int MIN_CTAS = GN_F8_MIN_CTAS;     // CTAs per SM the register budget is sized for (168 registers per thread)
+constexpr int STG = 10 * 10 * 16;  // floats of one TMA staging buffer
+constexpr unsigned kSpinLimit = 1u << 18;
 constexpr int SLOTS = 8;        // tile cells handled per thread when loading (8 * 128 >= 1000)
 // Per-slot descriptor, one register: bits 0..10 tile offset, bit 11 = halo cell (kept in both
 // ping-pong tiles), bits 12..31 global offset relative to the tile's origin cell.
@@ -67,11 +71,15 @@ __device__ __forceinline__ float ld_pinned(const float *ptr)
     return v;
 }
 
-template <int ACT, bool FUSE_IN, bool STATS_OUT>
-__global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS) step_fwd_fast8(const FastFwdParams p)
+template <int ACT, bool FUSE_IN, bool STATS_OUT, bool USE_TMA>
+__global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
+    step_fwd_fast8(const __grid_constant__ CUtensorMap x_map, const FastFwdParams p)
 {
     using namespace fast8;
-    __shared__ __align__(16) float tiles[2][SPS][TS];
+    __shared__ __align__(16) float tiles[2][2][TS];  // [sample parity][ping-pong]
+    // USE_TMA: raw 10x10 rows of 16 floats (x from 8*bx - 4, the nearest origin TMA accepts), two samples deep
+    __shared__ __align__(128) float staging[USE_TMA ? 2 : 1][USE_TMA ? STG : 4];
+    __shared__ __align__(8) unsigned long long bars[2];
     __shared__ float2 gbtab[FUSE_IN ? SLOTS * THREADS : 1];  // (gamma, beta) per tile cell
 
     const int tid = threadIdx.x;
@@ -97,15 +105,20 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS) step_fwd_fast
             const int gz = bz * 8 + cz - 1, gy = by * 8 + cy - 1, gx = bx * 8 + cx - 1;
             const int soff = cz * PS + cy * RS + cx;
             const bool halo = cx == 0 || cx == 9 || cy == 0 || cy == 9 || cz == 0 || cz == 9;
-            if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K) {
-                const int rel = (cz * p.N + cy) * K + cx;
+            const bool inside = gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K;
+            const int rel = (cz * p.N + cy) * K + cx;
+            if (inside && FUSE_IN) gb = make_float2(p.gamma[origin + rel], p.beta[origin + rel]);
+            if (USE_TMA) {
+                // every cell is copied from the staging buffer; TMA has zero-filled what lies outside the
+                // grid, and gamma = beta = 0 there keeps it zero through the normalisation
+                ci = (unsigned)soff | (halo ? 0x800u : 0u) | ((unsigned)((cz * 10 + cy) * 16 + cx + 3) << 12);
+            } else if (inside) {
                 ci = (unsigned)soff | (halo ? 0x800u : 0u) | ((unsigned)rel << 12);
-                if (FUSE_IN) gb = make_float2(p.gamma[origin + rel], p.beta[origin + rel]);
             } else {
                 ci = kOutside;
                 // cells outside the grid stay zero for the CTA's whole life
 #pragma unroll
-                for (int q = 0; q < 2 * SPS; ++q) (&tiles[0][0][0])[q * TS + soff] = 0.0f;
+                for (int q = 0; q < 4; ++q) (&tiles[0][0][0])[q * TS + soff] = 0.0f;
             }
         }
         cinfo[j] = ci;
@@ -135,135 +148,160 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS) step_fwd_fast
 
     const int s0 = blockIdx.y * p.spc;
     const int s1 = min(p.B, s0 + p.spc);
-    const int nstages = (s1 - s0 + SPS - 1) / SPS;
     const int toff = z * PS + 2 * yp * RS + 2 * xp;  // window origin of this thread inside a tile
 
-    // global -> registers for one stage; consumed by commit() one stage later
-    float pf[SPS][SLOTS];
-    auto prefetch = [&](int st) {
-#pragma unroll
-        for (int s = 0; s < SPS; ++s) {
-            const int smp = s0 + st * SPS + s;
-            if (smp < s1) {
+    // Software pipeline over the CTA's samples: while sample i iterates on tile set i & 1, the cells
+    // of sample i + 1 (fetched into registers during sample i - 1) are normalised and written into the
+    // other tile set, and the loads of sample i + 2 are issued. One barrier ends each sample: it
+    // publishes the next sample's tiles and retires the current ones.
+    float pf[USE_TMA ? 1 : SLOTS];
+    float2 pf_mr = make_float2(0.0f, 1.0f);  // (mean, rstd) of the sample that commit() handles next
+    const unsigned bar_base = smem_u32(bars);
+    // start the fetch of one sample: a bulk tensor copy into the staging ring (USE_TMA) or loads into
+    // registers
+    auto prefetch = [&](int smp) {
+        if (smp < s1) {
+            if (USE_TMA) {
+                if (tid == 0) {
+                    const int par = (smp - s0) & 1;
+                    mbar_expect_tx(bar_base + 8 * par, STG * 4);
+                    tma_load_4d(smem_u32(staging[par]), &x_map, bar_base + 8 * par, bx * 8 - 4, by * 8 - 1, bz * 8 - 1,
+                                smp);
+                }
+            } else {
                 const float *xs = p.x + (size_t)smp * P + origin;
 #pragma unroll
                 for (int j = 0; j < SLOTS; ++j)
-                    if (cinfo[j] < kFirstSpecial) pf[s][j] = ld_pinned(xs + (cinfo[j] >> 12));
+                    if (cinfo[j] < kFirstSpecial) pf[j] = ld_pinned(xs + (cinfo[j] >> 12));
             }
         }
     };
-    // registers -> tiles, normalising on the way when the input is a raw step output
-    auto commit = [&](int st) {
+    // fetched cells -> tile set `set`, normalising on the way when the input is a raw step output
+    auto commit = [&](int smp, int set) {
+        if (smp < s1) {
+            const float2 mr = pf_mr;
+            const int par = (smp - s0) & 1;
+            if (USE_TMA) {
+                if (!mbar_wait_bounded(bar_base + 8 * par, ((smp - s0) >> 1) & 1, kSpinLimit) && p.error_flag)
+                    *p.error_flag = 1;
+            }
 #pragma unroll
-        for (int s = 0; s < SPS; ++s) {
-            const int smp = s0 + st * SPS + s;
-            if (smp < s1) {
-                float2 mr = make_float2(0.0f, 1.0f);
-                if (FUSE_IN) mr = p.in_stats[smp];
-#pragma unroll
-                for (int j = 0; j < SLOTS; ++j) {
-                    const unsigned ci = cinfo[j];
-                    if (ci < kFirstSpecial) {
-                        float v = pf[s][j];
-                        if (FUSE_IN) {
-                            const float2 gb = gbtab[tid + j * THREADS];
-                            v = fmaf((v - mr.x) * mr.y, gb.x, gb.y);
-                        }
-                        tiles[0][s][ci & 0x7ff] = v;
-                        if (ci & 0x800) tiles[1][s][ci & 0x7ff] = v;
+            for (int j = 0; j < SLOTS; ++j) {
+                const unsigned ci = cinfo[j];
+                if (ci < kFirstSpecial) {
+                    float v = USE_TMA ? staging[par][ci >> 12] : pf[j];
+                    if (FUSE_IN) {
+                        const float2 gb = gbtab[tid + j * THREADS];
+                        v = fmaf((v - mr.x) * mr.y, gb.x, gb.y);
                     }
+                    tiles[set][0][ci & 0x7ff] = v;
+                    if (ci & 0x800) tiles[set][1][ci & 0x7ff] = v;
                 }
             }
         }
     };
+    auto load_stats = [&](int smp) {
+        if (FUSE_IN && smp < s1) pf_mr = p.in_stats[smp];
+    };
 
-    if (nstages > 0) prefetch(0);
-
-    for (int st = 0; st < nstages; ++st) {
-        const int smp0 = s0 + st * SPS;
-        __syncthreads();  // the previous stage no longer reads the tiles (and the zero fill is done)
-        commit(st);
+    if (USE_TMA) {
+        if (tid == 0) {
+            mbar_init(bar_base, 1);
+            mbar_init(bar_base + 8, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            fence_proxy_async();
+        }
         __syncthreads();
-        if (st + 1 < nstages) prefetch(st + 1);
+        prefetch(s0);
+        prefetch(s0 + 1);
+    } else {
+        prefetch(s0);
+    }
+    load_stats(s0);
+    __syncthreads();  // zero fill and gamma/beta table are in place
+    commit(s0, 0);
+    if (!USE_TMA) prefetch(s0 + 1);
+    load_stats(s0 + 1);
+    __syncthreads();
 
-        const int inner = p.inner;
+    const int inner = p.inner;
+    for (int smp = s0; smp < s1; ++smp) {
+        const int set = (smp - s0) & 1;
+        // TMA: the staging buffer of THIS sample was consumed a whole sample ago (a barrier has passed),
+        // so the copy for sample smp + 2 can start now; registers: they are free once smp + 1 is committed
+        if (USE_TMA) prefetch(smp + 2);
+        commit(smp + 1, set ^ 1);
+        if (!USE_TMA) prefetch(smp + 2);
+        load_stats(smp + 2);
         for (int it = 0; it < inner; ++it) {
             const bool last = it + 1 == inner;
             const int cur = it & 1;
+            const float *tl = tiles[set][cur] + toff;
+            float acc[2][2] = {{bias[0][0], bias[0][1]}, {bias[1][0], bias[1][1]}};
+            float old[2][2];
 #pragma unroll
-            for (int s = 0; s < SPS; ++s) {
-                if (smp0 + s < s1) {
-                    const float *tl = tiles[cur][s] + toff;
-                    float acc[2][2] = {{bias[0][0], bias[0][1]}, {bias[1][0], bias[1][1]}};
-                    float old[2][2];
+            for (int a = 0; a < 3; ++a)
 #pragma unroll
-                    for (int a = 0; a < 3; ++a)
+                for (int r = 0; r < 4; ++r) {
+                    const float2 v01 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS);
+                    const float2 v23 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS + 2);
+                    const float v[4] = {v01.x, v01.y, v23.x, v23.y};
+                    if (a == 1 && (r == 1 || r == 2)) {
+                        old[r - 1][0] = v[1];
+                        old[r - 1][1] = v[2];
+                    }
 #pragma unroll
-                        for (int r = 0; r < 4; ++r) {
-                            const float2 v01 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS);
-                            const float2 v23 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS + 2);
-                            const float v[4] = {v01.x, v01.y, v23.x, v23.y};
-                            if (a == 1 && (r == 1 || r == 2)) {
-                                old[r - 1][0] = v[1];
-                                old[r - 1][1] = v[2];
+                    for (int j = 0; j < 2; ++j) {
+                        const int bb = r - j;
+                        if (bb >= 0 && bb <= 2) {
+#pragma unroll
+                            for (int c = 0; c < 3; ++c) {
+                                acc[j][0] = fmaf(w[a * 9 + bb * 3 + c][j][0], v[c], acc[j][0]);
+                                acc[j][1] = fmaf(w[a * 9 + bb * 3 + c][j][1], v[c + 1], acc[j][1]);
                             }
-#pragma unroll
-                            for (int j = 0; j < 2; ++j) {
-                                const int bb = r - j;
-                                if (bb >= 0 && bb <= 2) {
-#pragma unroll
-                                    for (int c = 0; c < 3; ++c) {
-                                        acc[j][0] = fmaf(w[a * 9 + bb * 3 + c][j][0], v[c], acc[j][0]);
-                                        acc[j][1] = fmaf(w[a * 9 + bb * 3 + c][j][1], v[c + 1], acc[j][1]);
-                                    }
-                                }
-                            }
-                        }
-                    float nv[2][2];
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-#pragma unroll
-                        for (int i = 0; i < 2; ++i)
-                            nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
-                    if (!last) {
-                        // The two z-planes of a warp would hit the same 16 banks with the same
-                        // element of the pair; odd planes store the pair in the other order, so
-                        // each store instruction covers all 32 banks once.
-                        float *to = tiles[cur ^ 1][s] + toff + PS + RS + 1 + (z & 1);
-                        const int step = 1 - 2 * (z & 1);
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            to[j * RS] = (z & 1) ? nv[j][1] : nv[j][0];
-                            to[j * RS + step] = (z & 1) ? nv[j][0] : nv[j][1];
-                        }
-                    } else {
-                        float *ys = p.y + (size_t)(smp0 + s) * P + g00;
-#pragma unroll
-                        for (int j = 0; j < 2; ++j)
-                            *reinterpret_cast<float2 *>(ys + (size_t)j * K) = make_float2(nv[j][0], nv[j][1]);
-                        if (STATS_OUT) {
-                            double sm = 0.0, sq = 0.0;
-#pragma unroll
-                            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                                for (int i = 0; i < 2; ++i) {
-                                    const double v = (double)nv[j][i];
-                                    sm += v;
-                                    sq = fma(v, v, sq);
-                                }
-                            sm = warp_sum(sm);
-                            sq = warp_sum(sq);
-                            if ((tid & 31) == 0)
-                                p.out_partials[(size_t)(smp0 + s) * p.nparts + (size_t)blk * 4 + (tid >> 5)] =
-                                    make_double2(sm, sq);
                         }
                     }
                 }
-            }
+            float nv[2][2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
             if (!last) {
+                // The two z-planes of a warp would hit the same 16 banks with the same element of
+                // the pair; odd planes store the pair in the other order, so each store instruction
+                // covers all 32 banks once.
+                float *to = tiles[set][cur ^ 1] + toff + PS + RS + 1 + (z & 1);
+                const int step = 1 - 2 * (z & 1);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    to[j * RS] = (z & 1) ? nv[j][1] : nv[j][0];
+                    to[j * RS + step] = (z & 1) ? nv[j][0] : nv[j][1];
+                }
                 __syncthreads();  // the other tile is complete; this one may be overwritten next
+            } else {
+                float *ys = p.y + (size_t)smp * P + g00;
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    *reinterpret_cast<float2 *>(ys + (size_t)j * K) = make_float2(nv[j][0], nv[j][1]);
+                if (STATS_OUT) {
+                    double sm = 0.0, sq = 0.0;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const double v = (double)nv[j][i];
+                            sm += v;
+                            sq = fma(v, v, sq);
+                        }
+                    sm = warp_sum(sm);
+                    sq = warp_sum(sq);
+                    if ((tid & 31) == 0)
+                        p.out_partials[(size_t)smp * p.nparts + (size_t)blk * 4 + (tid >> 5)] = make_double2(sm, sq);
+                }
             }
         }
+        __syncthreads();  // next sample's tiles are complete; this sample's tiles are free
     }
 }
 
@@ -286,22 +324,46 @@ int fast8_default_spc(int B, long long nbricks)
     return (B + chunks - 1) / chunks;
 }
 
+// Tensor map over x [B, M, N, K]: dims (fastest first) {K, N, M, B}, box {16, 10, 10, 1}.
+static bool make_x_map(CUtensorMap *map, const FastFwdParams &p)
+{
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc || (reinterpret_cast<uintptr_t>(p.x) & 15) || (p.K & 3)) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)p.K, (cuuint64_t)p.N, (cuuint64_t)p.M, (cuuint64_t)p.B};
+    const cuuint64_t strides[3] = {(cuuint64_t)p.K * 4, (cuuint64_t)p.N * p.K * 4, (cuuint64_t)p.M * p.N * p.K * 4};
+    const cuuint32_t box[4] = {16, 10, 10, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(p.x), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
 {
+    const long long nb = (long long)(p.M / 8) * (p.N / 8) * (p.K / 8);
     if (p.kbn <= 0) {
         p.kb0 = 0;
         p.kbn = p.K / 8;
     }
-    const long long nb = (long long)(p.M / 8) * (p.N / 8) * p.kbn;
-    if (p.spc <= 0) p.spc = fast8_default_spc(p.B, nb);
-    dim3 grid((unsigned)nb, (unsigned)((p.B + p.spc - 1) / p.spc));
+    const long long nbl = (long long)(p.M / 8) * (p.N / 8) * p.kbn;
+    (void)nb;
+    if (p.spc <= 0) p.spc = fast8_default_spc(p.B, nbl);
+    dim3 grid((unsigned)nbl, (unsigned)((p.B + p.spc - 1) / p.spc));
     const bool fin = p.in_stats != nullptr, sout = p.out_partials != nullptr;
-#define LAUNCH_(A)                                                                          \
-    do {                                                                                    \
-        if (fin && sout) step_fwd_fast8<A, true, true><<<grid, fast8::THREADS, 0, st>>>(p);  \
-        else if (fin) step_fwd_fast8<A, true, false><<<grid, fast8::THREADS, 0, st>>>(p);    \
-        else if (sout) step_fwd_fast8<A, false, true><<<grid, fast8::THREADS, 0, st>>>(p);   \
-        else step_fwd_fast8<A, false, false><<<grid, fast8::THREADS, 0, st>>>(p);            \
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    const bool tma = make_x_map(&map, p);  // tiles by bulk tensor copy whenever x allows it
+#define ONE_(A, FI, SO)                                                                                   \
+    do {                                                                                                  \
+        if (tma) step_fwd_fast8<A, FI, SO, true><<<grid, fast8::THREADS, 0, st>>>(map, p);                \
+        else step_fwd_fast8<A, FI, SO, false><<<grid, fast8::THREADS, 0, st>>>(map, p);                   \
+    } while (0)
+#define LAUNCH_(A)                              \
+    do {                                        \
+        if (fin && sout) ONE_(A, true, true);   \
+        else if (fin) ONE_(A, true, false);     \
+        else if (sout) ONE_(A, false, true);    \
+        else ONE_(A, false, false);             \
     } while (0)
     switch (act) {
     case GN_ACT_RELU: LAUNCH_(GN_ACT_RELU); break;
@@ -310,6 +372,7 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
     default: LAUNCH_(GN_ACT_TANH); break;
     }
 #undef LAUNCH_
+#undef ONE_
     return check_launch("step_fwd_fast8");
 }
 

@@ -24,10 +24,9 @@
 //
 // Reference semantics: gridnet/backend_torch.py:61-142 (step), gridnet/scripts/train_mnist.py:62-64
 // (LayerNorm between steps: applied here to the tile right after it lands, FUSE_IN).
-#include <cuda.h>
-
 #include "common.cuh"
 #include "kernels.h"
+#include "tma.cuh"
 
 namespace gn {
 
@@ -65,43 +64,6 @@ struct LanesParams {
     int M, N, K, G, inner;
     int nblocks, nitems;
 };
-
-// ---- PTX wrappers --------------------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity)
-{
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void tma_load_4d(unsigned dst, const CUtensorMap *map, unsigned bar, int c0, int c1, int c2,
-                                            int c3)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-        : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async()
-{
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
 
 // ---- the kernel ----------------------------------------------------------------------------
 template <int ACT, bool FUSE_IN, bool STATS_OUT>
@@ -384,11 +346,7 @@ __global__ void __launch_bounds__(256) norm_apply_from_il16_k(const float *__res
 }
 
 // ---- host side --------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn()
+EncodeTiledFn encode_tiled_fn()
 {
     static EncodeTiledFn fn = []() -> EncodeTiledFn {
         void *ptr = nullptr;
