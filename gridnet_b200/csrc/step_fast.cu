@@ -71,7 +71,9 @@ __device__ __forceinline__ float ld_pinned(const float *ptr)
     return v;
 }
 
-template <int ACT, bool FUSE_IN, bool STATS_OUT, bool USE_TMA>
+// INNER_T > 0: the inner iteration count is a compile-time constant (loop unrolled, tile parity
+// folded into addresses); INNER_T == 0: taken from the parameters.
+template <int ACT, bool FUSE_IN, bool STATS_OUT, bool USE_TMA, int INNER_T>
 __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
     step_fwd_fast8(const __grid_constant__ CUtensorMap x_map, const FastFwdParams p)
 {
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
     load_stats(s0 + 1);
     __syncthreads();
 
-    const int inner = p.inner;
+    const int inner = INNER_T > 0 ? INNER_T : p.inner;
     for (int smp = s0; smp < s1; ++smp) {
         const int set = (smp - s0) & 1;
         // TMA: the staging buffer of THIS sample was consumed a whole sample ago (a barrier has passed),
@@ -233,7 +235,8 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
         commit(smp + 1, set ^ 1);
         if (!USE_TMA) prefetch(smp + 2);
         load_stats(smp + 2);
-        for (int it = 0; it < inner; ++it) {
+#pragma unroll
+        for (int it = 0; it < (INNER_T > 0 ? INNER_T : inner); ++it) {
             const bool last = it + 1 == inner;
             const int cur = it & 1;
             const float *tl = tiles[set][cur] + toff;
@@ -355,8 +358,10 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
     const bool tma = make_x_map(&map, p);  // tiles by bulk tensor copy whenever x allows it
 #define ONE_(A, FI, SO)                                                                                   \
     do {                                                                                                  \
-        if (tma) step_fwd_fast8<A, FI, SO, true><<<grid, fast8::THREADS, 0, st>>>(map, p);                \
-        else step_fwd_fast8<A, FI, SO, false><<<grid, fast8::THREADS, 0, st>>>(map, p);                   \
+        if (tma && p.inner == 4) step_fwd_fast8<A, FI, SO, true, 4><<<grid, fast8::THREADS, 0, st>>>(map, p);  \
+        else if (tma && p.inner == 2) step_fwd_fast8<A, FI, SO, true, 2><<<grid, fast8::THREADS, 0, st>>>(map, p); \
+        else if (tma) step_fwd_fast8<A, FI, SO, true, 0><<<grid, fast8::THREADS, 0, st>>>(map, p);        \
+        else step_fwd_fast8<A, FI, SO, false, 0><<<grid, fast8::THREADS, 0, st>>>(map, p);                \
     } while (0)
 #define LAUNCH_(A)                              \
     do {                                        \
