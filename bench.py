@@ -52,7 +52,7 @@ FP32_LANES = 148 * 128
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the capture summarised in profiles/step_fwd_fast8_c2_ncu_full.txt
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 173.7e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 173.0e6
 
 
 def neuron_updates(batch: int) -> float:
