@@ -14,11 +14,20 @@
 
 namespace gn {
 
+// Tile geometry. The tile is stored with padded strides so that a warp's 32 window reads fall
+// into 32 different banks: block 8 -> rows of 10, planes of 104 (= 8 mod 32) with a warp spanning
+// 8 x-positions x 4 z-planes; block 4 -> rows of 8, planes of 68 (= 4 mod 32) with a warp spanning
+// 4 x-positions x 4 rows x 2 planes.
 template <int BS>
 struct Geo {
     static constexpr int E = BS + 2;
-    static constexpr int T = E * E * E;
+    static constexpr int T = E * E * E;          // logical cells
     static constexpr int NT = BS * BS * BS;
+    static constexpr int RS = BS == 8 ? 10 : 8;  // row stride
+    static constexpr int PS = BS == 8 ? 104 : 68;  // plane stride
+    static constexpr int TP = E * PS;            // padded tile size
+    // logical cell number (z-major) -> offset in the padded tile
+    static __device__ __forceinline__ int pad(int i) { return (i / (E * E)) * PS + ((i / E) % E) * RS + i % E; }
 };
 
 struct BlockPos {
@@ -34,16 +43,22 @@ __device__ __forceinline__ BlockPos block_pos(int N, int K)
     constexpr int E = Geo<BS>::E;
     BlockPos p;
     const int tid = threadIdx.x;
-    p.tx = tid % BS;
-    p.ty = (tid / BS) % BS;
-    p.tz = tid / (BS * BS);
+    if (BS == 8) {  // a warp = 8 x-positions x 4 z-planes of one row
+        p.tx = tid & 7;
+        p.tz = (tid >> 3) & 7;
+        p.ty = tid >> 6;
+    } else {
+        p.tx = tid & 3;
+        p.ty = (tid >> 2) & 3;
+        p.tz = tid >> 4;
+    }
     const int nbx = K / BS, nby = N / BS;
     const unsigned blk = blockIdx.x;
     p.bx = blk % nbx;
     p.by = (blk / nbx) % nby;
     p.bz = blk / nbx / nby;
     p.g = ((size_t)(p.bz * BS + p.tz) * N + (p.by * BS + p.ty)) * K + (p.bx * BS + p.tx);
-    p.own = ((p.tz + 1) * E + p.ty + 1) * E + p.tx + 1;
+    p.own = (p.tz + 1) * Geo<BS>::PS + (p.ty + 1) * Geo<BS>::RS + p.tx + 1;
     return p;
 }
 
@@ -58,7 +73,7 @@ __device__ __forceinline__ void load_tile(R *tile, const R *xs, const BlockPos &
         R v = R(0);
         if (gz >= 0 && gz < M && gy >= 0 && gy < N && gx >= 0 && gx < K)
             v = xs[((size_t)gz * N + gy) * K + gx];
-        tile[i] = v;
+        tile[Geo<BS>::pad(i)] = v;
     }
 }
 
@@ -69,11 +84,11 @@ __device__ __forceinline__ void tile_stats(const R *tile, R *red, R eps, R &mu, 
 {
     constexpr int T = Geo<BS>::T, NT = Geo<BS>::NT;
     R s = R(0);
-    for (int i = threadIdx.x; i < T; i += NT) s += tile[i];
+    for (int i = threadIdx.x; i < T; i += NT) s += tile[Geo<BS>::pad(i)];
     mu = block_sum(s, red) / R(T);
     R q = R(0);
     for (int i = threadIdx.x; i < T; i += NT) {
-        const R d = tile[i] - mu;
+        const R d = tile[Geo<BS>::pad(i)] - mu;
         q += d * d;
     }
     sd = sqrt_<R>(block_sum(q, red) / R(T));
@@ -87,8 +102,8 @@ __global__ void __launch_bounds__(BS *BS *BS)
                      const R *__restrict__ x, R *__restrict__ y, int B, int M, int N, int K,
                      int inner, R eps, int spc)
 {
-    constexpr int E = Geo<BS>::E, T = Geo<BS>::T;
-    __shared__ R tile[T];
+    constexpr int T = Geo<BS>::T, RS = Geo<BS>::RS, PS = Geo<BS>::PS, TP = Geo<BS>::TP;
+    __shared__ R tile[TP];
     __shared__ R red[33];
     const BlockPos p = block_pos<BS>(N, K);
     const size_t P = (size_t)M * N * K;
@@ -115,7 +130,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
                 for (int bb = 0; bb < 3; ++bb)
 #pragma unroll
                     for (int c = 0; c < 3; ++c) {
-                        R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        R v = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
                         if (NORM) v = (v - mu) * inv;
                         acc = fma(v, wr[a * 9 + bb * 3 + c], acc);
                     }
@@ -129,7 +144,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
 }
 
 // ============================================================= plain backward
-// Dynamic shared memory: tile[T] | G[T] | Gin[T] | red[40] | stash[inner][NT]
+// Dynamic shared memory: tile[TP] | G[TP] | Gin[TP] | red[40] | stash[inner][NT] (TP = padded tile)
 // Recomputes the inner iterations (stashing each neuron's own activation per
 // iteration), then walks them in reverse. The 27 contributions of a neuron to the
 // gradient tile are scattered with shared-memory atomics, so the float summation
@@ -141,12 +156,12 @@ __global__ void __launch_bounds__(BS *BS *BS)
                      R *__restrict__ gb, R *__restrict__ gs, R *__restrict__ gx, int B, int M,
                      int N, int K, int inner, R eps, int spc, int atomic_params)
 {
-    constexpr int E = Geo<BS>::E, T = Geo<BS>::T, NT = Geo<BS>::NT;
+    constexpr int E = Geo<BS>::E, T = Geo<BS>::T, NT = Geo<BS>::NT, RS = Geo<BS>::RS, PS = Geo<BS>::PS, TP = Geo<BS>::TP;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     R *tile = reinterpret_cast<R *>(smem_raw);
-    R *G = tile + T;
-    R *Gin = G + T;
-    R *red = Gin + T;
+    R *G = tile + TP;
+    R *Gin = G + TP;
+    R *red = Gin + TP;
     R *stash = red + 40;
     const BlockPos p = block_pos<BS>(N, K);
     const size_t P = (size_t)M * N * K;
@@ -164,8 +179,8 @@ __global__ void __launch_bounds__(BS *BS *BS)
         __syncthreads();
         load_tile<R, BS>(tile, x + (size_t)smp * P, p, M, N, K);
         for (int i = tid; i < T; i += NT) {
-            G[i] = R(0);
-            Gin[i] = R(0);
+            G[Geo<BS>::pad(i)] = R(0);
+            Gin[Geo<BS>::pad(i)] = R(0);
         }
         __syncthreads();
         // forward replay
@@ -184,7 +199,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
                 for (int bb = 0; bb < 3; ++bb)
 #pragma unroll
                     for (int c = 0; c < 3; ++c) {
-                        R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        R v = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
                         if (NORM) v = (v - mu) * inv;
                         acc = fma(v, wr[a * 9 + bb * 3 + c], acc);
                     }
@@ -212,7 +227,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
                 for (int bb = 0; bb < 3; ++bb)
 #pragma unroll
                     for (int c = 0; c < 3; ++c) {
-                        R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        R v = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
                         if (NORM) v = (v - mu) * inv;
                         xv[a * 9 + bb * 3 + c] = v;
                         acc = fma(v, wr[a * 9 + bb * 3 + c], acc);
@@ -231,24 +246,26 @@ __global__ void __launch_bounds__(BS *BS *BS)
                     for (int c = 0; c < 3; ++c) {
                         const int t = a * 9 + bb * 3 + c;
                         dw[t] = fma(xv[t], dl, dw[t]);
-                        atomicAdd(&dst[((p.tz + a) * E + p.ty + bb) * E + p.tx + c], wr[t] * dl);
+                        atomicAdd(&dst[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c], wr[t] * dl);
                     }
             __syncthreads();
             if (NORM) {
                 // inputs were (cur - mu) * inv with inv = 1/(sd + eps): chain rule through mu, sd
                 R sg = R(0), sgc = R(0);
                 for (int i = tid; i < T; i += NT) {
-                    sg += Gin[i];
-                    sgc += Gin[i] * (tile[i] - mu);
+                    const int pi = Geo<BS>::pad(i);
+                    sg += Gin[pi];
+                    sgc += Gin[pi] * (tile[pi] - mu);
                 }
                 sg = block_sum(sg, red);
                 sgc = block_sum(sgc, red);
                 const R dsd = -sgc * inv * inv;
                 for (int i = tid; i < T; i += NT) {
-                    R v = Gin[i] * inv - sg * inv / R(T);
-                    v += dsd * (tile[i] - mu) / (R(T) * sd);
-                    G[i] += v;
-                    Gin[i] = R(0);
+                    const int pi = Geo<BS>::pad(i);
+                    R v = Gin[pi] * inv - sg * inv / R(T);
+                    v += dsd * (tile[pi] - mu) / (R(T) * sd);
+                    G[pi] += v;
+                    Gin[pi] = R(0);
                 }
                 __syncthreads();
             }
@@ -260,8 +277,154 @@ __global__ void __launch_bounds__(BS *BS *BS)
             const int px = i % E, py = (i / E) % E, pz = i / (E * E);
             const int gz = p.bz * BS + pz - 1, gyy = p.by * BS + py - 1, gxx = p.bx * BS + px - 1;
             if (gz >= 0 && gz < M && gyy >= 0 && gyy < N && gxx >= 0 && gxx < K)
-                atomicAdd(&gxs[((size_t)gz * N + gyy) * K + gxx], G[i]);
+                atomicAdd(&gxs[((size_t)gz * N + gyy) * K + gxx], G[Geo<BS>::pad(i)]);
         }
+    }
+    if (atomic_params) {
+#pragma unroll
+        for (int t = 0; t < 27; ++t) atomicAdd(&gw[(size_t)t * P + p.g], dw[t]);
+        atomicAdd(&gb[p.g], db);
+        atomicAdd(&gs[p.g], ds);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 27; ++t) gw[(size_t)t * P + p.g] = dw[t];
+        gb[p.g] = db;
+        gs[p.g] = ds;
+    }
+}
+
+// ================================================= plain backward, normalize off
+// Dynamic shared memory: tile[TP] | D[TP] | wsm[27][NT] | stash[inner][NT]
+// Same replay-and-reverse structure, but without shared-memory atomics: the gradient that flows
+// back to a block cell is GATHERED by the thread that owns the cell, from the per-iteration delta
+// tile D and a shared-memory copy of the block's weights (cell c receives w[n][t] * delta[n] from
+// every neuron n with c = n + offset(t)). The running gradient of an owned cell is a register.
+// Halo cells never feed back into the block, so their gradient is built once per sample from the
+// per-neuron sum of deltas. Everything inside the CTA is deterministic; only the final
+// accumulation into grad_x, where tiles of neighbouring blocks overlap, uses global atomics.
+template <typename R, int BS, int ACT>
+__global__ void __launch_bounds__(BS *BS *BS)
+    step_bwd_gather(const R *__restrict__ w, const R *__restrict__ b, const R *__restrict__ s,
+                    const R *__restrict__ x, const R *__restrict__ gy, R *__restrict__ gw, R *__restrict__ gb,
+                    R *__restrict__ gs, R *__restrict__ gx, int B, int M, int N, int K, int inner, int spc,
+                    int atomic_params)
+{
+    constexpr int E = Geo<BS>::E, T = Geo<BS>::T, NT = Geo<BS>::NT, RS = Geo<BS>::RS, PS = Geo<BS>::PS, TP = Geo<BS>::TP;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    R *tile = reinterpret_cast<R *>(smem_raw);
+    R *D = tile + TP;
+    R *wsm = D + TP;
+    R *stash = wsm + 27 * NT;
+    const BlockPos p = block_pos<BS>(N, K);
+    const size_t P = (size_t)M * N * K;
+    const int tid = threadIdx.x;
+    // thread-index distance to the neighbour one step along x, y, z (see block_pos)
+    constexpr int DX = 1, DY = BS == 8 ? 64 : 4, DZ = BS == 8 ? 8 : 16;
+    R wr[27], dw[27];
+    unsigned inside = 0;  // bit t: the neighbour at offset(t) is a neuron of this block
+#pragma unroll
+    for (int t = 0; t < 27; ++t) {
+        wr[t] = w[(size_t)t * P + p.g];
+        wsm[t * NT + tid] = wr[t];
+        dw[t] = R(0);
+        const int a = t / 9, bb = (t / 3) % 3, c = t % 3;
+        const bool in = (unsigned)(p.tz + a - 1) < (unsigned)BS && (unsigned)(p.ty + bb - 1) < (unsigned)BS &&
+                        (unsigned)(p.tx + c - 1) < (unsigned)BS;
+        inside |= (in ? 1u : 0u) << t;
+    }
+    const R br = b[p.g], sr = s[p.g];
+    R db = R(0), ds = R(0);
+    for (int i = tid; i < T; i += NT) D[Geo<BS>::pad(i)] = R(0);  // the halo of D stays zero
+    const int s0 = blockIdx.y * spc, s1 = min(B, s0 + spc);
+    for (int smp = s0; smp < s1; ++smp) {
+        __syncthreads();
+        load_tile<R, BS>(tile, x + (size_t)smp * P, p, M, N, K);
+        __syncthreads();
+        for (int it = 0; it < inner; ++it) {  // forward replay
+            stash[it * NT + tid] = tile[p.own];
+            R acc = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c)
+                        acc = fma(tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c], wr[a * 9 + bb * 3 + c], acc);
+            const R nv = fma(Act<ACT, R>::fwd(acc + br), sr, tile[p.own]);
+            __syncthreads();
+            tile[p.own] = nv;
+            __syncthreads();
+        }
+        R g = gy[(size_t)smp * P + p.g];  // gradient w.r.t. this neuron's current activation
+        R dsum = R(0);                    // sum of this neuron's deltas over the iterations
+        for (int it = inner - 1; it >= 0; --it) {
+            tile[p.own] = stash[it * NT + tid];
+            __syncthreads();
+            R xv[27];
+            R acc = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const int t = a * 9 + bb * 3 + c;
+                        xv[t] = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
+                        acc = fma(xv[t], wr[t], acc);
+                    }
+            R f, d;
+            Act<ACT, R>::both(acc + br, f, d);
+            ds = fma(f, g, ds);
+            const R dl = d * g * sr;
+            db += dl;
+            dsum += dl;
+#pragma unroll
+            for (int t = 0; t < 27; ++t) dw[t] = fma(xv[t], dl, dw[t]);
+            D[p.own] = dl;
+            __syncthreads();
+            // gather: the neighbour at offset o = offset(t) reaches this cell through its tap 26 - t
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const int t = a * 9 + bb * 3 + c;
+                        if (inside & (1u << t)) {
+                            const int nb_tid = tid + (c - 1) * DX + (bb - 1) * DY + (a - 1) * DZ;
+                            g = fma(wsm[(26 - t) * NT + nb_tid], D[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c], g);
+                        }
+                    }
+            __syncthreads();  // D and the tile may be overwritten by the next iteration
+        }
+        // ---- gradient of the input tile: owned cells from registers, halo cells from the delta sums
+        R *gxs = gx + (size_t)smp * P;
+        atomicAdd(&gxs[p.g], g);
+        D[p.own] = dsum;
+        __syncthreads();
+        for (int i = tid; i < T; i += NT) {
+            const int px = i % E, py = (i / E) % E, pz = i / (E * E);
+            const bool halo = px == 0 || px == E - 1 || py == 0 || py == E - 1 || pz == 0 || pz == E - 1;
+            const int gz = p.bz * BS + pz - 1, gyy = p.by * BS + py - 1, gxx = p.bx * BS + px - 1;
+            if (halo && gz >= 0 && gz < M && gyy >= 0 && gyy < N && gxx >= 0 && gxx < K) {
+                R acc = R(0);
+                // (fixed 27-trip loop with a validity test: measured faster than clipped loop bounds)
+                for (int a = 0; a < 3; ++a)
+                    for (int bb = 0; bb < 3; ++bb)
+                        for (int c = 0; c < 3; ++c) {
+                            // neuron n = cell - offset(t) in padded coordinates; it must be a block neuron
+                            const int nz = pz - (a - 1), ny = py - (bb - 1), nx = px - (c - 1);
+                            if (nz >= 1 && nz <= BS && ny >= 1 && ny <= BS && nx >= 1 && nx <= BS) {
+                                const int ntid = BS == 8 ? (nx - 1) + 8 * (nz - 1) + 64 * (ny - 1)
+                                                         : (nx - 1) + 4 * (ny - 1) + 16 * (nz - 1);
+                                acc = fma(wsm[(a * 9 + bb * 3 + c) * NT + ntid], D[nz * PS + ny * RS + nx], acc);
+                            }
+                        }
+                atomicAdd(&gxs[((size_t)gz * N + gyy) * K + gxx], acc);
+            }
+        }
+        __syncthreads();
+        D[p.own] = R(0);  // (halo of D is still zero)
     }
     if (atomic_params) {
 #pragma unroll
@@ -282,8 +445,8 @@ __global__ void __launch_bounds__(BS *BS *BS)
     gated_fwd_generic(const R *__restrict__ w, const R *__restrict__ b, const R *__restrict__ x,
                       R *__restrict__ y, int B, int M, int N, int K, int inner, int spc)
 {
-    constexpr int E = Geo<BS>::E, T = Geo<BS>::T;
-    __shared__ R tile[T];
+    constexpr int T = Geo<BS>::T, RS = Geo<BS>::RS, PS = Geo<BS>::PS, TP = Geo<BS>::TP;
+    __shared__ R tile[TP];
     const BlockPos p = block_pos<BS>(N, K);
     const size_t P = (size_t)M * N * K;
     R wv[27], wg[27];
@@ -306,7 +469,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
                 for (int bb = 0; bb < 3; ++bb)
 #pragma unroll
                     for (int c = 0; c < 3; ++c) {
-                        const R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        const R v = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
                         av = fma(v, wv[a * 9 + bb * 3 + c], av);
                         ag = fma(v, wg[a * 9 + bb * 3 + c], ag);
                     }
@@ -321,7 +484,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
 }
 
 // ============================================================= gated backward
-// Dynamic shared memory: tile[T] | G[T] | stash[inner][NT]
+// Dynamic shared memory: tile[TP] | G[TP] | stash[inner][NT]
 template <typename R, int BS, int ACT>
 __global__ void __launch_bounds__(BS *BS *BS)
     gated_bwd_generic(const R *__restrict__ w, const R *__restrict__ b, const R *__restrict__ x,
@@ -329,11 +492,11 @@ __global__ void __launch_bounds__(BS *BS *BS)
                       R *__restrict__ gx, int B, int M, int N, int K, int inner, int spc,
                       int atomic_params)
 {
-    constexpr int E = Geo<BS>::E, T = Geo<BS>::T, NT = Geo<BS>::NT;
+    constexpr int E = Geo<BS>::E, T = Geo<BS>::T, NT = Geo<BS>::NT, RS = Geo<BS>::RS, PS = Geo<BS>::PS, TP = Geo<BS>::TP;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     R *tile = reinterpret_cast<R *>(smem_raw);
-    R *G = tile + T;
-    R *stash = G + T;
+    R *G = tile + TP;
+    R *stash = G + TP;
     const BlockPos p = block_pos<BS>(N, K);
     const size_t P = (size_t)M * N * K;
     const int tid = threadIdx.x;
@@ -351,7 +514,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
     for (int smp = s0; smp < s1; ++smp) {
         __syncthreads();
         load_tile<R, BS>(tile, x + (size_t)smp * P, p, M, N, K);
-        for (int i = tid; i < T; i += NT) G[i] = R(0);
+        for (int i = tid; i < T; i += NT) G[Geo<BS>::pad(i)] = R(0);
         __syncthreads();
         for (int it = 0; it < inner; ++it) {
             stash[it * NT + tid] = tile[p.own];
@@ -362,7 +525,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
                 for (int bb = 0; bb < 3; ++bb)
 #pragma unroll
                     for (int c = 0; c < 3; ++c) {
-                        const R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        const R v = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
                         av = fma(v, wv[a * 9 + bb * 3 + c], av);
                         ag = fma(v, wg[a * 9 + bb * 3 + c], ag);
                     }
@@ -385,7 +548,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
                 for (int bb = 0; bb < 3; ++bb)
 #pragma unroll
                     for (int c = 0; c < 3; ++c) {
-                        const R v = tile[((p.tz + a) * E + p.ty + bb) * E + p.tx + c];
+                        const R v = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
                         av = fma(v, wv[a * 9 + bb * 3 + c], av);
                         ag = fma(v, wg[a * 9 + bb * 3 + c], ag);
                     }
@@ -406,7 +569,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
 #pragma unroll
                     for (int c = 0; c < 3; ++c) {
                         const int t = a * 9 + bb * 3 + c;
-                        const int ci = ((p.tz + a) * E + p.ty + bb) * E + p.tx + c;
+                        const int ci = (p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c;
                         const R v = tile[ci];
                         dwv[t] = fma(v, dv, dwv[t]);
                         dwg[t] = fma(v, dg, dwg[t]);
@@ -419,7 +582,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
             const int px = i % E, py = (i / E) % E, pz = i / (E * E);
             const int gz = p.bz * BS + pz - 1, gyy = p.by * BS + py - 1, gxx = p.bx * BS + px - 1;
             if (gz >= 0 && gz < M && gyy >= 0 && gyy < N && gxx >= 0 && gxx < K)
-                atomicAdd(&gxs[((size_t)gz * N + gyy) * K + gxx], G[i]);
+                atomicAdd(&gxs[((size_t)gz * N + gyy) * K + gxx], G[Geo<BS>::pad(i)]);
         }
     }
     if (atomic_params) {
@@ -447,7 +610,7 @@ static constexpr size_t kMaxDynSmem = 227 * 1024;
 template <typename R>
 static size_t bwd_smem_bytes(int bs, int inner, bool gated)
 {
-    const size_t T = (size_t)(bs + 2) * (bs + 2) * (bs + 2), NT = (size_t)bs * bs * bs;
+    const size_t T = (size_t)(bs + 2) * (bs == 8 ? 104 : 68), NT = (size_t)bs * bs * bs;  // padded tile
     const size_t fixed = gated ? 2 * T : 3 * T + 40;
     return (fixed + (size_t)inner * NT) * sizeof(R);
 }
@@ -455,7 +618,7 @@ static size_t bwd_smem_bytes(int bs, int inner, bool gated)
 int step_backward_max_inner(int block, int elem_size)
 {
     if ((block != 4 && block != 8) || (elem_size != 4 && elem_size != 8)) return -1;
-    const size_t T = (size_t)(block + 2) * (block + 2) * (block + 2), NT = (size_t)block * block * block;
+    const size_t T = (size_t)(block + 2) * (block == 8 ? 104 : 68), NT = (size_t)block * block * block;
     const size_t fixed = (3 * T + 40) * elem_size;
     return (int)((kMaxDynSmem - fixed) / (NT * elem_size));
 }
@@ -511,11 +674,17 @@ int launch_step_bwd_generic(const R *w, const R *b, const R *s, const R *x, cons
 {
     const size_t P = (size_t)M * N * K;
     const long long nb = (long long)(M / bs) * (N / bs) * (K / bs);
+    // one CTA per block covers the whole batch whenever the grid already fills the GPU: parameter
+    // gradients are then plain stores (splitting the batch further was measured slower: the atomics
+    // on 27 weight gradients per neuron cost more than the last partial wave)
     const int chunks = pick_batch_chunks(nb, B, bs == 8 ? 1 : 8);
     const int spc = (B + chunks - 1) / chunks;
     dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
     const int atomic_params = grid.y > 1;
-    const size_t smem = bwd_smem_bytes<R>(bs, inner, false);
+    const size_t tp = (size_t)(bs + 2) * (bs == 8 ? 104 : 68), nt = (size_t)bs * bs * bs;
+    const size_t smem_gather = (2 * tp + 27 * nt + (size_t)inner * nt) * sizeof(R);
+    const bool gather = !normalize && smem_gather <= kMaxDynSmem;
+    const size_t smem = gather ? smem_gather : bwd_smem_bytes<R>(bs, inner, false);
     if (smem > kMaxDynSmem) return GN_ERR_BAD_INNER;
     cudaError_t e = cudaMemsetAsync(gx, 0, sizeof(R) * B * P, st);
     if (e == cudaSuccess && atomic_params) {
@@ -535,20 +704,31 @@ int launch_step_bwd_generic(const R *w, const R *b, const R *s, const R *x, cons
         kern<<<grid, BSV * BSV * BSV, smem, st>>>(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, \
                                                   inner, eps, spc, atomic_params);             \
     } while (0)
-#define LAUNCH_(A)                          \
-    do {                                    \
-        if (bs == 8) {                      \
+#define GATHER_(BSV, A)                                                                              \
+    do {                                                                                             \
+        auto kern = step_bwd_gather<R, BSV, A>;                                                      \
+        int rc = opt_in_smem(kern, smem);                                                            \
+        if (rc != GN_OK) return rc;                                                                  \
+        kern<<<grid, BSV * BSV * BSV, smem, st>>>(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, \
+                                                  spc, atomic_params);                               \
+    } while (0)
+#define LAUNCH_(A)                           \
+    do {                                     \
+        if (bs == 8) {                       \
             if (normalize) ONE_(8, A, true); \
-            else ONE_(8, A, false);         \
-        } else {                            \
+            else if (gather) GATHER_(8, A);  \
+            else ONE_(8, A, false);          \
+        } else {                             \
             if (normalize) ONE_(4, A, true); \
-            else ONE_(4, A, false);         \
-        }                                   \
+            else if (gather) GATHER_(4, A);  \
+            else ONE_(4, A, false);          \
+        }                                    \
     } while (0)
     GN_ACT_SWITCH(act, LAUNCH_)
 #undef LAUNCH_
+#undef GATHER_
 #undef ONE_
-    return check_launch("step_bwd_generic");
+    return check_launch("step_bwd");
 }
 
 template <typename R>
