@@ -9,7 +9,8 @@ native extension module. Everything runs through ``libgridnet_b200.so`` (C ABI i
 from . import gridnet_cuda
 from ._lib import LIB_PATH, GridnetB200Error
 from .backend_cuda import (GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, HostPipelinedForward, fused_step, norm_apply,
-                           norm_finalize, outer_forward, outer_forward_workspace, step_stats_partials)
+                           norm_finalize, outer_forward, outer_forward_failed, outer_forward_workspace,
+                           step_stats_partials)
 
 from .modules import (GatedGridnet, Gridnet, GridnetModel, GridNorm, Readout, gated_gridnet_step,
                       gridnet_step)
@@ -28,6 +29,7 @@ __all__ = [
     "outer_forward",
     "HostPipelinedForward",
     "outer_forward_workspace",
+    "outer_forward_failed",
     "fused_step",
     "norm_finalize",
     "norm_apply",

@@ -147,6 +147,15 @@ class GridNormOp(torch.autograd.Function):
         return gx, gg, gb, None
 
 
+def outer_forward_failed(workspace: torch.Tensor, batch: int, shape, block_size: int) -> bool:
+    """True if the last :func:`outer_forward` that used ``workspace`` recorded a device-side failure
+    (a bounded wait on a bulk tile copy that gave up). Synchronises the device."""
+    m, n, k = shape
+    off = int(lib.gn_outer_forward_error_flag_offset(batch, m, n, k, block_size))
+    torch.cuda.synchronize(workspace.device)
+    return bool(workspace[off:off + 4].view(torch.int32).item())
+
+
 def outer_forward_workspace(batch: int, shape, block_size: int, device) -> torch.Tensor:
     """Scratch buffer for :func:`outer_forward`; reusable across calls of the same size."""
     m, n, k = shape

@@ -460,6 +460,13 @@ GN_API size_t gn_outer_forward_workspace_bytes(int B, int M, int N, int K, int b
     return carve_outer(nullptr, B, M, N, K, block).bytes;
 }
 
+GN_API size_t gn_outer_forward_error_flag_offset(int B, int M, int N, int K, int block)
+{
+    if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || (block != 4 && block != 8)) return 0;
+    const OuterWs w = carve_outer(nullptr, B, M, N, K, block);
+    return (size_t)((unsigned char *)w.error_flag - (unsigned char *)nullptr);
+}
+
 GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, const float *gamma, const float *beta,
                          const float *x, float *y, int B, int M, int N, int K, int inner, int outer, int block,
                          float ln_eps, int act, void *workspace, size_t workspace_bytes, void *stream)
@@ -514,12 +521,17 @@ GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, 
     }
     if (g_outer_kernel == 2) return GN_ERR_UNSUPPORTED;
 
+    if (cudaMemsetAsync(ws.error_flag, 0, sizeof(int), st) != cudaSuccess) {
+        record_cuda_error(cudaGetLastError(), "cudaMemsetAsync");
+        return GN_ERR_CUDA;
+    }
     const float *src = x;
     for (int o = 0; o < outer; ++o) {
         float *dst = ws.buf[o & 1];
         if (fused) {
             p.x = src;
             p.y = dst;
+            p.error_flag = ws.error_flag;
             p.in_stats = o > 0 ? ws.stats : nullptr;  // raw output of the previous step: normalise on load
             p.out_partials = ws.partials;
             p.nparts = nparts_fused;

@@ -201,6 +201,10 @@ GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *be
  * (With the optional lanes-of-samples kernel, gn_config_set("outer_kernel", 2), the activations
  * are kept interleaved by groups of 16 samples between steps, [group][M][N][K][16], and read by TMA.) */
 GN_API size_t gn_outer_forward_workspace_bytes(int B, int M, int N, int K, int block);
+/* Byte offset, inside the workspace, of an int that gn_outer_forward_f32 sets to 1 when a bounded
+ * wait on a bulk tile copy gave up (the results of that call are then invalid). It is cleared at
+ * the start of every call; read it after synchronising the stream. */
+GN_API size_t gn_outer_forward_error_flag_offset(int B, int M, int N, int K, int block);
 GN_API int gn_outer_forward_f32(const float *weight, const float *bias, const float *scale,
                          const float *gamma, const float *beta, const float *x, float *y,
                          int B, int M, int N, int K, int inner, int outer, int block,

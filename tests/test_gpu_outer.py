@@ -177,3 +177,15 @@ def test_lanes_kernel_matches_patch_kernel_and_oracle():
         assert torch.allclose(got, base, rtol=1e-5, atol=1e-6), (got - base).abs().max().item()
         a64 = [a.astype(np.float64) for a in (w, b, s, gamma, beta, x)]
         assert_close(got.cpu().numpy(), orc.outer_forward(*a64, inner, outer, 8), None, f"lanes kernel B={B}")
+
+
+def test_outer_forward_reports_no_device_failure():
+    from gridnet_b200 import outer_forward, outer_forward_failed, outer_forward_workspace
+
+    shape, B = (16, 16, 16), 4
+    w, b, s, gamma, beta = (dev(a) for a in model_params(29, shape))
+    x = dev(face_input(30, B, shape))
+    ws = outer_forward_workspace(B, shape, 8, x.device)
+    ws.fill_(255)  # the flag must be cleared by the call itself
+    outer_forward(w, b, s, gamma, beta, x, 2, 3, 8, workspace=ws)
+    assert not outer_forward_failed(ws, B, shape, 8)

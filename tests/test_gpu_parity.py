@@ -304,3 +304,20 @@ def test_extension_layer_errors():
     out = Op.apply(w, b, s, tx, 1, 8, 1e-5, False, "silu")
     out.transpose(1, 2).contiguous().transpose(1, 2).backward(torch.ones_like(out))
     assert torch.isfinite(tx.grad).all()
+
+
+def test_forward_with_unaligned_activations_uses_the_plain_load_path():
+    # TMA tile fetch needs a 16-byte aligned activation tensor; a view that starts 4 bytes into a
+    # buffer makes the tuned kernel fall back to plain loads, which must give the same result
+    Op, _ = ops()
+    shape = (16, 24, 16)
+    w, b, s, x = rng_inputs(40, 3, shape, unit_scale=True)
+    ref64 = orc.step_forward(*(a.astype(np.float64) for a in (w, b, s, x)), 4, 8, 1e-5, False, "silu")
+    store = torch.zeros(x.size + 1, device="cuda")
+    xv = store[1:].view(x.shape)
+    xv.copy_(torch.from_numpy(x))
+    assert xv.data_ptr() % 16 == 4 and xv.is_contiguous()
+    got_unaligned = Op.apply(dev(w), dev(b), dev(s), xv, 4, 8, 1e-5, False, "silu")
+    got_aligned = Op.apply(dev(w), dev(b), dev(s), dev(x), 4, 8, 1e-5, False, "silu")
+    assert torch.equal(got_unaligned, got_aligned)
+    assert_close(got_aligned.cpu().numpy(), ref64, None, "unaligned x")
