@@ -411,8 +411,8 @@ GN_API int gn_step_forward_fused_f32(const float *w, const float *b, const float
 
 GN_API int gn_step_forward_slab_f32(const float *w, const float *b, const float *s, const float *x, float *y,
                              const float *gamma, const float *beta, const float *in_mean_rstd,
-                             double *out_partials, int B, int M, int N, int K, int k_block_first,
-                             int k_block_count, int inner, int act, void *stream)
+                             double *out_partials, int partials_per_sample, int B, int M, int N, int K,
+                             int k_block_first, int k_block_count, int inner, int act, void *stream)
 {
     const int rc = check_geometry(B, M, N, K, inner, 8, act);
     if (rc != GN_OK) return rc;
@@ -425,6 +425,10 @@ GN_API int gn_step_forward_slab_f32(const float *w, const float *b, const float 
     p.in_stats = reinterpret_cast<const float2 *>(in_mean_rstd);
     p.out_partials = reinterpret_cast<double2 *>(out_partials);
     p.nparts = (M / 8) * (N / 8) * k_block_count * 4;
+    if (partials_per_sample > 0) {  // several launches share one partial buffer
+        if (partials_per_sample < p.nparts) return GN_ERR_BAD_SHAPE;
+        p.nparts = partials_per_sample;
+    }
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
     p.kb0 = k_block_first; p.kbn = k_block_count;
     if (!fast8_applicable(p, 8, 0)) return GN_ERR_UNSUPPORTED;

@@ -106,18 +106,40 @@ class CudaSlabBackend:
     def _stream(self):
         return torch.cuda.current_stream().cuda_stream
 
-    def step(self, x, y, in_stats):
-        """y[real blocks] = step(x) with x normalised on load when ``in_stats`` is given; returns the
-        local per-sample (sum, sum of squares) of what was written, ``[B, 2]`` float64."""
+    def _launch(self, x, y, in_stats, kb_first: int, kb_count: int, pair_offset: int):
         B = x.shape[0]
         if self._partials is None or self._partials.shape[0] != B:
             self._partials = torch.empty(B, self.nparts, 2, dtype=torch.float64, device=x.device)
-        lay = self.layout
         self.check(self.lib.gn_step_forward_slab_f32(
             self.w.data_ptr(), self.b.data_ptr(), self.s.data_ptr(), x.data_ptr(), y.data_ptr(),
             self.gamma.data_ptr(), self.beta.data_ptr(), None if in_stats is None else in_stats.data_ptr(),
-            self._partials.data_ptr(), B, self.M, self.N, lay.k_pad, 1, lay.k_loc // 8, self.inner, self.act,
-            self._stream()))
+            self._partials.data_ptr() + 16 * pair_offset, self.nparts, B, self.M, self.N, self.layout.k_pad,
+            kb_first, kb_count, self.inner, self.act, self._stream()))
+
+    @property
+    def _pairs_per_kblock(self) -> int:
+        return 4 * (self.M // 8) * (self.N // 8)
+
+    def step(self, x, y, in_stats):
+        """y[real blocks] = step(x) with x normalised on load when ``in_stats`` is given; returns the
+        local per-sample (sum, sum of squares) of what was written, ``[B, 2]`` float64."""
+        self._launch(x, y, in_stats, 1, self.layout.k_loc // 8, 0)
+        return self.sums()
+
+    # The same step in two parts, so that the faces can travel while the interior computes:
+    # the K-blocks that touch a neighbour slab first, the rest afterwards.
+    def step_boundary(self, x, y, in_stats):
+        n = self.layout.k_loc // 8
+        self._launch(x, y, in_stats, 1, 1, 0)
+        if n > 1:
+            self._launch(x, y, in_stats, n, 1, self._pairs_per_kblock)
+
+    def step_interior(self, x, y, in_stats):
+        n = self.layout.k_loc // 8
+        if n > 2:
+            self._launch(x, y, in_stats, 2, n - 2, 2 * self._pairs_per_kblock)
+
+    def sums(self):
         return self._partials.sum(1)
 
     def finalize(self, sums, count: int):
@@ -154,12 +176,26 @@ class SlabRunner:
         self.cur = nxt
         return sums
 
-    def faces_out(self):
-        b = self.bufs[self.cur]
+    def can_split(self) -> bool:
+        return hasattr(self.backend, "step_boundary")
+
+    def compute_boundary(self):
+        """First half of a step: only the K-blocks whose faces the neighbours need."""
+        self._nxt = 1 if self.cur != 1 else 2
+        self.backend.step_boundary(self.bufs[self.cur], self.bufs[self._nxt], self.stats)
+
+    def compute_interior(self):
+        """Second half; returns the local sums of the whole step."""
+        self.backend.step_interior(self.bufs[self.cur], self.bufs[self._nxt], self.stats)
+        self.cur = self._nxt
+        return self.backend.sums()
+
+    def faces_out(self, buf=None):
+        b = self.bufs[self.cur if buf is None else buf]
         return self.layout.face_to_left(b), self.layout.face_to_right(b)
 
-    def faces_in(self, from_left, from_right):
-        b = self.bufs[self.cur]
+    def faces_in(self, from_left, from_right, buf=None):
+        b = self.bufs[self.cur if buf is None else buf]
         if from_left is not None:
             self.layout.put_from_left(b, from_left)
         if from_right is not None:
@@ -176,39 +212,80 @@ class SlabRunner:
         return self.layout.real(out).contiguous()
 
 
-def run_distributed(runner: SlabRunner, outer: int, group=None) -> torch.Tensor:
-    """Drive one rank's :class:`SlabRunner` for ``outer`` steps over torch.distributed
-    (NCCL on GPUs, gloo on CPU): grouped send/recv of the two faces, all-reduce of the sums."""
+def _exchange(runner: SlabRunner, group, buf=None):
+    """Grouped send/recv of the two boundary faces of ``buf`` into its ghost columns."""
     import torch.distributed as dist
 
     lay = runner.layout
+    to_left, to_right = runner.faces_out(buf)
+    from_left = torch.empty_like(to_left) if lay.left is not None else None
+    from_right = torch.empty_like(to_right) if lay.right is not None else None
+    ops = []
+    if lay.left is not None:
+        ops += [dist.P2POp(dist.isend, to_left, lay.left, group), dist.P2POp(dist.irecv, from_left, lay.left, group)]
+    if lay.right is not None:
+        ops += [dist.P2POp(dist.isend, to_right, lay.right, group), dist.P2POp(dist.irecv, from_right, lay.right, group)]
+    for r in (dist.batch_isend_irecv(ops) if ops else []):
+        r.wait()
+    runner.faces_in(from_left, from_right, buf)
+
+
+def run_distributed(runner: SlabRunner, outer: int, group=None, overlap: bool = False) -> torch.Tensor:
+    """Drive one rank's :class:`SlabRunner` for ``outer`` steps over torch.distributed (NCCL on
+    GPUs, gloo on CPU): grouped send/recv of the two faces, all-reduce of the sums.
+
+    With ``overlap`` on a CUDA backend that can split a step, the K-blocks next to the neighbours
+    are computed first and their faces are packed, exchanged and unpacked on a second stream while
+    the interior blocks compute; only the tiny all-reduce of the statistics stays on the critical path.
+    It is off by default: with slabs as thin as 256^3 / 8 GPUs the loop is bound by host-side launch
+    and torch.distributed call overhead, and the extra launches made it slower (1.05 ms against
+    0.78 ms per outer step at that slab size on two B200s)."""
+    import torch.distributed as dist
+
+    on_gpu = runner.bufs[0].is_cuda
+    if not (overlap and on_gpu and runner.can_split()):
+        for _ in range(outer):
+            sums = runner.compute()
+            _exchange(runner, group)
+            dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
+            runner.set_global_sums(sums)
+        return runner.result()
+
+    main = torch.cuda.current_stream()
+    comm = getattr(runner, "_comm_stream", None)
+    if comm is None:
+        comm = runner._comm_stream = torch.cuda.Stream()
     for _ in range(outer):
-        sums = runner.compute()
-        to_left, to_right = runner.faces_out()
-        from_left = torch.empty_like(to_left) if lay.left is not None else None
-        from_right = torch.empty_like(to_right) if lay.right is not None else None
-        ops = []
-        if lay.left is not None:
-            ops += [dist.P2POp(dist.isend, to_left, lay.left, group), dist.P2POp(dist.irecv, from_left, lay.left, group)]
-        if lay.right is not None:
-            ops += [dist.P2POp(dist.isend, to_right, lay.right, group),
-                    dist.P2POp(dist.irecv, from_right, lay.right, group)]
-        reqs = dist.batch_isend_irecv(ops) if ops else []
+        runner.compute_boundary()
+        nxt = runner._nxt
+        boundary_done = torch.cuda.Event()
+        boundary_done.record(main)
+        with torch.cuda.stream(comm):
+            comm.wait_event(boundary_done)
+            _exchange(runner, group, nxt)
+            faces_done = torch.cuda.Event()
+            faces_done.record(comm)
+        sums = runner.compute_interior()
         dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
-        for r in reqs:
-            r.wait()
-        runner.faces_in(from_left, from_right)
+        main.wait_event(faces_done)
         runner.set_global_sums(sums)
     return runner.result()
 
 
-def run_emulated(runners, outer: int):
+def run_emulated(runners, outer: int, split: bool = False):
     """All ranks in one process, taking turns (for single-GPU tests): same data movement as
-    :func:`run_distributed`, with tensor copies in place of the collectives."""
+    :func:`run_distributed`, with tensor copies in place of the collectives. ``split`` uses the
+    boundary-first / interior-later order of the overlapped driver."""
     world = len(runners)
     for _ in range(outer):
-        sums = [r.compute() for r in runners]
-        faces = [r.faces_out() for r in runners]
+        if split:
+            for r in runners:
+                r.compute_boundary()
+            faces = [r.faces_out(r._nxt) for r in runners]
+            sums = [r.compute_interior() for r in runners]
+        else:
+            sums = [r.compute() for r in runners]
+            faces = [r.faces_out() for r in runners]
         total = torch.stack(sums).sum(0)
         for i, r in enumerate(runners):
             from_left = faces[i - 1][1] if i > 0 else None

@@ -177,14 +177,17 @@ GN_API int gn_step_forward_fused_f32(const float *weight, const float *bias, con
  * on each side that is not updated; only blocks k_block_first .. k_block_first + k_block_count - 1
  * (in units of 8 columns) are computed and written. The last column of the left ghost block and the
  * first column of the right ghost block carry the neighbours' boundary faces (zeros at the ends of
- * the grid) and are read as ordinary halo cells. out_partials holds
- * 4 * (M/8) * (N/8) * k_block_count pairs per sample. No counterpart in the reference (it is
- * single-GPU). */
+ * the grid) and are read as ordinary halo cells. out_partials receives
+ * 4 * (M/8) * (N/8) * k_block_count pairs per sample, laid out [B][partials_per_sample][2];
+ * partials_per_sample = 0 means exactly that count, a larger value lets several launches (for
+ * example boundary blocks first, interior blocks later) fill disjoint parts of one buffer, each
+ * launch being handed out_partials advanced to its first pair. No counterpart in the reference
+ * (it is single-GPU). */
 GN_API int gn_step_forward_slab_f32(const float *weight, const float *bias, const float *scale,
                              const float *x, float *y, const float *gamma, const float *beta,
-                             const float *in_mean_rstd, double *out_partials, int B, int M, int N,
-                             int K, int k_block_first, int k_block_count, int inner,
-                             int activation, void *stream);
+                             const float *in_mean_rstd, double *out_partials, int partials_per_sample,
+                             int B, int M, int N, int K, int k_block_first, int k_block_count,
+                             int inner, int activation, void *stream);
 GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_rstd, int B,
                          long long P, float eps, void *stream);
 GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *beta,
