@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE config 2): 64x64x64 grid, block size 8, 4 inner x 12 outer
+Workload (the headline configuration): 64x64x64 grid, block size 8, 4 inner x 12 outer
 iterations, batch 64 per GPU, float32, forward only, LayerNorm over the whole grid
 after every outer step. Inputs are synthetic: N(0,1) on the [..., 0] face, weights
 N(0, 1/27), bias 0, residual scale 1, gamma 1, beta 0, silu (seeded).
@@ -367,7 +367,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
 
 
 def run_slab(args, rank: int, local_rank: int, world: int):
-    """BASELINE config 5: 256^3 grid, block 8, 2 inner x 32 outer, batch 32, forward, the grid
+    """The large-grid configuration: 256^3 grid, block 8, 2 inner x 32 outer, batch 32, forward, the grid
     slab-sharded along K over all ranks (strong scaling: the total work is fixed)."""
     import torch
 

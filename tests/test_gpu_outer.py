@@ -124,7 +124,7 @@ def test_outer_forward_edge_cases():
 
 
 def test_full_size_properties_c2():
-    """BASELINE config 2 at full size (64^3, block 8, 4 inner x 12 outer, batch 64): too slow
+    """The benchmark configuration at full size (64^3, block 8, 4 inner x 12 outer, batch 64): too slow
     for the scalar oracle in float64 at full batch, so parity is carried by properties."""
     from gridnet_b200 import GridnetCudaOp, GridNormOp, outer_forward
 
