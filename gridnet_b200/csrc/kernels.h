@@ -36,9 +36,22 @@ struct FastFwdParams {
     // neighbour slab's boundary face.
     int kb0, kbn;
     int *error_flag;            // optional device int, set to 1 if a bounded wait on a bulk copy gave up
+    // Replay mode of the backward pass: keep what the reverse sweep needs. save_h [inner][B][M,N,K]
+    // receives every iteration's pre-activation, save_x [inner-1][B][M,N,K] the activations after
+    // iterations 1 .. inner-1 (y may then be nullptr: the final output is not wanted).
+    float *save_h, *save_x;
 };
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize);
 int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st);
+
+// ---- step_bwd_fast.cu (tuned float backward, block 8, normalize off; needs a workspace)
+size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner);
+bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
+                          float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block,
+                          int normalize);
+int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
+                          float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int act,
+                          float *ws, cudaStream_t st);
 
 // ---- step_lanes.cu ("lanes = samples" kernel of the fused loop; activations in the IL16 layout
 // [group][z][y][x][16 samples])

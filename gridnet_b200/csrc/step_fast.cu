@@ -270,6 +270,14 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int i = 0; i < 2; ++i) nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
+            if (p.save_h) {  // replay for the backward pass: pre-activations, and activations between iterations
+                const size_t o = ((size_t)it * p.B + smp) * P + g00;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    *reinterpret_cast<float2 *>(p.save_h + o + (size_t)j * K) = make_float2(acc[j][0], acc[j][1]);
+                    if (!last) *reinterpret_cast<float2 *>(p.save_x + o + (size_t)j * K) = make_float2(nv[j][0], nv[j][1]);
+                }
+            }
             if (!last) {
                 // The two z-planes of a warp would hit the same 16 banks with the same element of
                 // the pair; odd planes store the pair in the other order, so each store instruction
@@ -283,10 +291,12 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                 }
                 __syncthreads();  // the other tile is complete; this one may be overwritten next
             } else {
-                float *ys = p.y + (size_t)smp * P + g00;
+                if (p.y) {
+                    float *ys = p.y + (size_t)smp * P + g00;
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
-                    *reinterpret_cast<float2 *>(ys + (size_t)j * K) = make_float2(nv[j][0], nv[j][1]);
+                    for (int j = 0; j < 2; ++j)
+                        *reinterpret_cast<float2 *>(ys + (size_t)j * K) = make_float2(nv[j][0], nv[j][1]);
+                }
                 if (STATS_OUT) {
                     double sm = 0.0, sq = 0.0;
 #pragma unroll
@@ -316,7 +326,7 @@ bool fast8_applicable(const FastFwdParams &p, int block, int normalize)
     // the per-cell descriptor holds offsets relative to the tile origin in 20 bits
     if ((9LL * p.N + 9) * p.K + 9 >= fast8::kMaxRel) return false;
     auto al = [](const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; };
-    return al(p.w, 8) && al(p.b, 8) && al(p.s, 8) && al(p.x, 4) && al(p.y, 8);
+    return al(p.w, 8) && al(p.b, 8) && al(p.s, 8) && al(p.x, 4) && al(p.y, 8) && al(p.save_h, 8) && al(p.save_x, 8);
 }
 
 int fast8_default_spc(int B, long long nbricks)

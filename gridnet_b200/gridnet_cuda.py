@@ -61,8 +61,22 @@ def backward(weight, bias, scale, initActivations, outGrads, weightGradOut, bias
           ("weight", "bias", "scale", "initActivations", "outGrads", "weightGradOut", "biasGradOut",
            "scaleGradOut", "activationsGradOut"))
     B, M, N, K = initActivations.shape
-    fn = getattr(lib, "gn_step_backward_" + _suffix(weight))
+    sfx = _suffix(weight)
     with torch.cuda.device(weight.device):
+        need = 0
+        if sfx == "f32" and B > 0:
+            need = int(lib.gn_step_backward_workspace_bytes(B, M, N, K, int(innerIterations), int(blockSize),
+                                                            int(bool(normalize)), 4))
+        if need:
+            # scratch for the tuned four-kernel path (torch's caching allocator, stream ordered)
+            ws = torch.empty(need, dtype=torch.uint8, device=weight.device)
+            check(lib.gn_step_backward_ws_f32(
+                weight.data_ptr(), bias.data_ptr(), scale.data_ptr(), initActivations.data_ptr(), outGrads.data_ptr(),
+                weightGradOut.data_ptr(), biasGradOut.data_ptr(), scaleGradOut.data_ptr(),
+                activationsGradOut.data_ptr(), B, M, N, K, int(innerIterations), int(blockSize), float(eps),
+                int(bool(normalize)), activation_id(activation), ws.data_ptr(), ws.numel(), _stream(weight)))
+            return
+        fn = getattr(lib, "gn_step_backward_" + sfx)
         check(fn(weight.data_ptr(), bias.data_ptr(), scale.data_ptr(), initActivations.data_ptr(),
                  outGrads.data_ptr(), weightGradOut.data_ptr(), biasGradOut.data_ptr(),
                  scaleGradOut.data_ptr(), activationsGradOut.data_ptr(), B, M, N, K, int(innerIterations),

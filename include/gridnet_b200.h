@@ -97,6 +97,22 @@ GN_API int gn_step_backward_f64(const double *weight, const double *bias, const 
                          double *grad_bias, double *grad_scale, double *grad_x, int B, int M,
                          int N, int K, int inner, int block, double eps, int normalize,
                          int activation, void *stream);
+/* gn_step_backward_f32 with a scratch buffer. With block 8, normalize = 0 and
+ * gn_step_backward_workspace_bytes(...) bytes of workspace the gradient is computed by the tuned
+ * four-kernel path (replay of the inner iterations, reverse sweep with transposed weights, weight
+ * gradients, cross-block halo terms), which is several times faster than the one-kernel path and
+ * free of floating-point atomics unless the batch has to be split for occupancy. In every other
+ * case (workspace NULL or too small, other block size, normalize = 1) it behaves exactly like
+ * gn_step_backward_f32. gn_step_backward_workspace_bytes returns 0 when the tuned path does not
+ * apply. The workspace holds (3 * inner + 1) * B * M*N*K + 27 * M*N*K floats. */
+GN_API size_t gn_step_backward_workspace_bytes(int B, int M, int N, int K, int inner, int block,
+                                        int normalize, int elem_size);
+GN_API int gn_step_backward_ws_f32(const float *weight, const float *bias, const float *scale,
+                            const float *x, const float *grad_y, float *grad_weight,
+                            float *grad_bias, float *grad_scale, float *grad_x, int B, int M,
+                            int N, int K, int inner, int block, float eps, int normalize,
+                            int activation, void *workspace, size_t workspace_bytes,
+                            void *stream);
 /* Largest `inner` the backward entry points accept for this block size and
  * element size (the per-iteration stash lives in shared memory). */
 GN_API int gn_step_backward_max_inner(int block, int elem_size);
