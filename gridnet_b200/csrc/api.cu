@@ -262,6 +262,11 @@ GN_API int gn_config_set(const char *key, int value)
         g_outer_kernel = value;
         return GN_OK;
     }
+    if (!strcmp(key, "forward_samples_per_cta")) {  // 0: chosen from the grid and batch size
+        if (value < 0) return GN_ERR_UNSUPPORTED;
+        g_fast8_spc_override = value;
+        return GN_OK;
+    }
     return GN_ERR_UNSUPPORTED;
 }
 
@@ -298,6 +303,12 @@ GN_API size_t gn_step_backward_workspace_bytes(int B, int M, int N, int K, int i
     if (elem_size != 4 || block != 8 || normalize || inner < 1 || B <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
     if (M % 8 || N % 8 || K % 8) return 0;
     return align_up(sizeof(float) * bwd_fast8_workspace_floats(B, M, N, K, inner), 256);
+}
+
+GN_API size_t gn_step_backward_error_flag_offset(int B, int M, int N, int K, int inner)
+{
+    if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || inner < 1) return 0;
+    return sizeof(float) * (bwd_fast8_workspace_floats(B, M, N, K, inner) - 4);
 }
 
 GN_API int gn_step_backward_ws_f32(const float *w, const float *b, const float *s, const float *x, const float *gy,

@@ -124,6 +124,22 @@ __device__ __forceinline__ float sqrt_<float>(float v) { return sqrtf(v); }
 template <>
 __device__ __forceinline__ double sqrt_<double>(double v) { return sqrt(v); }
 
+// Global loads that stay where they are written: the compiler may sink an ordinary read-only
+// load past barriers down to its first use, which would put the whole memory latency back on
+// the critical path of the stage the load was issued ahead of.
+__device__ __forceinline__ float ld_pinned(const float *ptr)
+{
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 ld_pinned2(const float *ptr)  // 8-byte aligned
+{
+    float2 v;
+    asm volatile("ld.global.nc.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(ptr) : "memory");
+    return v;
+}
+
 // How many ways to split the batch across CTAs so that the grid fills the GPU.
 inline int pick_batch_chunks(long long grid_blocks, int B, int ctas_per_sm, int min_samples_per_cta = 1)
 {
@@ -135,6 +151,28 @@ inline int pick_batch_chunks(long long grid_blocks, int B, int ctas_per_sm, int 
     if (c < 1) c = 1;
     if (c > 65535) c = 65535;
     return (int)c;
+}
+
+// Splits the batch into chunks so that the CTAs finish in few, evenly filled rounds. The cost of a
+// split is rounds * (samples per chunk + overhead), where a round is one CTA on every resident
+// slot and the overhead is a CTA's fixed work (parameter loads, epilogue) in units of one sample.
+inline int pick_batch_chunks_balanced(long long grid_blocks, int B, int ctas_per_sm, double overhead_samples,
+                                      int max_chunks)
+{
+    const long long slots = (long long)kNumSMs * ctas_per_sm;
+    int best = 1;
+    double best_cost = 1e300;
+    for (int c = 1; c <= max_chunks && c <= B; ++c) {
+        const int spc = (B + c - 1) / c;
+        const int chunks = (B + spc - 1) / spc;
+        const long long rounds = (grid_blocks * chunks + slots - 1) / slots;
+        const double cost = (double)rounds * (spc + overhead_samples);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = chunks;
+        }
+    }
+    return best;
 }
 
 }  // namespace gn

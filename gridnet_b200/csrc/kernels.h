@@ -1,5 +1,6 @@
 // Internal launcher declarations shared by the .cu files and api.cu.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 
@@ -42,7 +43,11 @@ struct FastFwdParams {
     float *save_h, *save_x;
 };
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize);
+extern int g_fast8_spc_override;  // tuning knob: samples per CTA of the tuned forward kernel, 0 = automatic
 int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st);
+// Tensor map for 16 x 10 x 10 tile boxes of a float tensor [B, M, N, K]; false when bulk tensor copies cannot
+// be used (base not 16-byte aligned, K not a multiple of 4, driver entry point missing).
+bool fast8_make_tile_map(CUtensorMap *map, const float *base, int B, int M, int N, int K);
 
 // ---- step_bwd_fast.cu (tuned float backward, block 8, normalize off; needs a workspace)
 size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner);

@@ -15,29 +15,40 @@
 //            into its block, so its gradient only needs the per-neuron SUM of deltas:
 //            dX[c] += sum over neurons n of other blocks with c = n + offset(t) of w[n][t] * Dsum[n].
 //
-// Everything is deterministic (no floating-point atomics) as long as one CTA of wgrad covers a
-// block's whole batch; when the batch is split for occupancy, weight gradients are combined
-// with atomics.
+// Everything is deterministic: there are no floating-point atomics. When wgrad splits a block's
+// batch over several CTAs for occupancy, those CTAs form a thread-block cluster and combine
+// their partial sums through distributed shared memory in a fixed order. The input tiles of
+// wgrad arrive by bulk tensor copy like in the forward kernel; its bounded waits report through
+// the int at the end of the workspace (cleared by the first kernel of the pass).
 //
 // Reference semantics: the gradient of gridnet/backend_torch.py:61-142 with normalize=False;
 // the kernel this stands in for is gridnet_cuda_backward_kernel, src/gridnet_cuda_kernels.cu:202-450.
+#include <cooperative_groups.h>
+#include <string.h>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "tma.cuh"
 
 namespace gn {
+namespace cg = cooperative_groups;
 
 namespace bwd8 {
 constexpr int RS = 12, PS = 120, TS = 1200;  // tile strides, as in step_fast.cu
 constexpr int THREADS = 128;
 constexpr int SLOTS = 8;
+constexpr int STG = 10 * 10 * 16;  // floats of one bulk-copied tile
+constexpr unsigned kSpinLimit = 1u << 18;
+constexpr int RED_UNITS = 58;  // float2 partial sums per thread: 27 taps x 2 rows, bias x 2, scale x 2
 }  // namespace bwd8
 
 // wT[t][c] = w[26 - t][c + offset(t)] when that neighbour is a neuron of c's own block, else 0
 __global__ void __launch_bounds__(256) bwd_transpose_weights_k(const float *__restrict__ w, float *__restrict__ wT,
-                                                               int M, int N, int K)
+                                                               int M, int N, int K, int *error_flag)
 {
     const size_t P = (size_t)M * N * K;
     const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c == 0) *error_flag = 0;  // first kernel of the backward pass: clears the flag of the later bounded waits
     if (c >= P) return;
     const int x = (int)(c % K), y = (int)((c / K) % N), z = (int)(c / ((size_t)K * N));
 #pragma unroll
@@ -59,7 +70,8 @@ struct BwdParams {
     float *dsb;                    // [B][P] per-sample gradient of the residual scale
     float *gw, *gb, *gs, *gx;
     int B, M, N, K, inner, spc;
-    int atomic_params;
+    int *error_flag;     // set to 1 if a bounded wait on a bulk copy gave up
+    int cluster_reduce;  // wgrad: the batch chunks of a block are one cluster and reduce through shared memory
 };
 
 // ---------------------------------------------------------------------------- reverse sweep
@@ -99,20 +111,25 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
     const int toff = z * PS + 2 * yp * RS + 2 * xp;
     const int s0 = blockIdx.y * p.spc, s1 = min(p.B, s0 + p.spc);
     unsigned step = 0;  // picks the delta tile: consecutive iterations (also across samples) alternate
+    // pre-activations of the iteration handled next and the next sample's output gradient are
+    // fetched one iteration early
+    float2 hn[2], gn[2];
+    if (s0 < s1) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            hn[j] = ld_pinned2(p.save_h + ((size_t)(p.inner - 1) * p.B + s0) * P + g00 + (size_t)j * K);
+            gn[j] = ld_pinned2(p.gy + (size_t)s0 * P + g00 + (size_t)j * K);
+        }
+    }
     for (int smp = s0; smp < s1; ++smp) {
         const size_t so = (size_t)smp * P + g00;
         float g[2][2], dsum[2][2], dsacc[2][2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const float2 v = *reinterpret_cast<const float2 *>(p.gy + so + (size_t)j * K);
-            g[j][0] = v.x;
-            g[j][1] = v.y;
+            g[j][0] = gn[j].x;
+            g[j][1] = gn[j].y;
             dsum[j][0] = dsum[j][1] = dsacc[j][0] = dsacc[j][1] = 0.0f;
         }
-        float2 hn[2];  // pre-activations of the iteration handled next, fetched one iteration early
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-            hn[j] = *reinterpret_cast<const float2 *>(p.save_h + ((size_t)(p.inner - 1) * p.B + smp) * P + g00 + (size_t)j * K);
         for (int it = p.inner - 1; it >= 0; --it, ++step) {
             const size_t ho = ((size_t)it * p.B + smp) * P + g00;
             float *Dt = D[step & 1];
@@ -121,7 +138,13 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
             if (it > 0) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                    hn[j] = *reinterpret_cast<const float2 *>(p.save_h + ho - (size_t)p.B * P + (size_t)j * K);
+                    hn[j] = ld_pinned2(p.save_h + ho - (size_t)p.B * P + (size_t)j * K);
+            } else if (smp + 1 < s1) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    hn[j] = ld_pinned2(p.save_h + ((size_t)(p.inner - 1) * p.B + smp + 1) * P + g00 + (size_t)j * K);
+                    gn[j] = ld_pinned2(p.gy + so + P + (size_t)j * K);
+                }
             }
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -178,11 +201,14 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
 }
 
 // ------------------------------------------------------------------------- weight gradients
-template <int DUMMY>
-__global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const BwdParams p)
+template <bool USE_TMA>
+__global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_constant__ CUtensorMap x_map, const BwdParams p)
 {
     using namespace bwd8;
     __shared__ __align__(16) float tiles[2][TS];
+    // USE_TMA: raw 10 x 10 rows of 16 floats (x from 8 bx - 4) of the step input, two samples deep
+    __shared__ __align__(128) float staging[USE_TMA ? 2 : 1][USE_TMA ? STG : 4];
+    __shared__ __align__(8) unsigned long long bars[2];
     const int tid = threadIdx.x;
     const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
     const int nbx = p.K >> 3, nby = p.N >> 3;
@@ -204,7 +230,9 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const BwdParams p
             const int gz = bz * 8 + cz - 1, gy = by * 8 + cy - 1, gx = bx * 8 + cx - 1;
             const int soff = cz * PS + cy * RS + cx;
             const bool halo = cx == 0 || cx == 9 || cy == 0 || cy == 9 || cz == 0 || cz == 9;
-            if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K)
+            if (USE_TMA)  // every cell comes from the staging buffer; the copy zero-fills what lies outside the grid
+                ci = (unsigned)soff | (halo ? 0x800u : 0u) | ((unsigned)((cz * 10 + cy) * 16 + cx + 3) << 12);
+            else if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K)
                 ci = (unsigned)soff | (halo ? 0x800u : 0u) | ((unsigned)((cz * p.N + cy) * K + cx) << 12);
             else {
                 tiles[0][soff] = 0.0f;  // outside the grid: zero for the CTA's whole life
@@ -227,45 +255,68 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const BwdParams p
     // interior cells into tile 0 (iteration 0). Iteration t >= 1 only rewrites the block interior of
     // tile t & 1, every thread its own four cells, from the replayed activations. Loads run one
     // sample (tile cells) resp. one iteration (own activations, deltas) ahead of their use.
-    float pf[SLOTS];
+    float pf[USE_TMA ? 1 : SLOTS];
+    const unsigned bar_base = smem_u32(bars);
     auto fetch_tile = [&](int smp) {
         if (smp < s1) {
-            const float *xs = p.x + (size_t)smp * P + origin;
+            if (USE_TMA) {
+                if (tid == 0) {
+                    const int par = (smp - s0) & 1;
+                    mbar_expect_tx(bar_base + 8 * par, STG * 4);
+                    tma_load_4d(smem_u32(staging[par]), &x_map, bar_base + 8 * par, bx * 8 - 4, by * 8 - 1, bz * 8 - 1,
+                                smp);
+                }
+            } else {
+                const float *xs = p.x + (size_t)smp * P + origin;
 #pragma unroll
-            for (int j = 0; j < SLOTS; ++j)
-                if (cinfo[j] != 0xffffffffu) pf[j] = __ldg(xs + (cinfo[j] >> 12));
+                for (int j = 0; j < SLOTS; ++j)
+                    if (cinfo[j] != 0xffffffffu) pf[j] = ld_pinned(xs + (cinfo[j] >> 12));
+            }
         }
     };
+    if (USE_TMA) {
+        if (tid == 0) {
+            mbar_init(bar_base, 1);
+            mbar_init(bar_base + 8, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            fence_proxy_async();
+        }
+        __syncthreads();
+    }
     float2 xn[2], dn[2];  // own activations and deltas of the step handled next
     auto fetch_step = [&](int smp, int it) {
         if (smp < s1) {
             const size_t o = ((size_t)it * p.B + smp) * P + g00;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                dn[j] = *reinterpret_cast<const float2 *>(p.delta + o + (size_t)j * K);
-                if (it > 0) xn[j] = *reinterpret_cast<const float2 *>(p.save_x + o - (size_t)p.B * P + (size_t)j * K);
+                dn[j] = ld_pinned2(p.delta + o + (size_t)j * K);
+                if (it > 0) xn[j] = ld_pinned2(p.save_x + o - (size_t)p.B * P + (size_t)j * K);
             }
         }
     };
     fetch_tile(s0);
+    if (USE_TMA) fetch_tile(s0 + 1);
     fetch_step(s0, 0);
     for (int smp = s0; smp < s1; ++smp) {
+        float2 dsv[2];  // consumed after the sample's iterations
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const float2 v = *reinterpret_cast<const float2 *>(p.dsb + (size_t)smp * P + g00 + (size_t)j * K);
-            ds[j][0] += v.x;
-            ds[j][1] += v.y;
+        for (int j = 0; j < 2; ++j) dsv[j] = ld_pinned2(p.dsb + (size_t)smp * P + g00 + (size_t)j * K);
+        const int par = (smp - s0) & 1;
+        if (USE_TMA) {
+            if (!mbar_wait_bounded(bar_base + 8 * par, ((smp - s0) >> 1) & 1, kSpinLimit) && p.error_flag)
+                *p.error_flag = 1;
         }
         __syncthreads();  // the previous sample's tiles are no longer read
 #pragma unroll
         for (int j = 0; j < SLOTS; ++j) {
             const unsigned ci = cinfo[j];
             if (ci != 0xffffffffu) {
-                tiles[0][ci & 0x7ff] = pf[j];
-                if (ci & 0x800) tiles[1][ci & 0x7ff] = pf[j];
+                const float v = USE_TMA ? staging[par][ci >> 12] : pf[j];
+                tiles[0][ci & 0x7ff] = v;
+                if (ci & 0x800) tiles[1][ci & 0x7ff] = v;
             }
         }
-        fetch_tile(smp + 1);
+        if (!USE_TMA) fetch_tile(smp + 1);
         for (int it = 0; it < p.inner; ++it) {
             float dl[2][2] = {{dn[0].x, dn[0].y}, {dn[1].x, dn[1].y}};
             float *tl_w = tiles[it & 1];
@@ -285,6 +336,7 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const BwdParams p
                 db[j][1] += dl[j][1];
             }
             __syncthreads();  // tile complete (the other tile may still be read by slower threads)
+            if (USE_TMA && it == 0) fetch_tile(smp + 2);  // everyone has copied this sample's staging buffer
             const float *tl = tl_w + toff;
 #pragma unroll
             for (int a = 0; a < 3; ++a)
@@ -306,22 +358,42 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const BwdParams p
                     }
                 }
         }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            ds[j][0] += dsv[j].x;
+            ds[j][1] += dsv[j].y;
+        }
     }
-    if (p.atomic_params) {
+    if (p.cluster_reduce) {
+        // The chunks of one block form a thread-block cluster. Every CTA parks its partial sums in
+        // its own shared memory; CTA r of the cluster then sums the float2 units u = r, r + size, ...
+        // over all CTAs in rank order through distributed shared memory and stores them: no
+        // atomics, and the result does not depend on scheduling.
+        extern __shared__ __align__(16) float2 red[];  // [RED_UNITS][THREADS]
+        cg::cluster_group cl = cg::this_cluster();
+        const unsigned rank = cl.block_rank(), size = cl.num_blocks();
 #pragma unroll
         for (int t = 0; t < 27; ++t)
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                atomicAdd(p.gw + (size_t)t * P + g00 + (size_t)j * K, dw[t][j][0]);
-                atomicAdd(p.gw + (size_t)t * P + g00 + (size_t)j * K + 1, dw[t][j][1]);
-            }
+            for (int j = 0; j < 2; ++j) red[(t * 2 + j) * THREADS + tid] = make_float2(dw[t][j][0], dw[t][j][1]);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            atomicAdd(p.gb + g00 + (size_t)j * K, db[j][0]);
-            atomicAdd(p.gb + g00 + (size_t)j * K + 1, db[j][1]);
-            atomicAdd(p.gs + g00 + (size_t)j * K, ds[j][0]);
-            atomicAdd(p.gs + g00 + (size_t)j * K + 1, ds[j][1]);
+            red[(54 + j) * THREADS + tid] = make_float2(db[j][0], db[j][1]);
+            red[(56 + j) * THREADS + tid] = make_float2(ds[j][0], ds[j][1]);
         }
+        cl.sync();
+        for (unsigned u = rank; u < RED_UNITS; u += size) {
+            float2 acc = make_float2(0.0f, 0.0f);
+            for (unsigned r = 0; r < size; ++r) {
+                const float2 v = cl.map_shared_rank(red, r)[u * THREADS + tid];
+                acc.x += v.x;
+                acc.y += v.y;
+            }
+            const unsigned j = u & 1;
+            float *dst = u < 54 ? p.gw + (size_t)(u >> 1) * P : (u < 56 ? p.gb : p.gs);
+            *reinterpret_cast<float2 *>(dst + g00 + (size_t)j * K) = acc;
+        }
+        cl.sync();  // no CTA may exit while another still reads its shared memory
     } else {
 #pragma unroll
         for (int t = 0; t < 27; ++t)
@@ -337,39 +409,111 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const BwdParams p
 }
 
 // ------------------------------------------------------------ gradient across block borders
-// One thread per grid cell on a block surface and per batch chunk; a cell is handled by exactly
-// one thread per sample, so grad_x needs no atomics. grid (ceil(P / 256), chunks).
-__global__ void __launch_bounds__(256) bwd_halo8_k(const float *__restrict__ w, const float *__restrict__ dsum,
-                                                   float *__restrict__ gx, int B, int M, int N, int K, int spc)
+// grad_x of a cell on a block surface also receives w[n][t] * dsum[n] from every neuron n of a
+// neighbouring block that reads the cell as a halo cell. One CTA per block and batch chunk, one
+// thread per surface cell (296 of the 512 cells). Per sample the CTA stages the one-voxel shell
+// of dsum around its block in shared memory (the interior of the tile stays zero), and a thread
+// sums all 27 taps from the tile with its weights in registers: taps whose source lies inside the
+// block read a zero. A cell of a sample is handled by exactly one thread: no atomics.
+// The kernel is bound by the load/store unit: the 488 shell cells and 296 grad_x cells of a
+// sample are scattered 4-byte accesses (an x face has one useful float per 32-byte sector).
+// Tried and slower: 4-byte asynchronous copies three samples ahead (each costs several
+// shared-memory wavefronts) and a bulk tensor copy of the whole neighbourhood (its dense rows of
+// 16 floats put all cells of an x face on two shared-memory banks).
+namespace halo8 {
+constexpr int THREADS = 320;
+constexpr int CELLS = 296;
+constexpr int TS = 1000;
+constexpr int SLOTS = 4;  // ceil(1000 / 320) tile cells fetched per thread
+}  // namespace halo8
+
+__global__ void __launch_bounds__(halo8::THREADS) bwd_halo8_k(const float *__restrict__ w, const float *__restrict__ dsum,
+                                                              float *__restrict__ gx, int B, int M, int N, int K, int spc)
 {
+    using namespace halo8;
+    __shared__ float tile[2][TS];
+    const int tid = threadIdx.x;
+    const int nbx = K >> 3, nby = N >> 3;
+    const unsigned blk = blockIdx.x;
+    const int bx = blk % nbx, by = (blk / nbx) % nby, bz = blk / nbx / nby;
     const size_t P = (size_t)M * N * K;
-    const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= P) return;
-    const int x = (int)(c % K), y = (int)((c / K) % N), z = (int)(c / ((size_t)K * N));
-    const int lx = x & 7, ly = y & 7, lz = z & 7;
-    if (lx > 0 && lx < 7 && ly > 0 && ly < 7 && lz > 0 && lz < 7) return;  // no neighbour in another block
+    const long long origin = ((long long)(bz * 8 - 1) * N + (by * 8 - 1)) * K + (bx * 8 - 1);
+
+    for (int i = tid; i < 2 * TS; i += THREADS) (&tile[0][0])[i] = 0.0f;
+
+    // shell cells this thread fetches: bits 0..9 tile offset, bits 10.. offset from the origin
+    unsigned cinfo[SLOTS];
+#pragma unroll
+    for (int j = 0; j < SLOTS; ++j) {
+        const int i = tid + j * THREADS;
+        unsigned ci = 0xffffffffu;
+        if (i < TS) {
+            const int cx = i % 10, cy = (i / 10) % 10, cz = i / 100;
+            const int gz = bz * 8 + cz - 1, gy = by * 8 + cy - 1, gxx = bx * 8 + cx - 1;
+            const bool shell = cx == 0 || cx == 9 || cy == 0 || cy == 9 || cz == 0 || cz == 9;
+            if (shell && gz >= 0 && gz < M && gy >= 0 && gy < N && gxx >= 0 && gxx < K)
+                ci = (unsigned)i | ((unsigned)((cz * N + cy) * K + cx) << 10);
+        }
+        cinfo[j] = ci;
+    }
+
+    // the surface cell of this thread: the two z faces, then the y faces, then the x faces
+    int lz = 0, ly = 0, lx = 0;
+    const bool active = tid < CELLS;
+    if (tid < 128) {
+        lz = (tid >> 6) * 7; ly = (tid >> 3) & 7; lx = tid & 7;
+    } else if (tid < 224) {
+        const int j = tid - 128;
+        ly = (j / 48) * 7; lz = 1 + (j % 48) / 8; lx = j & 7;
+    } else if (active) {
+        const int j = tid - 224;
+        lx = (j / 36) * 7; lz = 1 + (j % 36) / 6; ly = 1 + j % 6;
+    }
+    const int z = bz * 8 + lz, y = by * 8 + ly, x = bx * 8 + lx;
+    const size_t c = ((size_t)z * N + y) * K + x;
     float wd[27];
-    unsigned valid = 0;
 #pragma unroll
     for (int t = 0; t < 27; ++t) {
         // neuron n = c - offset(t) reaches c through its tap t
         const int dz = t / 9 - 1, dy = (t / 3) % 3 - 1, dx = t % 3 - 1;
         const int nz = z - dz, ny = y - dy, nx = x - dx;
-        const bool other = ((nz >> 3) != (z >> 3) || (ny >> 3) != (y >> 3) || (nx >> 3) != (x >> 3)) && nz >= 0 &&
-                           nz < M && ny >= 0 && ny < N && nx >= 0 && nx < K;
-        wd[t] = other ? w[(size_t)t * P + (c - ((long long)dz * N + dy) * K - dx)] : 0.0f;
-        valid |= (other ? 1u : 0u) << t;
+        const bool other = active && ((nz >> 3) != bz || (ny >> 3) != by || (nx >> 3) != bx) && nz >= 0 && nz < M &&
+                           ny >= 0 && ny < N && nx >= 0 && nx < K;
+        wd[t] = other ? w[(size_t)t * P + ((size_t)nz * N + ny) * K + nx] : 0.0f;
     }
-    const int b0 = blockIdx.y * spc, b1 = min(B, b0 + spc);
-    for (int b = b0; b < b1; ++b) {
-        const float *ds = dsum + (size_t)b * P + c;
-        float acc = 0.0f;
+    const int tbase = (lz + 1) * 100 + (ly + 1) * 10 + (lx + 1);
+
+    const int s0 = blockIdx.y * spc, s1 = min(B, s0 + spc);
+    float pf[SLOTS];
+    auto fetch = [&](int smp) {
+        if (smp < s1) {
+            const float *src = dsum + (size_t)smp * P + origin;
 #pragma unroll
-        for (int t = 0; t < 27; ++t) {
-            const int dz = t / 9 - 1, dy = (t / 3) % 3 - 1, dx = t % 3 - 1;
-            if (valid & (1u << t)) acc = fmaf(wd[t], ds[-(((long long)dz * N + dy) * K + dx)], acc);
+            for (int j = 0; j < SLOTS; ++j)
+                if (cinfo[j] != 0xffffffffu) pf[j] = ld_pinned(src + (cinfo[j] >> 10));
         }
-        gx[(size_t)b * P + c] += acc;
+    };
+    fetch(s0);
+    float gnext = 0.0f;
+    if (active && s0 < s1) gnext = gx[(size_t)s0 * P + c];
+    __syncthreads();  // tiles are zeroed
+    for (int smp = s0; smp < s1; ++smp) {
+        float *tl = tile[smp & 1];
+#pragma unroll
+        for (int j = 0; j < SLOTS; ++j)
+            if (cinfo[j] != 0xffffffffu) tl[cinfo[j] & 0x3ff] = pf[j];
+        fetch(smp + 1);
+        float acc = gnext;
+        if (active && smp + 1 < s1) gnext = gx[(size_t)(smp + 1) * P + c];
+        __syncthreads();  // the other tile may still be read by slower threads; it is rewritten after the next barrier
+        if (active) {
+#pragma unroll
+            for (int t = 0; t < 27; ++t) {
+                const int dz = t / 9 - 1, dy = (t / 3) % 3 - 1, dx = t % 3 - 1;
+                acc = fmaf(wd[t], tl[tbase - (dz * 100 + dy * 10 + dx)], acc);
+            }
+            gx[(size_t)smp * P + c] = acc;
+        }
     }
 }
 
@@ -377,7 +521,9 @@ __global__ void __launch_bounds__(256) bwd_halo8_k(const float *__restrict__ w, 
 size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner)
 {
     const size_t P = (size_t)M * N * K, BP = (size_t)B * P;
-    return 27 * P + (size_t)inner * BP + (size_t)(inner > 1 ? inner - 1 : 0) * BP + (size_t)inner * BP + 2 * BP;
+    // transposed weights, pre-activations, activations between iterations, deltas, delta sums,
+    // scale-gradient terms, and 16 bytes whose first int is the error flag of the bounded waits
+    return 27 * P + (size_t)inner * BP + (size_t)(inner > 1 ? inner - 1 : 0) * BP + (size_t)inner * BP + 2 * BP + 4;
 }
 
 bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
@@ -388,6 +534,7 @@ bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const 
     f.w = w; f.b = b; f.s = s; f.x = x;
     f.B = B; f.M = M; f.N = N; f.K = K; f.inner = inner;
     if (!fast8_applicable(f, block, normalize)) return false;
+    if (!encode_tiled_fn()) return false;  // the border kernel fetches its tiles by bulk tensor copy only
     auto al8 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 7) == 0; };
     return al8(gy) && al8(gw) && al8(gb) && al8(gs) && al8(gx) && al8(x);
 }
@@ -403,8 +550,9 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     float *delta = save_x + (size_t)(inner > 1 ? inner - 1 : 0) * BP;
     float *dsum = delta + (size_t)inner * BP;
     float *dsb = dsum + BP;
+    int *error_flag = reinterpret_cast<int *>(dsb + BP);
 
-    bwd_transpose_weights_k<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(w, wT, M, N, K);
+    bwd_transpose_weights_k<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(w, wT, M, N, K, error_flag);
     int rc = check_launch("bwd_transpose_weights");
     if (rc != GN_OK) return rc;
 
@@ -413,6 +561,7 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     f.B = B; f.M = M; f.N = N; f.K = K; f.inner = inner;
     f.save_h = save_h;
     f.save_x = save_x;
+    f.error_flag = error_flag;
     rc = launch_step_fwd_fast8(f, act, st);
     if (rc != GN_OK) return rc;
 
@@ -422,7 +571,7 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     p.delta = delta; p.dsum = dsum; p.dsb = dsb; p.gw = gw; p.gb = gb; p.gs = gs; p.gx = gx;
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
     {
-        const int chunks = pick_batch_chunks(nb, B, 3 * 4, 8);
+        const int chunks = pick_batch_chunks_balanced(nb, B, 3, 1.5, 16);
         p.spc = (B + chunks - 1) / chunks;
         dim3 grid((unsigned)nb, (unsigned)((B + p.spc - 1) / p.spc));
         switch (act) {
@@ -435,30 +584,61 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
         if (rc != GN_OK) return rc;
     }
     {
-        // one CTA per block covers the batch when the grid already fills the GPU (deterministic plain
-        // stores); otherwise the batch is split and the parameter gradients are combined with atomics
-        const int chunks = nb >= 4LL * kNumSMs * 3 ? 1 : pick_batch_chunks(nb, B, 3 * 2, 8);
-        p.spc = (B + chunks - 1) / chunks;
-        dim3 grid((unsigned)nb, (unsigned)((B + p.spc - 1) / p.spc));
-        p.atomic_params = grid.y > 1;
-        if (p.atomic_params) {
-            cudaError_t e = cudaMemsetAsync(gw, 0, sizeof(float) * 27 * P, st);
-            if (e == cudaSuccess) e = cudaMemsetAsync(gb, 0, sizeof(float) * P, st);
-            if (e == cudaSuccess) e = cudaMemsetAsync(gs, 0, sizeof(float) * P, st);
+        // One CTA per block covers the batch when the grid already fills the GPU; otherwise the batch
+        // is split into at most 8 chunks that form a cluster and combine their sums on chip.
+        const int want = nb >= 4LL * kNumSMs * 3 ? 1 : pick_batch_chunks_balanced(nb, B, 3, 2.0, 8);
+        p.spc = (B + want - 1) / want;
+        const unsigned chunks = (unsigned)((B + p.spc - 1) / p.spc);
+        p.cluster_reduce = chunks > 1;
+        CUtensorMap map;
+        memset(&map, 0, sizeof(map));
+        const bool tma = fast8_make_tile_map(&map, x, B, M, N, K);  // tiles by bulk tensor copy whenever x allows it
+        p.error_flag = error_flag;
+        if (!p.cluster_reduce) {
+            if (tma) bwd_wgrad8<true><<<(unsigned)nb, bwd8::THREADS, 0, st>>>(map, p);
+            else bwd_wgrad8<false><<<(unsigned)nb, bwd8::THREADS, 0, st>>>(map, p);
+        } else {
+            const size_t red_bytes = sizeof(float2) * bwd8::RED_UNITS * bwd8::THREADS;
+            static bool attr_set[64] = {};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+                cudaError_t e = cudaFuncSetAttribute(bwd_wgrad8<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_bytes);
+                if (e == cudaSuccess)
+                    e = cudaFuncSetAttribute(bwd_wgrad8<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_bytes);
+                if (e != cudaSuccess) {
+                    record_cuda_error(e, "cudaFuncSetAttribute");
+                    return GN_ERR_CUDA;
+                }
+                if (dev >= 0 && dev < 64) attr_set[dev] = true;
+            }
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)nb, chunks, 1);
+            cfg.blockDim = dim3(bwd8::THREADS, 1, 1);
+            cfg.dynamicSmemBytes = red_bytes;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = chunks;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            cudaError_t e = tma ? cudaLaunchKernelEx(&cfg, bwd_wgrad8<true>, map, p)
+                                : cudaLaunchKernelEx(&cfg, bwd_wgrad8<false>, map, p);
             if (e != cudaSuccess) {
-                record_cuda_error(e, "cudaMemsetAsync");
+                record_cuda_error(e, "bwd_wgrad8 cluster launch");
                 return GN_ERR_CUDA;
             }
         }
-        bwd_wgrad8<0><<<grid, bwd8::THREADS, 0, st>>>(p);
         rc = check_launch("bwd_wgrad8");
         if (rc != GN_OK) return rc;
     }
     {
-        const int chunks = B >= 8 ? 8 : 1;
+        const int chunks = pick_batch_chunks_balanced(nb, B, 3, 8.0, 32);
         const int spc = (B + chunks - 1) / chunks;
-        dim3 grid((unsigned)((P + 255) / 256), (unsigned)((B + spc - 1) / spc));
-        bwd_halo8_k<<<grid, 256, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
+        dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
+        bwd_halo8_k<<<grid, halo8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
     }
     return check_launch("bwd_halo8");
 }

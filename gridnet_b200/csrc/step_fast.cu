@@ -61,16 +61,6 @@ constexpr unsigned kFirstSpecial = kOutside;
 constexpr long long kMaxRel = 1LL << 20;
 }  // namespace fast8
 
-// A global load that stays where it is written: the compiler may sink an ordinary read-only
-// load past barriers down to its first use, which would put the whole memory latency back on
-// the critical path of the next stage.
-__device__ __forceinline__ float ld_pinned(const float *ptr)
-{
-    float v;
-    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr) : "memory");
-    return v;
-}
-
 // INNER_T > 0: the inner iteration count is a compile-time constant (loop unrolled, tile parity
 // folded into addresses); INNER_T == 0: taken from the parameters.
 template <int ACT, bool FUSE_IN, bool STATS_OUT, bool USE_TMA, int INNER_T>
@@ -329,24 +319,27 @@ bool fast8_applicable(const FastFwdParams &p, int block, int normalize)
     return al(p.w, 8) && al(p.b, 8) && al(p.s, 8) && al(p.x, 4) && al(p.y, 8) && al(p.save_h, 8) && al(p.save_x, 8);
 }
 
+int g_fast8_spc_override = 0;
+
 int fast8_default_spc(int B, long long nbricks)
 {
-    // enough CTAs for several waves of 3 CTAs per SM, but at least 8 samples per
-    // CTA (when the batch allows) so that the weight fetch is amortised
-    const int chunks = pick_batch_chunks(nbricks, B, 3 * 4, 8);
+    if (g_fast8_spc_override > 0) return g_fast8_spc_override;
+    // evenly filled rounds of 3 CTAs per SM, but at least 8 samples per CTA (when the batch allows)
+    // so that the weight fetch is amortised
+    const int chunks = pick_batch_chunks_balanced(nbricks, B, fast8::MIN_CTAS, 1.0, B >= 16 ? B / 8 : 1);
     return (B + chunks - 1) / chunks;
 }
 
-// Tensor map over x [B, M, N, K]: dims (fastest first) {K, N, M, B}, box {16, 10, 10, 1}.
-static bool make_x_map(CUtensorMap *map, const FastFwdParams &p)
+// Tensor map over a float tensor [B, M, N, K]: dims (fastest first) {K, N, M, B}, box {16, 10, 10, 1}.
+bool fast8_make_tile_map(CUtensorMap *map, const float *base, int B, int M, int N, int K)
 {
     EncodeTiledFn enc = encode_tiled_fn();
-    if (!enc || (reinterpret_cast<uintptr_t>(p.x) & 15) || (p.K & 3)) return false;
-    const cuuint64_t dims[4] = {(cuuint64_t)p.K, (cuuint64_t)p.N, (cuuint64_t)p.M, (cuuint64_t)p.B};
-    const cuuint64_t strides[3] = {(cuuint64_t)p.K * 4, (cuuint64_t)p.N * p.K * 4, (cuuint64_t)p.M * p.N * p.K * 4};
+    if (!enc || (reinterpret_cast<uintptr_t>(base) & 15) || (K & 3)) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)B};
+    const cuuint64_t strides[3] = {(cuuint64_t)K * 4, (cuuint64_t)N * K * 4, (cuuint64_t)M * N * K * 4};
     const cuuint32_t box[4] = {16, 10, 10, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(p.x), dims, strides, box, estr,
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -365,7 +358,7 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
     const bool fin = p.in_stats != nullptr, sout = p.out_partials != nullptr;
     CUtensorMap map;
     memset(&map, 0, sizeof(map));
-    const bool tma = make_x_map(&map, p);  // tiles by bulk tensor copy whenever x allows it
+    const bool tma = fast8_make_tile_map(&map, p.x, p.B, p.M, p.N, p.K);  // tiles by bulk tensor copy whenever x allows it
 #define ONE_(A, FI, SO)                                                                                   \
     do {                                                                                                  \
         if (tma && p.inner == 4) step_fwd_fast8<A, FI, SO, true, 4><<<grid, fast8::THREADS, 0, st>>>(map, p);  \

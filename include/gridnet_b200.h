@@ -70,7 +70,9 @@ GN_API int gn_version(void);
 /* Process-wide tuning switches (not needed for normal use). Keys:
  *   "outer_kernel": which step kernel gn_outer_forward_f32 uses: 0 = automatic (default),
  *                   1 = the register-patch kernel, 2 = the lanes-of-samples kernel
- *                   (GN_ERR_UNSUPPORTED from gn_outer_forward_f32 when it does not apply). */
+ *                   (GN_ERR_UNSUPPORTED from gn_outer_forward_f32 when it does not apply).
+ *   "forward_samples_per_cta": samples one CTA of the tuned float forward kernel walks through;
+ *                   0 = chosen from the grid and batch size (default). */
 GN_API int gn_config_set(const char *key, int value);
 
 /* ------------------------------------------------------------------ plain step
@@ -98,15 +100,20 @@ GN_API int gn_step_backward_f64(const double *weight, const double *bias, const 
                          int N, int K, int inner, int block, double eps, int normalize,
                          int activation, void *stream);
 /* gn_step_backward_f32 with a scratch buffer. With block 8, normalize = 0 and
- * gn_step_backward_workspace_bytes(...) bytes of workspace the gradient is computed by the tuned
- * four-kernel path (replay of the inner iterations, reverse sweep with transposed weights, weight
- * gradients, cross-block halo terms), which is several times faster than the one-kernel path and
- * free of floating-point atomics unless the batch has to be split for occupancy. In every other
- * case (workspace NULL or too small, other block size, normalize = 1) it behaves exactly like
- * gn_step_backward_f32. gn_step_backward_workspace_bytes returns 0 when the tuned path does not
- * apply. The workspace holds (3 * inner + 1) * B * M*N*K + 27 * M*N*K floats. */
+ * gn_step_backward_workspace_bytes(...) bytes of 16-byte-aligned workspace the gradient is
+ * computed by the tuned four-kernel path (replay of the inner iterations, reverse sweep with
+ * transposed weights, weight gradients, cross-block halo terms), which is about twice as fast as
+ * the one-kernel path and free of floating-point atomics: two calls on the same inputs return
+ * the same bits. In every other case (workspace NULL, misaligned or too small, other block size,
+ * normalize = 1) it behaves exactly like gn_step_backward_f32. gn_step_backward_workspace_bytes
+ * returns 0 when the tuned path does not apply. The workspace holds
+ * (3 * inner + 1) * B * M*N*K + 27 * M*N*K floats and, at byte offset
+ * gn_step_backward_error_flag_offset(...), an int that the call clears and that a kernel sets to
+ * 1 if a bounded wait on a bulk copy gave up (the gradients are then not valid). The inner
+ * iteration count is not limited on this path. */
 GN_API size_t gn_step_backward_workspace_bytes(int B, int M, int N, int K, int inner, int block,
                                         int normalize, int elem_size);
+GN_API size_t gn_step_backward_error_flag_offset(int B, int M, int N, int K, int inner);
 GN_API int gn_step_backward_ws_f32(const float *weight, const float *bias, const float *scale,
                             const float *x, const float *grad_y, float *grad_weight,
                             float *grad_bias, float *grad_scale, float *grad_x, int B, int M,
