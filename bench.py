@@ -437,6 +437,129 @@ def run_slab(args, rank: int, local_rank: int, world: int):
     dist.destroy_process_group()
 
 
+TRAIN_WORKLOADS = {
+    # name: (grid, block, inner, outer, batch, description)
+    "c3": (128, 8, 2, 16, 256, "C3: 128^3 grid, block 8, 2 inner x 16 outer, batch 256, fp32, forward + backward, "
+                                "whole-grid LayerNorm per outer step"),
+    "c4": (64, 4, 8, 16, 128, "C4: 64^3 grid, block 4, 8 inner x 16 outer, batch 128, fp32, forward + backward, "
+                              "whole-grid LayerNorm per outer step"),
+}
+
+
+def run_train(args, rank: int, local_rank: int, world: int):
+    """The forward + backward configurations: one step = the outer loop forward, then the gradient of a
+    seeded random upstream gradient on the final grid back to the parameters and the input, through the
+    autograd ops of the package (the step op and the whole-grid norm op per outer step). The batch is
+    sharded over the ranks (strong scaling); with more than one rank the parameter gradients are
+    all-reduced once per step, inside the timed region."""
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    import gridnet_b200 as gb
+
+    G, block, inner, outer, batch, desc = TRAIN_WORKLOADS[args.workload]
+    if args.batch:
+        batch = args.batch
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+    if batch % world:
+        raise SystemExit(f"batch {batch} does not divide over {world} ranks")
+    b_loc = batch // world
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    g = torch.Generator().manual_seed(0)
+    model = gb.GridnetModel((G, G, G), inner, outer, block, device, activation=ACT)
+    with torch.no_grad():
+        model.network.weight.copy_((torch.randn(27, G, G, G, generator=g) / 27 ** 0.5).to(device))
+    params = [p for p in model.parameters()]
+    gsel = torch.Generator().manual_seed(1 + rank)
+    x = torch.zeros(b_loc, G, G, G, device=device)
+    x[..., 0] = torch.randn(b_loc, G, G, generator=gsel).to(device)
+    x.requires_grad_(True)
+    gy = torch.randn(b_loc, G, G, G, device=device, generator=torch.Generator(device=device).manual_seed(2 + rank))
+
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    t_fwd = t_bwd = 0.0
+
+    def step(timed: bool):
+        nonlocal t_fwd, t_bwd
+        ev[0].record()
+        y = model(x)
+        ev[1].record()
+        grads = torch.autograd.grad(y, params + [x], gy)
+        if dist is not None:
+            flat = torch.cat([t.reshape(-1) for t in grads[:-1]])
+            dist.all_reduce(flat)
+        ev[2].record()
+        if timed:
+            ev[2].synchronize()
+            t_fwd += ev[0].elapsed_time(ev[1])
+            t_bwd += ev[1].elapsed_time(ev[2])
+        return grads
+
+    warm = max(3, args.warmup)  # the first steps also grow torch's allocator cache
+    for _ in range(warm):
+        grads = step(False)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    steps = max(1, min(args.steps, 10))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        grads = step(True)
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    finite = all(bool(torch.isfinite(t_).all().item()) for t_ in grads)
+    if rank == 0:
+        nu = float(batch) * G ** 3 * inner * outer
+        hbm_gbs, hbm_src, _ = measured_peaks()
+        clock_ghz = ((clocks or {}).get("sm_max_mhz") or 1965.0) / 1e3
+        fp32_peak = FP32_LANES * 2 * clock_ghz / 1e3  # TFLOP/s
+        flops = 162.0 * nu / world  # per GPU: 27 forward FMAs and 54 backward FMAs per neuron update
+        # bytes per outer step and GPU: forward 124 P + 8 B P, backward 372 P + 12 B P
+        bytes_step = (124.0 + 372.0) * G ** 3 + 20.0 * b_loc * G ** 3
+        sec = ms * 1e-3 / steps
+        print(json.dumps({
+            "metric": METRIC, "value": nu / sec, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": desc if not args.batch else desc + f" (batch overridden to {batch})",
+                       "global_batch": batch, "parallelism": f"batch-sharded x{world}",
+                       "l2": "activations per outer step (%.0f MB) exceed the 126 MB L2" % (b_loc * G ** 3 * 4 / 1e6),
+                       "forward_ms": t_fwd / steps, "backward_ms": t_bwd / steps, "finite": finite,
+                       "samples_per_sec": batch / sec},
+            "roofline": {"bound": "fp32", "achieved": flops / sec / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
+                         "frac": flops / sec / 1e12 / fp32_peak,
+                         "peak_source": "148 SMs x 128 lanes x 2 x max SM clock (nominal; no measured FP32 peak on file)",
+                         "hbm": {"achieved": bytes_step * outer / sec / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                                 "frac": bytes_step * outer / sec / 1e9 / hbm_gbs,
+                                 "peak_source": hbm_src + " (MEASURED_PEAKS.json hbm_gbs)" if hbm_src == "measured"
+                                 else "fallback"},
+                         "traffic": None},
+            "clocks": clocks,
+        }), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -444,8 +567,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["c2", "c5-slab"], default="c2",
-                    help="c2 (default): the headline benchmark; c5-slab: the 256^3 grid sharded along K over all ranks")
+    ap.add_argument("--workload", choices=["c2", "c5-slab", "c3", "c4"], default="c2",
+                    help="c2 (default): the headline benchmark; c5-slab: the 256^3 grid sharded along K over all ranks; "
+                         "c3 / c4: the forward + backward configurations (128^3 block 8, 64^3 block 4)")
+    ap.add_argument("--batch", type=int, default=0, help="c3 / c4 only: override the global batch size")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -457,6 +582,9 @@ def main():
         return
     if args.workload == "c5-slab":
         run_slab(args, rank, local_rank, world)
+        return
+    if args.workload in TRAIN_WORKLOADS:
+        run_train(args, rank, local_rank, world)
         return
     run_ours(args, rank, local_rank, world)
 

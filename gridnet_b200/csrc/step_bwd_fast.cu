@@ -418,8 +418,9 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
 // The kernel is bound by the load/store unit: the 488 shell cells and 296 grad_x cells of a
 // sample are scattered 4-byte accesses (an x face has one useful float per 32-byte sector).
 // Tried and slower: 4-byte asynchronous copies three samples ahead (each costs several
-// shared-memory wavefronts) and a bulk tensor copy of the whole neighbourhood (its dense rows of
-// 16 floats put all cells of an x face on two shared-memory banks).
+// shared-memory wavefronts), a bulk tensor copy of the whole neighbourhood (its dense rows of
+// 16 floats put all cells of an x face on two shared-memory banks), and skipping the taps whose
+// weight is zero (the per-lane predicates cost more than the loads they save).
 namespace halo8 {
 constexpr int THREADS = 320;
 constexpr int CELLS = 296;

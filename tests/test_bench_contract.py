@@ -5,6 +5,8 @@ import os
 import subprocess
 import sys
 
+import pytest
+
 from conftest import ROOT
 
 
@@ -32,3 +34,18 @@ def test_reference_arm_prints_one_json_line():
 
 def test_reference_arm_other_ranks_print_nothing():
     assert _run({"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"}) == ""
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("workload", ["c3", "c4"])
+def test_training_workloads_print_one_json_line(workload):
+    """The forward + backward workloads at a reduced batch: one JSON line with finite gradients."""
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--workload", workload, "--batch", "4",
+                          "--steps", "1", "--warmup", "1"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    lines = [l for l in out.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["metric"] == "neuron_updates_per_sec" and d["value"] > 0 and d["config"]["finite"]
+    assert d["config"]["forward_ms"] > 0 and d["config"]["backward_ms"] > 0
+    assert workload.upper() in d["config"]["workload"] and d["roofline"]["bound"] == "fp32"
