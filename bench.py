@@ -560,6 +560,76 @@ def run_train(args, rank: int, local_rank: int, world: int):
         dist.destroy_process_group()
 
 
+def run_c1(args, rank: int, local_rank: int, world: int):
+    """The small MNIST-shaped configuration: 32^3 grid, block 8, 2 inner x 8 outer, batch 8, forward. It is
+    bound by launch latency (17 launches of a few microseconds each), so it is timed twice: issued launch by
+    launch, and replayed from a CUDA graph captured once (the fused loop neither allocates nor
+    synchronises, so it can be captured as is)."""
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    import gridnet_b200 as gb
+
+    G, block, inner, outer, B = 32, 8, 2, 8, 8
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(27, G, G, G, generator=g) / 27 ** 0.5).to(device)
+    b = torch.zeros(G, G, G, device=device)
+    s = torch.ones(G, G, G, device=device)
+    gamma, beta = torch.ones(G, G, G, device=device), torch.zeros(G, G, G, device=device)
+    x = torch.zeros(B, G, G, G)
+    x[:, 2:30, 2:30, 0] = torch.rand(B, 28, 28, generator=g)  # image placement of gridnet/scripts/train_mnist.py:59-60
+    x = x.to(device)
+    y = torch.empty_like(x)
+    ws = gb.outer_forward_workspace(B, (G, G, G), block, device)
+
+    def once():
+        gb.outer_forward(w, b, s, gamma, beta, x, inner, outer, block, ACT, out=y, workspace=ws)
+
+    def timed(fn, n):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    steps = max(args.steps, 20)
+    eager_ms = timed(once, steps)
+    eager_out = y.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        once()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        once()
+    graph_ms = timed(graph.replay, steps)
+    same = bool(torch.equal(eager_out, y))
+    failed = gb.outer_forward_failed(ws, B, (G, G, G), block)
+    nu = float(B) * G ** 3 * inner * outer
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": nu / (graph_ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps,
+            "warmup": max(3, args.warmup), "ms_per_step": graph_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "C1: 32^3 grid, block 8, 2 inner x 8 outer, batch 8, fp32, forward + whole-grid "
+                                   "LayerNorm per outer step; replayed from a CUDA graph",
+                       "launch_by_launch_ms": eager_ms, "graph_replay_ms": graph_ms,
+                       "graph_equals_launch_by_launch": same, "device_failure_flag": failed,
+                       "samples_per_sec": B / (graph_ms * 1e-3),
+                       "l2": "working set 4 MB: L2-resident by nature of the configuration"},
+            "gpu_launches": (2 * outer + 1) * steps,
+        }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -567,9 +637,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["c2", "c5-slab", "c3", "c4"], default="c2",
+    ap.add_argument("--workload", choices=["c2", "c5-slab", "c3", "c4", "c1"], default="c2",
                     help="c2 (default): the headline benchmark; c5-slab: the 256^3 grid sharded along K over all ranks; "
-                         "c3 / c4: the forward + backward configurations (128^3 block 8, 64^3 block 4)")
+                         "c3 / c4: the forward + backward configurations (128^3 block 8, 64^3 block 4); "
+                         "c1: the small launch-bound configuration, also replayed from a CUDA graph")
     ap.add_argument("--batch", type=int, default=0, help="c3 / c4 only: override the global batch size")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -585,6 +656,10 @@ def main():
         return
     if args.workload in TRAIN_WORKLOADS:
         run_train(args, rank, local_rank, world)
+        return
+    if args.workload == "c1":
+        if rank == 0:
+            run_c1(args, rank, local_rank, world)
         return
     run_ours(args, rank, local_rank, world)
 

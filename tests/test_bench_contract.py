@@ -49,3 +49,13 @@ def test_training_workloads_print_one_json_line(workload):
     assert d["metric"] == "neuron_updates_per_sec" and d["value"] > 0 and d["config"]["finite"]
     assert d["config"]["forward_ms"] > 0 and d["config"]["backward_ms"] > 0
     assert workload.upper() in d["config"]["workload"] and d["roofline"]["bound"] == "fp32"
+
+
+@pytest.mark.gpu
+def test_small_workload_graph_replay_equals_launch_by_launch():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--workload", "c1", "--steps", "5"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    d = json.loads(out.stdout.strip().splitlines()[-1])
+    assert d["config"]["graph_equals_launch_by_launch"] and not d["config"]["device_failure_flag"]
+    assert d["value"] > 0 and d["gpu_launches"] > 0
