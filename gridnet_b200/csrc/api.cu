@@ -70,7 +70,7 @@ int step_forward<float>(const float *w, const float *b, const float *s, const fl
 {
     FastFwdParams p{};
     p.w = w; p.b = b; p.s = s; p.x = x; p.y = y;
-    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner; p.sub = block;
     if (fast8_applicable(p, block, normalize)) return launch_step_fwd_fast8(p, act, st);
     return launch_step_fwd_generic<float>(w, b, s, x, y, B, M, N, K, inner, block, eps, normalize, act, st);
 }
@@ -417,7 +417,7 @@ GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float 
 
 GN_API int gn_step_stats_partials(int M, int N, int K, int block)
 {
-    if (M <= 0 || N <= 0 || K <= 0 || block != 8 || M % 8 || N % 8 || K % 8) return 0;
+    if (M <= 0 || N <= 0 || K <= 0 || (block != 8 && block != 4) || M % 8 || N % 8 || K % 8) return 0;
     const long long n = (long long)(M / 8) * (N / 8) * (K / 8) * 4;
     return n > 0x7fffffffLL ? 0 : (int)n;
 }
@@ -437,7 +437,7 @@ GN_API int gn_step_forward_fused_f32(const float *w, const float *b, const float
     p.in_stats = reinterpret_cast<const float2 *>(in_mean_rstd);
     p.out_partials = reinterpret_cast<double2 *>(out_partials);
     p.nparts = gn_step_stats_partials(M, N, K, block);
-    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner; p.sub = block;
     if (!fast8_applicable(p, block, 0)) return GN_ERR_UNSUPPORTED;
     if ((in_mean_rstd && reinterpret_cast<uintptr_t>(in_mean_rstd) % 8) ||
         (out_partials && reinterpret_cast<uintptr_t>(out_partials) % 16))
@@ -526,7 +526,7 @@ GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, 
 
     FastFwdParams p{};
     p.w = w; p.b = b; p.s = s; p.gamma = gamma; p.beta = beta;
-    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner; p.sub = block;
     p.x = x; p.y = ws.buf[0];
     const bool fused = fast8_applicable(p, block, 0);
     const int nparts_fused = (int)((long long)(M / 8) * (N / 8) * (K / 8) * 4);

@@ -31,6 +31,7 @@ struct FastFwdParams {
     double2 *out_partials;      // [B][nparts] (sum, sum of squares) of y per warp; nullptr = not wanted
     int nparts;                 // partial slots per sample (= blocks * 4)
     int B, M, N, K, inner;
+    int sub;                    // block size: 8 (also when 0) or 4; a CTA owns an 8 x 8 x 8 region either way
     int spc;                    // samples per CTA; <= 0 picks a default
     // Slab mode: only blocks kb0 .. kb0 + kbn - 1 along K are updated (kbn == 0: all of them). Tile
     // cells in the columns outside that range are read like any other cell, so they can carry a

@@ -37,14 +37,12 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "patch_geo.cuh"
 #include "tma.cuh"
 
 namespace gn {
 
 namespace fast8 {
-constexpr int RS = 12;          // row stride (floats)
-constexpr int PS = 10 * RS;     // plane stride
-constexpr int TS = 10 * PS;     // one tile
 constexpr int THREADS = 128;
 #ifndef GN_F8_MIN_CTAS
 #define GN_F8_MIN_CTAS 3
@@ -52,10 +50,11 @@ constexpr int THREADS = 128;
 constexpr int MIN_CTAS = GN_F8_MIN_CTAS;     // CTAs per SM the register budget is sized for (168 registers per thread)
 constexpr int STG = 10 * 10 * 16;  // floats of one TMA staging buffer
 constexpr unsigned kSpinLimit = 1u << 18;
-constexpr int SLOTS = 8;        // tile cells handled per thread when loading (8 * 128 >= 1000)
-// Per-slot descriptor, one register: bits 0..10 tile offset, bit 11 = halo cell (kept in both
-// ping-pong tiles), bits 12..31 global offset relative to the tile's origin cell.
-constexpr unsigned kSkip = 0xffffffffu;     // slot beyond the 1000 tile cells
+// Per-slot descriptor of a tile cell this thread fetches, one register: low bits tile offset
+// (PatchGeo::SOFF_BITS of them), next bit = halo cell (kept in both ping-pong tiles), the rest
+// the offset of the source: inside the staging buffer, or in global memory relative to the
+// tile's origin cell.
+constexpr unsigned kSkip = 0xffffffffu;     // slot beyond the tile cells
 constexpr unsigned kOutside = 0xfffffffeu;  // cell outside the grid: reads as zero
 constexpr unsigned kFirstSpecial = kOutside;
 constexpr long long kMaxRel = 1LL << 20;
@@ -63,12 +62,22 @@ constexpr long long kMaxRel = 1LL << 20;
 
 // INNER_T > 0: the inner iteration count is a compile-time constant (loop unrolled, tile parity
 // folded into addresses); INNER_T == 0: taken from the parameters.
-template <int ACT, bool FUSE_IN, bool STATS_OUT, bool USE_TMA, int INNER_T>
+// SUB: the block size (8: the CTA's region is one block; 4: eight blocks, each with its own tile).
+template <int SUB, int ACT, bool FUSE_IN, bool STATS_OUT, bool USE_TMA, int INNER_T>
 __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
     step_fwd_fast8(const __grid_constant__ CUtensorMap x_map, const FastFwdParams p)
 {
     using namespace fast8;
-    __shared__ __align__(16) float tiles[2][2][TS];  // [sample parity][ping-pong]
+    using Geo = PatchGeo<SUB>;
+    constexpr int RS = Geo::RS, PS = Geo::PS, TS = Geo::TS, SLOTS = Geo::SLOTS;
+    constexpr unsigned SOFF_MASK = (1u << Geo::SOFF_BITS) - 1, HALO_BIT = 1u << Geo::SOFF_BITS;
+    constexpr int SRC_SHIFT = Geo::SOFF_BITS + 1;
+    static_assert(SUB == 8 || USE_TMA, "block 4 tiles are fetched by bulk tensor copy only");
+    // tiles[sample parity][ping-pong][TS]: static for block 8; for block 4 (41.5 KB, past the 48 KB
+    // static limit together with the rest) in dynamic shared memory
+    __shared__ __align__(16) float tiles_static[SUB == 8 ? 4 * TS : 4];
+    extern __shared__ __align__(16) float tiles_dynamic[];
+    float(*tiles)[2][TS] = reinterpret_cast<float(*)[2][TS]>(SUB == 8 ? tiles_static : tiles_dynamic);
     // USE_TMA: raw 10x10 rows of 16 floats (x from 8*bx - 4, the nearest origin TMA accepts), two samples deep
     __shared__ __align__(128) float staging[USE_TMA ? 2 : 1][USE_TMA ? STG : 4];
     __shared__ __align__(8) unsigned long long bars[2];
@@ -92,20 +101,20 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
         const int i = tid + j * THREADS;
         unsigned ci = kSkip;
         float2 gb = make_float2(0.0f, 0.0f);
-        if (i < 1000) {
-            const int cx = i % 10, cy = (i / 10) % 10, cz = i / 100;
+        if (i < Geo::CELLS) {
+            int soff, cz, cy, cx;
+            bool halo;
+            Geo::cell(i, soff, cz, cy, cx, halo);
             const int gz = bz * 8 + cz - 1, gy = by * 8 + cy - 1, gx = bx * 8 + cx - 1;
-            const int soff = cz * PS + cy * RS + cx;
-            const bool halo = cx == 0 || cx == 9 || cy == 0 || cy == 9 || cz == 0 || cz == 9;
             const bool inside = gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K;
             const int rel = (cz * p.N + cy) * K + cx;
             if (inside && FUSE_IN) gb = make_float2(p.gamma[origin + rel], p.beta[origin + rel]);
             if (USE_TMA) {
                 // every cell is copied from the staging buffer; TMA has zero-filled what lies outside the
                 // grid, and gamma = beta = 0 there keeps it zero through the normalisation
-                ci = (unsigned)soff | (halo ? 0x800u : 0u) | ((unsigned)((cz * 10 + cy) * 16 + cx + 3) << 12);
+                ci = (unsigned)soff | (halo ? HALO_BIT : 0u) | ((unsigned)((cz * 10 + cy) * 16 + cx + 3) << SRC_SHIFT);
             } else if (inside) {
-                ci = (unsigned)soff | (halo ? 0x800u : 0u) | ((unsigned)rel << 12);
+                ci = (unsigned)soff | (halo ? HALO_BIT : 0u) | ((unsigned)rel << SRC_SHIFT);
             } else {
                 ci = kOutside;
                 // cells outside the grid stay zero for the CTA's whole life
@@ -114,7 +123,7 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
             }
         }
         cinfo[j] = ci;
-        if (FUSE_IN) gbtab[i] = gb;
+        if (FUSE_IN && i < SLOTS * THREADS) gbtab[i] = gb;
     }
 
     // ---- this thread's parameters: 4 neurons x (27 weights, bias, scale)
@@ -140,7 +149,7 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
 
     const int s0 = blockIdx.y * p.spc;
     const int s1 = min(p.B, s0 + p.spc);
-    const int toff = z * PS + 2 * yp * RS + 2 * xp;  // window origin of this thread inside a tile
+    const int toff = Geo::window_origin(xp, yp, z);  // window origin of this thread inside a tile
 
     // Software pipeline over the CTA's samples: while sample i iterates on tile set i & 1, the cells
     // of sample i + 1 (fetched into registers during sample i - 1) are normalised and written into the
@@ -164,7 +173,7 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                 const float *xs = p.x + (size_t)smp * P + origin;
 #pragma unroll
                 for (int j = 0; j < SLOTS; ++j)
-                    if (cinfo[j] < kFirstSpecial) pf[j] = ld_pinned(xs + (cinfo[j] >> 12));
+                    if (cinfo[j] < kFirstSpecial) pf[j] = ld_pinned(xs + (cinfo[j] >> SRC_SHIFT));
             }
         }
     };
@@ -181,13 +190,13 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
             for (int j = 0; j < SLOTS; ++j) {
                 const unsigned ci = cinfo[j];
                 if (ci < kFirstSpecial) {
-                    float v = USE_TMA ? staging[par][ci >> 12] : pf[j];
+                    float v = USE_TMA ? staging[par][ci >> SRC_SHIFT] : pf[j];
                     if (FUSE_IN) {
                         const float2 gb = gbtab[tid + j * THREADS];
                         v = fmaf((v - mr.x) * mr.y, gb.x, gb.y);
                     }
-                    tiles[set][0][ci & 0x7ff] = v;
-                    if (ci & 0x800) tiles[set][1][ci & 0x7ff] = v;
+                    tiles[set][0][ci & SOFF_MASK] = v;
+                    if (ci & HALO_BIT) tiles[set][1][ci & SOFF_MASK] = v;
                 }
             }
         }
@@ -311,12 +320,17 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
 // ------------------------------------------------------------------ launcher
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize)
 {
-    if (block != 8 || normalize || p.inner < 1) return false;
+    if ((block != 8 && block != 4) || normalize || p.inner < 1) return false;
+    if (p.M % 8 || p.N % 8 || p.K % 8) return false;  // a CTA owns an 8 x 8 x 8 region also with block 4
     if ((long long)p.M * p.N * p.K >= (1LL << 31)) return false;
     // the per-cell descriptor holds offsets relative to the tile origin in 20 bits
     if ((9LL * p.N + 9) * p.K + 9 >= fast8::kMaxRel) return false;
     auto al = [](const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; };
-    return al(p.w, 8) && al(p.b, 8) && al(p.s, 8) && al(p.x, 4) && al(p.y, 8) && al(p.save_h, 8) && al(p.save_x, 8);
+    if (!(al(p.w, 8) && al(p.b, 8) && al(p.s, 8) && al(p.x, 4) && al(p.y, 8) && al(p.save_h, 8) && al(p.save_x, 8)))
+        return false;
+    // block 4 tiles are fetched by bulk tensor copy only
+    if (block == 4 && (!encode_tiled_fn() || !al(p.x, 16))) return false;
+    return true;
 }
 
 int g_fast8_spc_override = 0;
@@ -359,12 +373,27 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
     CUtensorMap map;
     memset(&map, 0, sizeof(map));
     const bool tma = fast8_make_tile_map(&map, p.x, p.B, p.M, p.N, p.K);  // tiles by bulk tensor copy whenever x allows it
+#define SUB4_(A, FI, SO, IT)                                                                              \
+    do {                                                                                                  \
+        auto kern = step_fwd_fast8<4, A, FI, SO, true, IT>;                                               \
+        const size_t dyn = sizeof(float) * 4 * PatchGeo<4>::TS;                                           \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn); \
+        if (e != cudaSuccess) {                                                                           \
+            record_cuda_error(e, "cudaFuncSetAttribute");                                                 \
+            return GN_ERR_CUDA;                                                                           \
+        }                                                                                                 \
+        kern<<<grid, fast8::THREADS, dyn, st>>>(map, p);                                                  \
+    } while (0)
 #define ONE_(A, FI, SO)                                                                                   \
     do {                                                                                                  \
-        if (tma && p.inner == 4) step_fwd_fast8<A, FI, SO, true, 4><<<grid, fast8::THREADS, 0, st>>>(map, p);  \
-        else if (tma && p.inner == 2) step_fwd_fast8<A, FI, SO, true, 2><<<grid, fast8::THREADS, 0, st>>>(map, p); \
-        else if (tma) step_fwd_fast8<A, FI, SO, true, 0><<<grid, fast8::THREADS, 0, st>>>(map, p);        \
-        else step_fwd_fast8<A, FI, SO, false, 0><<<grid, fast8::THREADS, 0, st>>>(map, p);                \
+        if (p.sub == 4) {                                                                                 \
+            if (!tma) return GN_ERR_UNSUPPORTED;                                                          \
+            if (p.inner == 8) SUB4_(A, FI, SO, 8);                                                        \
+            else SUB4_(A, FI, SO, 0);                                                                     \
+        } else if (tma && p.inner == 4) step_fwd_fast8<8, A, FI, SO, true, 4><<<grid, fast8::THREADS, 0, st>>>(map, p);  \
+        else if (tma && p.inner == 2) step_fwd_fast8<8, A, FI, SO, true, 2><<<grid, fast8::THREADS, 0, st>>>(map, p); \
+        else if (tma) step_fwd_fast8<8, A, FI, SO, true, 0><<<grid, fast8::THREADS, 0, st>>>(map, p);     \
+        else step_fwd_fast8<8, A, FI, SO, false, 0><<<grid, fast8::THREADS, 0, st>>>(map, p);             \
     } while (0)
 #define LAUNCH_(A)                              \
     do {                                        \
@@ -381,6 +410,7 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
     }
 #undef LAUNCH_
 #undef ONE_
+#undef SUB4_
     return check_launch("step_fwd_fast8");
 }
 

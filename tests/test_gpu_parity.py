@@ -39,6 +39,8 @@ def ops():
         ((32, 64, 128), 8, True),
         ((32, 64, 128), 4, True),
         ((32, 16, 8), 4, False),
+        ((24, 16, 32), 4, False),  # tuned block-4 path: eight blocks per CTA region
+        ((12, 4, 20), 4, False),   # sides not multiples of 8: the one-thread-per-neuron kernel
         ((32, 16, 8), 8, False),
         ((32, 64, 128), 8, False),
         ((8, 8, 8), 8, False),
@@ -80,6 +82,20 @@ def test_forward_inner_depth_and_odd_batches(inner, batch):
     ref32 = orc.step_forward(w, b, s, x, inner, 8, 1e-5, False, "silu")
     got = Op.apply(dev(w), dev(b), dev(s), dev(x), inner, 8, 1e-5, False, "silu").cpu().numpy()
     assert_close(got, ref64, ref32, f"inner={inner} B={batch}")
+
+
+@pytest.mark.parametrize("inner", [1, 8, 9])
+@pytest.mark.parametrize("batch", [1, 5])
+def test_forward_block4_inner_depth_and_odd_batches(inner, batch):
+    """Block 4 through the tuned kernel (grid sides multiples of 8): the compile-time inner count 8, a
+    run-time one, and batches that leave CTAs with a single sample."""
+    Op, _ = ops()
+    shape = (16, 24, 8)
+    w, b, s, x = rng_inputs(5, batch, shape, unit_scale=True)
+    ref64 = orc.step_forward(*(a.astype(np.float64) for a in (w, b, s, x)), inner, 4, 1e-5, False, "silu")
+    ref32 = orc.step_forward(w, b, s, x, inner, 4, 1e-5, False, "silu")
+    got = Op.apply(dev(w), dev(b), dev(s), dev(x), inner, 4, 1e-5, False, "silu").cpu().numpy()
+    assert_close(got, ref64, ref32, f"block 4 inner={inner} B={batch}")
 
 
 def test_forward_float64_matches_oracle_tightly():
