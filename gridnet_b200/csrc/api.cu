@@ -300,7 +300,8 @@ GN_API int gn_step_backward_f64(const double *w, const double *b, const double *
 GN_API size_t gn_step_backward_workspace_bytes(int B, int M, int N, int K, int inner, int block, int normalize,
                                                int elem_size)
 {
-    if (elem_size != 4 || block != 8 || normalize || inner < 1 || B <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+    if (elem_size != 4 || (block != 8 && block != 4) || normalize || inner < 1 || B <= 0 || M <= 0 || N <= 0 || K <= 0)
+        return 0;
     if (M % 8 || N % 8 || K % 8) return 0;
     return align_up(sizeof(float) * bwd_fast8_workspace_floats(B, M, N, K, inner), 256);
 }
@@ -322,7 +323,7 @@ GN_API int gn_step_backward_ws_f32(const float *w, const float *b, const float *
     if (B > 0 && need > 0 && workspace && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) % 16) == 0 &&
         w && b && s && x && gy && gw && gb && gs && gx &&
         bwd_fast8_applicable(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, normalize))
-        return launch_step_bwd_fast8(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, act, (float *)workspace,
+        return launch_step_bwd_fast8(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, act, (float *)workspace,
                                      (cudaStream_t)stream);
     return api_step_backward<float>(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, eps, normalize, act,
                                     stream);

@@ -56,7 +56,7 @@ bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const 
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block,
                           int normalize);
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
-                          float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int act,
+                          float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
                           float *ws, cudaStream_t st);
 
 // ---- step_lanes.cu ("lanes = samples" kernel of the fused loop; activations in the IL16 layout

@@ -28,23 +28,22 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "patch_geo.cuh"
 #include "tma.cuh"
 
 namespace gn {
 namespace cg = cooperative_groups;
 
 namespace bwd8 {
-constexpr int RS = 12, PS = 120, TS = 1200;  // tile strides, as in step_fast.cu
 constexpr int THREADS = 128;
-constexpr int SLOTS = 8;
 constexpr int STG = 10 * 10 * 16;  // floats of one bulk-copied tile
 constexpr unsigned kSpinLimit = 1u << 18;
 constexpr int RED_UNITS = 58;  // float2 partial sums per thread: 27 taps x 2 rows, bias x 2, scale x 2
 }  // namespace bwd8
 
-// wT[t][c] = w[26 - t][c + offset(t)] when that neighbour is a neuron of c's own block, else 0
+// wT[t][c] = w[26 - t][c + offset(t)] when that neighbour is a neuron of c's own block (side 1 << bshift), else 0
 __global__ void __launch_bounds__(256) bwd_transpose_weights_k(const float *__restrict__ w, float *__restrict__ wT,
-                                                               int M, int N, int K, int *error_flag)
+                                                               int M, int N, int K, int bshift, int *error_flag)
 {
     const size_t P = (size_t)M * N * K;
     const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -56,7 +55,8 @@ __global__ void __launch_bounds__(256) bwd_transpose_weights_k(const float *__re
         const int dz = t / 9 - 1, dy = (t / 3) % 3 - 1, dx = t % 3 - 1;
         const int nz = z + dz, ny = y + dy, nx = x + dx;
         float v = 0.0f;
-        if ((nz >> 3) == (z >> 3) && (ny >> 3) == (y >> 3) && (nx >> 3) == (x >> 3) && nz >= 0 && ny >= 0 && nx >= 0)
+        if ((nz >> bshift) == (z >> bshift) && (ny >> bshift) == (y >> bshift) && (nx >> bshift) == (x >> bshift) &&
+            nz >= 0 && ny >= 0 && nx >= 0)
             v = w[(size_t)(26 - t) * P + ((size_t)nz * N + ny) * K + nx];
         wT[(size_t)t * P + c] = v;
     }
@@ -75,10 +75,12 @@ struct BwdParams {
 };
 
 // ---------------------------------------------------------------------------- reverse sweep
-template <int ACT>
+template <int SUB, int ACT>
 __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams p)
 {
     using namespace bwd8;
+    using Geo = PatchGeo<SUB>;
+    constexpr int RS = Geo::RS, PS = Geo::PS, TS = Geo::TS;
     __shared__ __align__(16) float D[2][TS];
     const int tid = threadIdx.x;
     const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
     for (int i = tid; i < 2 * TS; i += THREADS) (&D[0][0])[i] = 0.0f;  // the halo of both tiles stays zero
     __syncthreads();
 
-    const int toff = z * PS + 2 * yp * RS + 2 * xp;
+    const int toff = Geo::window_origin(xp, yp, z);
     const int s0 = blockIdx.y * p.spc, s1 = min(p.B, s0 + p.spc);
     unsigned step = 0;  // picks the delta tile: consecutive iterations (also across samples) alternate
     // pre-activations of the iteration handled next and the next sample's output gradient are
@@ -201,14 +203,21 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
 }
 
 // ------------------------------------------------------------------------- weight gradients
-template <bool USE_TMA>
+template <int SUB, bool USE_TMA>
 __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_constant__ CUtensorMap x_map, const BwdParams p)
 {
     using namespace bwd8;
+    using Geo = PatchGeo<SUB>;
+    constexpr int RS = Geo::RS, PS = Geo::PS, TS = Geo::TS, SLOTS = Geo::SLOTS;
+    constexpr unsigned SOFF_MASK = (1u << Geo::SOFF_BITS) - 1, HALO_BIT = 1u << Geo::SOFF_BITS;
+    constexpr int SRC_SHIFT = Geo::SOFF_BITS + 1;
+    constexpr bool CI_SMEM = SUB == 4;  // 14 cell descriptors per thread do not fit beside 108 accumulators
+    static_assert(SUB == 8 || USE_TMA, "block 4 tiles are fetched by bulk tensor copy only");
     __shared__ __align__(16) float tiles[2][TS];
     // USE_TMA: raw 10 x 10 rows of 16 floats (x from 8 bx - 4) of the step input, two samples deep
     __shared__ __align__(128) float staging[USE_TMA ? 2 : 1][USE_TMA ? STG : 4];
     __shared__ __align__(8) unsigned long long bars[2];
+    __shared__ unsigned ctab[CI_SMEM ? SLOTS * THREADS : 1];
     const int tid = threadIdx.x;
     const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
     const int nbx = p.K >> 3, nby = p.N >> 3;
@@ -219,28 +228,30 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
     const size_t g00 = ((size_t)(bz * 8 + z) * p.N + (by * 8 + 2 * yp)) * K + (bx * 8 + 2 * xp);
     const long long origin = ((long long)(bz * 8 - 1) * p.N + (by * 8 - 1)) * K + (bx * 8 - 1);
 
-    // tile cells this thread fetches: bits 0..10 tile offset, bit 11 halo, bits 12.. offset from the origin
-    unsigned cinfo[SLOTS];
+    // tile cells this thread fetches: low bits tile offset, then the halo bit, then the source offset
+    unsigned cinfo[CI_SMEM ? 1 : SLOTS];
 #pragma unroll
     for (int j = 0; j < SLOTS; ++j) {
         const int i = tid + j * THREADS;
         unsigned ci = 0xffffffffu;
-        if (i < 1000) {
-            const int cx = i % 10, cy = (i / 10) % 10, cz = i / 100;
+        if (i < Geo::CELLS) {
+            int soff, cz, cy, cx;
+            bool halo;
+            Geo::cell(i, soff, cz, cy, cx, halo);
             const int gz = bz * 8 + cz - 1, gy = by * 8 + cy - 1, gx = bx * 8 + cx - 1;
-            const int soff = cz * PS + cy * RS + cx;
-            const bool halo = cx == 0 || cx == 9 || cy == 0 || cy == 9 || cz == 0 || cz == 9;
             if (USE_TMA)  // every cell comes from the staging buffer; the copy zero-fills what lies outside the grid
-                ci = (unsigned)soff | (halo ? 0x800u : 0u) | ((unsigned)((cz * 10 + cy) * 16 + cx + 3) << 12);
+                ci = (unsigned)soff | (halo ? HALO_BIT : 0u) | ((unsigned)((cz * 10 + cy) * 16 + cx + 3) << SRC_SHIFT);
             else if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K)
-                ci = (unsigned)soff | (halo ? 0x800u : 0u) | ((unsigned)((cz * p.N + cy) * K + cx) << 12);
+                ci = (unsigned)soff | (halo ? HALO_BIT : 0u) | ((unsigned)((cz * p.N + cy) * K + cx) << SRC_SHIFT);
             else {
                 tiles[0][soff] = 0.0f;  // outside the grid: zero for the CTA's whole life
                 tiles[1][soff] = 0.0f;
             }
         }
-        cinfo[j] = ci;
+        if (CI_SMEM) ctab[i] = ci;
+        else cinfo[CI_SMEM ? 0 : j] = ci;
     }
+    auto cell_info = [&](int j) { return CI_SMEM ? ctab[tid + j * THREADS] : cinfo[CI_SMEM ? 0 : j]; };
     float dw[27][2][2];
 #pragma unroll
     for (int t = 0; t < 27; ++t)
@@ -249,7 +260,7 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
     float db[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}}, ds[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
     __syncthreads();
 
-    const int toff = z * PS + 2 * yp * RS + 2 * xp;
+    const int toff = Geo::window_origin(xp, yp, z);
     const int s0 = blockIdx.y * p.spc, s1 = min(p.B, s0 + p.spc);
     // Per sample the whole input tile is written once: halo cells into both tiles (they never change),
     // interior cells into tile 0 (iteration 0). Iteration t >= 1 only rewrites the block interior of
@@ -270,7 +281,7 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
                 const float *xs = p.x + (size_t)smp * P + origin;
 #pragma unroll
                 for (int j = 0; j < SLOTS; ++j)
-                    if (cinfo[j] != 0xffffffffu) pf[j] = ld_pinned(xs + (cinfo[j] >> 12));
+                    if (cell_info(j) != 0xffffffffu) pf[j] = ld_pinned(xs + (cell_info(j) >> SRC_SHIFT));
             }
         }
     };
@@ -309,11 +320,11 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
         __syncthreads();  // the previous sample's tiles are no longer read
 #pragma unroll
         for (int j = 0; j < SLOTS; ++j) {
-            const unsigned ci = cinfo[j];
+            const unsigned ci = cell_info(j);
             if (ci != 0xffffffffu) {
-                const float v = USE_TMA ? staging[par][ci >> 12] : pf[j];
-                tiles[0][ci & 0x7ff] = v;
-                if (ci & 0x800) tiles[1][ci & 0x7ff] = v;
+                const float v = USE_TMA ? staging[par][ci >> SRC_SHIFT] : pf[USE_TMA ? 0 : j];
+                tiles[0][ci & SOFF_MASK] = v;
+                if (ci & HALO_BIT) tiles[1][ci & SOFF_MASK] = v;
             }
         }
         if (!USE_TMA) fetch_tile(smp + 1);
@@ -421,17 +432,26 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
 // shared-memory wavefronts), a bulk tensor copy of the whole neighbourhood (its dense rows of
 // 16 floats put all cells of an x face on two shared-memory banks), and skipping the taps whose
 // weight is zero (the per-lane predicates cost more than the loads they save).
-namespace halo8 {
-constexpr int THREADS = 320;
-constexpr int CELLS = 296;
-constexpr int TS = 1000;
-constexpr int SLOTS = 4;  // ceil(1000 / 320) tile cells fetched per thread
-}  // namespace halo8
+// With block size 4 the CTA still owns an 8 x 8 x 8 region (eight blocks): one thread per cell, 448
+// of the 512 lie on a block surface, and the whole 10 x 10 x 10 neighbourhood of dsum is staged
+// because neighbouring blocks of the same region feed each other too.
+template <int SUB>
+struct HaloGeo;
+template <>
+struct HaloGeo<8> {
+    static constexpr int THREADS = 320, SLOTS = 4;  // 296 surface cells; ceil(1000 / 320) tile cells fetched per thread
+};
+template <>
+struct HaloGeo<4> {
+    static constexpr int THREADS = 512, SLOTS = 2;
+};
 
-__global__ void __launch_bounds__(halo8::THREADS) bwd_halo8_k(const float *__restrict__ w, const float *__restrict__ dsum,
-                                                              float *__restrict__ gx, int B, int M, int N, int K, int spc)
+template <int SUB>
+__global__ void __launch_bounds__(HaloGeo<SUB>::THREADS) bwd_halo8_k(const float *__restrict__ w, const float *__restrict__ dsum,
+                                                                     float *__restrict__ gx, int B, int M, int N, int K, int spc)
 {
-    using namespace halo8;
+    constexpr int THREADS = HaloGeo<SUB>::THREADS, SLOTS = HaloGeo<SUB>::SLOTS, TS = 1000;
+    constexpr int SH = SUB == 8 ? 3 : 2;
     __shared__ float tile[2][TS];
     const int tid = threadIdx.x;
     const int nbx = K >> 3, nby = N >> 3;
@@ -442,7 +462,7 @@ __global__ void __launch_bounds__(halo8::THREADS) bwd_halo8_k(const float *__res
 
     for (int i = tid; i < 2 * TS; i += THREADS) (&tile[0][0])[i] = 0.0f;
 
-    // shell cells this thread fetches: bits 0..9 tile offset, bits 10.. offset from the origin
+    // neighbourhood cells this thread fetches: bits 0..9 tile offset, bits 10.. offset from the origin
     unsigned cinfo[SLOTS];
 #pragma unroll
     for (int j = 0; j < SLOTS; ++j) {
@@ -451,24 +471,32 @@ __global__ void __launch_bounds__(halo8::THREADS) bwd_halo8_k(const float *__res
         if (i < TS) {
             const int cx = i % 10, cy = (i / 10) % 10, cz = i / 100;
             const int gz = bz * 8 + cz - 1, gy = by * 8 + cy - 1, gxx = bx * 8 + cx - 1;
-            const bool shell = cx == 0 || cx == 9 || cy == 0 || cy == 9 || cz == 0 || cz == 9;
-            if (shell && gz >= 0 && gz < M && gy >= 0 && gy < N && gxx >= 0 && gxx < K)
+            // block 8: only the shell is ever read with a non-zero weight, and the interior must stay zero
+            const bool wanted = SUB == 4 || cx == 0 || cx == 9 || cy == 0 || cy == 9 || cz == 0 || cz == 9;
+            if (wanted && gz >= 0 && gz < M && gy >= 0 && gy < N && gxx >= 0 && gxx < K)
                 ci = (unsigned)i | ((unsigned)((cz * N + cy) * K + cx) << 10);
         }
         cinfo[j] = ci;
     }
 
-    // the surface cell of this thread: the two z faces, then the y faces, then the x faces
+    // the cell of this thread inside the region
     int lz = 0, ly = 0, lx = 0;
-    const bool active = tid < CELLS;
-    if (tid < 128) {
-        lz = (tid >> 6) * 7; ly = (tid >> 3) & 7; lx = tid & 7;
-    } else if (tid < 224) {
-        const int j = tid - 128;
-        ly = (j / 48) * 7; lz = 1 + (j % 48) / 8; lx = j & 7;
-    } else if (active) {
-        const int j = tid - 224;
-        lx = (j / 36) * 7; lz = 1 + (j % 36) / 6; ly = 1 + j % 6;
+    bool active;
+    if (SUB == 8) {  // surface cells only: the two z faces, then the y faces, then the x faces
+        active = tid < 296;
+        if (tid < 128) {
+            lz = (tid >> 6) * 7; ly = (tid >> 3) & 7; lx = tid & 7;
+        } else if (tid < 224) {
+            const int j = tid - 128;
+            ly = (j / 48) * 7; lz = 1 + (j % 48) / 8; lx = j & 7;
+        } else if (active) {
+            const int j = tid - 224;
+            lx = (j / 36) * 7; lz = 1 + (j % 36) / 6; ly = 1 + j % 6;
+        }
+    } else {
+        lz = tid >> 6; ly = (tid >> 3) & 7; lx = tid & 7;
+        const int qz = lz & 3, qy = ly & 3, qx = lx & 3;
+        active = !(qz > 0 && qz < 3 && qy > 0 && qy < 3 && qx > 0 && qx < 3);  // the 2^3 core of a block has no outside neighbour
     }
     const int z = bz * 8 + lz, y = by * 8 + ly, x = bx * 8 + lx;
     const size_t c = ((size_t)z * N + y) * K + x;
@@ -478,8 +506,8 @@ __global__ void __launch_bounds__(halo8::THREADS) bwd_halo8_k(const float *__res
         // neuron n = c - offset(t) reaches c through its tap t
         const int dz = t / 9 - 1, dy = (t / 3) % 3 - 1, dx = t % 3 - 1;
         const int nz = z - dz, ny = y - dy, nx = x - dx;
-        const bool other = active && ((nz >> 3) != bz || (ny >> 3) != by || (nx >> 3) != bx) && nz >= 0 && nz < M &&
-                           ny >= 0 && ny < N && nx >= 0 && nx < K;
+        const bool other = active && ((nz >> SH) != (z >> SH) || (ny >> SH) != (y >> SH) || (nx >> SH) != (x >> SH)) &&
+                           nz >= 0 && nz < M && ny >= 0 && ny < N && nx >= 0 && nx < K;
         wd[t] = other ? w[(size_t)t * P + ((size_t)nz * N + ny) * K + nx] : 0.0f;
     }
     const int tbase = (lz + 1) * 100 + (ly + 1) * 10 + (lx + 1);
@@ -535,13 +563,59 @@ bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const 
     f.w = w; f.b = b; f.s = s; f.x = x;
     f.B = B; f.M = M; f.N = N; f.K = K; f.inner = inner;
     if (!fast8_applicable(f, block, normalize)) return false;
-    if (!encode_tiled_fn()) return false;  // the border kernel fetches its tiles by bulk tensor copy only
     auto al8 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 7) == 0; };
     return al8(gy) && al8(gw) && al8(gb) && al8(gs) && al8(gx) && al8(x);
 }
 
+// wgrad launch for one instantiation: plain when one CTA covers a block's batch, otherwise the
+// batch chunks of a block as one thread-block cluster
+template <int SUB, bool USE_TMA>
+static int launch_wgrad(const CUtensorMap &map, const BwdParams &p, long long nb, unsigned chunks, cudaStream_t st)
+{
+    auto kern = bwd_wgrad8<SUB, USE_TMA>;
+    if (chunks <= 1) {
+        kern<<<(unsigned)nb, bwd8::THREADS, 0, st>>>(map, p);
+        return GN_OK;
+    }
+    const size_t red_bytes = sizeof(float2) * bwd8::RED_UNITS * bwd8::THREADS;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_bytes);
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "cudaFuncSetAttribute");
+        return GN_ERR_CUDA;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)nb, chunks, 1);
+    cfg.blockDim = dim3(bwd8::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = red_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = chunks;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, map, p);
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "bwd_wgrad8 cluster launch");
+        return GN_ERR_CUDA;
+    }
+    return GN_OK;
+}
+
+template <int SUB>
+static void launch_reverse(const BwdParams &p, dim3 grid, int act, cudaStream_t st)
+{
+    switch (act) {
+    case GN_ACT_RELU: bwd_reverse8<SUB, GN_ACT_RELU><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+    case GN_ACT_LEAKY_RELU: bwd_reverse8<SUB, GN_ACT_LEAKY_RELU><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+    case GN_ACT_SILU: bwd_reverse8<SUB, GN_ACT_SILU><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+    default: bwd_reverse8<SUB, GN_ACT_TANH><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+    }
+}
+
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
-                          float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int act,
+                          float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
                           float *ws, cudaStream_t st)
 {
     const size_t P = (size_t)M * N * K, BP = (size_t)B * P;
@@ -553,39 +627,36 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     float *dsb = dsum + BP;
     int *error_flag = reinterpret_cast<int *>(dsb + BP);
 
-    bwd_transpose_weights_k<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(w, wT, M, N, K, error_flag);
+    bwd_transpose_weights_k<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(w, wT, M, N, K, block == 4 ? 2 : 3, error_flag);
     int rc = check_launch("bwd_transpose_weights");
     if (rc != GN_OK) return rc;
 
     FastFwdParams f{};
     f.w = w; f.b = b; f.s = s; f.x = x; f.y = nullptr;
-    f.B = B; f.M = M; f.N = N; f.K = K; f.inner = inner;
+    f.B = B; f.M = M; f.N = N; f.K = K; f.inner = inner; f.sub = block;
     f.save_h = save_h;
     f.save_x = save_x;
     f.error_flag = error_flag;
     rc = launch_step_fwd_fast8(f, act, st);
     if (rc != GN_OK) return rc;
 
-    const long long nb = (long long)(M / 8) * (N / 8) * (K / 8);
+    const long long nb = (long long)(M / 8) * (N / 8) * (K / 8);  // 8^3 regions, one CTA (per batch chunk) each
     BwdParams p{};
     p.w = w; p.wT = wT; p.s = s; p.x = x; p.gy = gy; p.save_h = save_h; p.save_x = save_x;
     p.delta = delta; p.dsum = dsum; p.dsb = dsb; p.gw = gw; p.gb = gb; p.gs = gs; p.gx = gx;
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
+    p.error_flag = error_flag;
     {
         const int chunks = pick_batch_chunks_balanced(nb, B, 3, 1.5, 16);
         p.spc = (B + chunks - 1) / chunks;
         dim3 grid((unsigned)nb, (unsigned)((B + p.spc - 1) / p.spc));
-        switch (act) {
-        case GN_ACT_RELU: bwd_reverse8<GN_ACT_RELU><<<grid, bwd8::THREADS, 0, st>>>(p); break;
-        case GN_ACT_LEAKY_RELU: bwd_reverse8<GN_ACT_LEAKY_RELU><<<grid, bwd8::THREADS, 0, st>>>(p); break;
-        case GN_ACT_SILU: bwd_reverse8<GN_ACT_SILU><<<grid, bwd8::THREADS, 0, st>>>(p); break;
-        default: bwd_reverse8<GN_ACT_TANH><<<grid, bwd8::THREADS, 0, st>>>(p); break;
-        }
+        if (block == 4) launch_reverse<4>(p, grid, act, st);
+        else launch_reverse<8>(p, grid, act, st);
         rc = check_launch("bwd_reverse8");
         if (rc != GN_OK) return rc;
     }
     {
-        // One CTA per block covers the batch when the grid already fills the GPU; otherwise the batch
+        // One CTA per region covers the batch when the grid already fills the GPU; otherwise the batch
         // is split into at most 8 chunks that form a cluster and combine their sums on chip.
         const int want = nb >= 4LL * kNumSMs * 3 ? 1 : pick_batch_chunks_balanced(nb, B, 3, 2.0, 8);
         p.spc = (B + want - 1) / want;
@@ -594,44 +665,15 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
         CUtensorMap map;
         memset(&map, 0, sizeof(map));
         const bool tma = fast8_make_tile_map(&map, x, B, M, N, K);  // tiles by bulk tensor copy whenever x allows it
-        p.error_flag = error_flag;
-        if (!p.cluster_reduce) {
-            if (tma) bwd_wgrad8<true><<<(unsigned)nb, bwd8::THREADS, 0, st>>>(map, p);
-            else bwd_wgrad8<false><<<(unsigned)nb, bwd8::THREADS, 0, st>>>(map, p);
+        if (block == 4) {
+            if (!tma) return GN_ERR_UNSUPPORTED;  // excluded by bwd_fast8_applicable
+            rc = launch_wgrad<4, true>(map, p, nb, chunks, st);
+        } else if (tma) {
+            rc = launch_wgrad<8, true>(map, p, nb, chunks, st);
         } else {
-            const size_t red_bytes = sizeof(float2) * bwd8::RED_UNITS * bwd8::THREADS;
-            static bool attr_set[64] = {};
-            int dev = 0;
-            cudaGetDevice(&dev);
-            if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-                cudaError_t e = cudaFuncSetAttribute(bwd_wgrad8<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_bytes);
-                if (e == cudaSuccess)
-                    e = cudaFuncSetAttribute(bwd_wgrad8<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_bytes);
-                if (e != cudaSuccess) {
-                    record_cuda_error(e, "cudaFuncSetAttribute");
-                    return GN_ERR_CUDA;
-                }
-                if (dev >= 0 && dev < 64) attr_set[dev] = true;
-            }
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3((unsigned)nb, chunks, 1);
-            cfg.blockDim = dim3(bwd8::THREADS, 1, 1);
-            cfg.dynamicSmemBytes = red_bytes;
-            cfg.stream = st;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeClusterDimension;
-            attr[0].val.clusterDim.x = 1;
-            attr[0].val.clusterDim.y = chunks;
-            attr[0].val.clusterDim.z = 1;
-            cfg.attrs = attr;
-            cfg.numAttrs = 1;
-            cudaError_t e = tma ? cudaLaunchKernelEx(&cfg, bwd_wgrad8<true>, map, p)
-                                : cudaLaunchKernelEx(&cfg, bwd_wgrad8<false>, map, p);
-            if (e != cudaSuccess) {
-                record_cuda_error(e, "bwd_wgrad8 cluster launch");
-                return GN_ERR_CUDA;
-            }
+            rc = launch_wgrad<8, false>(map, p, nb, chunks, st);
         }
+        if (rc != GN_OK) return rc;
         rc = check_launch("bwd_wgrad8");
         if (rc != GN_OK) return rc;
     }
@@ -639,7 +681,8 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
         const int chunks = pick_batch_chunks_balanced(nb, B, 3, 8.0, 32);
         const int spc = (B + chunks - 1) / chunks;
         dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
-        bwd_halo8_k<<<grid, halo8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
+        if (block == 4) bwd_halo8_k<4><<<grid, HaloGeo<4>::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
+        else bwd_halo8_k<8><<<grid, HaloGeo<8>::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
     }
     return check_launch("bwd_halo8");
 }

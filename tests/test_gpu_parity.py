@@ -341,10 +341,11 @@ def test_forward_with_unaligned_activations_uses_the_plain_load_path():
     assert_close(got_aligned.cpu().numpy(), ref64, None, "unaligned x")
 
 
-def test_tuned_backward_equals_one_kernel_backward():
-    """float32, block 8, normalize off: the four-kernel path (with workspace) against the one-kernel
-    path (without) and the float64 oracle, on a grid with interior, face, edge and corner blocks, an
-    odd batch, and through the C ABI directly."""
+@pytest.mark.parametrize("block", [8, 4])
+def test_tuned_backward_equals_one_kernel_backward(block):
+    """float32, normalize off: the four-kernel path (with workspace) against the one-kernel path
+    (without) and the float64 oracle, on a grid with interior, face, edge and corner blocks, an odd
+    batch, and through the C ABI directly."""
     from gridnet_b200._lib import lib
 
     shape, B, inner = (24, 16, 32), 5, 3
@@ -352,8 +353,8 @@ def test_tuned_backward_equals_one_kernel_backward():
     b = (0.1 * np.random.default_rng(42).standard_normal(shape)).astype(np.float32)
     s = (1 + 0.1 * np.random.default_rng(43).standard_normal(shape)).astype(np.float32)
     gy = np.random.default_rng(44).standard_normal(x.shape).astype(np.float32)
-    want = orc.step_backward(*(a.astype(np.float64) for a in (w, b, s, x, gy)), inner, 8, 1e-5, False, "silu")
-    noise = orc.step_backward(w, b, s, x, gy, inner, 8, 1e-5, False, "silu")
+    want = orc.step_backward(*(a.astype(np.float64) for a in (w, b, s, x, gy)), inner, block, 1e-5, False, "silu")
+    noise = orc.step_backward(w, b, s, x, gy, inner, block, 1e-5, False, "silu")
     tw, tb, ts, tx, tgy = (dev(a) for a in (w, b, s, x, gy))
     M, N, K = shape
     stream = torch.cuda.current_stream().cuda_stream
@@ -362,13 +363,13 @@ def test_tuned_backward_equals_one_kernel_backward():
         g = [torch.full_like(t, 3.0) for t in (tw, tb, ts, tx)]
         if tag == "plain":
             rc = lib.gn_step_backward_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), tgy.data_ptr(),
-                                          *(t.data_ptr() for t in g), B, M, N, K, inner, 8, 1e-5, 0, 2, stream)
+                                          *(t.data_ptr() for t in g), B, M, N, K, inner, block, 1e-5, 0, 2, stream)
         else:
-            need = lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, 8, 0, 4)
+            need = lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, block, 0, 4)
             assert need > 0
             ws = torch.empty(need, dtype=torch.uint8, device="cuda")
             rc = lib.gn_step_backward_ws_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), tgy.data_ptr(),
-                                             *(t.data_ptr() for t in g), B, M, N, K, inner, 8, 1e-5, 0, 2,
+                                             *(t.data_ptr() for t in g), B, M, N, K, inner, block, 1e-5, 0, 2,
                                              ws.data_ptr(), ws.numel(), stream)
         assert rc == 0, lib.gn_status_string(rc)
         outs[tag] = [t.cpu().numpy() for t in g]
@@ -384,5 +385,7 @@ def test_tuned_backward_equals_one_kernel_backward():
     # order), so two runs agree bit for bit
     for name, a, a2 in zip(("gw", "gb", "gs", "gx"), outs["tuned"], outs["tuned again"]):
         assert np.array_equal(a, a2), name
-    assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, 4, 0, 4) == 0
-    assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, 8, 1, 4) == 0
+    # no tuned path: sides that are not multiples of 8, per-block normalisation, double precision
+    assert lib.gn_step_backward_workspace_bytes(B, 12, N, K, inner, 4, 0, 4) == 0
+    assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, block, 1, 4) == 0
+    assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, block, 0, 8) == 0
