@@ -99,7 +99,8 @@ GN_API int gn_step_backward_f64(const double *weight, const double *bias, const 
                          double *grad_bias, double *grad_scale, double *grad_x, int B, int M,
                          int N, int K, int inner, int block, double eps, int normalize,
                          int activation, void *stream);
-/* gn_step_backward_f32 with a scratch buffer. With block 8, normalize = 0 and
+/* gn_step_backward_f32 with a scratch buffer. With normalize = 0, block 8 (or block 4 on a grid
+ * whose sides are multiples of 8 and a 16-byte-aligned x) and
  * gn_step_backward_workspace_bytes(...) bytes of 16-byte-aligned workspace the gradient is
  * computed by the tuned four-kernel path (replay of the inner iterations, reverse sweep with
  * transposed weights, weight gradients, cross-block halo terms), which is about twice as fast as
