@@ -213,9 +213,13 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
     constexpr int SRC_SHIFT = Geo::SOFF_BITS + 1;
     constexpr bool CI_SMEM = SUB == 4;  // 14 cell descriptors per thread do not fit beside 108 accumulators
     static_assert(SUB == 8 || USE_TMA, "block 4 tiles are fetched by bulk tensor copy only");
-    __shared__ __align__(16) float tiles[2][TS];
-    // USE_TMA: raw 10 x 10 rows of 16 floats (x from 8 bx - 4) of the step input, two samples deep
-    __shared__ __align__(128) float staging[USE_TMA ? 2 : 1][USE_TMA ? STG : 4];
+    // One pool: the staging ring (USE_TMA: raw 10 x 10 rows of 16 floats, x from 8 bx - 4, of the step
+    // input, two samples deep), then the two tiles. The cluster reduction at the end reuses all of it.
+    constexpr int STGF = USE_TMA ? 2 * STG : 4;
+    constexpr int POOL = STGF + 2 * TS;
+    __shared__ __align__(128) float pool[POOL];
+    float(*staging)[USE_TMA ? STG : 4] = reinterpret_cast<float(*)[USE_TMA ? STG : 4]>(pool);
+    float(*tiles)[TS] = reinterpret_cast<float(*)[TS]>(pool + STGF);
     __shared__ __align__(8) unsigned long long bars[2];
     __shared__ unsigned ctab[CI_SMEM ? SLOTS * THREADS : 1];
     const int tid = threadIdx.x;
@@ -376,35 +380,41 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
         }
     }
     if (p.cluster_reduce) {
-        // The chunks of one block form a thread-block cluster. Every CTA parks its partial sums in
-        // its own shared memory; CTA r of the cluster then sums the float2 units u = r, r + size, ...
-        // over all CTAs in rank order through distributed shared memory and stores them: no
-        // atomics, and the result does not depend on scheduling.
-        extern __shared__ __align__(16) float2 red[];  // [RED_UNITS][THREADS]
+        // The chunks of one region form a thread-block cluster. In rounds of as many float2 units as
+        // the shared-memory pool holds, every CTA parks its partial sums in its own shared memory;
+        // CTA r of the cluster then sums the units u = r, r + size, ... of the round over all CTAs
+        // in rank order through distributed shared memory and stores them: no atomics, and the
+        // result does not depend on scheduling.
+        constexpr int UPR = (POOL / 2) / THREADS;  // units per round
+        float2 *red = reinterpret_cast<float2 *>(pool);
         cg::cluster_group cl = cg::this_cluster();
         const unsigned rank = cl.block_rank(), size = cl.num_blocks();
 #pragma unroll
-        for (int t = 0; t < 27; ++t)
+        for (int base = 0; base < RED_UNITS; base += UPR) {
+            __syncthreads();  // the pool is no longer read: by the stencil, or by this CTA's previous round
 #pragma unroll
-            for (int j = 0; j < 2; ++j) red[(t * 2 + j) * THREADS + tid] = make_float2(dw[t][j][0], dw[t][j][1]);
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            red[(54 + j) * THREADS + tid] = make_float2(db[j][0], db[j][1]);
-            red[(56 + j) * THREADS + tid] = make_float2(ds[j][0], ds[j][1]);
-        }
-        cl.sync();
-        for (unsigned u = rank; u < RED_UNITS; u += size) {
-            float2 acc = make_float2(0.0f, 0.0f);
-            for (unsigned r = 0; r < size; ++r) {
-                const float2 v = cl.map_shared_rank(red, r)[u * THREADS + tid];
-                acc.x += v.x;
-                acc.y += v.y;
+            for (int u = base; u < base + UPR && u < RED_UNITS; ++u) {
+                float2 v;
+                if (u < 54) v = make_float2(dw[u >> 1][u & 1][0], dw[u >> 1][u & 1][1]);
+                else if (u < 56) v = make_float2(db[u & 1][0], db[u & 1][1]);
+                else v = make_float2(ds[u & 1][0], ds[u & 1][1]);
+                red[(u - base) * THREADS + tid] = v;
             }
-            const unsigned j = u & 1;
-            float *dst = u < 54 ? p.gw + (size_t)(u >> 1) * P : (u < 56 ? p.gb : p.gs);
-            *reinterpret_cast<float2 *>(dst + g00 + (size_t)j * K) = acc;
+            cl.sync();
+            const unsigned end = base + UPR < RED_UNITS ? base + UPR : RED_UNITS;
+            for (unsigned u = base + rank; u < end; u += size) {
+                float2 acc = make_float2(0.0f, 0.0f);
+                for (unsigned r = 0; r < size; ++r) {
+                    const float2 v = cl.map_shared_rank(red, r)[(u - base) * THREADS + tid];
+                    acc.x += v.x;
+                    acc.y += v.y;
+                }
+                const unsigned j = u & 1;
+                float *dst = u < 54 ? p.gw + (size_t)(u >> 1) * P : (u < 56 ? p.gb : p.gs);
+                *reinterpret_cast<float2 *>(dst + g00 + (size_t)j * K) = acc;
+            }
+            cl.sync();  // nobody overwrites or leaves while another CTA still reads its shared memory
         }
-        cl.sync();  // no CTA may exit while another still reads its shared memory
     } else {
 #pragma unroll
         for (int t = 0; t < 27; ++t)
@@ -577,16 +587,10 @@ static int launch_wgrad(const CUtensorMap &map, const BwdParams &p, long long nb
         kern<<<(unsigned)nb, bwd8::THREADS, 0, st>>>(map, p);
         return GN_OK;
     }
-    const size_t red_bytes = sizeof(float2) * bwd8::RED_UNITS * bwd8::THREADS;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_bytes);
-    if (e != cudaSuccess) {
-        record_cuda_error(e, "cudaFuncSetAttribute");
-        return GN_ERR_CUDA;
-    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)nb, chunks, 1);
     cfg.blockDim = dim3(bwd8::THREADS, 1, 1);
-    cfg.dynamicSmemBytes = red_bytes;
+    cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -595,7 +599,7 @@ static int launch_wgrad(const CUtensorMap &map, const BwdParams &p, long long nb
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, kern, map, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, p);
     if (e != cudaSuccess) {
         record_cuda_error(e, "bwd_wgrad8 cluster launch");
         return GN_ERR_CUDA;
