@@ -14,6 +14,7 @@ from .backend_cuda import (GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, HostPi
 
 from .modules import (GatedGridnet, Gridnet, GridnetModel, GridNorm, Readout, gated_gridnet_step,
                       gridnet_step)
+from .script_models import ImageNetModel, MnistModel
 
 __all__ = [
     "Gridnet",
@@ -21,6 +22,8 @@ __all__ = [
     "GridNorm",
     "Readout",
     "GridnetModel",
+    "MnistModel",
+    "ImageNetModel",
     "gridnet_step",
     "gated_gridnet_step",
     "GridnetCudaOp",

@@ -340,7 +340,7 @@ int fast8_default_spc(int B, long long nbricks)
     if (g_fast8_spc_override > 0) return g_fast8_spc_override;
     // evenly filled rounds of 3 CTAs per SM, but at least 8 samples per CTA (when the batch allows)
     // so that the weight fetch is amortised
-    const int chunks = pick_batch_chunks_balanced(nbricks, B, fast8::MIN_CTAS, 1.0, B >= 16 ? B / 8 : 1);
+    const int chunks = pick_batch_chunks_balanced(nbricks, B, fast8::MIN_CTAS, 0.5, B >= 16 ? B / 8 : 1);
     return (B + chunks - 1) / chunks;
 }
 

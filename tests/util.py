@@ -62,3 +62,47 @@ def assert_close(ours, ref64, ref32=None, what="", rtol=RTOL, atol=ATOL):
     raise AssertionError(
         f"{what}: {int(bad.sum())}/{bad.size} elements outside tolerance; worst at {i}: "
         f"ours={ours[i]!r} ref={ref64[i]!r} err={err[i]:.3e} tol={tol[i]:.3e}{detail}")
+
+
+# ---- the reference scripts' model classes (tests/golden/make_script_model_fixtures.py, tests/test_script_models.py)
+SCRIPT_MODEL_CONFIGS = {
+    "mnist": ("mnist", dict(inner_iters=2, outer_iters=3, init_scale=1.0, residual_scale=1.0, gated=False,
+                            remember_bias=1.0, activation="silu")),
+    "mnist_gated": ("mnist", dict(inner_iters=2, outer_iters=2, init_scale=1.0, residual_scale=1.0, gated=True,
+                                  remember_bias=1.0, activation="tanh")),
+    "imagenet_plain": ("imagenet", dict(inner_iters=2, outer_iters=2, outer_residual=False, init_scale=1.0,
+                                        residual_scale=0.5, emb_channels=4, grid_size=32, activation="leaky_relu",
+                                        separate_params=False)),
+    "imagenet_residual_separate": ("imagenet", dict(inner_iters=2, outer_iters=2, outer_residual=True, init_scale=1.0,
+                                                    residual_scale=0.5, emb_channels=4, grid_size=32,
+                                                    activation="leaky_relu", separate_params=True)),
+}
+
+
+def fill_state_dict(model, seed: int) -> None:
+    """Overwrites every entry of ``model.state_dict()`` (in sorted name order) with seeded values that keep
+    the activations tame: grid weights N(0, 0.2^2), scales 1 + 0.1 N, everything else 0.1 N."""
+    import torch
+
+    rng = np.random.default_rng(seed)
+    sd = model.state_dict()
+    with torch.no_grad():
+        for name in sorted(sd):
+            t = sd[name]
+            v = rng.standard_normal(tuple(t.shape)).astype(np.float32)
+            if name.endswith("residual_scale") or (name.endswith("norm.weight")):
+                v = 1.0 + 0.1 * v
+            elif t.dim() >= 4 and t.shape[0] == 27:
+                v = 0.2 * v
+            else:
+                v = 0.1 * v
+            t.copy_(torch.from_numpy(v).to(t.device))
+
+
+def script_model_inputs(kind: str, seed: int):
+    import torch
+
+    rng = np.random.default_rng(seed)
+    if kind == "mnist":
+        return torch.from_numpy(rng.random((3, 1, 28, 28)).astype(np.float32))
+    return torch.from_numpy(rng.standard_normal((2, 3, 256, 256)).astype(np.float32))
