@@ -189,3 +189,65 @@ def test_outer_forward_reports_no_device_failure():
     ws.fill_(255)  # the flag must be cleared by the call itself
     outer_forward(w, b, s, gamma, beta, x, 2, 3, 8, workspace=ws)
     assert not outer_forward_failed(ws, B, shape, 8)
+
+
+@pytest.mark.parametrize("name,shape,B,bs,inner", [("C3", (128, 128, 128), 16, 8, 2), ("C4", (64, 64, 64), 128, 4, 8)])
+def test_full_size_step_gradients(name, shape, B, bs, inner):
+    """One outer step of the forward + backward configurations on their full grids (C4 at its full batch,
+    C3 at 16 of its 256 samples: the kernels walk the batch sample by sample, so the batch size only changes
+    how CTAs split it). The scalar oracle is too slow here, so parity is carried by properties: the tuned
+    four-kernel backward against the independent one-kernel backward, bit-reproducibility, independence of
+    the samples, and two samples against the float64 oracle."""
+    from gridnet_b200 import GridnetCudaOp
+    from gridnet_b200._lib import lib
+
+    w, b, s, _, _ = (dev(a) for a in model_params(61, shape))
+    g = torch.Generator(device="cuda").manual_seed(62)
+    x = torch.randn(B, *shape, device="cuda", generator=g)
+    gy = torch.randn(B, *shape, device="cuda", generator=g)
+    M, N, K = shape
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def backward(tuned, xs, gys):
+        n = xs.shape[0]
+        outs = [torch.empty_like(t) for t in (w, b, s, xs)]
+        if tuned:
+            need = lib.gn_step_backward_workspace_bytes(n, M, N, K, inner, bs, 0, 4)
+            assert need > 0
+            ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+            rc = lib.gn_step_backward_ws_f32(w.data_ptr(), b.data_ptr(), s.data_ptr(), xs.data_ptr(), gys.data_ptr(),
+                                             *(t.data_ptr() for t in outs), n, M, N, K, inner, bs, 1e-5, 0, 2,
+                                             ws.data_ptr(), ws.numel(), stream)
+            assert rc == 0 and int(ws.view(torch.int32)[lib.gn_step_backward_error_flag_offset(n, M, N, K, inner) // 4]) == 0
+        else:
+            rc = lib.gn_step_backward_f32(w.data_ptr(), b.data_ptr(), s.data_ptr(), xs.data_ptr(), gys.data_ptr(),
+                                          *(t.data_ptr() for t in outs), n, M, N, K, inner, bs, 1e-5, 0, 2, stream)
+            assert rc == 0
+        return outs
+
+    tuned = backward(True, x, gy)
+    again = backward(True, x, gy)
+    plain = backward(False, x, gy)
+    for name_, a, a2, p in zip(("gw", "gb", "gs", "gx"), tuned, again, plain):
+        assert torch.isfinite(a).all(), name_
+        assert torch.equal(a, a2), name_  # no atomics: bit-reproducible
+        scale = p.abs().max().item()
+        assert (a - p).abs().max().item() <= 2e-4 * scale, (name_, (a - p).abs().max().item(), scale)
+    # grad_x of a sample does not depend on the rest of the batch
+    sub = backward(True, x[3:5].contiguous(), gy[3:5].contiguous())
+    assert torch.allclose(tuned[3][3:5], sub[3], rtol=1e-5, atol=1e-6 * tuned[3].abs().max().item())
+    # forward and grad_x of two samples against the float64 oracle (parameter gradients of those two
+    # samples alone come with it)
+    idx = [0, B - 1]
+    a64 = [t.cpu().numpy().astype(np.float64) for t in (w, b, s)]
+    x64, gy64 = (t[idx].cpu().numpy().astype(np.float64) for t in (x, gy))
+    y = GridnetCudaOp.apply(w, b, s, x, inner, bs, 1e-5, False, "silu")
+    ref_y = orc.step_forward(*a64, x64, inner, bs, 1e-5, False, "silu")
+    ref_y32 = orc.step_forward(*(a.astype(np.float32) for a in a64), x64.astype(np.float32), inner, bs, 1e-5, False, "silu")
+    assert_close(y[idx].cpu().numpy(), ref_y, ref_y32, f"{name} forward, sampled rows")
+    ref_g = orc.step_backward(*a64, x64, gy64, inner, bs, 1e-5, False, "silu")
+    ref_g32 = orc.step_backward(*(a.astype(np.float32) for a in a64), x64.astype(np.float32), gy64.astype(np.float32),
+                                inner, bs, 1e-5, False, "silu")
+    two = backward(True, x[idx].contiguous(), gy[idx].contiguous())
+    for name_, a, r, n32 in zip(("gw", "gb", "gs", "gx"), two, ref_g, ref_g32):
+        assert_close(a.cpu().numpy(), r, n32, f"{name} {name_}, two samples")
