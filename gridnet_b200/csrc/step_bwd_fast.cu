@@ -444,7 +444,9 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
 // weight is zero (the per-lane predicates cost more than the loads they save).
 // With block size 4 the CTA still owns an 8 x 8 x 8 region (eight blocks): one thread per cell, 448
 // of the 512 lie on a block surface, and the whole 10 x 10 x 10 neighbourhood of dsum is staged
-// because neighbouring blocks of the same region feed each other too.
+// because neighbouring blocks of the same region feed each other too. There a tap whose source
+// lies in the cell's own block reads a real value and multiplies it by a zero weight, so a
+// non-finite dsum spreads to the cells around it (the in-block sweep has spread it to them anyway).
 template <int SUB>
 struct HaloGeo;
 template <>
