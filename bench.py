@@ -371,7 +371,8 @@ def run_slab(args, rank: int, local_rank: int, world: int):
     slab-sharded along K over all ranks (strong scaling: the total work is fixed)."""
     import torch
 
-    from gridnet_b200.slab import GHOST, CudaSlabBackend, SlabLayout, SlabRunner, run_distributed
+    from gridnet_b200.slab import (GHOST, CudaSlabBackend, PeerFaceBuffers, SlabLayout, SlabRunner, run_direct,
+                                   run_distributed)
 
     G, B, inner, outer = 256, 32, 2, 32
     torch.cuda.set_device(local_rank)
@@ -402,9 +403,14 @@ def run_slab(args, rank: int, local_rank: int, world: int):
         x[..., GHOST] = torch.randn(B, G, G, generator=g, device=device)
     backend = CudaSlabBackend(lay, w, b, s, gamma, beta, inner, ACT)
 
+    # faces: stored by the step kernel straight into the neighbours' memory (default), or packed and sent
+    # with NCCL send/recv (--slab-exchange nccl)
+    direct = args.slab_exchange == "direct" and world > 1
+    peers = PeerFaceBuffers(lay, B, G, G, device) if direct else None
+
     def one_pass():
         runner = SlabRunner(lay, backend, x, G * G * G)
-        return run_distributed(runner, outer)
+        return run_direct(runner, outer, peers) if direct else run_distributed(runner, outer)
 
     for _ in range(max(1, min(args.warmup, 2))):
         one_pass()
@@ -422,6 +428,8 @@ def run_slab(args, rank: int, local_rank: int, world: int):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     finite = bool(torch.isfinite(out).all().item())
+    chk = out.double().sum().reshape(1)  # the same bits whichever way the faces travel: compare between runs
+    dist.all_reduce(chk)
     if rank == 0:
         nu = float(B) * G ** 3 * inner * outer
         print(json.dumps({
@@ -430,8 +438,10 @@ def run_slab(args, rank: int, local_rank: int, world: int):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "C5: 256^3 grid, block 8, 2 inner x 32 outer, batch 32, fp32, forward + whole-grid "
                                    "LayerNorm, slab-sharded along K", "parallelism": f"slab x{world}",
-                       "exchange": "per outer step: 2 faces [32,256,256] fp32 send/recv per neighbour + all-reduce of [32,2] f64",
-                       "samples_per_sec": B * steps / (ms * 1e-3), "finite": finite},
+                       "exchange": ("per outer step: the step kernel stores 2 faces [32,256,256] fp32 into the neighbours' memory "
+                                    "over NVLink; all-reduce of [32,2] f64" if direct else
+                                    "per outer step: 2 faces [32,256,256] fp32 send/recv per neighbour + all-reduce of [32,2] f64"),
+                       "samples_per_sec": B * steps / (ms * 1e-3), "finite": finite, "output_checksum": float(chk.item())},
             "gpu_launches": (outer * 2 + 1) * steps,
         }), flush=True)
     dist.destroy_process_group()
@@ -641,6 +651,8 @@ def main():
                     help="c2 (default): the headline benchmark; c5-slab: the 256^3 grid sharded along K over all ranks; "
                          "c3 / c4: the forward + backward configurations (128^3 block 8, 64^3 block 4); "
                          "c1: the small launch-bound configuration, also replayed from a CUDA graph")
+    ap.add_argument("--slab-exchange", choices=["direct", "nccl"], default="direct",
+                    help="c5-slab only: how the boundary faces travel (direct = stored by the step kernel into peer memory)")
     ap.add_argument("--batch", type=int, default=0, help="c3 / c4 only: override the global batch size")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -41,6 +41,8 @@ SIGNATURES = {
     "gn_step_stats_partials": (c_int, [c_int] * 4),
     "gn_step_forward_fused_f32": (c_int, [_P] * 9 + _geom + [c_int, c_int, c_int, _P]),
     "gn_step_forward_slab_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P]),
+    "gn_step_forward_slab_faces_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P, _P, _P]),
+    "gn_slab_unpack_faces_f32": (c_int, [_P] * 3 + _geom + [c_int, c_int, _P]),
     "gn_norm_finalize_f32": (c_int, [_P, c_int, _P, c_int, c_longlong, c_float, _P]),
     "gn_norm_apply_f32": (c_int, [_P] * 5 + [c_int, c_longlong, _P]),
     "gn_outer_forward_workspace_bytes": (c_size_t, [c_int] * 5),

@@ -446,10 +446,11 @@ GN_API int gn_step_forward_fused_f32(const float *w, const float *b, const float
     return launch_step_fwd_fast8(p, act, (cudaStream_t)stream);
 }
 
-GN_API int gn_step_forward_slab_f32(const float *w, const float *b, const float *s, const float *x, float *y,
+static int slab_forward(const float *w, const float *b, const float *s, const float *x, float *y,
                              const float *gamma, const float *beta, const float *in_mean_rstd,
                              double *out_partials, int partials_per_sample, int B, int M, int N, int K,
-                             int k_block_first, int k_block_count, int inner, int act, void *stream)
+                             int k_block_first, int k_block_count, int inner, int act, float *face_to_left,
+                             float *face_to_right, void *stream)
 {
     const int rc = check_geometry(B, M, N, K, inner, 8, act);
     if (rc != GN_OK) return rc;
@@ -468,11 +469,41 @@ GN_API int gn_step_forward_slab_f32(const float *w, const float *b, const float 
     }
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
     p.kb0 = k_block_first; p.kbn = k_block_count;
+    p.face_left = face_to_left; p.face_right = face_to_right;
+    if ((reinterpret_cast<uintptr_t>(face_to_left) | reinterpret_cast<uintptr_t>(face_to_right)) & 7) return GN_ERR_UNSUPPORTED;
     if (!fast8_applicable(p, 8, 0)) return GN_ERR_UNSUPPORTED;
     if ((in_mean_rstd && reinterpret_cast<uintptr_t>(in_mean_rstd) % 8) ||
         (out_partials && reinterpret_cast<uintptr_t>(out_partials) % 16))
         return GN_ERR_UNSUPPORTED;
     return launch_step_fwd_fast8(p, act, (cudaStream_t)stream);
+}
+
+GN_API int gn_step_forward_slab_f32(const float *w, const float *b, const float *s, const float *x, float *y,
+                             const float *gamma, const float *beta, const float *in_mean_rstd,
+                             double *out_partials, int partials_per_sample, int B, int M, int N, int K,
+                             int k_block_first, int k_block_count, int inner, int act, void *stream)
+{
+    return slab_forward(w, b, s, x, y, gamma, beta, in_mean_rstd, out_partials, partials_per_sample, B, M, N, K,
+                        k_block_first, k_block_count, inner, act, nullptr, nullptr, stream);
+}
+
+GN_API int gn_step_forward_slab_faces_f32(const float *w, const float *b, const float *s, const float *x, float *y,
+                                   const float *gamma, const float *beta, const float *in_mean_rstd,
+                                   double *out_partials, int partials_per_sample, int B, int M, int N, int K,
+                                   int k_block_first, int k_block_count, int inner, int act, float *face_to_left,
+                                   float *face_to_right, void *stream)
+{
+    return slab_forward(w, b, s, x, y, gamma, beta, in_mean_rstd, out_partials, partials_per_sample, B, M, N, K,
+                        k_block_first, k_block_count, inner, act, face_to_left, face_to_right, stream);
+}
+
+GN_API int gn_slab_unpack_faces_f32(const float *from_left, const float *from_right, float *x, int B, int M, int N, int K,
+                             int col_left, int col_right, void *stream)
+{
+    if (B < 0 || M <= 0 || N <= 0 || K <= 0 || col_left < 0 || col_left >= K || col_right < 0 || col_right >= K)
+        return GN_ERR_BAD_SHAPE;
+    if (!x) return GN_ERR_NULL_POINTER;
+    return launch_slab_unpack_faces(from_left, from_right, x, B, M, N, K, col_left, col_right, (cudaStream_t)stream);
 }
 
 GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_rstd, int B, long long P, float eps,

@@ -42,6 +42,10 @@ struct FastFwdParams {
     // receives every iteration's pre-activation, save_x [inner-1][B][M,N,K] the activations after
     // iterations 1 .. inner-1 (y may then be nullptr: the final output is not wanted).
     float *save_h, *save_x;
+    // Slab mode with direct face delivery: the CTAs of the first / last updated K-block also store their
+    // first / last column, packed as [B][M][N], to these addresses (normally a buffer in the neighbouring
+    // GPU's memory, written over NVLink); nullptr = no neighbour on that side.
+    float *face_left, *face_right;
 };
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize);
 extern int g_fast8_spc_override;  // tuning knob: samples per CTA of the tuned forward kernel, 0 = automatic
@@ -49,6 +53,10 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st);
 // Tensor map for 16 x 10 x 10 tile boxes of a float tensor [B, M, N, K]; false when bulk tensor copies cannot
 // be used (base not 16-byte aligned, K not a multiple of 4, driver entry point missing).
 bool fast8_make_tile_map(CUtensorMap *map, const float *base, int B, int M, int N, int K);
+
+// ---- slab.cu
+int launch_slab_unpack_faces(const float *from_left, const float *from_right, float *x, int B, int M, int N, int K,
+                             int col_left, int col_right, cudaStream_t st);
 
 // ---- step_bwd_fast.cu (tuned float backward, block 8, normalize off; needs a workspace)
 size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner);

@@ -14,6 +14,14 @@ parameter. Per outer step there is exactly one exchange:
 Local layout: ``[..., 8 + K_loc + 8]`` — one ghost block of 8 columns on each side keeps
 block alignment; only ghost column 7 (left) and ``8 + K_loc`` (right) are ever read.
 
+There are two ways to move the faces. :func:`run_distributed` packs them with torch indexing and
+sends them with grouped NCCL send/recv. :func:`run_direct` needs neither: the step kernel of a
+boundary K-block stores its face straight into a packed buffer in the NEIGHBOUR's memory (mapped
+into this process through torch's symmetric memory, :class:`PeerFaceBuffers`), so the transfer rides
+inside the compute kernel over NVLink; the all-reduce of the statistics that every step needs anyway
+is also the point after which a rank knows its neighbours' kernels - and with them their face
+stores - have finished.
+
 The arithmetic is delegated to a backend object so that the orchestration can be exercised
 on CPU ranks (gloo) with a checker backend in the tests; :class:`CudaSlabBackend` is the
 product backend and calls the C ABI (``gn_step_forward_slab_f32`` and friends).
@@ -126,6 +134,27 @@ class CudaSlabBackend:
         self._launch(x, y, in_stats, 1, self.layout.k_loc // 8, 0)
         return self.sums()
 
+    def step_with_faces(self, x, y, in_stats, face_to_left: int, face_to_right: int):
+        """:meth:`step` whose boundary K-blocks also store their faces, packed ``[B, M, N]``, to the two
+        device addresses (0 = no neighbour on that side; normally peer memory)."""
+        B = x.shape[0]
+        if self._partials is None or self._partials.shape[0] != B:
+            self._partials = torch.empty(B, self.nparts, 2, dtype=torch.float64, device=x.device)
+        self.check(self.lib.gn_step_forward_slab_faces_f32(
+            self.w.data_ptr(), self.b.data_ptr(), self.s.data_ptr(), x.data_ptr(), y.data_ptr(),
+            self.gamma.data_ptr(), self.beta.data_ptr(), None if in_stats is None else in_stats.data_ptr(),
+            self._partials.data_ptr(), self.nparts, B, self.M, self.N, self.layout.k_pad,
+            1, self.layout.k_loc // 8, self.inner, self.act, face_to_left or None, face_to_right or None,
+            self._stream()))
+        return self.sums()
+
+    def unpack_faces(self, from_left, from_right, x):
+        """Packed faces ``[B, M, N]`` (or None) -> the two ghost columns of the padded slab ``x``."""
+        B = x.shape[0]
+        self.check(self.lib.gn_slab_unpack_faces_f32(
+            None if from_left is None else from_left.data_ptr(), None if from_right is None else from_right.data_ptr(),
+            x.data_ptr(), B, self.M, self.N, self.layout.k_pad, GHOST - 1, GHOST + self.layout.k_loc, self._stream()))
+
     # The same step in two parts, so that the faces can travel while the interior computes:
     # the K-blocks that touch a neighbour slab first, the rest afterwards.
     def step_boundary(self, x, y, in_stats):
@@ -175,6 +204,16 @@ class SlabRunner:
         sums = self.backend.step(self.bufs[self.cur], self.bufs[nxt], self.stats)
         self.cur = nxt
         return sums
+
+    def compute_direct(self, face_to_left: int, face_to_right: int):
+        """One step whose faces the kernel delivers itself; returns the local sums."""
+        nxt = 1 if self.cur != 1 else 2
+        sums = self.backend.step_with_faces(self.bufs[self.cur], self.bufs[nxt], self.stats, face_to_left, face_to_right)
+        self.cur = nxt
+        return sums
+
+    def unpack(self, from_left, from_right):
+        self.backend.unpack_faces(from_left, from_right, self.bufs[self.cur])
 
     def can_split(self) -> bool:
         return hasattr(self.backend, "step_boundary")
@@ -270,6 +309,90 @@ def run_distributed(runner: SlabRunner, outer: int, group=None, overlap: bool = 
         main.wait_event(faces_done)
         runner.set_global_sums(sums)
     return runner.result()
+
+
+class PeerFaceBuffers:
+    """Receive buffers for the faces, two step parities deep, allocated in torch's symmetric memory so that
+    the neighbours' kernels can store into them: ``recv[parity][side]`` is ``[B, M, N]`` float32, side 0 =
+    the face arriving from the left neighbour, 1 = from the right one. ``target(parity)`` gives the two
+    device addresses THIS rank's step kernel stores to: the left neighbour's from-the-right buffer and the
+    right neighbour's from-the-left buffer (0 where there is no neighbour).
+
+    Two parities are needed because a neighbour may start its next step (and store the next face) before
+    this rank has unpacked the current one; it cannot get two steps ahead, because every step ends with an
+    all-reduce that needs this rank's contribution.
+
+    NVLink multicast is switched off for the mapping (plain peer stores only)."""
+
+    def __init__(self, layout: SlabLayout, B: int, M: int, N: int, device, group=None):
+        import os
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.layout = layout
+        group = group if group is not None else dist.group.WORLD
+        self.buf = symm.empty(2, 2, B, M, N, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, group)
+        face_bytes = B * M * N * 4
+        ptrs = self.handle.buffer_ptrs
+
+        def addr(rank, parity, side):
+            return int(ptrs[rank]) + (parity * 2 + side) * face_bytes
+
+        self._targets = [
+            (addr(layout.left, q, 1) if layout.left is not None else 0,
+             addr(layout.right, q, 0) if layout.right is not None else 0)
+            for q in (0, 1)
+        ]
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def target(self, parity: int):
+        return self._targets[parity]
+
+    def received(self, parity: int):
+        lay = self.layout
+        return (self.buf[parity, 0] if lay.left is not None else None,
+                self.buf[parity, 1] if lay.right is not None else None)
+
+
+def run_direct(runner: SlabRunner, outer: int, peers: PeerFaceBuffers, group=None) -> torch.Tensor:
+    """Drive one rank for ``outer`` steps with the faces delivered by the step kernel itself
+    (:class:`PeerFaceBuffers`): per step one kernel, the all-reduce of the sums, the finalisation of the
+    statistics and the unpacking of the received faces - no pack kernels, no send/recv calls."""
+    import torch.distributed as dist
+
+    for k in range(outer):
+        q = k & 1
+        sums = runner.compute_direct(*peers.target(q))
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)  # also: every neighbour's step k has finished
+        runner.set_global_sums(sums)
+        runner.unpack(*peers.received(q))
+    return runner.result()
+
+
+def run_emulated_direct(runners, outer: int):
+    """:func:`run_direct` with all ranks in one process on one GPU: the "peer" buffers are ordinary tensors
+    of the other runners, everything else (kernel-side face stores, parity, unpacking) is the same."""
+    world = len(runners)
+    first = runners[0].bufs[0]
+    B, M, N = first.shape[0], first.shape[1], first.shape[2]
+    recv = [torch.zeros(2, 2, B, M, N, dtype=torch.float32, device=first.device) for _ in range(world)]
+    for k in range(outer):
+        q = k & 1
+        sums = []
+        for i, r in enumerate(runners):
+            to_left = recv[i - 1][q, 1].data_ptr() if i > 0 else 0
+            to_right = recv[i + 1][q, 0].data_ptr() if i + 1 < world else 0
+            sums.append(r.compute_direct(to_left, to_right))
+        total = torch.stack(sums).sum(0)
+        for i, r in enumerate(runners):
+            r.set_global_sums(total.clone())
+            r.unpack(recv[i][q, 0] if i > 0 else None, recv[i][q, 1] if i + 1 < world else None)
+    return [r.result() for r in runners]
 
 
 def run_emulated(runners, outer: int, split: bool = False):

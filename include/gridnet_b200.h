@@ -212,6 +212,26 @@ GN_API int gn_step_forward_slab_f32(const float *weight, const float *bias, cons
                              const float *in_mean_rstd, double *out_partials, int partials_per_sample,
                              int B, int M, int N, int K, int k_block_first, int k_block_count,
                              int inner, int activation, void *stream);
+/* gn_step_forward_slab_f32 that also delivers the boundary faces: the first updated K-block stores
+ * its first column, the last one its last column, packed as [B][M][N] floats, to face_to_left /
+ * face_to_right (8-byte aligned; NULL = no neighbour on that side). The addresses are normally
+ * buffers in the neighbouring GPUs' memory mapped into this process, so the faces cross NVLink
+ * from inside the step kernel and no pack kernel or send/recv call is needed; the receiver moves
+ * them into its ghost columns with gn_slab_unpack_faces_f32 once it knows the sender's kernel
+ * has finished (for instance after the all-reduce of the statistics of the same step). The raw
+ * step output is sent: the receiver normalises it on load like every other cell.
+ * No counterpart in the reference (it is single-GPU). */
+GN_API int gn_step_forward_slab_faces_f32(const float *weight, const float *bias, const float *scale,
+                                   const float *x, float *y, const float *norm_weight,
+                                   const float *norm_bias, const float *in_mean_rstd,
+                                   double *out_partials, int partials_per_sample, int B, int M,
+                                   int N, int K, int k_block_first, int k_block_count, int inner,
+                                   int activation, float *face_to_left, float *face_to_right,
+                                   void *stream);
+/* x[b][m][n][col_left] = from_left[b][m][n], x[b][m][n][col_right] = from_right[b][m][n] for a
+ * float array x [B, M, N, K]; either source may be NULL. */
+GN_API int gn_slab_unpack_faces_f32(const float *from_left, const float *from_right, float *x, int B,
+                             int M, int N, int K, int col_left, int col_right, void *stream);
 GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_rstd, int B,
                          long long P, float eps, void *stream);
 GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *beta,

@@ -109,6 +109,11 @@ def test_cuda_slabs_match_single_device(world, shape):
     # the boundary-first / interior-later order of the overlapped driver gives the same bits
     runners2 = [make_cuda_runner(SlabLayout(shape[2], world, r), w, b, s, gamma, beta, x, inner) for r in range(world)]
     assert torch.equal(torch.cat(run_emulated(runners2, outer, split=True), -1), got)
+    # faces stored by the step kernel itself into the neighbours' packed buffers, then unpacked: same bits
+    from gridnet_b200.slab import run_emulated_direct
+
+    runners3 = [make_cuda_runner(SlabLayout(shape[2], world, r), w, b, s, gamma, beta, x, inner) for r in range(world)]
+    assert torch.equal(torch.cat(run_emulated_direct(runners3, outer), -1), got)
     single = gb.outer_forward(*(t.cuda() for t in prob), inner, outer, 8)
     assert torch.allclose(got, single, rtol=1e-5, atol=1e-6), (got - single).abs().max().item()
     want = orc.outer_forward(*(t.double().numpy() for t in prob), inner, outer, 8)
