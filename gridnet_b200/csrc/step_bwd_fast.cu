@@ -1,6 +1,6 @@
-// Tuned float backward of the block-local grid update (block 8, per-block normalisation off),
-// split into four kernels so that every stencil runs with the register-patch mapping of the
-// forward kernel (a thread owns a 1x2x2 patch and keeps 4 x 27 values in registers):
+// Tuned float backward of the block-local grid update (block 8 or 4, per-block normalisation
+// off), split into four kernels so that every stencil runs with the register-patch mapping of
+// the forward kernel (a thread owns a 1x2x2 patch and keeps 4 x 27 values in registers):
 //
 //   replay   step_fwd_fast8 (step_fast.cu) in replay mode: runs the inner iterations once and
 //            stores every iteration's pre-activation h_t and the activations x_t in between —
@@ -8,7 +8,8 @@
 //   reverse  bwd_reverse8: walks the iterations backwards. delta_t = act'(h_t) * g * scale, and
 //            the gradient flowing back inside the block is a 27-tap stencil over the delta tile
 //            with TRANSPOSED weights (cell c receives w[n][t] * delta[n] from the neuron
-//            n = c + o through its tap pointing back at c), so it is a gather, with no atomics;
+//            n = c + o through its tap pointing back at c; the kernel reads them straight from
+//            the weight tensor), so it is a gather, with no atomics;
 //   wgrad    bwd_wgrad8: dW[n][t] += x_t[n + offset(t)] * delta_t[n], accumulated in registers
 //            over samples and iterations, plus dB and dS;
 //   halo     bwd_halo8: the part of dX that crosses block borders. A halo cell never feeds back
@@ -19,7 +20,7 @@
 // batch over several CTAs for occupancy, those CTAs form a thread-block cluster and combine
 // their partial sums through distributed shared memory in a fixed order. The input tiles of
 // wgrad arrive by bulk tensor copy like in the forward kernel; its bounded waits report through
-// the int at the end of the workspace (cleared by the first kernel of the pass).
+// the int at the end of the workspace (cleared when the pass starts).
 //
 // Reference semantics: the gradient of gridnet/backend_torch.py:61-142 with normalize=False;
 // the kernel this stands in for is gridnet_cuda_backward_kernel, src/gridnet_cuda_kernels.cu:202-450.
@@ -41,29 +42,8 @@ constexpr unsigned kSpinLimit = 1u << 18;
 constexpr int RED_UNITS = 58;  // float2 partial sums per thread: 27 taps x 2 rows, bias x 2, scale x 2
 }  // namespace bwd8
 
-// wT[t][c] = w[26 - t][c + offset(t)] when that neighbour is a neuron of c's own block (side 1 << bshift), else 0
-__global__ void __launch_bounds__(256) bwd_transpose_weights_k(const float *__restrict__ w, float *__restrict__ wT,
-                                                               int M, int N, int K, int bshift, int *error_flag)
-{
-    const size_t P = (size_t)M * N * K;
-    const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c == 0) *error_flag = 0;  // first kernel of the backward pass: clears the flag of the later bounded waits
-    if (c >= P) return;
-    const int x = (int)(c % K), y = (int)((c / K) % N), z = (int)(c / ((size_t)K * N));
-#pragma unroll
-    for (int t = 0; t < 27; ++t) {
-        const int dz = t / 9 - 1, dy = (t / 3) % 3 - 1, dx = t % 3 - 1;
-        const int nz = z + dz, ny = y + dy, nx = x + dx;
-        float v = 0.0f;
-        if ((nz >> bshift) == (z >> bshift) && (ny >> bshift) == (y >> bshift) && (nx >> bshift) == (x >> bshift) &&
-            nz >= 0 && ny >= 0 && nx >= 0)
-            v = w[(size_t)(26 - t) * P + ((size_t)nz * N + ny) * K + nx];
-        wT[(size_t)t * P + c] = v;
-    }
-}
-
 struct BwdParams {
-    const float *w, *wT, *s, *x, *gy;
+    const float *w, *s, *x, *gy;
     const float *save_h, *save_x;  // from the replay
     float *delta;                  // [inner][B][P]
     float *dsum;                   // [B][P] sum of deltas over the iterations
@@ -91,15 +71,25 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
     const int K = p.K;
     const size_t g00 = ((size_t)(bz * 8 + z) * p.N + (by * 8 + 2 * yp)) * K + (bx * 8 + 2 * xp);
 
+    // Transposed weights: cell c receives w[n][26 - t] * delta[n] from its neighbour n = c + offset(t)
+    // (n reads c through the tap that points back), if n is a neuron of c's own block; otherwise 0.
     float wt[27][2][2];
 #pragma unroll
-    for (int t = 0; t < 27; ++t)
+    for (int t = 0; t < 27; ++t) {
+        const int dz = t / 9 - 1, dy = (t / 3) % 3 - 1, dx = t % 3 - 1;
+        const int lz = (z & (SUB - 1)) + dz;
+        const float *wp = p.w + (size_t)(26 - t) * P + g00 + ((long long)dz * p.N + dy) * K + dx;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const float2 v = *reinterpret_cast<const float2 *>(p.wT + (size_t)t * P + g00 + (size_t)j * K);
-            wt[t][j][0] = v.x;
-            wt[t][j][1] = v.y;
+            const int ly = ((2 * yp + j) & (SUB - 1)) + dy;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int lx = ((2 * xp + i) & (SUB - 1)) + dx;
+                const bool same = lz >= 0 && lz < SUB && ly >= 0 && ly < SUB && lx >= 0 && lx < SUB;
+                wt[t][j][i] = same ? __ldg(wp + (size_t)j * K + i) : 0.0f;
+            }
         }
+    }
     float scl[2][2];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
@@ -562,9 +552,9 @@ __global__ void __launch_bounds__(HaloGeo<SUB>::THREADS) bwd_halo8_k(const float
 size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner)
 {
     const size_t P = (size_t)M * N * K, BP = (size_t)B * P;
-    // transposed weights, pre-activations, activations between iterations, deltas, delta sums,
-    // scale-gradient terms, and 16 bytes whose first int is the error flag of the bounded waits
-    return 27 * P + (size_t)inner * BP + (size_t)(inner > 1 ? inner - 1 : 0) * BP + (size_t)inner * BP + 2 * BP + 4;
+    // pre-activations, activations between iterations, deltas, delta sums, scale-gradient terms, and
+    // 16 bytes whose first int is the error flag of the bounded waits
+    return (size_t)inner * BP + (size_t)(inner > 1 ? inner - 1 : 0) * BP + (size_t)inner * BP + 2 * BP + 4;
 }
 
 bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
@@ -625,17 +615,17 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
                           float *ws, cudaStream_t st)
 {
     const size_t P = (size_t)M * N * K, BP = (size_t)B * P;
-    float *wT = ws;
-    float *save_h = wT + 27 * P;
+    float *save_h = ws;
     float *save_x = save_h + (size_t)inner * BP;
     float *delta = save_x + (size_t)(inner > 1 ? inner - 1 : 0) * BP;
     float *dsum = delta + (size_t)inner * BP;
     float *dsb = dsum + BP;
     int *error_flag = reinterpret_cast<int *>(dsb + BP);
-
-    bwd_transpose_weights_k<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(w, wT, M, N, K, block == 4 ? 2 : 3, error_flag);
-    int rc = check_launch("bwd_transpose_weights");
-    if (rc != GN_OK) return rc;
+    if (cudaMemsetAsync(error_flag, 0, sizeof(int), st) != cudaSuccess) {
+        record_cuda_error(cudaGetLastError(), "cudaMemsetAsync");
+        return GN_ERR_CUDA;
+    }
+    int rc;
 
     FastFwdParams f{};
     f.w = w; f.b = b; f.s = s; f.x = x; f.y = nullptr;
@@ -648,7 +638,7 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
 
     const long long nb = (long long)(M / 8) * (N / 8) * (K / 8);  // 8^3 regions, one CTA (per batch chunk) each
     BwdParams p{};
-    p.w = w; p.wT = wT; p.s = s; p.x = x; p.gy = gy; p.save_h = save_h; p.save_x = save_x;
+    p.w = w; p.s = s; p.x = x; p.gy = gy; p.save_h = save_h; p.save_x = save_x;
     p.delta = delta; p.dsum = dsum; p.dsb = dsb; p.gw = gw; p.gb = gb; p.gs = gs; p.gx = gx;
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
     p.error_flag = error_flag;

@@ -108,7 +108,7 @@ GN_API int gn_step_backward_f64(const double *weight, const double *bias, const 
  * the same bits. In every other case (workspace NULL, misaligned or too small, other block size,
  * normalize = 1) it behaves exactly like gn_step_backward_f32. gn_step_backward_workspace_bytes
  * returns 0 when the tuned path does not apply. The workspace holds
- * (3 * inner + 1) * B * M*N*K + 27 * M*N*K floats and, at byte offset
+ * (3 * inner + 1) * B * M*N*K floats and, at byte offset
  * gn_step_backward_error_flag_offset(...), an int that the call clears and that a kernel sets to
  * 1 if a bounded wait on a bulk copy gave up (the gradients are then not valid). The inner
  * iteration count is not limited on this path. */
