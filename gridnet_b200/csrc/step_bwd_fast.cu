@@ -55,7 +55,8 @@ struct BwdParams {
 };
 
 // ---------------------------------------------------------------------------- reverse sweep
-template <int SUB, int ACT>
+// INNER_T > 0: the inner iteration count is a compile-time constant (loop unrolled); 0: from the parameters.
+template <int SUB, int ACT, int INNER_T>
 __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams p)
 {
     using namespace bwd8;
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
     if (s0 < s1) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            hn[j] = ld_pinned2(p.save_h + ((size_t)(p.inner - 1) * p.B + s0) * P + g00 + (size_t)j * K);
+            hn[j] = ld_pinned2(p.save_h + ((size_t)((INNER_T > 0 ? INNER_T : p.inner) - 1) * p.B + s0) * P + g00 + (size_t)j * K);
             gn[j] = ld_pinned2(p.gy + (size_t)s0 * P + g00 + (size_t)j * K);
         }
     }
@@ -122,7 +123,9 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
             g[j][1] = gn[j].y;
             dsum[j][0] = dsum[j][1] = dsacc[j][0] = dsacc[j][1] = 0.0f;
         }
-        for (int it = p.inner - 1; it >= 0; --it, ++step) {
+        const int inner = INNER_T > 0 ? INNER_T : p.inner;
+#pragma unroll
+        for (int it = (INNER_T > 0 ? INNER_T : inner) - 1; it >= 0; --it, ++step) {
             const size_t ho = ((size_t)it * p.B + smp) * P + g00;
             float *Dt = D[step & 1];
             float dl[2][2];
@@ -134,7 +137,7 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
             } else if (smp + 1 < s1) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    hn[j] = ld_pinned2(p.save_h + ((size_t)(p.inner - 1) * p.B + smp + 1) * P + g00 + (size_t)j * K);
+                    hn[j] = ld_pinned2(p.save_h + ((size_t)(inner - 1) * p.B + smp + 1) * P + g00 + (size_t)j * K);
                     gn[j] = ld_pinned2(p.gy + so + P + (size_t)j * K);
                 }
             }
@@ -736,15 +739,24 @@ static int launch_wgrad(const CUtensorMap &map, const BwdParams &p, long long nb
     return GN_OK;
 }
 
+template <int SUB, int INNER_T>
+static void launch_reverse_inner(const BwdParams &p, dim3 grid, int act, cudaStream_t st)
+{
+    switch (act) {
+    case GN_ACT_RELU: bwd_reverse8<SUB, GN_ACT_RELU, INNER_T><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+    case GN_ACT_LEAKY_RELU: bwd_reverse8<SUB, GN_ACT_LEAKY_RELU, INNER_T><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+    case GN_ACT_SILU: bwd_reverse8<SUB, GN_ACT_SILU, INNER_T><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+    default: bwd_reverse8<SUB, GN_ACT_TANH, INNER_T><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+    }
+}
+
 template <int SUB>
 static void launch_reverse(const BwdParams &p, dim3 grid, int act, cudaStream_t st)
 {
-    switch (act) {
-    case GN_ACT_RELU: bwd_reverse8<SUB, GN_ACT_RELU><<<grid, bwd8::THREADS, 0, st>>>(p); break;
-    case GN_ACT_LEAKY_RELU: bwd_reverse8<SUB, GN_ACT_LEAKY_RELU><<<grid, bwd8::THREADS, 0, st>>>(p); break;
-    case GN_ACT_SILU: bwd_reverse8<SUB, GN_ACT_SILU><<<grid, bwd8::THREADS, 0, st>>>(p); break;
-    default: bwd_reverse8<SUB, GN_ACT_TANH><<<grid, bwd8::THREADS, 0, st>>>(p); break;
-    }
+    // two inner iterations (the large configurations of the reference) get an unrolled instantiation:
+    // 5 % faster; unrolling four iterations was 5 % slower than the run-time loop
+    if (SUB == 8 && p.inner == 2) launch_reverse_inner<SUB, 2>(p, grid, act, st);
+    else launch_reverse_inner<SUB, 0>(p, grid, act, st);
 }
 
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
