@@ -754,7 +754,8 @@ template <int SUB>
 static void launch_reverse(const BwdParams &p, dim3 grid, int act, cudaStream_t st)
 {
     // two inner iterations (the large configurations of the reference) get an unrolled instantiation:
-    // 5 % faster; unrolling four iterations was 5 % slower than the run-time loop
+    // 5 % faster; unrolling four iterations was 5 % slower than the run-time loop, and the
+    // weight-gradient kernel unrolled for two spills registers and is 8 % slower
     if (SUB == 8 && p.inner == 2) launch_reverse_inner<SUB, 2>(p, grid, act, st);
     else launch_reverse_inner<SUB, 0>(p, grid, act, st);
 }
