@@ -124,6 +124,13 @@ static int api_gated_forward(const R *w, const R *b, const R *x, R *y, int B, in
     if (!w || !b || !x || !y) return GN_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;
     if (inner == 0) return copy_through(x, y, B, M, N, K, st);
+    if (sizeof(R) == sizeof(float)) {  // tuned float kernel where it applies
+        const float *fw = reinterpret_cast<const float *>(w), *fb = reinterpret_cast<const float *>(b);
+        const float *fx = reinterpret_cast<const float *>(x);
+        float *fy = reinterpret_cast<float *>(y);
+        if (gated_fast8_applicable(fw, fb, fx, fy, M, N, K, block, inner))
+            return launch_gated_fwd_fast8(fw, fb, fx, fy, B, M, N, K, inner, act, st);
+    }
     return launch_gated_fwd_generic<R>(w, b, x, y, B, M, N, K, inner, block, act, st);
 }
 

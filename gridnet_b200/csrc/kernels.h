@@ -54,6 +54,12 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st);
 // be used (base not 16-byte aligned, K not a multiple of 4, driver entry point missing).
 bool fast8_make_tile_map(CUtensorMap *map, const float *base, int B, int M, int N, int K);
 
+// ---- step_gated_fast.cu (tuned float forward of the gated update, block 8; tiles by bulk tensor copy only)
+bool gated_fast8_applicable(const float *w, const float *b, const float *x, const float *y, int M, int N, int K, int block,
+                            int inner);
+int launch_gated_fwd_fast8(const float *w, const float *b, const float *x, float *y, int B, int M, int N, int K, int inner,
+                           int act, cudaStream_t st);
+
 // ---- slab.cu
 int launch_slab_unpack_faces(const float *from_left, const float *from_right, float *x, int B, int M, int N, int K,
                              int col_left, int col_right, cudaStream_t st);

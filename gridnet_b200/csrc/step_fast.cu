@@ -345,9 +345,10 @@ int g_fast8_spc_override = 0;
 int fast8_default_spc(int B, long long nbricks)
 {
     if (g_fast8_spc_override > 0) return g_fast8_spc_override;
-    // evenly filled rounds of 3 CTAs per SM, but at least 8 samples per CTA (when the batch allows)
-    // so that the weight fetch is amortised
-    const int chunks = pick_batch_chunks_balanced(nbricks, B, fast8::MIN_CTAS, 0.5, B >= 16 ? B / 8 : 1);
+    // evenly filled rounds of 3 CTAs per SM; a CTA's fixed work (weight fetch, pipeline fill) is
+    // charged as 1.5 samples, which keeps CTAs long where the batch allows it and still splits
+    // a small batch over the whole GPU
+    const int chunks = pick_batch_chunks_balanced(nbricks, B, fast8::MIN_CTAS, 1.5, B < 64 ? B : 64);
     return (B + chunks - 1) / chunks;
 }
 
