@@ -252,6 +252,21 @@ def test_forward_equivalence_gated(shape, block_size):
     assert_close(got, ref64, ref32, f"gated {shape}/{block_size}")
 
 
+@pytest.mark.parametrize("activation", ["relu", "leaky_relu", "silu", "tanh"])
+@pytest.mark.parametrize("inner,batch", [(1, 1), (3, 5), (8, 9)])
+def test_gated_forward_tuned_kernel_details(activation, inner, batch):
+    """The tuned gated forward (float32, block 8): every activation, inner counts that end on either
+    ping-pong tile, batches that leave CTAs with one sample, a non-cubic grid with corner blocks."""
+    _, Gated = ops()
+    shape = (8, 24, 16)
+    w, b, x = rng_inputs(18, batch, shape, gated=True)
+    w = (w / 3).astype(np.float32)  # keeps eight iterations tame
+    ref64 = orc.gated_forward(*(a.astype(np.float64) for a in (w, b, x)), inner, 8, activation)
+    ref32 = orc.gated_forward(w, b, x, inner, 8, activation)
+    got = Gated.apply(dev(w), dev(b), dev(x), inner, 8, activation).cpu().numpy()
+    assert_close(got, ref64, ref32, f"gated {activation} inner={inner} B={batch}")
+
+
 @pytest.mark.parametrize(
     "shape,inner_iters,block_size",
     [((16, 16, 16), 1, 8), ((16, 16, 16), 2, 8), ((32, 64, 128), 2, 8), ((32, 64, 128), 2, 4)],
