@@ -558,7 +558,9 @@ def run_train(args, rank: int, local_rank: int, world: int):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": desc if not args.batch else desc + f" (batch overridden to {batch})",
                        "global_batch": batch, "parallelism": f"batch-sharded x{world}",
-                       "l2": "activations per outer step (%.0f MB) exceed the 126 MB L2" % (b_loc * G ** 3 * 4 / 1e6),
+                       "l2": "one activation tensor is %.0f MB per rank; the %d saved step and norm inputs of a step "
+                             "alone are %.0f MB, larger than the 126 MB L2"
+                             % (b_loc * G ** 3 * 4 / 1e6, 2 * outer, 2 * outer * b_loc * G ** 3 * 4 / 1e6),
                        "forward_ms": t_fwd / steps, "backward_ms": t_bwd / steps, "finite": finite,
                        "samples_per_sec": batch / sec},
             "roofline": {"bound": "fp32", "achieved": flops / sec / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
