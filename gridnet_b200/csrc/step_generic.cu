@@ -483,6 +483,186 @@ __global__ void __launch_bounds__(BS *BS *BS)
     }
 }
 
+// ============================================== gated backward without shared-memory atomics
+// Dynamic shared memory: tile[TP] | Dv[TP] | Dg[TP] | wsm[54][NT] | stash[inner][NT]
+// The gated counterpart of step_bwd_gather: the gradient flowing back to a block cell is gathered by
+// the thread that owns the cell from the two per-iteration delta tiles (value path and gate path)
+// and a shared-memory copy of the block's weights; the running gradient of an owned cell is a
+// register that is scaled by the gate before the gathered terms are added (the remembered part of
+// the state passes its gradient straight through). Halo cells are handled once per sample from the
+// per-neuron sums of the two deltas. Deterministic inside the CTA; the final accumulation into
+// grad_x uses global atomics where tiles of neighbouring blocks overlap.
+template <typename R, int BS, int ACT>
+__global__ void __launch_bounds__(BS *BS *BS)
+    gated_bwd_gather(const R *__restrict__ w, const R *__restrict__ b, const R *__restrict__ x,
+                     const R *__restrict__ gy, R *__restrict__ gw, R *__restrict__ gb, R *__restrict__ gx, int B,
+                     int M, int N, int K, int inner, int spc, int atomic_params)
+{
+    constexpr int E = Geo<BS>::E, T = Geo<BS>::T, NT = Geo<BS>::NT, RS = Geo<BS>::RS, PS = Geo<BS>::PS, TP = Geo<BS>::TP;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    R *tile = reinterpret_cast<R *>(smem_raw);
+    R *Dv = tile + TP;
+    R *Dg = Dv + TP;
+    R *wsm = Dg + TP;  // [0..26] value weights, [27..53] gate weights, each [NT]
+    R *stash = wsm + 54 * NT;
+    const BlockPos p = block_pos<BS>(N, K);
+    const size_t P = (size_t)M * N * K;
+    const int tid = threadIdx.x;
+    constexpr int DX = 1, DY = BS == 8 ? 64 : 4, DZ = BS == 8 ? 8 : 16;  // thread-index distance to the x, y, z neighbour
+    R wv[27], wg[27], dwv[27], dwg[27];
+    unsigned inside = 0;  // bit t: the neighbour at offset(t) is a neuron of this block
+#pragma unroll
+    for (int t = 0; t < 27; ++t) {
+        wv[t] = w[(size_t)(2 * t) * P + p.g];
+        wg[t] = w[(size_t)(2 * t + 1) * P + p.g];
+        wsm[t * NT + tid] = wv[t];
+        wsm[(27 + t) * NT + tid] = wg[t];
+        dwv[t] = R(0);
+        dwg[t] = R(0);
+        const int a = t / 9, bb = (t / 3) % 3, c = t % 3;
+        const bool in = (unsigned)(p.tz + a - 1) < (unsigned)BS && (unsigned)(p.ty + bb - 1) < (unsigned)BS &&
+                        (unsigned)(p.tx + c - 1) < (unsigned)BS;
+        inside |= (in ? 1u : 0u) << t;
+    }
+    const R bv = b[p.g], bg = b[P + p.g];
+    R dbv = R(0), dbg = R(0);
+    for (int i = tid; i < T; i += NT) {  // the halo of both delta tiles stays zero
+        Dv[Geo<BS>::pad(i)] = R(0);
+        Dg[Geo<BS>::pad(i)] = R(0);
+    }
+    const int s0 = blockIdx.y * spc, s1 = min(B, s0 + spc);
+    for (int smp = s0; smp < s1; ++smp) {
+        __syncthreads();
+        load_tile<R, BS>(tile, x + (size_t)smp * P, p, M, N, K);
+        __syncthreads();
+        for (int it = 0; it < inner; ++it) {  // forward replay
+            stash[it * NT + tid] = tile[p.own];
+            R av = R(0), ag = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const R v = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
+                        av = fma(v, wv[a * 9 + bb * 3 + c], av);
+                        ag = fma(v, wg[a * 9 + bb * 3 + c], ag);
+                    }
+            const R gate = sigmoid_(ag + bg);
+            const R nv = gate * tile[p.own] + (R(1) - gate) * Act<ACT, R>::fwd(av + bv);
+            __syncthreads();
+            tile[p.own] = nv;
+            __syncthreads();
+        }
+        R g = gy[(size_t)smp * P + p.g];  // gradient w.r.t. this neuron's current activation
+        R dvsum = R(0), dgsum = R(0);     // sums of this neuron's two deltas over the iterations
+        for (int it = inner - 1; it >= 0; --it) {
+            const R xo = stash[it * NT + tid];
+            tile[p.own] = xo;
+            __syncthreads();
+            R av = R(0), ag = R(0);
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const R v = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
+                        av = fma(v, wv[a * 9 + bb * 3 + c], av);
+                        ag = fma(v, wg[a * 9 + bb * 3 + c], ag);
+                    }
+            const R gate = sigmoid_(ag + bg);
+            R f, d;
+            Act<ACT, R>::both(av + bv, f, d);
+            const R dv = g * (R(1) - gate) * d;
+            const R dg = g * gate * (R(1) - gate) * (xo - f);
+            dbv += dv;
+            dbg += dg;
+            dvsum += dv;
+            dgsum += dg;
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const int t = a * 9 + bb * 3 + c;
+                        const R v = tile[(p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c];
+                        dwv[t] = fma(v, dv, dwv[t]);
+                        dwg[t] = fma(v, dg, dwg[t]);
+                    }
+            Dv[p.own] = dv;
+            Dg[p.own] = dg;
+            g *= gate;  // the remembered part of the state
+            __syncthreads();
+            // gather: the neighbour at offset o = offset(t) reaches this cell through its tap 26 - t
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int bb = 0; bb < 3; ++bb)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        const int t = a * 9 + bb * 3 + c;
+                        if (inside & (1u << t)) {
+                            const int nb_tid = tid + (c - 1) * DX + (bb - 1) * DY + (a - 1) * DZ;
+                            const int ci = (p.tz + a) * PS + (p.ty + bb) * RS + p.tx + c;
+                            g = fma(wsm[(26 - t) * NT + nb_tid], Dv[ci], g);
+                            g = fma(wsm[(27 + 26 - t) * NT + nb_tid], Dg[ci], g);
+                        }
+                    }
+            __syncthreads();  // the delta tiles and the tile may be overwritten by the next iteration
+        }
+        // ---- gradient of the input tile: owned cells from registers, halo cells from the delta sums
+        R *gxs = gx + (size_t)smp * P;
+        atomicAdd(&gxs[p.g], g);
+        Dv[p.own] = dvsum;
+        Dg[p.own] = dgsum;
+        __syncthreads();
+        for (int i = tid; i < T; i += NT) {
+            const int px = i % E, py = (i / E) % E, pz = i / (E * E);
+            const bool halo = px == 0 || px == E - 1 || py == 0 || py == E - 1 || pz == 0 || pz == E - 1;
+            const int gz = p.bz * BS + pz - 1, gyy = p.by * BS + py - 1, gxx = p.bx * BS + px - 1;
+            if (halo && gz >= 0 && gz < M && gyy >= 0 && gyy < N && gxx >= 0 && gxx < K) {
+                R acc = R(0);
+                for (int a = 0; a < 3; ++a)
+                    for (int bb = 0; bb < 3; ++bb)
+                        for (int c = 0; c < 3; ++c) {
+                            // neuron n = cell - offset(t) in padded coordinates; it must be a block neuron
+                            const int nz = pz - (a - 1), ny = py - (bb - 1), nx = px - (c - 1);
+                            if (nz >= 1 && nz <= BS && ny >= 1 && ny <= BS && nx >= 1 && nx <= BS) {
+                                const int ntid = BS == 8 ? (nx - 1) + 8 * (nz - 1) + 64 * (ny - 1)
+                                                         : (nx - 1) + 4 * (ny - 1) + 16 * (nz - 1);
+                                const int t = a * 9 + bb * 3 + c, ci = nz * PS + ny * RS + nx;
+                                acc = fma(wsm[t * NT + ntid], Dv[ci], acc);
+                                acc = fma(wsm[(27 + t) * NT + ntid], Dg[ci], acc);
+                            }
+                        }
+                atomicAdd(&gxs[((size_t)gz * N + gyy) * K + gxx], acc);
+            }
+        }
+        __syncthreads();
+        Dv[p.own] = R(0);  // (the halo of the delta tiles is still zero)
+        Dg[p.own] = R(0);
+    }
+    if (atomic_params) {
+#pragma unroll
+        for (int t = 0; t < 27; ++t) {
+            atomicAdd(&gw[(size_t)(2 * t) * P + p.g], dwv[t]);
+            atomicAdd(&gw[(size_t)(2 * t + 1) * P + p.g], dwg[t]);
+        }
+        atomicAdd(&gb[p.g], dbv);
+        atomicAdd(&gb[P + p.g], dbg);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 27; ++t) {
+            gw[(size_t)(2 * t) * P + p.g] = dwv[t];
+            gw[(size_t)(2 * t + 1) * P + p.g] = dwg[t];
+        }
+        gb[p.g] = dbv;
+        gb[P + p.g] = dbg;
+    }
+}
+
 // ============================================================= gated backward
 // Dynamic shared memory: tile[TP] | G[TP] | stash[inner][NT]
 template <typename R, int BS, int ACT>
@@ -759,7 +939,13 @@ int launch_gated_bwd_generic(const R *w, const R *b, const R *x, const R *gy, R 
     const int spc = (B + chunks - 1) / chunks;
     dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
     const int atomic_params = grid.y > 1;
-    const size_t smem = bwd_smem_bytes<R>(bs, inner, true);
+    const size_t tp = (size_t)(bs + 2) * (bs == 8 ? 104 : 68), nt = (size_t)bs * bs * bs;
+    const size_t smem_gather = (3 * tp + 54 * nt + (size_t)inner * nt) * sizeof(R);
+    // block 4 only: at block 8 the 110 KB weight copy leaves one CTA per SM and the kernel spills
+    // registers (measured 3.96 ms against 2.27 ms for the atomic kernel on 64^3 x 64 samples, 2 inner;
+    // block 4, 8 inner: 4.73 ms against 6.25 ms)
+    const bool gather = bs == 4 && smem_gather <= kMaxDynSmem;
+    const size_t smem = gather ? smem_gather : bwd_smem_bytes<R>(bs, inner, true);
     if (smem > kMaxDynSmem) return GN_ERR_BAD_INNER;
     cudaError_t e = cudaMemsetAsync(gx, 0, sizeof(R) * B * P, st);
     if (e == cudaSuccess && atomic_params) {
@@ -778,15 +964,28 @@ int launch_gated_bwd_generic(const R *w, const R *b, const R *x, const R *gy, R 
         kern<<<grid, BSV * BSV * BSV, smem, st>>>(w, b, x, gy, gw, gb, gx, B, M, N, K, inner, \
                                                   spc, atomic_params);                        \
     } while (0)
-#define LAUNCH_(A)               \
-    do {                         \
-        if (bs == 8) ONE_(8, A); \
-        else ONE_(4, A);         \
+#define GATHER_(BSV, A)                                                                       \
+    do {                                                                                      \
+        auto kern = gated_bwd_gather<R, BSV, A>;                                              \
+        int rc = opt_in_smem(kern, smem);                                                     \
+        if (rc != GN_OK) return rc;                                                           \
+        kern<<<grid, BSV * BSV * BSV, smem, st>>>(w, b, x, gy, gw, gb, gx, B, M, N, K, inner, \
+                                                  spc, atomic_params);                        \
+    } while (0)
+#define LAUNCH_(A)                          \
+    do {                                    \
+        if (bs == 8) {                      \
+            ONE_(8, A);                     \
+        } else {                            \
+            if (gather) GATHER_(4, A);      \
+            else ONE_(4, A);                \
+        }                                   \
     } while (0)
     GN_ACT_SWITCH(act, LAUNCH_)
 #undef LAUNCH_
+#undef GATHER_
 #undef ONE_
-    return check_launch("gated_bwd_generic");
+    return check_launch("gated_bwd");
 }
 
 // explicit instantiations used by api.cu
