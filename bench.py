@@ -476,6 +476,8 @@ def run_train(args, rank: int, local_rank: int, world: int):
     G, block, inner, outer, batch, desc = TRAIN_WORKLOADS[args.workload]
     if args.batch:
         batch = args.batch
+    if args.stash:  # keep the inner iterations' intermediate results from the forward pass (memory for time)
+        gb.keep_forward_stash(True)
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     dist = None
@@ -562,6 +564,7 @@ def run_train(args, rank: int, local_rank: int, world: int):
                              "alone are %.0f MB, larger than the 126 MB L2"
                              % (b_loc * G ** 3 * 4 / 1e6, 2 * outer, 2 * outer * b_loc * G ** 3 * 4 / 1e6),
                        "forward_ms": t_fwd / steps, "backward_ms": t_bwd / steps, "finite": finite,
+                       "intermediate_results": "kept from the forward pass" if args.stash else "recomputed in the backward pass",
                        "samples_per_sec": batch / sec},
             "roofline": {"bound": "fp32", "achieved": flops / sec / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
                          "frac": flops / sec / 1e12 / fp32_peak,
@@ -660,6 +663,9 @@ def main():
                          "c1: the small launch-bound configuration, also replayed from a CUDA graph")
     ap.add_argument("--slab-exchange", choices=["direct", "nccl"], default="direct",
                     help="c5-slab only: how the boundary faces travel (direct = stored by the step kernel into peer memory)")
+    ap.add_argument("--stash", action="store_true",
+                    help="c3 / c4 only: keep the forward pass's intermediate results instead of recomputing them in the "
+                         "backward pass ((2 inner - 1) extra activation tensors per outer step)")
     ap.add_argument("--batch", type=int, default=0, help="c3 / c4 only: override the global batch size")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

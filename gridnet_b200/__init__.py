@@ -8,7 +8,8 @@ native extension module. Everything runs through ``libgridnet_b200.so`` (C ABI i
 """
 from . import gridnet_cuda
 from ._lib import LIB_PATH, GridnetB200Error
-from .backend_cuda import (GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, HostPipelinedForward, fused_step, norm_apply,
+from .backend_cuda import (GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, HostPipelinedForward, fused_step,
+                           keep_forward_stash, norm_apply,
                            norm_finalize, outer_forward, outer_forward_failed, outer_forward_workspace,
                            step_stats_partials)
 
@@ -30,6 +31,7 @@ __all__ = [
     "GatedGridnetCudaOp",
     "GridNormOp",
     "outer_forward",
+    "keep_forward_stash",
     "HostPipelinedForward",
     "outer_forward_workspace",
     "outer_forward_failed",

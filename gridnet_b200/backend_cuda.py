@@ -38,6 +38,20 @@ def _assert_step_args(weight, bias, residual_scale, init_activations, block_size
     return batch_size
 
 
+_keep_forward_stash = False
+
+
+def keep_forward_stash(enabled: bool) -> bool:
+    """Trade memory for time in training: when on, a :class:`GridnetCudaOp` forward that will be
+    differentiated (float32, per-block normalisation off, tuned path) also keeps every inner iteration's
+    pre-activations and intermediate activations, ``(2 * inner_iters - 1)`` extra activation tensors per
+    call, and its backward skips recomputing them (about a quarter of the backward time). Off by default:
+    the reference recomputes, and so does this package unless asked. Returns the previous setting."""
+    global _keep_forward_stash
+    previous, _keep_forward_stash = _keep_forward_stash, bool(enabled)
+    return previous
+
+
 class GridnetCudaOp(torch.autograd.Function):
     """One outer-loop step of the plain gridnet (gridnet/backend_cuda.py:5-108)."""
 
@@ -49,7 +63,13 @@ class GridnetCudaOp(torch.autograd.Function):
             return init_activations.clone()
         ctx.save_for_backward(weight, bias, residual_scale, init_activations)
         ctx.cfg = (inner_iters, block_size, eps, normalize, activation)
+        ctx.stash = None
         outputs = torch.empty_like(init_activations)
+        if (_keep_forward_stash and not normalize and weight.dtype == torch.float32
+                and any(ctx.needs_input_grad[:4])):
+            ctx.stash = gridnet_cuda.forward_with_stash(weight, bias, residual_scale, init_activations, outputs,
+                                                        inner_iters, block_size, activation)
+            return outputs
         gridnet_cuda.forward(weight, bias, residual_scale, init_activations, outputs, inner_iters, block_size,
                              eps, normalize, activation)
         return outputs
@@ -63,6 +83,12 @@ class GridnetCudaOp(torch.autograd.Function):
         bias_grad = torch.empty_like(bias)
         scale_grad = torch.empty_like(residual_scale)
         act_grad = torch.empty_like(init_activations)
+        if ctx.stash is not None:
+            stash, ctx.stash = ctx.stash, None
+            gridnet_cuda.backward_with_stash(weight, bias, residual_scale, init_activations, grad_output.contiguous(),
+                                             weight_grad, bias_grad, scale_grad, act_grad, inner_iters, block_size,
+                                             activation, stash)
+            return weight_grad, bias_grad, scale_grad, act_grad, None, None, None, None, None
         gridnet_cuda.backward(weight, bias, residual_scale, init_activations, grad_output.contiguous(),
                               weight_grad, bias_grad, scale_grad, act_grad, inner_iters, block_size, eps,
                               normalize, activation)

@@ -310,13 +310,13 @@ GN_API size_t gn_step_backward_workspace_bytes(int B, int M, int N, int K, int i
     if (elem_size != 4 || (block != 8 && block != 4) || normalize || inner < 1 || B <= 0 || M <= 0 || N <= 0 || K <= 0)
         return 0;
     if (M % 8 || N % 8 || K % 8) return 0;
-    return align_up(sizeof(float) * bwd_fast8_workspace_floats(B, M, N, K, inner), 256);
+    return align_up(sizeof(float) * bwd_fast8_workspace_floats(B, M, N, K, inner, true), 256);
 }
 
 GN_API size_t gn_step_backward_error_flag_offset(int B, int M, int N, int K, int inner)
 {
     if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || inner < 1) return 0;
-    return sizeof(float) * (bwd_fast8_workspace_floats(B, M, N, K, inner) - 4);
+    return sizeof(float) * (bwd_fast8_workspace_floats(B, M, N, K, inner, true) - 4);
 }
 
 GN_API int gn_step_backward_ws_f32(const float *w, const float *b, const float *s, const float *x, const float *gy,
@@ -330,10 +330,75 @@ GN_API int gn_step_backward_ws_f32(const float *w, const float *b, const float *
     if (B > 0 && need > 0 && workspace && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) % 16) == 0 &&
         w && b && s && x && gy && gw && gb && gs && gx &&
         bwd_fast8_applicable(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, normalize))
-        return launch_step_bwd_fast8(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, act, (float *)workspace,
-                                     (cudaStream_t)stream);
+        return launch_step_bwd_fast8(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, act, nullptr,
+                                     (float *)workspace, (cudaStream_t)stream);
     return api_step_backward<float>(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, eps, normalize, act,
                                     stream);
+}
+
+// ---- the same pair with the replay's results kept from the forward pass (a "stash")
+static bool stash_geometry_ok(int B, int M, int N, int K, int inner, int block)
+{
+    return (block == 8 || block == 4) && inner >= 1 && B > 0 && M > 0 && N > 0 && K > 0 && !(M % 8 || N % 8 || K % 8);
+}
+
+GN_API size_t gn_step_stash_bytes(int B, int M, int N, int K, int inner, int block)
+{
+    if (!stash_geometry_ok(B, M, N, K, inner, block)) return 0;
+    return align_up(sizeof(float) * bwd_fast8_stash_floats(B, M, N, K, inner), 256);
+}
+
+GN_API size_t gn_step_backward_stash_workspace_bytes(int B, int M, int N, int K, int inner, int block)
+{
+    if (!stash_geometry_ok(B, M, N, K, inner, block)) return 0;
+    return align_up(sizeof(float) * bwd_fast8_workspace_floats(B, M, N, K, inner, false), 256);
+}
+
+GN_API size_t gn_step_backward_stash_error_flag_offset(int B, int M, int N, int K, int inner)
+{
+    if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || inner < 1) return 0;
+    return sizeof(float) * (bwd_fast8_workspace_floats(B, M, N, K, inner, false) - 4);
+}
+
+GN_API int gn_step_forward_stash_f32(const float *w, const float *b, const float *s, const float *x, float *y, int B,
+                                     int M, int N, int K, int inner, int block, int act, void *stash, size_t stash_bytes,
+                                     void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (B == 0) return GN_OK;
+    if (!w || !b || !s || !x || !y || !stash) return GN_ERR_NULL_POINTER;
+    const size_t need = gn_step_stash_bytes(B, M, N, K, inner, block);
+    if (need == 0) return GN_ERR_UNSUPPORTED;
+    if (stash_bytes < need || reinterpret_cast<uintptr_t>(stash) % 16) return GN_ERR_WORKSPACE;
+    FastFwdParams p{};
+    p.w = w; p.b = b; p.s = s; p.x = x; p.y = y;
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner; p.sub = block;
+    p.save_h = static_cast<float *>(stash);
+    p.save_x = p.save_h + (size_t)inner * B * M * N * K;
+    if (!fast8_applicable(p, block, 0)) return GN_ERR_UNSUPPORTED;
+    return launch_step_fwd_fast8(p, act, (cudaStream_t)stream);
+}
+
+GN_API int gn_step_backward_stash_f32(const float *w, const float *b, const float *s, const float *x, const float *gy,
+                                      float *gw, float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner,
+                                      int block, int act, const void *stash, size_t stash_bytes, void *workspace,
+                                      size_t workspace_bytes, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (!w || !b || !s || !gw || !gb || !gs) return GN_ERR_NULL_POINTER;
+    if (B == 0) return GN_ERR_UNSUPPORTED;  // nothing was stashed: use gn_step_backward_f32
+    if (!x || !gy || !gx || !stash || !workspace) return GN_ERR_NULL_POINTER;
+    const size_t need_stash = gn_step_stash_bytes(B, M, N, K, inner, block);
+    const size_t need_ws = gn_step_backward_stash_workspace_bytes(B, M, N, K, inner, block);
+    if (need_stash == 0) return GN_ERR_UNSUPPORTED;
+    if (stash_bytes < need_stash || workspace_bytes < need_ws || reinterpret_cast<uintptr_t>(stash) % 16 ||
+        reinterpret_cast<uintptr_t>(workspace) % 16)
+        return GN_ERR_WORKSPACE;
+    if (!bwd_fast8_applicable(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, 0)) return GN_ERR_UNSUPPORTED;
+    return launch_step_bwd_fast8(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, act,
+                                 static_cast<const float *>(stash), static_cast<float *>(workspace), (cudaStream_t)stream);
 }
 
 GN_API int gn_step_backward_max_inner(int block, int elem_size) { return step_backward_max_inner(block, elem_size); }

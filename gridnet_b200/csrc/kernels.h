@@ -65,13 +65,14 @@ int launch_slab_unpack_faces(const float *from_left, const float *from_right, fl
                              int col_left, int col_right, cudaStream_t st);
 
 // ---- step_bwd_fast.cu (tuned float backward, block 8, normalize off; needs a workspace)
-size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner);
+size_t bwd_fast8_stash_floats(int B, int M, int N, int K, int inner);
+size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner, bool with_stash);
 bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block,
                           int normalize);
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
-                          float *ws, cudaStream_t st);
+                          const float *stash, float *ws, cudaStream_t st);
 
 // ---- step_lanes.cu ("lanes = samples" kernel of the fused loop; activations in the IL16 layout
 // [group][z][y][x][16 samples])

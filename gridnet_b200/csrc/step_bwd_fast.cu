@@ -689,12 +689,19 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
 }
 
 // ---------------------------------------------------------------------------------- launcher
-size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner)
+size_t bwd_fast8_stash_floats(int B, int M, int N, int K, int inner)
 {
-    const size_t P = (size_t)M * N * K, BP = (size_t)B * P;
-    // pre-activations, activations between iterations, deltas, delta sums, scale-gradient terms, and
-    // 16 bytes whose first int is the error flag of the bounded waits
-    return (size_t)inner * BP + (size_t)(inner > 1 ? inner - 1 : 0) * BP + (size_t)inner * BP + 2 * BP + 4;
+    // pre-activations of every iteration and the activations between iterations
+    const size_t BP = (size_t)B * M * N * K;
+    return (size_t)inner * BP + (size_t)(inner > 1 ? inner - 1 : 0) * BP;
+}
+
+size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner, bool with_stash)
+{
+    // [the stash, unless the forward pass kept it,] deltas, delta sums, scale-gradient terms, and 16 bytes
+    // whose first int is the error flag of the bounded waits
+    const size_t BP = (size_t)B * M * N * K;
+    return (with_stash ? bwd_fast8_stash_floats(B, M, N, K, inner) : 0) + (size_t)inner * BP + 2 * BP + 4;
 }
 
 bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
@@ -762,12 +769,14 @@ static void launch_reverse(const BwdParams &p, dim3 grid, int act, cudaStream_t 
 
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
-                          float *ws, cudaStream_t st)
+                          const float *stash, float *ws, cudaStream_t st)
 {
+    // stash != nullptr: the forward pass kept the pre-activations and intermediate activations
+    // (launch_step_fwd_fast8 with save_h / save_x), so the replay is skipped
     const size_t P = (size_t)M * N * K, BP = (size_t)B * P;
-    float *save_h = ws;
+    float *save_h = stash ? const_cast<float *>(stash) : ws;
     float *save_x = save_h + (size_t)inner * BP;
-    float *delta = save_x + (size_t)(inner > 1 ? inner - 1 : 0) * BP;
+    float *delta = stash ? ws : save_x + (size_t)(inner > 1 ? inner - 1 : 0) * BP;
     float *dsum = delta + (size_t)inner * BP;
     float *dsb = dsum + BP;
     int *error_flag = reinterpret_cast<int *>(dsb + BP);
@@ -783,8 +792,10 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     f.save_h = save_h;
     f.save_x = save_x;
     f.error_flag = error_flag;
-    rc = launch_step_fwd_fast8(f, act, st);
-    if (rc != GN_OK) return rc;
+    if (!stash) {
+        rc = launch_step_fwd_fast8(f, act, st);
+        if (rc != GN_OK) return rc;
+    }
 
     const long long nb = (long long)(M / 8) * (N / 8) * (K / 8);  // 8^3 regions, one CTA (per batch chunk) each
     BwdParams p{};

@@ -84,6 +84,49 @@ def backward(weight, bias, scale, initActivations, outGrads, weightGradOut, bias
                  _stream(weight)))
 
 
+def forward_with_stash(weight, bias, scale, initActivations, outActivations, innerIterations, blockSize, activation):
+    """:func:`forward` (normalize off, float32) that also keeps what the backward pass would otherwise
+    recompute. Returns the stash tensor, or ``None`` (after running the ordinary forward) where the
+    tuned path does not apply. Not part of the reference's module: it always recomputes."""
+    _same((weight, bias, scale, initActivations, outActivations),
+          ("weight", "bias", "scale", "initActivations", "outActivations"))
+    B, M, N, K = initActivations.shape
+    need = 0
+    if weight.dtype == torch.float32 and B > 0:
+        need = int(lib.gn_step_stash_bytes(B, M, N, K, int(innerIterations), int(blockSize)))
+    with torch.cuda.device(weight.device):
+        if need:
+            stash = torch.empty(need, dtype=torch.uint8, device=weight.device)
+            rc = lib.gn_step_forward_stash_f32(
+                weight.data_ptr(), bias.data_ptr(), scale.data_ptr(), initActivations.data_ptr(),
+                outActivations.data_ptr(), B, M, N, K, int(innerIterations), int(blockSize), activation_id(activation),
+                stash.data_ptr(), stash.numel(), _stream(weight))
+            if rc == 0:
+                return stash
+            if rc != -8:  # anything but "the tuned path does not apply here"
+                check(rc)
+    forward(weight, bias, scale, initActivations, outActivations, innerIterations, blockSize, 1e-5, False, activation)
+    return None
+
+
+def backward_with_stash(weight, bias, scale, initActivations, outGrads, weightGradOut, biasGradOut, scaleGradOut,
+                        activationsGradOut, innerIterations, blockSize, activation, stash) -> None:
+    """:func:`backward` for a step whose forward pass went through :func:`forward_with_stash`."""
+    _same((weight, bias, scale, initActivations, outGrads, weightGradOut, biasGradOut, scaleGradOut,
+           activationsGradOut),
+          ("weight", "bias", "scale", "initActivations", "outGrads", "weightGradOut", "biasGradOut",
+           "scaleGradOut", "activationsGradOut"))
+    B, M, N, K = initActivations.shape
+    with torch.cuda.device(weight.device):
+        need = int(lib.gn_step_backward_stash_workspace_bytes(B, M, N, K, int(innerIterations), int(blockSize)))
+        ws = torch.empty(need, dtype=torch.uint8, device=weight.device)
+        check(lib.gn_step_backward_stash_f32(
+            weight.data_ptr(), bias.data_ptr(), scale.data_ptr(), initActivations.data_ptr(), outGrads.data_ptr(),
+            weightGradOut.data_ptr(), biasGradOut.data_ptr(), scaleGradOut.data_ptr(), activationsGradOut.data_ptr(),
+            B, M, N, K, int(innerIterations), int(blockSize), activation_id(activation), stash.data_ptr(), stash.numel(),
+            ws.data_ptr(), ws.numel(), _stream(weight)))
+
+
 def forward_gated(weight, bias, initActivations, outActivations, innerIterations, blockSize,
                   activation) -> None:
     _same((weight, bias, initActivations, outActivations),

@@ -121,6 +121,30 @@ GN_API int gn_step_backward_ws_f32(const float *weight, const float *bias, const
                             int N, int K, int inner, int block, float eps, int normalize,
                             int activation, void *workspace, size_t workspace_bytes,
                             void *stream);
+/* The tuned pair with the intermediate results kept from the forward pass ("stash"), for callers
+ * that can afford the memory: gn_step_forward_stash_f32 is gn_step_forward_f32 (normalize = 0) that
+ * also stores every inner iteration's pre-activation and the activations between iterations into
+ * `stash` ((2 * inner - 1) * B * M*N*K floats, 16-byte aligned, gn_step_stash_bytes); the stash must
+ * stay untouched until gn_step_backward_stash_f32 has consumed it. That call then skips the
+ * recomputation of the inner iterations (about a quarter of the tuned backward) and needs only
+ * gn_step_backward_stash_workspace_bytes of scratch ((inner + 2) * B * M*N*K floats; error flag at
+ * gn_step_backward_stash_error_flag_offset). Same results, bit for bit, as gn_step_backward_ws_f32.
+ * GN_ERR_UNSUPPORTED where the tuned path does not apply (the size queries return 0 there): grid
+ * sides not multiples of 8, misaligned pointers, no bulk-tensor-copy support for block 4.
+ * The reference always recomputes (src/gridnet_cuda_kernels.cu:246-300); no counterpart. */
+GN_API size_t gn_step_stash_bytes(int B, int M, int N, int K, int inner, int block);
+GN_API size_t gn_step_backward_stash_workspace_bytes(int B, int M, int N, int K, int inner, int block);
+GN_API size_t gn_step_backward_stash_error_flag_offset(int B, int M, int N, int K, int inner);
+GN_API int gn_step_forward_stash_f32(const float *weight, const float *bias, const float *scale,
+                              const float *x, float *y, int B, int M, int N, int K, int inner,
+                              int block, int activation, void *stash, size_t stash_bytes,
+                              void *stream);
+GN_API int gn_step_backward_stash_f32(const float *weight, const float *bias, const float *scale,
+                               const float *x, const float *grad_y, float *grad_weight,
+                               float *grad_bias, float *grad_scale, float *grad_x, int B, int M,
+                               int N, int K, int inner, int block, int activation,
+                               const void *stash, size_t stash_bytes, void *workspace,
+                               size_t workspace_bytes, void *stream);
 /* Largest `inner` the backward entry points accept for this block size and
  * element size (the per-iteration stash lives in shared memory). */
 GN_API int gn_step_backward_max_inner(int block, int elem_size);

@@ -357,6 +357,35 @@ def test_forward_with_unaligned_activations_uses_the_plain_load_path():
 
 
 @pytest.mark.parametrize("block", [8, 4])
+def test_keep_forward_stash_gives_identical_gradients(block):
+    """The autograd op with the memory-for-time switch on: same output and the same gradient bits, also when
+    the graph is differentiated twice (the second pass has no stash left and recomputes)."""
+    import gridnet_b200 as gb
+
+    Op, _ = ops()
+    shape, B, inner = (16, 24, 8), 3, 4
+    w, b, s, x = rng_inputs(51, B, shape, unit_scale=True)
+    gy = dev(np.random.default_rng(52).standard_normal(x.shape).astype(np.float32))
+
+    def run():
+        t = [dev(a).requires_grad_(True) for a in (w, b, s, x)]
+        y = Op.apply(*t, inner, block, 1e-5, False, "silu")
+        g1 = torch.autograd.grad(y, t, gy, retain_graph=True)
+        g2 = torch.autograd.grad(y, t, gy)
+        return y.detach(), g1, g2
+
+    y0, ga, gb2 = run()
+    previous = gb.keep_forward_stash(True)
+    try:
+        y1, gc, gd = run()
+    finally:
+        gb.keep_forward_stash(previous)
+    assert previous is False and torch.equal(y0, y1)
+    for a, b_, c, d in zip(ga, gb2, gc, gd):
+        assert torch.equal(a, b_) and torch.equal(a, c) and torch.equal(a, d)
+
+
+@pytest.mark.parametrize("block", [8, 4])
 def test_tuned_backward_equals_one_kernel_backward(block):
     """float32, normalize off: the four-kernel path (with workspace) against the one-kernel path
     (without) and the float64 oracle, on a grid with interior, face, edge and corner blocks, an odd
@@ -400,7 +429,34 @@ def test_tuned_backward_equals_one_kernel_backward(block):
     # order), so two runs agree bit for bit
     for name, a, a2 in zip(("gw", "gb", "gs", "gx"), outs["tuned"], outs["tuned again"]):
         assert np.array_equal(a, a2), name
+    # the same gradients, bit for bit, when the forward pass kept its intermediate results (no replay)
+    y_plain = torch.empty_like(tx)
+    assert lib.gn_step_forward_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), y_plain.data_ptr(),
+                                   B, M, N, K, inner, block, 1e-5, 0, 2, stream) == 0
+    nst = lib.gn_step_stash_bytes(B, M, N, K, inner, block)
+    nws = lib.gn_step_backward_stash_workspace_bytes(B, M, N, K, inner, block)
+    assert nst > 0 and 0 < nws < need
+    stash = torch.empty(nst, dtype=torch.uint8, device="cuda")
+    ws2 = torch.empty(nws, dtype=torch.uint8, device="cuda")
+    y_stash = torch.empty_like(tx)
+    assert lib.gn_step_forward_stash_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), y_stash.data_ptr(),
+                                         B, M, N, K, inner, block, 2, stash.data_ptr(), stash.numel(), stream) == 0
+    assert torch.equal(y_stash, y_plain)
+    g = [torch.full_like(t, 3.0) for t in (tw, tb, ts, tx)]
+    rc = lib.gn_step_backward_stash_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), tgy.data_ptr(),
+                                        *(t.data_ptr() for t in g), B, M, N, K, inner, block, 2, stash.data_ptr(),
+                                        stash.numel(), ws2.data_ptr(), ws2.numel(), stream)
+    assert rc == 0, lib.gn_status_string(rc)
+    off = lib.gn_step_backward_stash_error_flag_offset(B, M, N, K, inner)
+    assert int(ws2.view(torch.int32)[off // 4].item()) == 0
+    for name, a, t in zip(("gw", "gb", "gs", "gx"), outs["tuned"], g):
+        assert np.array_equal(a, t.cpu().numpy()), name
+    # too small a stash or workspace is refused, not overrun
+    assert lib.gn_step_backward_stash_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), tgy.data_ptr(),
+                                          *(t.data_ptr() for t in g), B, M, N, K, inner, block, 2, stash.data_ptr(),
+                                          stash.numel() - 512, ws2.data_ptr(), ws2.numel(), stream) == -6
     # no tuned path: sides that are not multiples of 8, per-block normalisation, double precision
+    assert lib.gn_step_stash_bytes(B, 12, N, K, inner, 4) == 0
     assert lib.gn_step_backward_workspace_bytes(B, 12, N, K, inner, 4, 0, 4) == 0
     assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, block, 1, 4) == 0
     assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, block, 0, 8) == 0
