@@ -562,7 +562,9 @@ __global__ void __launch_bounds__(HaloGeo<SUB>::THREADS) bwd_halo8_k(const float
 // thread instead of 27. The partial sums go to shared memory, and after a barrier one thread per
 // surface cell adds the up to three of them to grad_x in the fixed order z, y, x.
 // (Also tried: the reverse sweep writing the x faces of the delta sums packed, so that this kernel
-// reads them as whole sectors: 3 % here, and it costs the reverse sweep as much.)
+// reads them as whole sectors: 3 % here, and it costs the reverse sweep as much. The same face
+// split for block 4, with 8 x 6 faces of 16 cells and 768 threads, was 13 % slower than the first
+// form there, which therefore still runs block 4.)
 namespace border8 {
 constexpr int THREADS = 384;
 constexpr int TS = 1000;
