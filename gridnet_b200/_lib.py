@@ -81,12 +81,17 @@ class GridnetB200Error(RuntimeError):
     pass
 
 
+# gn_status values the Python layer looks at (include/gridnet_b200.h)
+GN_ERR_CUDA = -7
+GN_ERR_UNSUPPORTED = -8
+
+
 def check(status: int) -> None:
     """Turn a non-zero gn_status into a RuntimeError, like the reference's C++
     exceptions surface in Python (src/gridnet_cuda.cpp:6-10)."""
     if status != 0:
         msg = lib.gn_status_string(status).decode()
-        if status == -7:
+        if status == GN_ERR_CUDA:
             msg += ": " + lib.gn_last_cuda_error().decode()
         raise GridnetB200Error(msg)
 

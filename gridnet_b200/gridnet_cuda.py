@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-from ._lib import GridnetB200Error, activation_id, check, lib
+from ._lib import GN_ERR_UNSUPPORTED, GridnetB200Error, activation_id, check, lib
 
 
 def _check_input(t: torch.Tensor, name: str) -> None:
@@ -103,7 +103,7 @@ def forward_with_stash(weight, bias, scale, initActivations, outActivations, inn
                 stash.data_ptr(), stash.numel(), _stream(weight))
             if rc == 0:
                 return stash
-            if rc != -8:  # anything but "the tuned path does not apply here"
+            if rc != GN_ERR_UNSUPPORTED:  # anything but "the tuned path does not apply here"
                 check(rc)
     forward(weight, bias, scale, initActivations, outActivations, innerIterations, blockSize, 1e-5, False, activation)
     return None
