@@ -509,21 +509,39 @@ def run_train(args, rank: int, local_rank: int, world: int):
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     t_fwd = t_bwd = 0.0
 
+    nmb = max(1, args.microbatches)
+    if b_loc % nmb:
+        raise SystemExit(f"the per-rank batch {b_loc} does not divide into {nmb} micro-batches")
+    mb = b_loc // nmb
+
     def step(timed: bool):
+        """Forward + backward over the rank's whole batch; with --microbatches N in N slices whose parameter
+        gradients are accumulated (less memory live at once: what --stash needs at C3's full batch)."""
         nonlocal t_fwd, t_bwd
-        ev[0].record()
-        y = model(x)
-        ev[1].record()
-        grads = torch.autograd.grad(y, params + [x], gy)
+        total, gxs = None, []
+        for i in range(nmb):
+            xs = x if nmb == 1 else x[i * mb:(i + 1) * mb].detach().requires_grad_(True)
+            gys = gy if nmb == 1 else gy[i * mb:(i + 1) * mb]
+            ev[0].record()
+            y = model(xs)
+            ev[1].record()
+            grads = torch.autograd.grad(y, params + [xs], gys)
+            del y
+            gxs.append(grads[-1])
+            if total is None:
+                total = list(grads[:-1])
+            else:
+                for acc, gnew in zip(total, grads[:-1]):
+                    acc.add_(gnew)
+            ev[2].record()
+            if timed:
+                ev[2].synchronize()
+                t_fwd += ev[0].elapsed_time(ev[1])
+                t_bwd += ev[1].elapsed_time(ev[2])
         if dist is not None:
-            flat = torch.cat([t.reshape(-1) for t in grads[:-1]])
+            flat = torch.cat([t.reshape(-1) for t in total])
             dist.all_reduce(flat)
-        ev[2].record()
-        if timed:
-            ev[2].synchronize()
-            t_fwd += ev[0].elapsed_time(ev[1])
-            t_bwd += ev[1].elapsed_time(ev[2])
-        return grads
+        return total + gxs
 
     warm = max(3, args.warmup)  # the first steps also grow torch's allocator cache
     for _ in range(warm):
@@ -565,6 +583,7 @@ def run_train(args, rank: int, local_rank: int, world: int):
                              % (b_loc * G ** 3 * 4 / 1e6, 2 * outer, 2 * outer * b_loc * G ** 3 * 4 / 1e6),
                        "forward_ms": t_fwd / steps, "backward_ms": t_bwd / steps, "finite": finite,
                        "intermediate_results": "kept from the forward pass" if args.stash else "recomputed in the backward pass",
+                       "microbatches": nmb,
                        "samples_per_sec": batch / sec},
             "roofline": {"bound": "fp32", "achieved": flops / sec / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
                          "frac": flops / sec / 1e12 / fp32_peak,
@@ -666,6 +685,8 @@ def main():
     ap.add_argument("--stash", action="store_true",
                     help="c3 / c4 only: keep the forward pass's intermediate results instead of recomputing them in the "
                          "backward pass ((2 inner - 1) extra activation tensors per outer step)")
+    ap.add_argument("--microbatches", type=int, default=1,
+                    help="c3 / c4 only: run a step as this many slices of the batch, accumulating parameter gradients")
     ap.add_argument("--batch", type=int, default=0, help="c3 / c4 only: override the global batch size")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
