@@ -268,6 +268,74 @@ def norm_apply(x, norm_weight, norm_bias, mean_rstd, out) -> torch.Tensor:
     return out
 
 
+# ---- building blocks of the large-batch step kernel (gn_pair64_* in include/gridnet_b200.h) ----------------
+def _il64_groups(batch: int) -> int:
+    return (int(batch) + 63) // 64
+
+
+@torch.no_grad()
+def pair64_pack_weights(weight, bias, residual_scale) -> torch.Tensor:
+    """weight [27,M,N,K], bias, residual_scale [M,N,K] (float32, M, N, K multiples of 8) -> the parameters in
+    the order the large-batch step kernel reads them (one flat float32 tensor)."""
+    _require_f32_cuda(weight=weight, bias=bias, residual_scale=residual_scale)
+    M, N, K = bias.shape
+    nbytes = int(lib.gn_pair64_packed_weight_bytes(M, N, K))
+    if nbytes == 0:
+        raise RuntimeError(f"grid {tuple(bias.shape)} is not a multiple of 8 in every dimension")
+    packed = torch.empty(nbytes // 4, dtype=torch.float32, device=weight.device)
+    with torch.cuda.device(weight.device):
+        check(lib.gn_pair64_pack_weights_f32(weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(),
+                                             packed.data_ptr(), M, N, K, torch.cuda.current_stream().cuda_stream))
+    return packed
+
+
+@torch.no_grad()
+def pair64_interleave(x, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [B,M,N,K] -> the same activations interleaved by groups of 64 samples, [ceil(B/64), M, N, K, 64]
+    (samples beyond B are zero)."""
+    _require_f32_cuda(x=x)
+    B, M, N, K = x.shape
+    if out is None:
+        out = torch.empty(_il64_groups(B), M, N, K, 64, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.gn_pair64_interleave_f32(x.data_ptr(), out.data_ptr(), B, M, N, K,
+                                           torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+@torch.no_grad()
+def pair64_deinterleave(x_il64, batch: int, shape, mean_rstd=None, norm_weight=None, norm_bias=None,
+                        out: torch.Tensor | None = None) -> torch.Tensor:
+    """Inverse of :func:`pair64_interleave`; with ``mean_rstd`` the whole-grid normalisation is applied on the
+    way: ``(v - mean) * rstd * norm_weight + norm_bias``."""
+    _require_f32_cuda(x_il64=x_il64)
+    M, N, K = shape
+    if out is None:
+        out = torch.empty(batch, M, N, K, dtype=torch.float32, device=x_il64.device)
+    ptr = lambda t: None if t is None else t.data_ptr()
+    with torch.cuda.device(x_il64.device):
+        check(lib.gn_pair64_deinterleave_f32(x_il64.data_ptr(), ptr(mean_rstd), ptr(norm_weight), ptr(norm_bias),
+                                             out.data_ptr(), int(batch), M, N, K,
+                                             torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+@torch.no_grad()
+def pair64_step(packed, x_il64, y_il64, batch: int, shape, inner_iters: int, activation: str = "silu",
+                norm_weight=None, norm_bias=None, in_mean_rstd=None, out_partials=None, error_flag=None) -> torch.Tensor:
+    """One step of the large-batch kernel on interleaved activations (``gn_step_forward_pair64_f32``); the
+    optional arguments have the meaning they have in :func:`fused_step`, with ``64 * ceil(B/64)`` rows."""
+    M, N, K = shape
+    ptr = lambda t: None if t is None else t.data_ptr()
+    nparts = 0 if out_partials is None else int(out_partials.shape[1])
+    with torch.cuda.device(x_il64.device):
+        check(lib.gn_step_forward_pair64_f32(packed.data_ptr(), x_il64.data_ptr(), y_il64.data_ptr(), ptr(norm_weight),
+                                             ptr(norm_bias), ptr(in_mean_rstd), ptr(out_partials), nparts, int(batch),
+                                             M, N, K, int(inner_iters), activation_id(activation), ptr(error_flag),
+                                             torch.cuda.current_stream().cuda_stream))
+    return y_il64
+
+
 class HostPipelinedForward:
     """The fused inference loop for batches that live in (pinned) HOST memory.
 

@@ -183,21 +183,23 @@ static NormWs carve_norm(void *base, int B)
 }
 
 struct OuterWs {
-    float *buf[2];      // [Bpad,M,N,K] each (Bpad = batch rounded up to 16: the IL16 layout works in groups of 16)
+    float *buf[2];      // [Bpad,M,N,K] each (Bpad = batch rounded up to 64: the IL64 layout works in groups of 64)
     double2 *partials;  // [Bpad][blocks * 4]
     float2 *stats;      // [Bpad]
+    float *packed;      // block 8 only: pair64_packed_floats(M, N, K) floats (weights in the large-batch kernel's order)
     int *error_flag;
     size_t bytes;
 };
 
-static int round_up16(int B) { return (B + 15) / 16 * 16; }
+static int round_up64(int B) { return (B + 63) / 64 * 64; }
 
 static OuterWs carve_outer(void *base, int B, int M, int N, int K, int block)
 {
     OuterWs w;
     const size_t P = (size_t)M * N * K;
     const size_t nb = (size_t)(M / block) * (N / block) * (K / block);
-    const size_t Bp = (size_t)round_up16(B);
+    const bool pair = block == 8 && M % 8 == 0 && N % 8 == 0 && K % 8 == 0;
+    const size_t Bp = pair ? (size_t)round_up64(B) : (size_t)B;
     size_t off = 0;
     unsigned char *p = (unsigned char *)base;
     for (int i = 0; i < 2; ++i) {
@@ -208,15 +210,22 @@ static OuterWs carve_outer(void *base, int B, int M, int N, int K, int block)
     off = align_up(off + sizeof(double2) * Bp * nb * 4, 256);
     w.stats = (float2 *)(p + off);
     off = align_up(off + sizeof(float2) * Bp, 256);
+    w.packed = (float *)(p + off);
+    if (pair) off = align_up(off + sizeof(float) * pair64_packed_floats(M, N, K), 256);
     w.error_flag = (int *)(p + off);
     off = align_up(off + sizeof(int), 256);
     w.bytes = off;
     return w;
 }
 
-// 0 = choose automatically (currently always the register-patch kernel), 1 = register-patch kernel
-// (step_fast.cu), 2 = lanes kernel (step_lanes.cu)
+// 0 = choose automatically (the large-batch kernel of step_pair64.cu when the batch fills its groups of
+// 64 samples well, else the register-patch kernel of step_fast.cu), 1 = always the register-patch
+// kernel, 2 = always the large-batch kernel
 static int g_outer_kernel = 0;
+
+// The large-batch kernel computes whole groups of 64 samples: worth it when at most a quarter of the
+// last group is padding.
+static bool pair64_fills_groups(int B) { return round_up64(B) * 3 <= B * 4; }
 
 static int check_ws(const void *ws, size_t have, size_t need)
 {
@@ -598,6 +607,82 @@ GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *be
                              (cudaStream_t)stream);
 }
 
+GN_API int gn_probe_fp32_fma(float *sink, int iters_per_chain, long long *fma_count, void *stream)
+{
+    if (!sink) return GN_ERR_NULL_POINTER;
+    if (iters_per_chain <= 0) return GN_ERR_BAD_SHAPE;
+    return launch_ffma_probe(sink, iters_per_chain, fma_count, (cudaStream_t)stream);
+}
+
+GN_API int gn_pair64_supported(int M, int N, int K, int block, int inner)
+{
+    return pair64_applicable(M, N, K, block, inner) ? 1 : 0;
+}
+
+GN_API size_t gn_pair64_packed_weight_bytes(int M, int N, int K)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || M % 8 || N % 8 || K % 8) return 0;
+    return sizeof(float) * pair64_packed_floats(M, N, K);
+}
+
+GN_API int gn_pair64_pack_weights_f32(const float *w, const float *b, const float *s, float *packed, int M, int N, int K,
+                                      void *stream)
+{
+    if (M <= 0 || N <= 0 || K <= 0) return GN_ERR_BAD_SHAPE;
+    if (M % 8 || N % 8 || K % 8) return GN_ERR_BAD_BLOCK;
+    if (!w || !b || !s || !packed) return GN_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(packed) % 16) return GN_ERR_UNSUPPORTED;
+    return launch_pair64_pack(w, b, s, packed, M, N, K, (cudaStream_t)stream);
+}
+
+GN_API int gn_pair64_interleave_f32(const float *x, float *x_il64, int B, int M, int N, int K, void *stream)
+{
+    if (B <= 0 || M <= 0 || N <= 0 || K <= 0) return GN_ERR_BAD_SHAPE;
+    if (((long long)M * N * K) % 32) return GN_ERR_BAD_SHAPE;
+    if (!x || !x_il64) return GN_ERR_NULL_POINTER;
+    return launch_to_il64(x, x_il64, B, round_up64(B) / 64, (long long)M * N * K, (cudaStream_t)stream);
+}
+
+GN_API int gn_pair64_deinterleave_f32(const float *y_il64, const float *mean_rstd, const float *gamma, const float *beta,
+                                      float *y, int B, int M, int N, int K, void *stream)
+{
+    if (B <= 0 || M <= 0 || N <= 0 || K <= 0) return GN_ERR_BAD_SHAPE;
+    if (((long long)M * N * K) % 32) return GN_ERR_BAD_SHAPE;
+    if (!y_il64 || !y) return GN_ERR_NULL_POINTER;
+    if (mean_rstd && (!gamma || !beta)) return GN_ERR_NULL_POINTER;
+    return launch_from_il64(y_il64, reinterpret_cast<const float2 *>(mean_rstd), gamma, beta, y, B, round_up64(B) / 64,
+                            (long long)M * N * K, (cudaStream_t)stream);
+}
+
+GN_API int gn_step_forward_pair64_f32(const float *packed, const float *x_il64, float *y_il64, const float *gamma,
+                                      const float *beta, const float *in_mean_rstd, double *out_partials,
+                                      int partials_per_sample, int B, int M, int N, int K, int inner, int act,
+                                      int *error_flag, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, 8, act);
+    if (rc != GN_OK) return rc;
+    if (B == 0) return GN_OK;
+    if (!packed || !x_il64 || !y_il64) return GN_ERR_NULL_POINTER;
+    if (in_mean_rstd && (!gamma || !beta)) return GN_ERR_NULL_POINTER;
+    if (!pair64_applicable(M, N, K, 8, inner)) return GN_ERR_UNSUPPORTED;
+    const int nblocks = (M / 8) * (N / 8) * (K / 8);
+    if (out_partials && partials_per_sample < nblocks * 4) return GN_ERR_BAD_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(x_il64) | reinterpret_cast<uintptr_t>(y_il64)) % 16)
+        return GN_ERR_UNSUPPORTED;
+    if ((in_mean_rstd && reinterpret_cast<uintptr_t>(in_mean_rstd) % 8) ||
+        (out_partials && reinterpret_cast<uintptr_t>(out_partials) % 16))
+        return GN_ERR_UNSUPPORTED;
+    Pair64Step a{};
+    a.packed = packed; a.gamma = gamma; a.beta = beta;
+    a.in_il64 = x_il64; a.out_il64 = y_il64;
+    a.in_stats = reinterpret_cast<const float2 *>(in_mean_rstd);
+    a.out_partials = reinterpret_cast<double2 *>(out_partials);
+    a.nparts = partials_per_sample;
+    a.error_flag = error_flag;
+    a.M = M; a.N = N; a.K = K; a.G = round_up64(B) / 64; a.inner = inner;
+    return launch_step_fwd_pair64(a, act, (cudaStream_t)stream);
+}
+
 GN_API size_t gn_outer_forward_workspace_bytes(int B, int M, int N, int K, int block)
 {
     if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || (block != 4 && block != 8)) return 256;
@@ -635,33 +720,35 @@ GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, 
     const bool fused = fast8_applicable(p, block, 0);
     const int nparts_fused = (int)((long long)(M / 8) * (N / 8) * (K / 8) * 4);
 
-    // automatic choice = the register-patch kernel: measured faster on B200 (3.27 ms vs 3.58 ms per
-    // 12-step loop of a 64^3 grid, batch 64); the lanes kernel runs only when asked for
-    if (g_outer_kernel == 2 && lanes16_applicable(M, N, K, block, inner, w, b, s)) {
-        const int Bp = round_up16(B), G = Bp / 16;
+    const bool pair_ok = pair64_applicable(M, N, K, block, inner);
+    if (pair_ok && (g_outer_kernel == 2 || (g_outer_kernel == 0 && pair64_fills_groups(B)))) {
+        const int Bp = round_up64(B), G = Bp / 64;
         const int nblocks = (M / 8) * (N / 8) * (K / 8);
         cudaError_t e = cudaMemsetAsync(ws.error_flag, 0, sizeof(int), st);
         if (e != cudaSuccess) {
             record_cuda_error(e, "cudaMemsetAsync");
             return GN_ERR_CUDA;
         }
-        rc = launch_to_il16(x, ws.buf[0], B, G, P, st);
+        rc = launch_pair64_pack(w, b, s, ws.packed, M, N, K, st);
+        if (rc != GN_OK) return rc;
+        rc = launch_to_il64(x, ws.buf[0], B, G, P, st);
         if (rc != GN_OK) return rc;
         for (int o = 0; o < outer; ++o) {
-            LanesStep a{};
-            a.w = w; a.b = b; a.s = s; a.gamma = gamma; a.beta = beta;
-            a.in_il16 = ws.buf[o & 1];
-            a.out_il16 = ws.buf[(o + 1) & 1];
+            Pair64Step a{};
+            a.packed = ws.packed; a.gamma = gamma; a.beta = beta;
+            a.in_il64 = ws.buf[o & 1];
+            a.out_il64 = ws.buf[(o + 1) & 1];
             a.in_stats = o > 0 ? ws.stats : nullptr;
             a.out_partials = ws.partials;
+            a.nparts = nblocks * 4;
             a.error_flag = ws.error_flag;
             a.M = M; a.N = N; a.K = K; a.G = G; a.inner = inner;
-            rc = launch_step_fwd_lanes16(a, act, st);
+            rc = launch_step_fwd_pair64(a, act, st);
             if (rc != GN_OK) return rc;
-            rc = launch_norm_finalize(ws.partials, nblocks, ws.stats, Bp, P, ln_eps, st);
+            rc = launch_norm_finalize(ws.partials, nblocks * 4, ws.stats, Bp, P, ln_eps, st);
             if (rc != GN_OK) return rc;
         }
-        return launch_norm_apply_from_il16(ws.buf[outer & 1], ws.stats, gamma, beta, y, B, G, P, st);
+        return launch_from_il64(ws.buf[outer & 1], ws.stats, gamma, beta, y, B, G, P, st);
     }
     if (g_outer_kernel == 2) return GN_ERR_UNSUPPORTED;
 

@@ -74,22 +74,30 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
                           const float *stash, float *ws, cudaStream_t st);
 
-// ---- step_lanes.cu ("lanes = samples" kernel of the fused loop; activations in the IL16 layout
-// [group][z][y][x][16 samples])
-struct LanesStep {
-    const float *w, *b, *s, *gamma, *beta;
-    const float *in_il16;
-    float *out_il16;
-    const float2 *in_stats;   // [G*16] or nullptr
-    double2 *out_partials;    // [G*16][blocks] or nullptr
+// ---- step_pair64.cu ("lanes = samples" kernel for large batches; activations in the IL64 layout
+// [group][z][y][x][64 samples], weights pre-packed per block half)
+struct Pair64Step {
+    const float *packed;      // pair64_packed_floats(M, N, K) floats from launch_pair64_pack
+    const float *gamma, *beta;
+    const float *in_il64;
+    float *out_il64;
+    const float2 *in_stats;   // [G*64] or nullptr
+    double2 *out_partials;    // [G*64][nparts] or nullptr; slots block*4 .. block*4+3 are written
+    int nparts;
     int *error_flag;          // device int, set when a bounded wait gave up
     int M, N, K, G, inner;
 };
-bool lanes16_applicable(int M, int N, int K, int block, int inner, const void *w, const void *b, const void *s);
-int launch_step_fwd_lanes16(const LanesStep &a, int act, cudaStream_t st);
-int launch_to_il16(const float *x, float *il, int B, int G, long long P, cudaStream_t st);
-int launch_norm_apply_from_il16(const float *il, const float2 *stats, const float *gamma, const float *beta, float *y,
-                                int B, int G, long long P, cudaStream_t st);
+bool pair64_applicable(int M, int N, int K, int block, int inner);
+size_t pair64_packed_floats(int M, int N, int K);
+int launch_pair64_pack(const float *w, const float *b, const float *s, float *packed, int M, int N, int K, cudaStream_t st);
+int launch_step_fwd_pair64(const Pair64Step &a, int act, cudaStream_t st);
+int launch_to_il64(const float *x, float *il, int B, int G, long long P, cudaStream_t st);
+// stats == nullptr: plain layout conversion; otherwise y = (v - mean) * rstd * gamma + beta
+int launch_from_il64(const float *il, const float2 *stats, const float *gamma, const float *beta, float *y, int B, int G,
+                     long long P, cudaStream_t st);
+
+// ---- probe.cu (FFMA-only kernel for the measured FP32 peak)
+int launch_ffma_probe(float *sink, int iters, long long *fma_count, cudaStream_t st);
 
 // ---- norm.cu
 constexpr int kNormMaxParts = 64;

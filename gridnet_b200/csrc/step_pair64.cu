@@ -1,0 +1,652 @@
+// "Lanes = samples" forward kernel for large batches (float, block 8, per-block normalisation off).
+//
+// The register-patch kernel of step_fast.cu keeps a neuron's weights in registers and therefore
+// reads 48 shared-memory floats for 108 FMAs; it runs out of shared-memory wavefronts at about a
+// quarter of the FP32 peak. Here the roles are swapped: a lane owns SAMPLES, and the weights are what
+// is fetched from shared memory, once per warp for all the samples of its lanes.
+//
+//   * Activations are interleaved by groups of 64 samples ("IL64": [group][z][y][x][64 samples]), in
+//     HBM between the steps of the fused loop and in shared memory inside the kernel. A cell is 256
+//     bytes; 16 lanes x one 128-bit load fetch it for all 64 samples.
+//   * A half-warp (16 lanes x 4 samples) works on a 2x2 (z, y) patch of neurons and sweeps along x,
+//     one tile column per step. A column is 4x4 cells; it feeds the three x-taps of three
+//     neighbouring output columns at once, so the 16 cell loads of a step serve 4 x 27 FMAs per
+//     sample. The two half-warps of a warp take the two halves of the x range and sweep towards the
+//     middle (columns 0..5 and 9..4), which doubles the number of independent work units.
+//   * The weights of a step (36 floats per x-tap: 4 neurons x 9 (z, y) taps) are read as 128-bit
+//     loads whose address is uniform per half-warp: two wavefronts per load, amortised over four
+//     samples per lane. FMAs are issued as packed fma.rn.f32x2 over sample pairs.
+//   * The 64-sample tile of a whole block does not fit one SM (256 KB), so a block is split along z
+//     over the two CTAs of a thread-block cluster (6 x 10 x 10 cells x 64 samples = 150 KB each).
+//     After every inner iteration the plane next to the cut is handed to the partner through
+//     distributed shared memory (plain st.shared::cluster stores into a buffer that alternates with
+//     the iteration's parity) followed by a cluster barrier whose wait sits one step later.
+//   * New activations go back into the tile in place. A column may be overwritten once every warp
+//     has read it; four mbarriers (one per step that completes an output column) carry that order:
+//     a warp arrives after the reads of a step and waits one step later, so nobody stalls as long as
+//     the warps stay within a step of each other.
+//   * The tile arrives by one 5-d bulk tensor copy (TMA; zero fill outside the grid), the block's
+//     pre-packed weights (pair64_pack_k) by one bulk copy; both complete on mbarriers with bounded
+//     waits.
+//
+// Fusion with the whole-grid normalisation (gridnet/scripts/train_mnist.py:62-64): FUSE_IN
+// normalises the freshly loaded tile in place, STATS_OUT reduces per-sample sum / sum of squares of
+// the step's output to one partial per (sample, block half).
+//
+// Reference semantics: gridnet/backend_torch.py:61-142; the kernel it stands in for is
+// gridnet_cuda_forward_kernel, src/gridnet_cuda_kernels.cu:101-200.
+#include <string.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "tma.cuh"
+
+namespace gn {
+
+namespace pair64 {
+constexpr int THREADS = 256;
+constexpr int NS = 64;                       // samples per group = floats per cell
+constexpr int XS = NS, YS = 10 * NS, ZS = 100 * NS;
+constexpr int TILE_F = 6 * ZS;               // 38400 floats
+constexpr int TILE_BYTES = TILE_F * 4;       // 153600
+constexpr int PLANE_BYTES = ZS * 4;          // 25600
+constexpr int WPK_W = 6912;                  // packed weights of half a block
+constexpr int WPK_F = WPK_W + 512;           // + bias[256] + scale[256]
+constexpr int WPK_BYTES = WPK_F * 4;         // 29696
+constexpr int GB_CELLS = 600;
+constexpr unsigned kSpinLimit = 1u << 20;    // bounded waits on mbarriers
+
+constexpr int OFF_TILE = 0;
+constexpr int OFF_ALT = OFF_TILE + TILE_BYTES;
+constexpr int OFF_W = OFF_ALT + PLANE_BYTES;
+constexpr int OFF_GB = OFF_W + WPK_BYTES;
+constexpr int OFF_RED = OFF_GB + GB_CELLS * 8;
+constexpr int OFF_BAR = OFF_RED + 16 * NS * 16;  // 16 contributors x 64 samples x double2
+constexpr int SMEM_BYTES = OFF_BAR + 64;
+static_assert(SMEM_BYTES <= 232448, "shared memory budget of one SM");
+}  // namespace pair64
+
+struct Pair64Params {
+    const float *wpk;            // [blocks][2][WPK_F] from pair64_pack_k
+    const float *gamma, *beta;   // [M,N,K] (FUSE_IN)
+    const float2 *in_stats;      // [G*64] (mean, rstd) of the input (FUSE_IN)
+    double2 *out_partials;       // [G*64][nparts]; this kernel fills slots block*4 .. block*4+3 (STATS_OUT)
+    int nparts;
+    float *y;                    // IL64 output
+    int *error_flag;             // set to 1 if a bounded wait gave up
+    int M, N, K, G, inner;
+    int nblocks, nitems;
+};
+
+typedef unsigned long long u64;
+struct Quad {
+    u64 lo, hi;  // samples (0,1) and (2,3) of the lane
+};
+
+__device__ __forceinline__ u64 pack2(float a, float b)
+{
+    u64 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(u64 v, float &a, float &b)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ void ffma2(u64 &acc, u64 a, u64 w)
+{
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(w));
+}
+__device__ __forceinline__ Quad lds_quad(const float *p)
+{
+    const ulonglong2 t = *reinterpret_cast<const ulonglong2 *>(p);
+    Quad q;
+    q.lo = t.x;
+    q.hi = t.y;
+    return q;
+}
+__device__ __forceinline__ unsigned cluster_rank()
+{
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_arrive()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait()
+{
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned map_to_rank(unsigned local_addr, unsigned rank)
+{
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f4(unsigned addr, float4 v)
+{
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(unsigned dst, const CUtensorMap *map, unsigned bar, int c0, int c1, int c2, int c3,
+                                            int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(unsigned dst, const void *src, unsigned bytes, unsigned bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// ---- the kernel ----------------------------------------------------------------------------
+template <int ACT, bool FUSE_IN, bool STATS_OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
+    step_fwd_pair64(const __grid_constant__ CUtensorMap in_map, const Pair64Params p)
+{
+    using namespace pair64;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    float *const tile = reinterpret_cast<float *>(smem + OFF_TILE);
+    float *const alt = reinterpret_cast<float *>(smem + OFF_ALT);
+    float *const wsm = reinterpret_cast<float *>(smem + OFF_W);
+    float2 *const gbt = reinterpret_cast<float2 *>(smem + OFF_GB);
+    double2 *const red = reinterpret_cast<double2 *>(smem + OFF_RED);
+    const unsigned bar_tile = smem_u32(smem + OFF_BAR), bar_w = bar_tile + 8, bar_r = bar_tile + 16;  // bar_r: 4 barriers
+
+    const int tid = threadIdx.x, lane = tid & 31, u = tid >> 5;
+    const int h = lane >> 4, li = lane & 15;  // x half (0: columns 0..5 upwards, 1: columns 9..4 downwards), sample quad
+    const int zp = u >> 2, yp = u & 3;
+    const unsigned rank = cluster_rank();
+    const int cl = blockIdx.x >> 1, ncl = gridDim.x >> 1;
+    const int it0 = (int)((long long)p.nitems * cl / ncl);
+    const int it1 = (int)((long long)p.nitems * (cl + 1) / ncl);
+
+    if (tid == 0) {
+        mbar_init(bar_tile, 1);
+        mbar_init(bar_w, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(bar_r + 8 * i, 8);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+    }
+    __syncthreads();
+    cluster_arrive();  // pairs with the wait before the first item's first exchange
+
+    const int nbx = p.K >> 3, nby = p.N >> 3;
+    const int xs = h ? -XS : XS;
+    // exchange plane: the tile plane that belongs to the partner CTA (rank 0: plane 5, rank 1: plane 0)
+    const int ez = rank ? 0 : 5;
+    const int exrow = ez - 2 * zp;                                 // this unit's window row on that plane, if in 0..3
+    const bool exporter = rank ? (zp == 0) : (zp == 1);            // this unit owns the plane the partner needs
+    const int edz = rank ? 0 : 1;                                  // ... its neurons with this dz
+    // the partner's two buffers for my plane (its exchange plane): parity 0 = inside its tile, 1 = its alt plane
+    const unsigned partner = rank ^ 1u;
+    const int pez = partner ? 0 : 5;
+    const unsigned rem0 = map_to_rank(smem_u32(tile + pez * ZS), partner), rem1 = map_to_rank(smem_u32(alt), partner);
+    const int cell_off = (2 * yp) * YS + (h ? 9 : 0) * XS + 4 * li;  // window origin inside a plane
+    const float *const wp = wsm + (h * 96 + u) * 36;
+    const float *const bp = wsm + WPK_W + (h * 32 + u) * 4;
+
+    unsigned ph_tile = 0, ph_w = 0, ph2 = 0, ph3 = 0, ph4 = 0, ph5 = 0;
+    bool failed = false;
+    auto wait_bar = [&](unsigned bar, unsigned &ph) {
+        if (!mbar_wait_bounded(bar, ph, kSpinLimit)) failed = true;
+        ph ^= 1;
+    };
+    auto arrive_r = [&](int i) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_r + 8 * i);
+    };
+
+    int cur_brick = -1;
+    for (int item = it0; item < it1; ++item) {
+        const int brick = item / p.G, g = item - brick * p.G;
+        const int bx = brick % nbx, by = (brick / nbx) % nby, bz = brick / nbx / nby;
+        const bool new_brick = brick != cur_brick;
+        cur_brick = brick;
+        if (tid == 0) {
+            fence_proxy_async();  // the generic-proxy reads and writes of the previous item precede the bulk writes
+            mbar_expect_tx(bar_tile, TILE_BYTES);
+            tma_load_5d(smem_u32(tile), &in_map, bar_tile, 0, bx * 8 - 1, by * 8 - 1, bz * 8 + 4 * (int)rank - 1, g);
+            if (new_brick) {
+                mbar_expect_tx(bar_w, WPK_BYTES);
+                bulk_load_1d(smem_u32(wsm), p.wpk + ((size_t)brick * 2 + rank) * WPK_F, WPK_BYTES, bar_w);
+            }
+        }
+        if (FUSE_IN && new_brick) {
+            for (int c = tid; c < GB_CELLS; c += THREADS) {
+                const int cx = c % 10, cy = (c / 10) % 10, cz = c / 100;
+                const int gz = bz * 8 + 4 * (int)rank - 1 + cz, gy = by * 8 - 1 + cy, gx = bx * 8 - 1 + cx;
+                float2 gb = make_float2(0.0f, 0.0f);  // outside the grid: the zero fill stays zero
+                if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < p.K) {
+                    const size_t gi = ((size_t)gz * p.N + gy) * p.K + gx;
+                    gb = make_float2(p.gamma[gi], p.beta[gi]);
+                }
+                gbt[c] = gb;
+            }
+        }
+        float na[4], nb[4];  // normalise: v * na + nb, then * gamma + beta
+        if (FUSE_IN) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 mr = p.in_stats[g * NS + 4 * li + q];
+                na[q] = mr.y;
+                nb[q] = -mr.x * mr.y;
+            }
+        }
+        wait_bar(bar_tile, ph_tile);
+        if (new_brick) wait_bar(bar_w, ph_w);
+        if (FUSE_IN) __syncthreads();  // the gamma/beta table is complete
+        // normalise the tile in place; copy the rim of the exchange plane (stale halo cells) to its alternate buffer
+        for (int c = tid >> 4; c < GB_CELLS; c += THREADS / 16) {
+            const int cz = c / 100, r = c - cz * 100, cy = r / 10, cx = r - cy * 10;
+            const bool rim = cz == ez && (cy == 0 || cy == 9 || cx == 0 || cx == 9);
+            if (!FUSE_IN && !rim) continue;
+            float4 *ptr = reinterpret_cast<float4 *>(tile + c * NS + 4 * li);
+            float4 v = *ptr;
+            if (FUSE_IN) {
+                const float2 gb = gbt[c];
+                v.x = fmaf(fmaf(v.x, na[0], nb[0]), gb.x, gb.y);
+                v.y = fmaf(fmaf(v.y, na[1], nb[1]), gb.x, gb.y);
+                v.z = fmaf(fmaf(v.z, na[2], nb[2]), gb.x, gb.y);
+                v.w = fmaf(fmaf(v.w, na[3], nb[3]), gb.x, gb.y);
+                *ptr = v;
+            }
+            if (rim) *reinterpret_cast<float4 *>(alt + r * NS + 4 * li) = v;
+        }
+        __syncthreads();
+        cluster_wait();  // the partner has finished the previous item: its exchange buffers may be written
+
+        // output position of (dz = 0, dy = 0, first column of this half) in the IL64 output
+        float *const yb = p.y +
+                          ((((size_t)g * p.M + (bz * 8 + 4 * (int)rank + 2 * zp)) * p.N + (by * 8 + 2 * yp)) * p.K +
+                           (bx * 8 + (h ? 7 : 0))) * NS + 4 * li;
+        const size_t ydz = (size_t)p.N * p.K * NS, ydy = (size_t)p.K * NS;
+        float ssum[4] = {0.f, 0.f, 0.f, 0.f}, ssq[4] = {0.f, 0.f, 0.f, 0.f};
+        float4 carry[4];  // output column 3 of the previous iteration, written one step late
+
+        for (int t = 0; t < p.inner; ++t) {
+            const bool last = t + 1 == p.inner;
+            const int par = t & 1;
+            // window rows: planes 2*zp .. 2*zp+3 of the tile; the exchange plane alternates between its two buffers
+            const float *rowp[4];
+#pragma unroll
+            for (int rz = 0; rz < 4; ++rz)
+                rowp[rz] = ((rz == exrow && par) ? alt : tile + (2 * zp + rz) * ZS) + cell_off;
+            float *const wrow = tile + (2 * zp + 1) * ZS + YS + cell_off;  // own cell of (dz = 0, dy = 0) in column 0
+            const unsigned rem = (par ? rem0 : rem1) + 4u * (unsigned)((2 * yp + 1) * YS + (h ? 9 : 0) * XS + 4 * li);
+
+            Quad acc[4][4], cen[4][4];
+            float4 pend[4];
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                if (j == 1 && t > 0) cluster_wait();  // the partner's plane of the previous iteration has landed
+                Quad col[4][4];
+#pragma unroll
+                for (int rz = 0; rz < 4; ++rz)
+#pragma unroll
+                    for (int ry = 0; ry < 4; ++ry) col[rz][ry] = lds_quad(rowp[rz] + j * xs + ry * YS);
+                if (j >= 1 && j <= 4) {
+#pragma unroll
+                    for (int jn = 0; jn < 4; ++jn) cen[j - 1][jn] = col[1 + (jn >> 1)][1 + (jn & 1)];
+                }
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    const int xo = j - c;
+                    if (xo < 0 || xo > 3) continue;
+                    if (c == 0) {
+                        const float4 b4 = *reinterpret_cast<const float4 *>(bp + xo * 32);
+                        acc[xo][0].lo = acc[xo][0].hi = pack2(b4.x, b4.x);
+                        acc[xo][1].lo = acc[xo][1].hi = pack2(b4.y, b4.y);
+                        acc[xo][2].lo = acc[xo][2].hi = pack2(b4.z, b4.z);
+                        acc[xo][3].lo = acc[xo][3].hi = pack2(b4.w, b4.w);
+                    }
+                    const float *wq = wp + (xo * 3 + c) * 288;
+#pragma unroll
+                    for (int e4 = 0; e4 < 9; ++e4) {
+                        const float4 w4 = *reinterpret_cast<const float4 *>(wq + 4 * e4);
+                        const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int e = 4 * e4 + q, jn = e / 9, ab = e % 9, a = ab / 3, b = ab % 3;
+                            const Quad v = col[(jn >> 1) + a][(jn & 1) + b];
+                            const u64 ww = pack2(wv[q], wv[q]);
+                            ffma2(acc[xo][jn].lo, v.lo, ww);
+                            ffma2(acc[xo][jn].hi, v.hi, ww);
+                        }
+                    }
+                }
+                float4 o[4];
+                if (j >= 2) {
+                    const int xo = j - 2;
+                    const float4 s4 = *reinterpret_cast<const float4 *>(bp + 256 + xo * 32);
+                    const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                    for (int jn = 0; jn < 4; ++jn) {
+                        float a0, a1, a2, a3, c0, c1, c2, c3;
+                        unpack2(acc[xo][jn].lo, a0, a1);
+                        unpack2(acc[xo][jn].hi, a2, a3);
+                        unpack2(cen[xo][jn].lo, c0, c1);
+                        unpack2(cen[xo][jn].hi, c2, c3);
+                        o[jn].x = fmaf(Act<ACT, float>::fwd(a0), sv[jn], c0);
+                        o[jn].y = fmaf(Act<ACT, float>::fwd(a1), sv[jn], c1);
+                        o[jn].z = fmaf(Act<ACT, float>::fwd(a2), sv[jn], c2);
+                        o[jn].w = fmaf(Act<ACT, float>::fwd(a3), sv[jn], c3);
+                    }
+                    if (last) {
+#pragma unroll
+                        for (int jn = 0; jn < 4; ++jn) {
+                            *reinterpret_cast<float4 *>(yb + (jn >> 1) * ydz + (jn & 1) * ydy + xo * xs) = o[jn];
+                            if (STATS_OUT) {
+                                ssum[0] += o[jn].x; ssq[0] = fmaf(o[jn].x, o[jn].x, ssq[0]);
+                                ssum[1] += o[jn].y; ssq[1] = fmaf(o[jn].y, o[jn].y, ssq[1]);
+                                ssum[2] += o[jn].z; ssq[2] = fmaf(o[jn].z, o[jn].z, ssq[2]);
+                                ssum[3] += o[jn].w; ssq[3] = fmaf(o[jn].w, o[jn].w, ssq[3]);
+                            }
+                        }
+                    } else if (exporter) {
+                        // the partner reads this plane in its next iteration, from the buffer of the other parity
+#pragma unroll
+                        for (int dy = 0; dy < 2; ++dy)
+                            st_cluster_f4(rem + 4u * (unsigned)(dy * YS + (xo + 1) * xs), edz ? o[2 + dy] : o[dy]);
+                    }
+                }
+                // local writes, one step late: a column is overwritten after every warp has read it
+                if (j == 0 && t > 0) {
+                    wait_bar(bar_r + 24, ph5);
+#pragma unroll
+                    for (int jn = 0; jn < 4; ++jn)
+                        *reinterpret_cast<float4 *>(wrow + (jn >> 1) * ZS + (jn & 1) * YS + 4 * xs) = carry[jn];
+                }
+                if (j == 2 && (!last || t > 0)) arrive_r(0);
+                if (j == 3 && (!last || t > 0)) wait_bar(bar_r, ph2);
+                if (j == 4 && !last) wait_bar(bar_r + 8, ph3);
+                if (j == 5 && !last) wait_bar(bar_r + 16, ph4);
+                if (j >= 3 && !last) {
+#pragma unroll
+                    for (int jn = 0; jn < 4; ++jn)
+                        *reinterpret_cast<float4 *>(wrow + (jn >> 1) * ZS + (jn & 1) * YS + (j - 2) * xs) = pend[jn];
+                    arrive_r(j - 2);
+                }
+                if (j >= 2) {
+#pragma unroll
+                    for (int jn = 0; jn < 4; ++jn) pend[jn] = o[jn];
+                }
+                if (j == 5 && !last) {
+#pragma unroll
+                    for (int jn = 0; jn < 4; ++jn) carry[jn] = o[jn];
+                    cluster_arrive();  // all exports of this iteration are stored
+                }
+            }
+        }
+
+        if (STATS_OUT) {
+            // 16 contributors per sample: 8 units x 2 halves
+#pragma unroll
+            for (int q = 0; q < 4; ++q) red[(u * 2 + h) * NS + 4 * li + q] = make_double2((double)ssum[q], (double)ssq[q]);
+        }
+        __syncthreads();  // every read of the tile and of the weights is done; the partials are in place
+        if (STATS_OUT && tid < NS) {
+            double s = 0.0, q = 0.0;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const double2 v = red[k * NS + tid];
+                s += v.x;
+                q += v.y;
+            }
+            double2 *dst = p.out_partials + (size_t)(g * NS + tid) * p.nparts + (size_t)brick * 4 + 2 * rank;
+            dst[0] = make_double2(s, q);
+            dst[1] = make_double2(0.0, 0.0);
+        }
+        cluster_arrive();  // this CTA no longer reads its exchange buffers of this item
+    }
+    cluster_wait();  // no CTA leaves while its partner may still store into its shared memory
+    if (failed && p.error_flag) *p.error_flag = 1;
+}
+
+// ---- weight packing ---------------------------------------------------------------------------
+// One CTA per block: the block's 27 x 512 weights, biases and scales are staged in shared memory with
+// coalesced reads and written out in the order the step kernel reads them:
+//   [block][rank][ (h, xo, c, unit) x 36 floats (jn * 9 + a * 3 + b) | bias (h, xo, unit, jn) | scale (same) ]
+// rank = z half of the block, h = x half, xo = output column counted from the half's outer end,
+// c = x tap in sweep order (h = 1 sweeps downwards, so its taps are mirrored), unit = (zp, yp) patch,
+// jn = (dz, dy) inside the patch, (a, b) = (z, y) tap. Tap numbering a * 9 + b * 3 + c follows
+// gridnet/backend_torch.py:283-298.
+__global__ void __launch_bounds__(256) pair64_pack_k(const float *__restrict__ w, const float *__restrict__ b,
+                                                     const float *__restrict__ s, float *__restrict__ out, int M, int N,
+                                                     int K)
+{
+    extern __shared__ float stage[];  // [29][512]: 27 taps, bias, scale
+    const int nbx = K >> 3, nby = N >> 3;
+    const int brick = blockIdx.x;
+    const int bx = brick % nbx, by = (brick / nbx) % nby, bz = brick / nbx / nby;
+    const size_t P = (size_t)M * N * K;
+    for (int idx = threadIdx.x; idx < 29 * 512; idx += 256) {
+        const int t = idx >> 9, n = idx & 511;
+        const int z = n >> 6, y = (n >> 3) & 7, x = n & 7;
+        const size_t gi = ((size_t)(bz * 8 + z) * N + (by * 8 + y)) * K + (bx * 8 + x);
+        stage[idx] = t < 27 ? w[(size_t)t * P + gi] : (t == 27 ? b[gi] : s[gi]);
+    }
+    __syncthreads();
+    float *o = out + (size_t)brick * 2 * pair64::WPK_F;
+    for (int idx = threadIdx.x; idx < 2 * pair64::WPK_F; idx += 256) {
+        const int rank = idx / pair64::WPK_F, e = idx - rank * pair64::WPK_F;
+        int h, xo, un, jn, src_t, cc = 0, ab = 0;
+        if (e < pair64::WPK_W) {
+            const int grp = e / 36, k = e - grp * 36;
+            un = grp & 7;
+            const int c = (grp >> 3) % 3, hx = (grp >> 3) / 3;
+            h = hx >> 2;
+            xo = hx & 3;
+            jn = k / 9;
+            ab = k - jn * 9;
+            cc = h ? 2 - c : c;
+            src_t = (ab / 3) * 9 + (ab % 3) * 3 + cc;
+        } else {
+            const int k = (e - pair64::WPK_W) & 255;
+            src_t = e - pair64::WPK_W < 256 ? 27 : 28;
+            jn = k & 3;
+            un = (k >> 2) & 7;
+            xo = (k >> 5) & 3;
+            h = k >> 7;
+        }
+        const int z = 4 * rank + 2 * (un >> 2) + (jn >> 1), y = 2 * (un & 3) + (jn & 1), x = h ? 7 - xo : xo;
+        o[idx] = stage[src_t * 512 + (z * 8 + y) * 8 + x];
+    }
+}
+
+// ---- layout conversion at the two ends of the fused loop --------------------------------------
+// [B, P] -> IL64 [G][P][64]; samples beyond B are written as zeros. grid (P / 32, G), 256 threads.
+__global__ void __launch_bounds__(256) to_il64_k(const float *__restrict__ x, float *__restrict__ il, int B, size_t P)
+{
+    __shared__ float t[64][33];
+    const int g = blockIdx.y;
+    const size_t p0 = (size_t)blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int sidx = ty + 8 * k, bb = g * 64 + sidx;
+        t[sidx][tx] = bb < B ? x[(size_t)bb * P + p0 + tx] : 0.0f;
+    }
+    __syncthreads();
+    float *o = il + ((size_t)g * P + p0) * 64;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int idx = threadIdx.x + 256 * k;
+        o[idx] = t[idx & 63][idx >> 6];
+    }
+}
+
+// IL64 raw step output -> y [B, P] = (v - mean) * rstd * gamma + beta (stats == nullptr: plain copy).
+__global__ void __launch_bounds__(256) from_il64_k(const float *__restrict__ il, const float2 *__restrict__ stats,
+                                                   const float *__restrict__ gamma, const float *__restrict__ beta,
+                                                   float *__restrict__ y, int B, size_t P)
+{
+    __shared__ float t[64][33];
+    const int g = blockIdx.y;
+    const size_t p0 = (size_t)blockIdx.x * 32;
+    const float *in = il + ((size_t)g * P + p0) * 64;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int idx = threadIdx.x + 256 * k;
+        t[idx & 63][idx >> 6] = in[idx];
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    float gm = 1.0f, bt = 0.0f;
+    if (stats) {
+        gm = gamma[p0 + tx];
+        bt = beta[p0 + tx];
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int sidx = ty + 8 * k, bb = g * 64 + sidx;
+        if (bb < B) {
+            float v = t[sidx][tx];
+            if (stats) {
+                const float2 mr = stats[bb];
+                v = fmaf((v - mr.x) * mr.y, gm, bt);
+            }
+            y[(size_t)bb * P + p0 + tx] = v;
+        }
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+size_t pair64_packed_floats(int M, int N, int K)
+{
+    return (size_t)(M / 8) * (N / 8) * (K / 8) * 2 * pair64::WPK_F;
+}
+
+bool pair64_applicable(int M, int N, int K, int block, int inner)
+{
+    if (block != 8 || inner < 1) return false;
+    if (M % 8 || N % 8 || K % 8) return false;
+    if ((long long)M * N * K >= (1LL << 31) / 64) return false;  // element offsets inside one group stay below 2^31
+    return encode_tiled_fn() != nullptr;
+}
+
+// Tensor map over an IL64 buffer: dims (fastest first) {64, K, N, M, G}, box {64, 10, 10, 6, 1}.
+static int make_il64_map(CUtensorMap *map, const float *il, int M, int N, int K, int G)
+{
+    const cuuint64_t dims[5] = {64, (cuuint64_t)K, (cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)G};
+    const cuuint64_t strides[4] = {256, (cuuint64_t)K * 256, (cuuint64_t)N * K * 256, (cuuint64_t)M * N * K * 256};
+    const cuuint32_t box[5] = {64, 10, 10, 6, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(il), dims, strides,
+                                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+        return GN_ERR_CUDA;
+    }
+    return GN_OK;
+}
+
+int launch_pair64_pack(const float *w, const float *b, const float *s, float *packed, int M, int N, int K, cudaStream_t st)
+{
+    static bool attr_set = false;
+    const int smem = 29 * 512 * 4;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(pair64_pack_k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) {
+            record_cuda_error(e, "cudaFuncSetAttribute(pair64_pack_k)");
+            return GN_ERR_CUDA;
+        }
+        attr_set = true;
+    }
+    const int nblocks = (M / 8) * (N / 8) * (K / 8);
+    pair64_pack_k<<<nblocks, 256, smem, st>>>(w, b, s, packed, M, N, K);
+    return check_launch("pair64_pack");
+}
+
+int launch_to_il64(const float *x, float *il, int B, int G, long long P, cudaStream_t st)
+{
+    dim3 grid((unsigned)(P / 32), (unsigned)G);
+    to_il64_k<<<grid, 256, 0, st>>>(x, il, B, (size_t)P);
+    return check_launch("to_il64");
+}
+
+int launch_from_il64(const float *il, const float2 *stats, const float *gamma, const float *beta, float *y, int B, int G,
+                     long long P, cudaStream_t st)
+{
+    dim3 grid((unsigned)(P / 32), (unsigned)G);
+    from_il64_k<<<grid, 256, 0, st>>>(il, stats, gamma, beta, y, B, (size_t)P);
+    return check_launch("from_il64");
+}
+
+int launch_step_fwd_pair64(const Pair64Step &a, int act, cudaStream_t st)
+{
+    CUtensorMap map;
+    int rc = make_il64_map(&map, a.in_il64, a.M, a.N, a.K, a.G);
+    if (rc != GN_OK) return rc;
+    Pair64Params p{};
+    p.wpk = a.packed; p.gamma = a.gamma; p.beta = a.beta;
+    p.in_stats = a.in_stats; p.out_partials = a.out_partials; p.nparts = a.nparts;
+    p.y = a.out_il64; p.error_flag = a.error_flag;
+    p.M = a.M; p.N = a.N; p.K = a.K; p.G = a.G; p.inner = a.inner;
+    p.nblocks = (a.M / 8) * (a.N / 8) * (a.K / 8);
+    p.nitems = p.nblocks * a.G;
+    int dev = 0, sms = kNumSMs;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int ncl = sms / 2;
+    if (ncl > p.nitems) ncl = p.nitems;
+    // evenly filled rounds: with r = ceil(items / clusters) rounds, use just as many clusters as r rounds need
+    const int rounds = (p.nitems + ncl - 1) / ncl;
+    ncl = (p.nitems + rounds - 1) / rounds;
+    const bool fin = a.in_stats != nullptr, sout = a.out_partials != nullptr;
+    static bool attr_done[4][2][2] = {};
+#define ONE_(A, FI, SO)                                                                                    \
+    do {                                                                                                   \
+        auto kern = step_fwd_pair64<A, FI, SO>;                                                            \
+        if (!attr_done[A][FI][SO]) {                                                                       \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair64::SMEM_BYTES); \
+            if (e != cudaSuccess) {                                                                        \
+                record_cuda_error(e, "cudaFuncSetAttribute(step_fwd_pair64)");                            \
+                return GN_ERR_CUDA;                                                                        \
+            }                                                                                              \
+            attr_done[A][FI][SO] = true;                                                                   \
+        }                                                                                                  \
+        kern<<<2 * ncl, pair64::THREADS, pair64::SMEM_BYTES, st>>>(map, p);                                \
+    } while (0)
+#define LAUNCH_(A)                          \
+    do {                                    \
+        if (fin && sout) ONE_(A, true, true);   \
+        else if (fin) ONE_(A, true, false);     \
+        else if (sout) ONE_(A, false, true);    \
+        else ONE_(A, false, false);             \
+    } while (0)
+    switch (act) {
+    case GN_ACT_RELU: LAUNCH_(GN_ACT_RELU); break;
+    case GN_ACT_LEAKY_RELU: LAUNCH_(GN_ACT_LEAKY_RELU); break;
+    case GN_ACT_SILU: LAUNCH_(GN_ACT_SILU); break;
+    default: LAUNCH_(GN_ACT_TANH); break;
+    }
+#undef LAUNCH_
+#undef ONE_
+    return check_launch("step_fwd_pair64");
+}
+
+}  // namespace gn

@@ -68,12 +68,20 @@ GN_API const char *gn_last_cuda_error(void);
 GN_API int gn_activation_from_name(const char *name);
 GN_API int gn_version(void);
 /* Process-wide tuning switches (not needed for normal use). Keys:
- *   "outer_kernel": which step kernel gn_outer_forward_f32 uses: 0 = automatic (default),
- *                   1 = the register-patch kernel, 2 = the lanes-of-samples kernel
- *                   (GN_ERR_UNSUPPORTED from gn_outer_forward_f32 when it does not apply).
+ *   "outer_kernel": which step kernel gn_outer_forward_f32 uses: 0 = automatic (default: the
+ *                   large-batch kernel when at most a quarter of the last group of 64 samples
+ *                   would be padding, else the register-patch kernel), 1 = the register-patch
+ *                   kernel, 2 = the large-batch kernel (GN_ERR_UNSUPPORTED from
+ *                   gn_outer_forward_f32 when it does not apply).
  *   "forward_samples_per_cta": samples one CTA of the tuned float forward kernel walks through;
  *                   0 = chosen from the grid and batch size (default). */
 GN_API int gn_config_set(const char *key, int value);
+
+/* Measurement helper, on no product path and without a counterpart in the reference: launches a
+ * kernel of nothing but dependent-chain-free FP32 FMAs on every SM (sink: one device float that is
+ * practically never written) and returns in *fma_count (host, may be NULL) how many FMAs it executes.
+ * Timed with events around it, it gives the FP32 pipe rate the roofline fractions are quoted against. */
+GN_API int gn_probe_fp32_fma(float *sink, int iters_per_chain, long long *fma_count, void *stream);
 
 /* ------------------------------------------------------------------ plain step
  * Replaces gridnet_cuda.forward (src/gridnet_cuda.cpp:61-89 ->
@@ -220,6 +228,33 @@ GN_API int gn_step_forward_fused_f32(const float *weight, const float *bias, con
                               const float *x, float *y, const float *gamma, const float *beta,
                               const float *in_mean_rstd, double *out_partials, int B, int M,
                               int N, int K, int inner, int block, int activation, void *stream);
+/* Large-batch form of gn_step_forward_fused_f32 (block 8, normalize = 0, inner >= 1, M, N, K
+ * multiples of 8): same arithmetic as src/gridnet_cuda_kernels.cu:101-200, but a thread owns
+ * samples instead of neurons, which needs the activations interleaved by groups of 64 samples
+ * ("IL64": [ceil(B/64)][M][N][K][64] floats, samples beyond B zero) and the parameters re-ordered
+ * per block half. No counterpart in the reference.
+ *   gn_pair64_supported            1 if this device and shape can run it
+ *   gn_pair64_packed_weight_bytes  size of the re-ordered parameters (weights, bias, scale)
+ *   gn_pair64_pack_weights_f32     weight [27,M,N,K], bias, scale [M,N,K] -> packed (16-byte aligned)
+ *   gn_pair64_interleave_f32       x [B,M,N,K] -> x_il64
+ *   gn_step_forward_pair64_f32     one step, IL64 in, IL64 out; in_mean_rstd ([64*ceil(B/64)][2]),
+ *                                  gamma, beta and out_partials ([64*ceil(B/64)][partials_per_sample][2]
+ *                                  doubles, partials_per_sample >= gn_step_stats_partials(M,N,K,8)) as in
+ *                                  gn_step_forward_fused_f32; error_flag (device int, may be NULL) is set
+ *                                  to 1 if a bounded wait on a bulk copy gave up
+ *   gn_pair64_deinterleave_f32     y_il64 -> y [B,M,N,K]; with mean_rstd != NULL y = (v - mean) * rstd *
+ *                                  gamma + beta */
+GN_API int gn_pair64_supported(int M, int N, int K, int block, int inner);
+GN_API size_t gn_pair64_packed_weight_bytes(int M, int N, int K);
+GN_API int gn_pair64_pack_weights_f32(const float *weight, const float *bias, const float *scale, float *packed,
+                               int M, int N, int K, void *stream);
+GN_API int gn_pair64_interleave_f32(const float *x, float *x_il64, int B, int M, int N, int K, void *stream);
+GN_API int gn_pair64_deinterleave_f32(const float *y_il64, const float *mean_rstd, const float *gamma,
+                               const float *beta, float *y, int B, int M, int N, int K, void *stream);
+GN_API int gn_step_forward_pair64_f32(const float *packed, const float *x_il64, float *y_il64, const float *gamma,
+                               const float *beta, const float *in_mean_rstd, double *out_partials,
+                               int partials_per_sample, int B, int M, int N, int K, int inner, int activation,
+                               int *error_flag, void *stream);
 /* Slab form of gn_step_forward_fused_f32 for a grid that is split along K across GPUs. The
  * arrays have the usual layout with K = the local width INCLUDING one ghost block of 8 columns
  * on each side that is not updated; only blocks k_block_first .. k_block_first + k_block_count - 1
@@ -268,9 +303,10 @@ GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *be
  * per-sample statistics of what it writes, and the next step applies
  * (x - mean) * rstd * gamma + beta while it loads its tiles; only the last
  * step's output is normalised by a separate kernel into y.
- * workspace: two [B rounded up to 16, M,N,K] float buffers plus the statistics partials.
- * (With the optional lanes-of-samples kernel, gn_config_set("outer_kernel", 2), the activations
- * are kept interleaved by groups of 16 samples between steps, [group][M][N][K][16], and read by TMA.) */
+ * workspace: two [B rounded up to 64, M,N,K] float buffers, the statistics partials and, for
+ * block 8, the weights re-ordered for the large-batch kernel (29/27 of the weight tensor).
+ * With the large-batch kernel (see gn_step_forward_pair64_f32 below) the activations stay
+ * interleaved by groups of 64 samples between steps, [group][M][N][K][64], and are read by TMA. */
 GN_API size_t gn_outer_forward_workspace_bytes(int B, int M, int N, int K, int block);
 /* Byte offset, inside the workspace, of an int that gn_outer_forward_f32 sets to 1 when a bounded
  * wait on a bulk tile copy gave up (the results of that call are then invalid). It is cleared at

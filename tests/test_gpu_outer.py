@@ -157,26 +157,63 @@ def test_full_size_properties_c2():
     assert_close(y[idx].cpu().numpy(), ref64, ref32, "C2 full size, sampled rows")
 
 
-def test_lanes_kernel_matches_patch_kernel_and_oracle():
-    """The optional lanes-of-samples step kernel (TMA tiles, activations interleaved by 16 samples)
-    must give the same fused loop as the default kernel; odd batch sizes exercise the zero-padded
-    last group."""
-    from gridnet_b200 import outer_forward
+@pytest.mark.parametrize("B,shape,inner,outer,act", [
+    (64, (16, 16, 16), 4, 3, "silu"),      # one full group; blocks on every face of the grid
+    (5, (16, 16, 16), 2, 3, "silu"),       # mostly padding: the zero-padded last group
+    (70, (8, 16, 24), 3, 2, "tanh"),       # two groups, non-cubic grid, odd inner count
+    (64, (8, 8, 8), 1, 2, "leaky_relu"),   # a single block (only stale halo), one inner iteration
+    (128, (24, 8, 16), 2, 2, "relu"),      # two full groups, z is the long axis
+])
+def test_large_batch_kernel_matches_patch_kernel_and_oracle(B, shape, inner, outer, act):
+    """The large-batch step kernel (lanes own samples, a block split over a cluster of two CTAs, activations
+    interleaved by 64 samples) must give the same fused loop as the register-patch kernel and the oracle."""
+    from gridnet_b200 import outer_forward, outer_forward_failed, outer_forward_workspace
     from gridnet_b200._lib import lib
 
-    for B, shape, inner, outer in ((5, (16, 16, 16), 2, 3), (33, (8, 16, 24), 3, 2), (16, (32, 32, 32), 1, 2)):
-        w, b, s, gamma, beta = model_params(27, shape)
-        x = face_input(28, B, shape)
-        args = [dev(a) for a in (w, b, s, gamma, beta, x)]
-        base = outer_forward(*args, inner, outer, 8)
-        try:
-            assert lib.gn_config_set(b"outer_kernel", 2) == 0
-            got = outer_forward(*args, inner, outer, 8)
-        finally:
-            lib.gn_config_set(b"outer_kernel", 0)
-        assert torch.allclose(got, base, rtol=1e-5, atol=1e-6), (got - base).abs().max().item()
-        a64 = [a.astype(np.float64) for a in (w, b, s, gamma, beta, x)]
-        assert_close(got.cpu().numpy(), orc.outer_forward(*a64, inner, outer, 8), None, f"lanes kernel B={B}")
+    w, b, s, gamma, beta = model_params(27, shape)
+    x = face_input(28, B, shape)
+    x[:, 1::3, ::2, 1:] = 0.3 * np.random.default_rng(31).standard_normal(x[:, 1::3, ::2, 1:].shape)
+    args = [dev(a) for a in (w, b, s, gamma, beta, x)]
+    ws = outer_forward_workspace(B, shape, 8, args[0].device)
+    try:
+        assert lib.gn_config_set(b"outer_kernel", 1) == 0
+        base = outer_forward(*args, inner, outer, 8, act)
+        assert lib.gn_config_set(b"outer_kernel", 2) == 0
+        got = outer_forward(*args, inner, outer, 8, act, workspace=ws)
+        again = outer_forward(*args, inner, outer, 8, act, workspace=ws)
+    finally:
+        lib.gn_config_set(b"outer_kernel", 0)
+    assert not outer_forward_failed(ws, B, shape, 8)
+    assert torch.equal(got, again), "two runs differ"
+    assert torch.allclose(got, base, rtol=2e-5, atol=2e-6), (got - base).abs().max().item()
+    a64 = [a.astype(np.float64) for a in (w, b, s, gamma, beta, x)]
+    assert_close(got.cpu().numpy(), orc.outer_forward(*a64, inner, outer, 8, activation=act), None,
+                 f"large-batch kernel B={B}")
+
+
+def test_large_batch_step_building_blocks():
+    """gn_pair64_* through the C ABI: interleave -> one step without normalisation -> de-interleave equals the
+    plain step op; interleave -> de-interleave is the identity."""
+    from gridnet_b200 import GridnetCudaOp
+    from gridnet_b200.backend_cuda import pair64_deinterleave, pair64_interleave, pair64_pack_weights, pair64_step
+
+    B, shape, inner = 64, (16, 8, 24), 3
+    w, b, s, _, _ = model_params(33, shape)
+    x = np.random.default_rng(34).standard_normal((B, *shape)).astype(np.float32)
+    tw, tb, ts, tx = (dev(a) for a in (w, b, s, x))
+    xi = pair64_interleave(tx)
+    assert torch.equal(pair64_deinterleave(xi, B, shape), tx)
+    packed = pair64_pack_weights(tw, tb, ts)
+    yi = torch.empty_like(xi)
+    flag = torch.zeros(1, dtype=torch.int32, device=tx.device)
+    pair64_step(packed, xi, yi, B, shape, inner, "silu", error_flag=flag)
+    got = pair64_deinterleave(yi, B, shape)
+    assert int(flag.item()) == 0
+    want = GridnetCudaOp.apply(tw, tb, ts, tx, inner, 8, 1e-5, False, "silu")
+    assert torch.allclose(got, want, rtol=2e-5, atol=2e-6), (got - want).abs().max().item()
+    ref = orc.step_forward(w.astype(np.float64), b.astype(np.float64), s.astype(np.float64), x.astype(np.float64),
+                           inner, 8, normalize=False, activation="silu")
+    assert_close(got.cpu().numpy(), ref, None, "large-batch single step")
 
 
 def test_outer_forward_reports_no_device_failure():
