@@ -22,12 +22,14 @@
 //     distributed shared memory (plain st.shared::cluster stores into a buffer that alternates with
 //     the iteration's parity) followed by a cluster barrier whose wait sits one step later.
 //   * New activations go back into the tile in place. A column may be overwritten once every warp
-//     has read it; four mbarriers (one per step that completes an output column) carry that order:
-//     a warp arrives after the reads of a step and waits one step later, so nobody stalls as long as
-//     the warps stay within a step of each other.
-//   * The tile arrives by one 5-d bulk tensor copy (TMA; zero fill outside the grid), the block's
-//     pre-packed weights (pair64_pack_k) by one bulk copy; both complete on mbarriers with bounded
-//     waits.
+//     has read it; four mbarriers carry that order: a warp arrives after the reads of a step and
+//     waits one step later, so nobody stalls as long as the warps stay within a step of each other.
+//   * The tile is stored column by column (x outermost), and every column arrives by its own 5-d
+//     bulk tensor copy (TMA; zero fill outside the grid). In the last inner iteration of a work
+//     item a column is dead as soon as every warp has read it, so the same column of the NEXT item
+//     is fetched right then: the tile is re-filled in place underneath the running iteration and
+//     no second buffer is needed. The block's pre-packed weights (pair64_pack_k) arrive by one
+//     bulk copy. All of these complete on mbarriers with bounded waits.
 //
 // Fusion with the whole-grid normalisation (gridnet/scripts/train_mnist.py:62-64): FUSE_IN
 // normalises the freshly loaded tile in place, STATS_OUT reduces per-sample sum / sum of squares of
@@ -36,6 +38,8 @@
 // Reference semantics: gridnet/backend_torch.py:61-142; the kernel it stands in for is
 // gridnet_cuda_forward_kernel, src/gridnet_cuda_kernels.cu:101-200.
 #include <string.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -46,10 +50,15 @@ namespace gn {
 namespace pair64 {
 constexpr int THREADS = 256;
 constexpr int NS = 64;                       // samples per group = floats per cell
-constexpr int XS = NS, YS = 10 * NS, ZS = 100 * NS;
-constexpr int TILE_F = 6 * ZS;               // 38400 floats
+// tile[x column 0..9][z plane 0..5][y row 0..9][64 samples]: a column is contiguous, so it can be
+// fetched (and re-filled for the next work item) by one bulk tensor copy of its own
+constexpr int YS = NS, ZS = 10 * NS, XS = 60 * NS;
+constexpr int COL_BYTES = XS * 4;            // 15360
+constexpr int TILE_F = 10 * XS;              // 38400 floats
 constexpr int TILE_BYTES = TILE_F * 4;       // 153600
-constexpr int PLANE_BYTES = ZS * 4;          // 25600
+// alternate buffer of the exchange plane: alt[x column][y row][64 samples]
+constexpr int AXS = 10 * NS;
+constexpr int PLANE_BYTES = 100 * NS * 4;    // 25600
 constexpr int WPK_W = 6912;                  // packed weights of half a block
 constexpr int WPK_F = WPK_W + 512;           // + bias[256] + scale[256]
 constexpr int WPK_BYTES = WPK_F * 4;         // 29696
@@ -62,7 +71,7 @@ constexpr int OFF_W = OFF_ALT + PLANE_BYTES;
 constexpr int OFF_GB = OFF_W + WPK_BYTES;
 constexpr int OFF_RED = OFF_GB + GB_CELLS * 8;
 constexpr int OFF_BAR = OFF_RED + 16 * NS * 16;  // 16 contributors x 64 samples x double2
-constexpr int SMEM_BYTES = OFF_BAR + 64;
+constexpr int SMEM_BYTES = OFF_BAR + 192;
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of one SM");
 }  // namespace pair64
 
@@ -150,6 +159,11 @@ __device__ __forceinline__ void bulk_load_1d(unsigned dst, const void *src, unsi
 }
 
 // ---- the kernel ----------------------------------------------------------------------------
+// Barriers in shared memory (8 bytes each, from OFF_BAR): C[0..4] column pair (j, 9-j) of the tile has
+// landed; W weights have landed; R1, R2, R3, R5 every warp has finished step 1 / 2 / 3 / 5 (and every
+// tile write it does before that point); D[0..4] in a work item's last iteration every warp has read
+// column pair j for the last time (pairs 0..3 in step j, pair 4 = columns 4 and 5 in step 5), so the
+// columns can be re-filled for the next item.
 template <int ACT, bool FUSE_IN, bool STATS_OUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
     step_fwd_pair64(const __grid_constant__ CUtensorMap in_map, const Pair64Params p)
@@ -161,7 +175,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
     float *const wsm = reinterpret_cast<float *>(smem + OFF_W);
     float2 *const gbt = reinterpret_cast<float2 *>(smem + OFF_GB);
     double2 *const red = reinterpret_cast<double2 *>(smem + OFF_RED);
-    const unsigned bar_tile = smem_u32(smem + OFF_BAR), bar_w = bar_tile + 8, bar_r = bar_tile + 16;  // bar_r: 4 barriers
+    const unsigned bar0 = smem_u32(smem + OFF_BAR);
+    const unsigned bar_c = bar0, bar_w = bar0 + 48, bar_r = bar0 + 56, bar_d = bar0 + 88;
 
     const int tid = threadIdx.x, lane = tid & 31, u = tid >> 5;
     const int h = lane >> 4, li = lane & 15;  // x half (0: columns 0..5 upwards, 1: columns 9..4 downwards), sample quad
@@ -172,9 +187,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
     const int it1 = (int)((long long)p.nitems * (cl + 1) / ncl);
 
     if (tid == 0) {
-        mbar_init(bar_tile, 1);
+        for (int i = 0; i < 5; ++i) mbar_init(bar_c + 8 * i, 1);
         mbar_init(bar_w, 1);
         for (int i = 0; i < 4; ++i) mbar_init(bar_r + 8 * i, 8);
+        for (int i = 0; i < 5; ++i) mbar_init(bar_d + 8 * i, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
@@ -182,7 +198,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
     cluster_arrive();  // pairs with the wait before the first item's first exchange
 
     const int nbx = p.K >> 3, nby = p.N >> 3;
-    const int xs = h ? -XS : XS;
+    const int xs = h ? -XS : XS, axs = h ? -AXS : AXS;
     // exchange plane: the tile plane that belongs to the partner CTA (rank 0: plane 5, rank 1: plane 0)
     const int ez = rank ? 0 : 5;
     const int exrow = ez - 2 * zp;                                 // this unit's window row on that plane, if in 0..3
@@ -191,21 +207,51 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
     // the partner's two buffers for my plane (its exchange plane): parity 0 = inside its tile, 1 = its alt plane
     const unsigned partner = rank ^ 1u;
     const int pez = partner ? 0 : 5;
-    const unsigned rem0 = map_to_rank(smem_u32(tile + pez * ZS), partner), rem1 = map_to_rank(smem_u32(alt), partner);
-    const int cell_off = (2 * yp) * YS + (h ? 9 : 0) * XS + 4 * li;  // window origin inside a plane
+    const unsigned rem_tile = map_to_rank(smem_u32(tile + pez * ZS), partner), rem_alt = map_to_rank(smem_u32(alt), partner);
+    const int col0 = h ? 9 : 0;
     const float *const wp = wsm + (h * 96 + u) * 36;
     const float *const bp = wsm + WPK_W + (h * 32 + u) * 4;
 
-    unsigned ph_tile = 0, ph_w = 0, ph2 = 0, ph3 = 0, ph4 = 0, ph5 = 0;
+    unsigned ph_w = 0, ph1 = 0, ph2 = 0, ph3 = 0, ph5 = 0;
     bool failed = false;
     auto wait_bar = [&](unsigned bar, unsigned &ph) {
         if (!mbar_wait_bounded(bar, ph, kSpinLimit)) failed = true;
         ph ^= 1;
     };
-    auto arrive_r = [&](int i) {
+    auto arrive = [&](unsigned bar) {
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_r + 8 * i);
+        if (lane == 0) mbar_arrive(bar);
     };
+    // thread 0: fetch column pair j of the tile whose origin cell is (tx0, ty0, tz0) in sample group tg
+    struct TileOrigin {
+        int x, y, z, g;
+    };
+    auto tile_origin = [&](int item) {
+        const int brick = item / p.G, g = item - brick * p.G;
+        TileOrigin o;
+        o.x = (brick % nbx) * 8 - 1;
+        o.y = ((brick / nbx) % nby) * 8 - 1;
+        o.z = (brick / nbx / nby) * 8 + 4 * (int)rank - 1;
+        o.g = g;
+        return o;
+    };
+    auto issue_cols = [&](const TileOrigin &o, int j) {
+        fence_proxy_async();  // earlier generic-proxy accesses to these columns precede the bulk writes
+        mbar_expect_tx(bar_c + 8 * j, 2 * COL_BYTES);
+        tma_load_5d(smem_u32(tile + j * XS), &in_map, bar_c + 8 * j, 0, o.x + j, o.y, o.z, o.g);
+        tma_load_5d(smem_u32(tile + (9 - j) * XS), &in_map, bar_c + 8 * j, 0, o.x + 9 - j, o.y, o.z, o.g);
+    };
+    auto issue_weights = [&](int brick) {
+        fence_proxy_async();
+        mbar_expect_tx(bar_w, WPK_BYTES);
+        bulk_load_1d(smem_u32(wsm), p.wpk + ((size_t)brick * 2 + rank) * WPK_F, WPK_BYTES, bar_w);
+    };
+
+    if (tid == 0 && it0 < it1) {
+        const TileOrigin o = tile_origin(it0);
+        for (int j = 0; j < 5; ++j) issue_cols(o, j);
+        issue_weights(it0 / p.G);
+    }
 
     int cur_brick = -1;
     for (int item = it0; item < it1; ++item) {
@@ -213,18 +259,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
         const int bx = brick % nbx, by = (brick / nbx) % nby, bz = brick / nbx / nby;
         const bool new_brick = brick != cur_brick;
         cur_brick = brick;
-        if (tid == 0) {
-            fence_proxy_async();  // the generic-proxy reads and writes of the previous item precede the bulk writes
-            mbar_expect_tx(bar_tile, TILE_BYTES);
-            tma_load_5d(smem_u32(tile), &in_map, bar_tile, 0, bx * 8 - 1, by * 8 - 1, bz * 8 + 4 * (int)rank - 1, g);
-            if (new_brick) {
-                mbar_expect_tx(bar_w, WPK_BYTES);
-                bulk_load_1d(smem_u32(wsm), p.wpk + ((size_t)brick * 2 + rank) * WPK_F, WPK_BYTES, bar_w);
-            }
-        }
+        const bool has_next = item + 1 < it1;
+        unsigned ph_item = (unsigned)(item - it0) & 1u;  // C and D barriers complete once per item
         if (FUSE_IN && new_brick) {
             for (int c = tid; c < GB_CELLS; c += THREADS) {
-                const int cx = c % 10, cy = (c / 10) % 10, cz = c / 100;
+                const int cy = c % 10, cz = (c / 10) % 6, cx = c / 60;
                 const int gz = bz * 8 + 4 * (int)rank - 1 + cz, gy = by * 8 - 1 + cy, gx = bx * 8 - 1 + cx;
                 float2 gb = make_float2(0.0f, 0.0f);  // outside the grid: the zero fill stays zero
                 if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < p.K) {
@@ -242,27 +281,40 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                 na[q] = mr.y;
                 nb[q] = -mr.x * mr.y;
             }
+            __syncthreads();  // the gamma/beta table is complete
         }
-        wait_bar(bar_tile, ph_tile);
-        if (new_brick) wait_bar(bar_w, ph_w);
-        if (FUSE_IN) __syncthreads();  // the gamma/beta table is complete
-        // normalise the tile in place; copy the rim of the exchange plane (stale halo cells) to its alternate buffer
-        for (int c = tid >> 4; c < GB_CELLS; c += THREADS / 16) {
-            const int cz = c / 100, r = c - cz * 100, cy = r / 10, cx = r - cy * 10;
-            const bool rim = cz == ez && (cy == 0 || cy == 9 || cx == 0 || cx == 9);
-            if (!FUSE_IN && !rim) continue;
-            float4 *ptr = reinterpret_cast<float4 *>(tile + c * NS + 4 * li);
-            float4 v = *ptr;
+        // normalise the columns in place as they land
+        for (int j = 0; j < 5; ++j) {
+            unsigned phc = ph_item;
+            wait_bar(bar_c + 8 * j, phc);
             if (FUSE_IN) {
-                const float2 gb = gbt[c];
-                v.x = fmaf(fmaf(v.x, na[0], nb[0]), gb.x, gb.y);
-                v.y = fmaf(fmaf(v.y, na[1], nb[1]), gb.x, gb.y);
-                v.z = fmaf(fmaf(v.z, na[2], nb[2]), gb.x, gb.y);
-                v.w = fmaf(fmaf(v.w, na[3], nb[3]), gb.x, gb.y);
-                *ptr = v;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int cx = half ? 9 - j : j;
+                    float4 *cp = reinterpret_cast<float4 *>(tile + cx * XS + 4 * li);
+                    const float2 *gp = gbt + cx * 60;
+                    for (int r = tid >> 4; r < 60; r += THREADS / 16) {
+                        float4 v = cp[r * (NS / 4)];
+                        const float2 gb = gp[r];
+                        v.x = fmaf(fmaf(v.x, na[0], nb[0]), gb.x, gb.y);
+                        v.y = fmaf(fmaf(v.y, na[1], nb[1]), gb.x, gb.y);
+                        v.z = fmaf(fmaf(v.z, na[2], nb[2]), gb.x, gb.y);
+                        v.w = fmaf(fmaf(v.w, na[3], nb[3]), gb.x, gb.y);
+                        cp[r * (NS / 4)] = v;
+                    }
+                }
             }
-            if (rim) *reinterpret_cast<float4 *>(alt + r * NS + 4 * li) = v;
         }
+        if (FUSE_IN) __syncthreads();
+        // the rim of the exchange plane (stale halo cells) also goes to the plane's alternate buffer
+        for (int k = tid >> 4; k < 36; k += THREADS / 16) {
+            // rim cells in order: row 0 (10), row 9 (10), then columns 0 and 9 of rows 1..8
+            const int cy = k < 10 ? 0 : (k < 20 ? 9 : 1 + ((k - 20) >> 1));
+            const int cx = k < 20 ? (k < 10 ? k : k - 10) : ((k & 1) ? 9 : 0);
+            *reinterpret_cast<float4 *>(alt + cx * AXS + cy * NS + 4 * li) =
+                *reinterpret_cast<const float4 *>(tile + cx * XS + ez * ZS + cy * YS + 4 * li);
+        }
+        if (new_brick) wait_bar(bar_w, ph_w);
         __syncthreads();
         cluster_wait();  // the partner has finished the previous item: its exchange buffers may be written
 
@@ -271,22 +323,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                           ((((size_t)g * p.M + (bz * 8 + 4 * (int)rank + 2 * zp)) * p.N + (by * 8 + 2 * yp)) * p.K +
                            (bx * 8 + (h ? 7 : 0))) * NS + 4 * li;
         const size_t ydz = (size_t)p.N * p.K * NS, ydy = (size_t)p.K * NS;
+        const int ysx = h ? -NS : NS;
         float ssum[4] = {0.f, 0.f, 0.f, 0.f}, ssq[4] = {0.f, 0.f, 0.f, 0.f};
-        float4 carry[4];  // output column 3 of the previous iteration, written one step late
+        float4 carry[4];  // output column 3 of the previous iteration: written after every warp has finished step 5
 
-        for (int t = 0; t < p.inner; ++t) {
-            const bool last = t + 1 == p.inner;
+        TileOrigin nxt{};
+        if (has_next) nxt = tile_origin(item + 1);
+
+        // One inner iteration. LAST: the results go to global memory instead of the tile, and the tile's
+        // columns are handed over to the next item's bulk copies as they die.
+        auto iteration = [&](auto last_tag, const int t) {
+            constexpr bool LAST = decltype(last_tag)::value;
             const int par = t & 1;
-            // window rows: planes 2*zp .. 2*zp+3 of the tile; the exchange plane alternates between its two buffers
+            // window rows: planes 2*zp .. 2*zp+3, rows 2*yp .. 2*yp+3 of column col0; the exchange plane alternates
+            // between its place in the tile and the alternate buffer
             const float *rowp[4];
+            int rxs[4];
 #pragma unroll
-            for (int rz = 0; rz < 4; ++rz)
-                rowp[rz] = ((rz == exrow && par) ? alt : tile + (2 * zp + rz) * ZS) + cell_off;
-            float *const wrow = tile + (2 * zp + 1) * ZS + YS + cell_off;  // own cell of (dz = 0, dy = 0) in column 0
-            const unsigned rem = (par ? rem0 : rem1) + 4u * (unsigned)((2 * yp + 1) * YS + (h ? 9 : 0) * XS + 4 * li);
+            for (int rz = 0; rz < 4; ++rz) {
+                const bool ex = rz == exrow && par;
+                rowp[rz] = (ex ? alt + col0 * AXS : tile + col0 * XS + (2 * zp + rz) * ZS) + (2 * yp) * YS + 4 * li;
+                rxs[rz] = ex ? axs : xs;
+            }
+            float *const wrow = tile + col0 * XS + (2 * zp + 1) * ZS + (2 * yp + 1) * YS + 4 * li;  // own cell (dz 0, dy 0)
+            // where the partner reads my plane next iteration: the buffer of the other parity
+            const unsigned rem = par ? rem_tile + 4u * (unsigned)(col0 * XS + (2 * yp + 1) * YS + 4 * li)
+                                     : rem_alt + 4u * (unsigned)(col0 * AXS + (2 * yp + 1) * YS + 4 * li);
+            const int rstep = par ? xs : axs;
 
             Quad acc[4][4], cen[4][4];
-            float4 pend[4];
 #pragma unroll
             for (int j = 0; j < 6; ++j) {
                 if (j == 1 && t > 0) cluster_wait();  // the partner's plane of the previous iteration has landed
@@ -294,32 +359,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
 #pragma unroll
                 for (int rz = 0; rz < 4; ++rz)
 #pragma unroll
-                    for (int ry = 0; ry < 4; ++ry) col[rz][ry] = lds_quad(rowp[rz] + j * xs + ry * YS);
+                    for (int ry = 0; ry < 4; ++ry) col[rz][ry] = lds_quad(rowp[rz] + j * rxs[rz] + ry * YS);
+                if (LAST) {
+                    // this warp is done with column pair j of the item's tile (columns 4 and 5: after step 5)
+                    if (j <= 3) arrive(bar_d + 8 * j);
+                    if (j == 5) arrive(bar_d + 32);
+                    if (tid == 0 && j >= 1 && j <= 4 && has_next) {
+                        unsigned phd = ph_item;
+                        wait_bar(bar_d + 8 * (j - 1), phd);
+                        issue_cols(nxt, j - 1);
+                    }
+                }
                 if (j >= 1 && j <= 4) {
 #pragma unroll
                     for (int jn = 0; jn < 4; ++jn) cen[j - 1][jn] = col[1 + (jn >> 1)][1 + (jn & 1)];
                 }
+                if (j <= 3) {
+                    const float4 b4 = *reinterpret_cast<const float4 *>(bp + j * 32);
+                    acc[j][0].lo = acc[j][0].hi = pack2(b4.x, b4.x);
+                    acc[j][1].lo = acc[j][1].hi = pack2(b4.y, b4.y);
+                    acc[j][2].lo = acc[j][2].hi = pack2(b4.z, b4.z);
+                    acc[j][3].lo = acc[j][3].hi = pack2(b4.w, b4.w);
+                }
+                // taps outermost: the 8 to 24 FMAs of one (z, y) tap go to different accumulators
 #pragma unroll
-                for (int c = 0; c < 3; ++c) {
-                    const int xo = j - c;
-                    if (xo < 0 || xo > 3) continue;
-                    if (c == 0) {
-                        const float4 b4 = *reinterpret_cast<const float4 *>(bp + xo * 32);
-                        acc[xo][0].lo = acc[xo][0].hi = pack2(b4.x, b4.x);
-                        acc[xo][1].lo = acc[xo][1].hi = pack2(b4.y, b4.y);
-                        acc[xo][2].lo = acc[xo][2].hi = pack2(b4.z, b4.z);
-                        acc[xo][3].lo = acc[xo][3].hi = pack2(b4.w, b4.w);
-                    }
-                    const float *wq = wp + (xo * 3 + c) * 288;
+                for (int ab = 0; ab < 9; ++ab) {
+                    const int a = ab / 3, b = ab % 3;
 #pragma unroll
-                    for (int e4 = 0; e4 < 9; ++e4) {
-                        const float4 w4 = *reinterpret_cast<const float4 *>(wq + 4 * e4);
+                    for (int c = 0; c < 3; ++c) {
+                        const int xo = j - c;
+                        if (xo < 0 || xo > 3) continue;
+                        const float4 w4 = *reinterpret_cast<const float4 *>(wp + (xo * 3 + c) * 288 + 4 * ab);
                         const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int e = 4 * e4 + q, jn = e / 9, ab = e % 9, a = ab / 3, b = ab % 3;
+                        for (int jn = 0; jn < 4; ++jn) {
                             const Quad v = col[(jn >> 1) + a][(jn & 1) + b];
-                            const u64 ww = pack2(wv[q], wv[q]);
+                            const u64 ww = pack2(wv[jn], wv[jn]);
                             ffma2(acc[xo][jn].lo, v.lo, ww);
                             ffma2(acc[xo][jn].hi, v.hi, ww);
                         }
@@ -342,10 +417,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                         o[jn].z = fmaf(Act<ACT, float>::fwd(a2), sv[jn], c2);
                         o[jn].w = fmaf(Act<ACT, float>::fwd(a3), sv[jn], c3);
                     }
-                    if (last) {
+                    if (LAST) {
 #pragma unroll
                         for (int jn = 0; jn < 4; ++jn) {
-                            *reinterpret_cast<float4 *>(yb + (jn >> 1) * ydz + (jn & 1) * ydy + xo * xs) = o[jn];
+                            *reinterpret_cast<float4 *>(yb + (jn >> 1) * ydz + (jn & 1) * ydy + xo * ysx) = o[jn];
                             if (STATS_OUT) {
                                 ssum[0] += o[jn].x; ssq[0] = fmaf(o[jn].x, o[jn].x, ssq[0]);
                                 ssum[1] += o[jn].y; ssq[1] = fmaf(o[jn].y, o[jn].y, ssq[1]);
@@ -354,39 +429,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                             }
                         }
                     } else if (exporter) {
-                        // the partner reads this plane in its next iteration, from the buffer of the other parity
 #pragma unroll
                         for (int dy = 0; dy < 2; ++dy)
-                            st_cluster_f4(rem + 4u * (unsigned)(dy * YS + (xo + 1) * xs), edz ? o[2 + dy] : o[dy]);
+                            st_cluster_f4(rem + 4u * (unsigned)(dy * YS + (xo + 1) * rstep), edz ? o[2 + dy] : o[dy]);
                     }
                 }
-                // local writes, one step late: a column is overwritten after every warp has read it
+                // Tile writes. Output column xo overwrites tile column xo+1 (counted from this half's outer end), which
+                // this half read one step earlier and the other half never reads - except xo = 3, whose column the other
+                // half reads in step 5: that one waits for the next iteration's step 0.
                 if (j == 0 && t > 0) {
                     wait_bar(bar_r + 24, ph5);
 #pragma unroll
                     for (int jn = 0; jn < 4; ++jn)
                         *reinterpret_cast<float4 *>(wrow + (jn >> 1) * ZS + (jn & 1) * YS + 4 * xs) = carry[jn];
                 }
-                if (j == 2 && (!last || t > 0)) arrive_r(0);
-                if (j == 3 && (!last || t > 0)) wait_bar(bar_r, ph2);
-                if (j == 4 && !last) wait_bar(bar_r + 8, ph3);
-                if (j == 5 && !last) wait_bar(bar_r + 16, ph4);
-                if (j >= 3 && !last) {
+                if (j == 1 && (!LAST || t > 0)) arrive(bar_r);
+                if (j == 2 && (!LAST || t > 0)) wait_bar(bar_r, ph1);
+                if (!LAST) {
+                    if (j == 3) wait_bar(bar_r + 8, ph2);
+                    if (j == 4) wait_bar(bar_r + 16, ph3);
+                    if (j >= 2 && j <= 4) {
 #pragma unroll
-                    for (int jn = 0; jn < 4; ++jn)
-                        *reinterpret_cast<float4 *>(wrow + (jn >> 1) * ZS + (jn & 1) * YS + (j - 2) * xs) = pend[jn];
-                    arrive_r(j - 2);
-                }
-                if (j >= 2) {
+                        for (int jn = 0; jn < 4; ++jn)
+                            *reinterpret_cast<float4 *>(wrow + (jn >> 1) * ZS + (jn & 1) * YS + (j - 1) * xs) = o[jn];
+                    }
+                    if (j == 2) arrive(bar_r + 8);
+                    if (j == 3) arrive(bar_r + 16);
+                    if (j == 5) {
 #pragma unroll
-                    for (int jn = 0; jn < 4; ++jn) pend[jn] = o[jn];
-                }
-                if (j == 5 && !last) {
-#pragma unroll
-                    for (int jn = 0; jn < 4; ++jn) carry[jn] = o[jn];
-                    cluster_arrive();  // all exports of this iteration are stored
+                        for (int jn = 0; jn < 4; ++jn) carry[jn] = o[jn];
+                        arrive(bar_r + 24);
+                        cluster_arrive();  // all exports of this iteration are stored
+                    }
                 }
             }
+        };
+        for (int t = 0; t + 1 < p.inner; ++t) iteration(std::false_type{}, t);
+        iteration(std::true_type{}, p.inner - 1);
+        if (tid == 0 && has_next) {
+            unsigned phd = ph_item;
+            wait_bar(bar_d + 32, phd);
+            issue_cols(nxt, 4);
         }
 
         if (STATS_OUT) {
@@ -394,7 +477,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
 #pragma unroll
             for (int q = 0; q < 4; ++q) red[(u * 2 + h) * NS + 4 * li + q] = make_double2((double)ssum[q], (double)ssq[q]);
         }
-        __syncthreads();  // every read of the tile and of the weights is done; the partials are in place
+        __syncthreads();  // every read of the weights is done; the partials are in place
+        if (tid == 0 && has_next && (item + 1) / p.G != brick) issue_weights((item + 1) / p.G);
         if (STATS_OUT && tid < NS) {
             double s = 0.0, q = 0.0;
 #pragma unroll
@@ -416,7 +500,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
 // ---- weight packing ---------------------------------------------------------------------------
 // One CTA per block: the block's 27 x 512 weights, biases and scales are staged in shared memory with
 // coalesced reads and written out in the order the step kernel reads them:
-//   [block][rank][ (h, xo, c, unit) x 36 floats (jn * 9 + a * 3 + b) | bias (h, xo, unit, jn) | scale (same) ]
+//   [block][rank][ (h, xo, c, unit) x 36 floats ((a * 3 + b) * 4 + jn) | bias (h, xo, unit, jn) | scale (same) ]
 // rank = z half of the block, h = x half, xo = output column counted from the half's outer end,
 // c = x tap in sweep order (h = 1 sweeps downwards, so its taps are mirrored), unit = (zp, yp) patch,
 // jn = (dz, dy) inside the patch, (a, b) = (z, y) tap. Tap numbering a * 9 + b * 3 + c follows
@@ -447,8 +531,8 @@ __global__ void __launch_bounds__(256) pair64_pack_k(const float *__restrict__ w
             const int c = (grp >> 3) % 3, hx = (grp >> 3) / 3;
             h = hx >> 2;
             xo = hx & 3;
-            jn = k / 9;
-            ab = k - jn * 9;
+            ab = k >> 2;
+            jn = k & 3;
             cc = h ? 2 - c : c;
             src_t = (ab / 3) * 9 + (ab % 3) * 3 + cc;
         } else {
@@ -548,12 +632,12 @@ bool pair64_applicable(int M, int N, int K, int block, int inner)
     return encode_tiled_fn() != nullptr;
 }
 
-// Tensor map over an IL64 buffer: dims (fastest first) {64, K, N, M, G}, box {64, 10, 10, 6, 1}.
+// Tensor map over an IL64 buffer: dims (fastest first) {64, K, N, M, G}, box {64, 1, 10, 6, 1}: one tile column.
 static int make_il64_map(CUtensorMap *map, const float *il, int M, int N, int K, int G)
 {
     const cuuint64_t dims[5] = {64, (cuuint64_t)K, (cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)G};
     const cuuint64_t strides[4] = {256, (cuuint64_t)K * 256, (cuuint64_t)N * K * 256, (cuuint64_t)M * N * K * 256};
-    const cuuint32_t box[5] = {64, 10, 10, 6, 1};
+    const cuuint32_t box[5] = {64, 1, 10, 6, 1};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(il), dims, strides,
                                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
