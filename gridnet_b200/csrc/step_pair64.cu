@@ -124,6 +124,12 @@ __device__ __forceinline__ void cluster_arrive()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
+// Arrival without a fence: enough where the arrival only says "I have finished READING" (the loads have
+// returned before the instruction issues); a release arrival would also wait for every global store in flight.
+__device__ __forceinline__ void cluster_arrive_relaxed()
+{
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_wait()
 {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -194,8 +200,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
-    __syncthreads();
-    cluster_arrive();  // pairs with the wait before the first item's first exchange
+    cluster_arrive_relaxed();  // pairs with the wait before the first item's first exchange
 
     const int nbx = p.K >> 3, nby = p.N >> 3;
     const int xs = h ? -XS : XS, axs = h ? -AXS : AXS;
@@ -247,6 +252,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
         bulk_load_1d(smem_u32(wsm), p.wpk + ((size_t)brick * 2 + rank) * WPK_F, WPK_BYTES, bar_w);
     };
 
+    // (gamma, beta) of the tile cells of a block half, zero outside the grid (there the zero fill must stay zero)
+    auto build_gb_table = [&](int brick) {
+        const int bx = brick % nbx, by = (brick / nbx) % nby, bz = brick / nbx / nby;
+        for (int c = tid; c < GB_CELLS; c += THREADS) {
+            const int cy = c % 10, cz = (c / 10) % 6, cx = c / 60;
+            const int gz = bz * 8 + 4 * (int)rank - 1 + cz, gy = by * 8 - 1 + cy, gx = bx * 8 - 1 + cx;
+            float2 gb = make_float2(0.0f, 0.0f);
+            if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < p.K) {
+                const size_t gi = ((size_t)gz * p.N + gy) * p.K + gx;
+                gb = make_float2(p.gamma[gi], p.beta[gi]);
+            }
+            gbt[c] = gb;
+        }
+    };
+    if (FUSE_IN && it0 < it1) build_gb_table(it0 / p.G);
+    __syncthreads();  // barriers initialised, table complete
+
     if (tid == 0 && it0 < it1) {
         const TileOrigin o = tile_origin(it0);
         for (int j = 0; j < 5; ++j) issue_cols(o, j);
@@ -261,18 +283,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
         cur_brick = brick;
         const bool has_next = item + 1 < it1;
         unsigned ph_item = (unsigned)(item - it0) & 1u;  // C and D barriers complete once per item
-        if (FUSE_IN && new_brick) {
-            for (int c = tid; c < GB_CELLS; c += THREADS) {
-                const int cy = c % 10, cz = (c / 10) % 6, cx = c / 60;
-                const int gz = bz * 8 + 4 * (int)rank - 1 + cz, gy = by * 8 - 1 + cy, gx = bx * 8 - 1 + cx;
-                float2 gb = make_float2(0.0f, 0.0f);  // outside the grid: the zero fill stays zero
-                if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < p.K) {
-                    const size_t gi = ((size_t)gz * p.N + gy) * p.K + gx;
-                    gb = make_float2(p.gamma[gi], p.beta[gi]);
-                }
-                gbt[c] = gb;
-            }
-        }
         float na[4], nb[4];  // normalise: v * na + nb, then * gamma + beta
         if (FUSE_IN) {
 #pragma unroll
@@ -281,7 +291,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                 na[q] = mr.y;
                 nb[q] = -mr.x * mr.y;
             }
-            __syncthreads();  // the gamma/beta table is complete
         }
         // normalise the columns in place as they land
         for (int j = 0; j < 5; ++j) {
@@ -305,8 +314,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                 }
             }
         }
-        if (FUSE_IN) __syncthreads();
-        // the rim of the exchange plane (stale halo cells) also goes to the plane's alternate buffer
+        if (new_brick) wait_bar(bar_w, ph_w);
+        __syncthreads();
+        cluster_wait();  // the partner has finished the previous item: its exchange buffers may be written
+        // The rim of the exchange plane (stale halo cells) also goes to the plane's alternate buffer, which is first
+        // read in iteration 1: the arrive / wait chain of iteration 0 orders these stores before those loads.
         for (int k = tid >> 4; k < 36; k += THREADS / 16) {
             // rim cells in order: row 0 (10), row 9 (10), then columns 0 and 9 of rows 1..8
             const int cy = k < 10 ? 0 : (k < 20 ? 9 : 1 + ((k - 20) >> 1));
@@ -314,9 +326,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
             *reinterpret_cast<float4 *>(alt + cx * AXS + cy * NS + 4 * li) =
                 *reinterpret_cast<const float4 *>(tile + cx * XS + ez * ZS + cy * YS + 4 * li);
         }
-        if (new_brick) wait_bar(bar_w, ph_w);
-        __syncthreads();
-        cluster_wait();  // the partner has finished the previous item: its exchange buffers may be written
 
         // output position of (dz = 0, dy = 0, first column of this half) in the IL64 output
         float *const yb = p.y +
@@ -477,8 +486,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
 #pragma unroll
             for (int q = 0; q < 4; ++q) red[(u * 2 + h) * NS + 4 * li + q] = make_double2((double)ssum[q], (double)ssq[q]);
         }
-        __syncthreads();  // every read of the weights is done; the partials are in place
-        if (tid == 0 && has_next && (item + 1) / p.G != brick) issue_weights((item + 1) / p.G);
+        cluster_arrive_relaxed();  // this CTA no longer reads its exchange buffers of this item
+        const bool next_is_new_brick = has_next && (item + 1) / p.G != brick;
+        if (FUSE_IN && next_is_new_brick) build_gb_table((item + 1) / p.G);  // not read before the next item's normalisation
+        __syncthreads();  // every read of the weights is done; the partials and the table are in place
+        if (tid == 0 && next_is_new_brick) issue_weights((item + 1) / p.G);
         if (STATS_OUT && tid < NS) {
             double s = 0.0, q = 0.0;
 #pragma unroll
@@ -491,7 +503,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
             dst[0] = make_double2(s, q);
             dst[1] = make_double2(0.0, 0.0);
         }
-        cluster_arrive();  // this CTA no longer reads its exchange buffers of this item
     }
     cluster_wait();  // no CTA leaves while its partner may still store into its shared memory
     if (failed && p.error_flag) *p.error_flag = 1;
