@@ -13,13 +13,17 @@ neuron-updates/s = batch * grid^3 * inner * outer / seconds, whole job over all 
 (batch sharding: every rank runs its own batch, no collective on the data path).
 
 The JSON line also carries
-  roofline      the dominant kernel (fused step) timed alone with CUDA events: algorithmic
-                HBM bytes per launch / duration against the measured copy bandwidth, and
-                algorithmic FP32 FMA rate against the FP32 pipe peak (the binding bound);
+  roofline      the dominant kernel (fused step) timed alone with CUDA events: its binding
+                bound at the top level (algorithmic FP32 FMA rate against the FP32 pipe rate
+                measured with an FFMA-only kernel in the same run), the HBM bound nested;
   e2e           the same metric through the public op with pinned HOST buffers, copies
                 inside the timed region;
   cpu_baseline  the CPU oracle (C restatement of the reference's backend_torch, OpenMP)
-                on a bounded sample of the workload.
+                on the same full batch (N = 1 only);
+  c1, c3, c4    (N = 1) sub-records of the other single-GPU configurations;
+  c5_slab       (every N) the 256^3 grid slab-sharded along K over the N ranks (strong scaling),
+                preceded for N > 1 by a parity check of both face-exchange paths on the real ranks.
+`--workload X` runs one of them alone and prints its record as the line.
 `--impl reference` times that CPU oracle alone on all host threads.
 """
 from __future__ import annotations
@@ -50,9 +54,12 @@ UNIT = "neuron-updates/s"
 # FP32 pipe: 148 SMs x 128 FMA lanes x 2 FLOP at the maximum SM clock
 FP32_LANES = 148 * 128
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
-# from the capture summarised in profiles/step_fwd_fast8_c2_ncu_full.txt
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 173.0e6
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum): a constant taken
+# from the ncu capture summarised in the named file, not a measurement of this run
+NCU_TRAFFIC = {
+    "step_fwd_pair64": (141.9e6, "profiles/step_fwd_pair64_c2_ncu_full.txt"),
+    "step_fwd_fast8": (173.0e6, "profiles/step_fwd_fast8_c2_ncu_full.txt"),
+}
 
 
 def neuron_updates(batch: int) -> float:
@@ -178,70 +185,132 @@ def cpu_oracle_pass(inputs) -> float:
     return time.perf_counter() - t0
 
 
-def pick_cpu_sample(target_seconds: float):
-    """Batch size for the CPU oracle so that one pass takes roughly `target_seconds`;
-    also returns the number of OpenMP threads it runs on (all host cores)."""
-    from oracle import gridnet_oracle as orc
-
-    # all host threads this process may use, whatever OMP_NUM_THREADS says (torch.distributed.run
-    # sets it to 1 for its children)
-    orc.set_threads(len(os.sched_getaffinity(0)))
-    dt = cpu_oracle_pass(cpu_inputs(1))
-    n = int(max(1, min(BATCH, target_seconds / max(dt, 1e-6))))
-    return n, orc.max_threads()
-
-
 def run_reference(args, rank: int):
+    """The reference arm: the CPU oracle on all host threads, on the same full batch as the GPU arm."""
     if rank != 0:
         return
-    n, threads = pick_cpu_sample(3.0)
-    inputs = cpu_inputs(n)
+    from oracle import gridnet_oracle as orc
+
+    orc.set_threads(len(os.sched_getaffinity(0)))
+    threads = orc.max_threads()
+    inputs = cpu_inputs(BATCH)
     for _ in range(args.warmup):
         cpu_oracle_pass(inputs)
     dt = 0.0
     for _ in range(args.steps):
         dt += cpu_oracle_pass(inputs)
-    value = neuron_updates(n) * args.steps / dt
-    sample = f"{n} of {BATCH} samples per step, full 12 outer x 4 inner loop incl. LayerNorm"
+    value = neuron_updates(BATCH) * args.steps / dt
+    sample = f"{BATCH} of {BATCH} samples per step, full 12 outer x 4 inner loop incl. LayerNorm"
     line = {
         "impl": "reference",
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 0, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "implementation": "CPU oracle (C restatement of gridnet/backend_torch.py, OpenMP)"},
+        "config": {"workload": WORKLOAD, "global_batch": BATCH,
+                   "implementation": "CPU oracle (C restatement of gridnet/backend_torch.py, OpenMP)"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args, rank: int, local_rank: int, world: int):
-    import torch
+class Ctx:
+    """What every part of a GPU run shares: rank layout, device, the process group (None at one rank)."""
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
-    import gridnet_b200 as gb
+    def __init__(self, args, rank, local_rank, world):
+        import torch
 
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+        self.args, self.rank, self.local_rank, self.world = args, rank, local_rank, world
+        torch.cuda.set_device(local_rank)
+        self.device = torch.device("cuda", local_rank)
+        self.dist = None
+        self._own_group = False
 
-        dist = dist_mod
-        dist.init_process_group("nccl", device_id=device)
+    def need_group(self):
+        """A process group, also at one rank (the slab driver issues collectives either way)."""
+        import torch.distributed as dist
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
+        if self.dist is None:
+            if self.world == 1:
+                os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+                os.environ.setdefault("MASTER_PORT", "29533")
+                dist.init_process_group("nccl", rank=0, world_size=1, device_id=self.device)
+            else:
+                dist.init_process_group("nccl", device_id=self.device)
+            self.dist = dist
+        return self.dist
+
+    def barrier(self):
+        import torch
+
+        if self.dist is not None:
+            self.dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(self, ms: float) -> float:
+        import torch
+
+        if self.dist is None or self.world == 1:
+            return ms
+        t = torch.tensor([ms], device=self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def release(self):
+        import gc
+
+        import torch
+
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+            self.dist = None
+
+
+def measure_fp32_peak(torch, device):
+    """TFLOP/s of an FFMA-only kernel that fills every SM (CUDA events, best of 5 launches of a few ms)."""
+    import ctypes
+
+    from gridnet_b200._lib import check, lib
+
+    sink = torch.zeros(1, device=device)
+    count = ctypes.c_longlong(0)
+    st = torch.cuda.current_stream().cuda_stream
+    iters = 1 << 15
+    check(lib.gn_probe_fp32_fma(sink.data_ptr(), iters, ctypes.byref(count), st))
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        check(lib.gn_probe_fp32_fma(sink.data_ptr(), iters, ctypes.byref(count), st))
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        best = ms if best is None else min(best, ms)
+    return 2.0 * count.value / (best * 1e-3) / 1e12
+
+
+def bench_c2(ctx: Ctx):
+    import torch
+
+    import gridnet_b200 as gb
+    from gridnet_b200._lib import lib
+
+    args, rank, world, device = ctx.args, ctx.rank, ctx.world, ctx.device
+    if world > 1:
+        ctx.need_group()
     NSETS = 4  # rotating input/output sets: 4 x 67 MB in + the 300 MB working set >> 126 MB L2
     w, b, s, gamma, beta, xs_host = make_inputs(torch, device, NSETS)
     xs = [x.to(device) for x in xs_host]
     ys = [torch.empty_like(x) for x in xs]
     ws = gb.outer_forward_workspace(BATCH, GRID, BLOCK, device)
-    P = GRID[0] * GRID[1] * GRID[2]
+    large_batch = bool(lib.gn_pair64_supported(GRID[0], GRID[1], GRID[2], BLOCK, INNER))
 
     def step(i):
         gb.outer_forward(w, b, s, gamma, beta, xs[i % NSETS], INNER, OUTER, BLOCK, ACT, out=ys[i % NSETS],
@@ -250,8 +319,8 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     # ---------------- device-resident timing (value)
     for i in range(max(args.warmup, 3)):
         step(i)
-    barrier()
-    sampler = ClockSampler(local_rank)
+    ctx.barrier()
+    sampler = ClockSampler(ctx.local_rank)
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -259,14 +328,13 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     for i in range(args.steps):
         step(i)
     e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches_per_step = OUTER * 2 + 1  # per outer step: fused step kernel + statistics finalize; one final apply
-    if dist is not None:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ctx.barrier()
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1))
+    # per outer step: step kernel + statistics finalize; plus, once per forward, the layout conversion in and out
+    # (and the weight re-ordering) of the large-batch kernel, or the final normalisation of the register-patch one
+    launches_per_step = OUTER * 2 + (3 if large_batch else 1)
     value = neuron_updates(BATCH) * world * args.steps / (ms * 1e-3)
+    failed = gb.outer_forward_failed(ws, BATCH, GRID, BLOCK)
 
     # ---------------- the dominant kernel alone (roofline)
     nparts = gb.step_stats_partials(GRID, BLOCK)
@@ -276,32 +344,58 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     stats[:, 0] = 0.0
     stats[:, 1] = 1.0
     reps = max(args.steps, 3) * OUTER
+    if large_batch:
+        from gridnet_b200.backend_cuda import pair64_interleave, pair64_pack_weights, pair64_step
+
+        kernel_name = "step_fwd_pair64<silu, fuse_in, stats_out>"
+        packed = pair64_pack_weights(w, b, s)
+        xi = [pair64_interleave(x) for x in xs]
+        yi = [torch.empty_like(x) for x in xi]
+        flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+        def kernel(i):
+            pair64_step(packed, xi[i % NSETS], yi[(i + 1) % NSETS], BATCH, GRID, INNER, ACT, gamma, beta, stats,
+                        partials, flag)
+    else:
+        kernel_name = "step_fwd_fast8<silu, fuse_in, stats_out>"
+
+        def kernel(i):
+            gb.fused_step(w, b, s, xs[i % NSETS], ys[(i + 1) % NSETS], INNER, BLOCK, ACT, gamma, beta, stats, partials)
+
     for i in range(6):
-        gb.fused_step(w, b, s, xs[i % NSETS], ys[(i + 1) % NSETS], INNER, BLOCK, ACT, gamma, beta, stats, partials)
+        kernel(i)
     torch.cuda.synchronize()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record()
     for i in range(reps):
-        gb.fused_step(w, b, s, xs[i % NSETS], ys[(i + 1) % NSETS], INNER, BLOCK, ACT, gamma, beta, stats, partials)
+        kernel(i)
     k1.record()
     torch.cuda.synchronize()
     kms = k0.elapsed_time(k1) / reps
+    if large_batch:
+        del xi, yi, packed
+    fp32_measured = measure_fp32_peak(torch, device)
     hbm_peak, peak_kind, sm_max_mhz = measured_peaks()
     ach_gbs = algorithmic_bytes_per_launch(BATCH) / (kms * 1e-3) / 1e9
-    fp32_peak_tflops = FP32_LANES * 2 * sm_max_mhz * 1e6 / 1e12
+    fp32_nominal = FP32_LANES * 2 * sm_max_mhz * 1e6 / 1e12
     ach_tflops = 2 * algorithmic_fma_per_launch(BATCH) / (kms * 1e-3) / 1e12
-    roofline = {
-        "kernel": "step_fwd_fast8<silu, fuse_in, stats_out>",
-        "bound": "hbm", "achieved": ach_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": ach_gbs / hbm_peak,
-        "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
-        "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-        "algorithmic_bytes_per_launch": algorithmic_bytes_per_launch(BATCH),
-        "kernel_ms": kms,
-        "note": "this kernel is bound by the FP32 FMA pipe, not HBM; see fp32",
-        "fp32": {"achieved": ach_tflops, "peak": fp32_peak_tflops, "unit": "TFLOP/s", "frac": ach_tflops / fp32_peak_tflops,
-                 "peak_source": f"148 SMs x 128 lanes x 2 x {sm_max_mhz:.0f} MHz (nominal; no measured FP32 peak on file)",
-                 "algorithmic_flop_per_launch": 2 * algorithmic_fma_per_launch(BATCH)},
-    }
+    traffic, traffic_src = NCU_TRAFFIC["step_fwd_pair64" if large_batch else "step_fwd_fast8"]
+    fp32 = {"bound": "fp32", "achieved": ach_tflops, "peak": fp32_measured, "unit": "TFLOP/s",
+            "frac": ach_tflops / fp32_measured,
+            "peak_source": "measured in this run: FFMA-only kernel on every SM, CUDA events (gn_probe_fp32_fma)",
+            "peak_nominal": fp32_nominal, "frac_of_nominal": ach_tflops / fp32_nominal,
+            "algorithmic_flop_per_launch": 2 * algorithmic_fma_per_launch(BATCH)}
+    hbm = {"bound": "hbm", "achieved": ach_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": ach_gbs / hbm_peak,
+           "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
+           "algorithmic_bytes_per_launch": algorithmic_bytes_per_launch(BATCH)}
+    # the binding bound is the one whose roofline time is longer
+    t_fp32 = fp32["algorithmic_flop_per_launch"] / (fp32_measured * 1e12)
+    t_hbm = hbm["algorithmic_bytes_per_launch"] / (hbm_peak * 1e9)
+    binding, other = (fp32, hbm) if t_fp32 >= t_hbm else (hbm, fp32)
+    roofline = dict(binding)
+    roofline.update({"kernel": kernel_name, "kernel_ms": kms, "traffic": traffic,
+                     "traffic_source": f"constant from the ncu capture summarised in {traffic_src}, not measured in this run",
+                     "other_bound": other})
 
     # ---------------- end to end through the public op with pinned host buffers
     # Host batches go through HostPipelinedForward: host->device copy, the fused loop and the
@@ -314,7 +408,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     for i in range(3):
         pipe.submit(hx[i % 2], hy[i % 2])
     pipe.synchronize()
-    barrier()
+    ctx.barrier()
     n_e2e = max(3, args.steps)  # the same K as the device-resident figure; includes filling and draining the pipeline
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
@@ -323,55 +417,101 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         pipe.submit(hx[i % 2], hy[i % 2])
     pipe.join()  # the current stream waits for the last device->host copy
     t1.record()
-    barrier()
-    ems = t0.elapsed_time(t1)
-    if dist is not None:
-        t = torch.tensor([ems], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ems = float(t.item())
+    ctx.barrier()
+    ems = ctx.max_over_ranks(t0.elapsed_time(t1))
     ok = bool(torch.isfinite(hy[0]).all().item())
     e2e_value = neuron_updates(BATCH) * world * n_e2e / (ems * 1e-3)
     nbytes = xs[0].numel() * 4
     e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
            "ms_per_step": ems / n_e2e, "steps": n_e2e,
            "finite": ok,
+           "host_gbs_per_rank": 2 * nbytes * n_e2e / (ems * 1e-3) / 1e9,
            "note": "full [B,M,N,K] activations in and out through HostPipelinedForward (pinned host memory; copies of one "
                    "step overlap the compute of its neighbours on separate streams)"}
 
     # clocks were sampled over all three timed regions (value, kernel-only, end to end)
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---------------- CPU baseline on rank 0 at N = 1
+    # ---------------- CPU baseline on rank 0 at N = 1: the oracle on the same full batch
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        n, threads = pick_cpu_sample(10.0)
-        inputs = cpu_inputs(n)
+        from oracle import gridnet_oracle as orc
+
+        orc.set_threads(len(os.sched_getaffinity(0)))
+        inputs = cpu_inputs(BATCH)
         dt, passes = 0.0, 0
         while passes < 8 and (passes == 0 or dt < 10.0):  # about 10 s of CPU work, whole passes only
             dt += cpu_oracle_pass(inputs)
             passes += 1
-        rate = neuron_updates(n) * passes / dt
-        cpu = {"value": rate, "unit": UNIT, "cores": threads, "kind": "port",
-               "sample": f"{passes} pass(es) over {n} of {BATCH} samples, full 12 outer x 4 inner loop incl. LayerNorm, "
-                         f"{dt:.1f} s"}
+        rate = neuron_updates(BATCH) * passes / dt
+        cpu = {"value": rate, "unit": UNIT, "cores": orc.max_threads(), "kind": "port",
+               "sample": f"{passes} pass(es) over {BATCH} of {BATCH} samples, full 12 outer x 4 inner loop incl. LayerNorm, "
+                         f"{dt:.1f} s", "note": "measured at N = 1 only"}
 
+    del pipe, hx, hy, xs, ys, ws
+    ctx.release()
+    return {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "parallelism": f"batch-sharded x{world}",
+                   "l2": f"{NSETS} rotating input/output sets (4 x 67 MB each way) plus a 300 MB working set per step, larger than the 126 MB L2",
+                   "samples_per_sec": BATCH * world * args.steps / (ms * 1e-3),
+                   "step_kernel": "large-batch (step_pair64.cu)" if large_batch else "register-patch (step_fast.cu)",
+                   "device_failure_flag": failed},
+        "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu,
+        "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+    }
+
+
+def slab_parity_on_ranks(ctx: Ctx) -> dict:
+    """Both face-exchange paths of the slab mode on the real ranks against rank 0's single-GPU fused loop, on a
+    grid small enough for one GPU: 64 x 64 x (16 * world), batch 8, 2 inner x 3 outer."""
+    import torch
+
+    import gridnet_b200 as gb
+    from gridnet_b200.slab import PeerFaceBuffers, SlabLayout, make_cuda_runner, run_direct, run_distributed
+
+    dist = ctx.need_group()
+    world, rank, device = ctx.world, ctx.rank, ctx.device
+    M = N = 64
+    K = 16 * world
+    B, inner, outer = 8, 2, 3
+    g = torch.Generator().manual_seed(7)  # the same full tensors on every rank
+    w = torch.randn(27, M, N, K, generator=g) / 27 ** 0.5
+    b = 0.1 * torch.randn(M, N, K, generator=g)
+    s = 1 + 0.1 * torch.randn(M, N, K, generator=g)
+    gamma = 1 + 0.1 * torch.randn(M, N, K, generator=g)
+    beta = 0.1 * torch.randn(M, N, K, generator=g)
+    x = torch.zeros(B, M, N, K)
+    x[..., 0] = torch.randn(B, M, N, generator=g)
+    lay = SlabLayout(K, world, rank)
+    peers = PeerFaceBuffers(lay, B, M, N, device)
+    outs = {}
+    for name in ("direct", "nccl"):
+        runner = make_cuda_runner(lay, w, b, s, gamma, beta, x, inner, ACT, device=device)
+        local = run_direct(runner, outer, peers) if name == "direct" else run_distributed(runner, outer)
+        parts = [torch.empty_like(local) for _ in range(world)] if rank == 0 else None
+        dist.gather(local.contiguous(), parts, dst=0)
+        if rank == 0:
+            outs[name] = torch.cat(parts, dim=-1)
+    verdict = torch.zeros(3, device=device)
     if rank == 0:
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "parallelism": f"batch-sharded x{world}",
-                       "l2": f"{NSETS} rotating input/output sets (4 x 67 MB each way) plus a 300 MB working set per step, larger than the 126 MB L2",
-                       "samples_per_sec": BATCH * world * args.steps / (ms * 1e-3)},
-            "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu,
-            "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
-        }
-        print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+        ref = gb.outer_forward(*(t.to(device) for t in (w, b, s, gamma, beta, x)), inner, outer, 8, ACT)
+        tol = 1e-5 + 1e-4 * ref.abs()
+        e_direct = (outs["direct"] - ref).abs()
+        e_nccl = (outs["nccl"] - ref).abs()
+        ok = bool((e_direct <= tol).all().item()) and bool((e_nccl <= tol).all().item())
+        verdict = torch.tensor([1.0 if ok else 0.0, float(e_direct.max().item()), float(e_nccl.max().item())], device=device)
+    dist.broadcast(verdict, src=0)
+    del peers
+    return {"slab_parity_ok": bool(verdict[0].item() > 0.5), "grid": [M, N, K], "batch": B,
+            "max_abs_err_direct": float(verdict[1].item()), "max_abs_err_nccl": float(verdict[2].item()),
+            "same_bits_both_paths": None if rank != 0 else bool(torch.equal(outs["direct"], outs["nccl"])),
+            "tolerance": "1e-5 + 1e-4 |ref| against outer_forward on the whole grid on rank 0"}
 
 
-def run_slab(args, rank: int, local_rank: int, world: int):
+def bench_slab(ctx: Ctx):
     """The large-grid configuration: 256^3 grid, block 8, 2 inner x 32 outer, batch 32, forward, the grid
     slab-sharded along K over all ranks (strong scaling: the total work is fixed)."""
     import torch
@@ -379,17 +519,11 @@ def run_slab(args, rank: int, local_rank: int, world: int):
     from gridnet_b200.slab import (GHOST, CudaSlabBackend, PeerFaceBuffers, SlabLayout, SlabRunner, run_direct,
                                    run_distributed)
 
+    args, rank, world, device = ctx.args, ctx.rank, ctx.world, ctx.device
+    dist = ctx.need_group()
+    parity = slab_parity_on_ranks(ctx) if world > 1 else None
+    ctx.release()
     G, B, inner, outer = 256, 32, 2, 32
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    import torch.distributed as dist
-
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    else:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29533")
-        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
     lay = SlabLayout(G, world, rank)
     g = torch.Generator(device=device).manual_seed(100 + rank)
     kp = lay.k_pad
@@ -417,11 +551,12 @@ def run_slab(args, rank: int, local_rank: int, world: int):
         runner = SlabRunner(lay, backend, x, G * G * G)
         return run_direct(runner, outer, peers) if direct else run_distributed(runner, outer)
 
-    for _ in range(max(1, min(args.warmup, 2))):
+    warm = max(1, min(args.warmup, 2))
+    for _ in range(warm):
         one_pass()
     dist.barrier()
     torch.cuda.synchronize()
-    steps = max(1, min(args.steps, 5))
+    steps = max(1, min(args.steps, 3))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -429,27 +564,28 @@ def run_slab(args, rank: int, local_rank: int, world: int):
     e1.record()
     dist.barrier()
     torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1)], device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1))
     finite = bool(torch.isfinite(out).all().item())
     chk = out.double().sum().reshape(1)  # the same bits whichever way the faces travel: compare between runs
     dist.all_reduce(chk)
-    if rank == 0:
-        nu = float(B) * G ** 3 * inner * outer
-        print(json.dumps({
-            "metric": METRIC, "value": nu * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
-            "warmup": max(1, min(args.warmup, 2)), "ms_per_step": ms / steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "C5: 256^3 grid, block 8, 2 inner x 32 outer, batch 32, fp32, forward + whole-grid "
-                                   "LayerNorm, slab-sharded along K", "parallelism": f"slab x{world}",
-                       "exchange": ("per outer step: the step kernel stores 2 faces [32,256,256] fp32 into the neighbours' memory "
-                                    "over NVLink; all-reduce of [32,2] f64" if direct else
-                                    "per outer step: 2 faces [32,256,256] fp32 send/recv per neighbour + all-reduce of [32,2] f64"),
-                       "samples_per_sec": B * steps / (ms * 1e-3), "finite": finite, "output_checksum": float(chk.item())},
-            "gpu_launches": (outer * 2 + 1) * steps,
-        }), flush=True)
-    dist.destroy_process_group()
+    nu = float(B) * G ** 3 * inner * outer
+    rec = {
+        "metric": METRIC, "value": nu * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warm, "ms_per_step": ms / steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "C5: 256^3 grid, block 8, 2 inner x 32 outer, batch 32, fp32, forward + whole-grid "
+                               "LayerNorm, slab-sharded along K", "parallelism": f"slab x{world}",
+                   "exchange": ("per outer step: the step kernel stores 2 faces [32,256,256] fp32 into the neighbours' memory "
+                                "over NVLink; all-reduce of [32,2] f64" if direct else
+                                "per outer step: 2 faces [32,256,256] fp32 send/recv per neighbour + all-reduce of [32,2] f64"),
+                   "samples_per_sec": B * steps / (ms * 1e-3), "finite": finite, "output_checksum": float(chk.item())},
+        "gpu_launches": (outer * 2 + 1) * steps,
+    }
+    if parity is not None:
+        rec.update(parity)
+    del backend, peers, w, x, out
+    ctx.release()
+    return rec
 
 
 TRAIN_WORKLOADS = {
@@ -461,7 +597,7 @@ TRAIN_WORKLOADS = {
 }
 
 
-def run_train(args, rank: int, local_rank: int, world: int):
+def bench_train(ctx: Ctx, name: str, stash=None, microbatches=None, steps_cap: int = 10):
     """The forward + backward configurations: one step = the outer loop forward, then the gradient of a
     seeded random upstream gradient on the final grid back to the parameters and the input, through the
     autograd ops of the package (the step op and the whole-grid norm op per outer step). The batch is
@@ -469,31 +605,20 @@ def run_train(args, rank: int, local_rank: int, world: int):
     all-reduced once per step, inside the timed region."""
     import torch
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     import gridnet_b200 as gb
 
-    G, block, inner, outer, batch, desc = TRAIN_WORKLOADS[args.workload]
+    args, rank, local_rank, world, device = ctx.args, ctx.rank, ctx.local_rank, ctx.world, ctx.device
+    G, block, inner, outer, batch, desc = TRAIN_WORKLOADS[name]
     if args.batch:
         batch = args.batch
-    if args.stash:  # keep the inner iterations' intermediate results from the forward pass (memory for time)
-        gb.keep_forward_stash(True)
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-
-        dist = dist_mod
-        dist.init_process_group("nccl", device_id=device)
+    stash = args.stash if stash is None else stash
+    # keep the inner iterations' intermediate results from the forward pass (memory for time)
+    previous_stash = gb.keep_forward_stash(bool(stash))
+    dist = ctx.need_group() if world > 1 else None
     if batch % world:
         raise SystemExit(f"batch {batch} does not divide over {world} ranks")
     b_loc = batch // world
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    barrier = ctx.barrier
 
     g = torch.Generator().manual_seed(0)
     model = gb.GridnetModel((G, G, G), inner, outer, block, device, activation=ACT)
@@ -509,7 +634,7 @@ def run_train(args, rank: int, local_rank: int, world: int):
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     t_fwd = t_bwd = 0.0
 
-    nmb = max(1, args.microbatches)
+    nmb = max(1, args.microbatches if microbatches is None else microbatches)
     if b_loc % nmb:
         raise SystemExit(f"the per-rank batch {b_loc} does not divide into {nmb} micro-batches")
     mb = b_loc // nmb
@@ -550,7 +675,7 @@ def run_train(args, rank: int, local_rank: int, world: int):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    steps = max(1, min(args.steps, 10))
+    steps = max(1, min(args.steps, steps_cap))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -558,21 +683,19 @@ def run_train(args, rank: int, local_rank: int, world: int):
     e1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([e0.elapsed_time(e1)], device=device)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1))
     finite = all(bool(torch.isfinite(t_).all().item()) for t_ in grads)
-    if rank == 0:
+    fp32_peak = measure_fp32_peak(torch, device)
+    rec = None
+    if True:
         nu = float(batch) * G ** 3 * inner * outer
-        hbm_gbs, hbm_src, _ = measured_peaks()
-        clock_ghz = ((clocks or {}).get("sm_max_mhz") or 1965.0) / 1e3
-        fp32_peak = FP32_LANES * 2 * clock_ghz / 1e3  # TFLOP/s
+        hbm_gbs, hbm_src, sm_max_mhz = measured_peaks()
+        fp32_nominal = FP32_LANES * 2 * sm_max_mhz * 1e6 / 1e12
         flops = 162.0 * nu / world  # per GPU: 27 forward FMAs and 54 backward FMAs per neuron update
         # bytes per outer step and GPU: forward 124 P + 8 B P, backward 372 P + 12 B P
         bytes_step = (124.0 + 372.0) * G ** 3 + 20.0 * b_loc * G ** 3
         sec = ms * 1e-3 / steps
-        print(json.dumps({
+        rec = ({
             "metric": METRIC, "value": nu / sec, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warm,
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
@@ -582,37 +705,38 @@ def run_train(args, rank: int, local_rank: int, world: int):
                              "alone are %.0f MB, larger than the 126 MB L2"
                              % (b_loc * G ** 3 * 4 / 1e6, 2 * outer, 2 * outer * b_loc * G ** 3 * 4 / 1e6),
                        "forward_ms": t_fwd / steps, "backward_ms": t_bwd / steps, "finite": finite,
-                       "intermediate_results": "kept from the forward pass" if args.stash else "recomputed in the backward pass",
+                       "intermediate_results": "kept from the forward pass" if stash else "recomputed in the backward pass",
                        "microbatches": nmb,
                        "samples_per_sec": batch / sec},
             "roofline": {"bound": "fp32", "achieved": flops / sec / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
                          "frac": flops / sec / 1e12 / fp32_peak,
-                         "peak_source": "148 SMs x 128 lanes x 2 x max SM clock (nominal; no measured FP32 peak on file)",
-                         "hbm": {"achieved": bytes_step * outer / sec / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                         "peak_source": "measured in this run: FFMA-only kernel on every SM, CUDA events (gn_probe_fp32_fma)",
+                         "peak_nominal": fp32_nominal, "frac_of_nominal": flops / sec / 1e12 / fp32_nominal,
+                         "other_bound": {"bound": "hbm", "achieved": bytes_step * outer / sec / 1e9, "peak": hbm_gbs, "unit": "GB/s",
                                  "frac": bytes_step * outer / sec / 1e9 / hbm_gbs,
                                  "peak_source": hbm_src + " (MEASURED_PEAKS.json hbm_gbs)" if hbm_src == "measured"
                                  else "fallback"},
-                         "traffic": None},
+                         "traffic": None,
+                         "traffic_source": "not captured for the training step (many kernels; see profiles/train_step_c3_launch_list.txt for their shares)"},
             "clocks": clocks,
-        }), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+        })
+    gb.keep_forward_stash(previous_stash)
+    del grads, model, params, x, gy
+    ctx.release()
+    return rec
 
 
-def run_c1(args, rank: int, local_rank: int, world: int):
+def bench_c1(ctx: Ctx):
     """The small MNIST-shaped configuration: 32^3 grid, block 8, 2 inner x 8 outer, batch 8, forward. It is
     bound by launch latency (17 launches of a few microseconds each), so it is timed twice: issued launch by
     launch, and replayed from a CUDA graph captured once (the fused loop neither allocates nor
     synchronises, so it can be captured as is)."""
     import torch
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     import gridnet_b200 as gb
 
+    args, rank, device = ctx.args, ctx.rank, ctx.device
     G, block, inner, outer, B = 32, 8, 2, 8, 8
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
     g = torch.Generator().manual_seed(0)
     w = (torch.randn(27, G, G, G, generator=g) / 27 ** 0.5).to(device)
     b = torch.zeros(G, G, G, device=device)
@@ -654,8 +778,9 @@ def run_c1(args, rank: int, local_rank: int, world: int):
     same = bool(torch.equal(eager_out, y))
     failed = gb.outer_forward_failed(ws, B, (G, G, G), block)
     nu = float(B) * G ** 3 * inner * outer
-    if rank == 0:
-        print(json.dumps({
+    del graph
+    if True:
+        return ({
             "metric": METRIC, "value": nu / (graph_ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps,
             "warmup": max(3, args.warmup), "ms_per_step": graph_ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -666,7 +791,14 @@ def run_c1(args, rank: int, local_rank: int, world: int):
                        "samples_per_sec": B / (graph_ms * 1e-3),
                        "l2": "working set 4 MB: L2-resident by nature of the configuration"},
             "gpu_launches": (2 * outer + 1) * steps,
-        }), flush=True)
+        })
+
+
+def brief(rec):
+    """A sub-record: the full record of a workload without the keys that only make sense at the top level."""
+    if rec is None:
+        return None
+    return {k: v for k, v in rec.items() if k not in ("metric", "unit", "higher_is_better", "vs_baseline", "dtype", "data")}
 
 
 def main():
@@ -676,10 +808,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["c2", "c5-slab", "c3", "c4", "c1"], default="c2",
-                    help="c2 (default): the headline benchmark; c5-slab: the 256^3 grid sharded along K over all ranks; "
-                         "c3 / c4: the forward + backward configurations (128^3 block 8, 64^3 block 4); "
-                         "c1: the small launch-bound configuration, also replayed from a CUDA graph")
+    ap.add_argument("--workload", choices=["all", "c2", "c5-slab", "c3", "c4", "c1"], default="all",
+                    help="all (default): the headline benchmark c2 with the other configurations as sub-records of the same "
+                         "line (c5_slab at every N; c1, c3, c4 at N = 1); c2: the headline alone; c5-slab: the 256^3 grid "
+                         "sharded along K over all ranks; c3 / c4: the forward + backward configurations (128^3 block 8, "
+                         "64^3 block 4); c1: the small launch-bound configuration, also replayed from a CUDA graph")
     ap.add_argument("--slab-exchange", choices=["direct", "nccl"], default="direct",
                     help="c5-slab only: how the boundary faces travel (direct = stored by the step kernel into peer memory)")
     ap.add_argument("--stash", action="store_true",
@@ -697,17 +830,35 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank)
         return
+    ctx = Ctx(args, rank, local_rank, world)
+    line, rc = None, 0
     if args.workload == "c5-slab":
-        run_slab(args, rank, local_rank, world)
-        return
-    if args.workload in TRAIN_WORKLOADS:
-        run_train(args, rank, local_rank, world)
-        return
-    if args.workload == "c1":
-        if rank == 0:
-            run_c1(args, rank, local_rank, world)
-        return
-    run_ours(args, rank, local_rank, world)
+        line = bench_slab(ctx)
+        if line.get("slab_parity_ok") is False:
+            rc = 3
+    elif args.workload in TRAIN_WORKLOADS:
+        line = bench_train(ctx, args.workload)
+    elif args.workload == "c1":
+        line = bench_c1(ctx) if rank == 0 else None
+    else:
+        line = bench_c2(ctx)
+        if args.workload == "all":
+            # the other configurations ride on the same line; the driver only ever runs this command
+            slab = bench_slab(ctx)
+            line["c5_slab"] = brief(slab)
+            if slab.get("slab_parity_ok") is False:
+                rc = 3
+            if world == 1:
+                line["c1"] = brief(bench_c1(ctx))
+                # C3 at its full batch keeps the forward pass's intermediate results in two micro-batches of 128
+                # (in one piece they do not fit beside the 68 GB of saved step and norm inputs); C4 keeps them too
+                line["c3"] = brief(bench_train(ctx, "c3", stash=True, microbatches=2, steps_cap=3))
+                line["c4"] = brief(bench_train(ctx, "c4", stash=True, microbatches=1, steps_cap=5))
+    if rank == 0 and line is not None:
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    if rc:
+        raise SystemExit(rc)
 
 
 if __name__ == "__main__":
