@@ -45,6 +45,8 @@ SIGNATURES = {
     "gn_norm_forward_static_f32": (c_int, [_P] * 4 + [c_int, c_longlong, c_float, _P]),
     "gn_step_stats_partials": (c_int, [c_int] * 4),
     "gn_step_forward_fused_f32": (c_int, [_P] * 9 + _geom + [c_int, c_int, c_int, _P]),
+    "gn_device_status": (c_int, [c_int]),
+    "gn_device_status_set": (c_int, [c_int]),
     "gn_probe_fp32_fma": (c_int, [_P, c_int, _P, _P]),
     "gn_pair64_supported": (c_int, [c_int] * 5),
     "gn_pair64_packed_weight_bytes": (c_size_t, [c_int] * 3),

@@ -173,6 +173,18 @@ class GridNormOp(torch.autograd.Function):
         return gx, gg, gb, None
 
 
+def device_status(clear: bool = True, device=None) -> bool:
+    """True if, since the last clear, a kernel on ``device`` gave up a bounded wait on a bulk tile copy and had
+    no workspace flag to report it in (the results of that call are invalid). Synchronises the device."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        torch.cuda.synchronize(dev)
+        rc = int(lib.gn_device_status(1 if clear else 0))
+    if rc < 0:
+        check(rc)
+    return rc == 1
+
+
 def outer_forward_failed(workspace: torch.Tensor, batch: int, shape, block_size: int) -> bool:
     """True if the last :func:`outer_forward` that used ``workspace`` recorded a device-side failure
     (a bounded wait on a bulk tile copy that gave up). Synchronises the device."""

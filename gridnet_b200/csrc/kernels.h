@@ -96,6 +96,11 @@ int launch_to_il64(const float *x, float *il, int B, int G, long long P, cudaStr
 int launch_from_il64(const float *il, const float2 *stats, const float *gamma, const float *beta, float *y, int B, int G,
                      long long P, cudaStream_t st);
 
+// ---- status.cu: device address of the per-device status word that kernels set when a bounded wait gives up
+// and the caller passed no flag of its own (nullptr if it cannot be resolved)
+int *device_status_ptr();
+int launch_propagate_flag(const int *flag, cudaStream_t st);
+
 // ---- probe.cu (FFMA-only kernel for the measured FP32 peak)
 int launch_ffma_probe(float *sink, int iters, long long *fma_count, cudaStream_t st);
 

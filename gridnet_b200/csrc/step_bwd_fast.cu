@@ -843,7 +843,10 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
         if (block == 4) bwd_halo8_k<4><<<grid, HaloGeo<4>::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
         else bwd_border8_k<<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
     }
-    return check_launch("bwd_halo8");
+    rc = check_launch("bwd_halo8");
+    if (rc != GN_OK) return rc;
+    // callers of the backward rarely look into the workspace: a set flag also goes to the library's status word
+    return launch_propagate_flag(error_flag, st);
 }
 
 }  // namespace gn

@@ -369,6 +369,7 @@ bool fast8_make_tile_map(CUtensorMap *map, const float *base, int B, int M, int 
 int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
 {
     const long long nb = (long long)(p.M / 8) * (p.N / 8) * (p.K / 8);
+    if (!p.error_flag) p.error_flag = device_status_ptr();  // callers without a flag of their own: the library's status word
     if (p.kbn <= 0) {
         p.kb0 = 0;
         p.kbn = p.K / 8;

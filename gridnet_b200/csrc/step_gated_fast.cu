@@ -182,6 +182,7 @@ int launch_gated_fwd_fast8(const float *w, const float *b, const float *x, float
     GatedFastParams p{};
     p.w = w; p.b = b; p.x = x; p.y = y;
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
+    p.error_flag = device_status_ptr();  // this entry point has no workspace: report to the library's status word
     const int chunks = pick_batch_chunks_balanced(nb, B, 1, 1.5, B < 64 ? B : 64);
     p.spc = (B + chunks - 1) / chunks;
     dim3 grid((unsigned)nb, (unsigned)((B + p.spc - 1) / p.spc));

@@ -757,6 +757,7 @@ __global__ void __launch_bounds__(BS *BS *BS)
                     }
             __syncthreads();
         }
+        if (inner == 0) __syncthreads();  // no iteration ran: the G cells written above are read by other threads below
         R *gxs = gx + (size_t)smp * P;
         for (int i = tid; i < T; i += NT) {
             const int px = i % E, py = (i / E) % E, pz = i / (E * E);

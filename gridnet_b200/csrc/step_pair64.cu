@@ -700,7 +700,8 @@ int launch_step_fwd_pair64(const Pair64Step &a, int act, cudaStream_t st)
     Pair64Params p{};
     p.wpk = a.packed; p.gamma = a.gamma; p.beta = a.beta;
     p.in_stats = a.in_stats; p.out_partials = a.out_partials; p.nparts = a.nparts;
-    p.y = a.out_il64; p.error_flag = a.error_flag;
+    p.y = a.out_il64;
+    p.error_flag = a.error_flag ? a.error_flag : device_status_ptr();
     p.M = a.M; p.N = a.N; p.K = a.K; p.G = a.G; p.inner = a.inner;
     p.nblocks = (a.M / 8) * (a.N / 8) * (a.K / 8);
     p.nitems = p.nblocks * a.G;

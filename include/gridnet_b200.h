@@ -77,6 +77,18 @@ GN_API int gn_version(void);
  *                   0 = chosen from the grid and batch size (default). */
 GN_API int gn_config_set(const char *key, int value);
 
+/* Kernels that fetch tiles by bulk copy wait for them with an iteration limit, so that a failed copy
+ * can never hang the GPU; a wait that gives up makes the call's results invalid. Entry points with a
+ * workspace record that in a flag inside the workspace (gn_*_error_flag_offset); entry points without
+ * one (gn_step_forward_f32, gn_step_forward_fused_f32, the slab forms, gn_gated_forward_f32,
+ * gn_step_forward_pair64_f32 with error_flag == NULL) and the workspace backward set one int per device
+ * inside the library instead. gn_device_status(clear) returns 1 if it is set on the current device, 0 if
+ * not, a negative status on a CUDA error; clear != 0 resets it. It copies the word back with a blocking
+ * copy: synchronise the streams you care about first. gn_device_status_set(v) writes the word (tests).
+ * No counterpart in the reference, whose kernels never wait. */
+GN_API int gn_device_status(int clear);
+GN_API int gn_device_status_set(int value);
+
 /* Measurement helper, on no product path and without a counterpart in the reference: launches a
  * kernel of nothing but dependent-chain-free FP32 FMAs on every SM (sink: one device float that is
  * practically never written) and returns in *fma_count (host, may be NULL) how many FMAs it executes.
@@ -200,7 +212,10 @@ GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float 
  *   - at most gn_norm_static_max_batch() (256) samples per call; a larger B returns
  *     GN_ERR_TOO_LARGE and nothing is launched;
  *   - the first call on each device looks up the array's device address (with that device
- *     current); make that first call before any stream capture begins;
+ *     current) and keeps it for the life of the process; make that first call before any stream
+ *     capture begins. The kept address belongs to the device's primary context: a process that
+ *     calls cudaDeviceReset, or makes another context current on the same device, must not use
+ *     this entry point afterwards;
  *   - all calls on a device share the array: two calls whose kernels can overlap on the
  *     GPU (different streams, no ordering between them) race on it. Calls on one stream,
  *     or otherwise ordered, are safe; nothing needs clearing between calls.

@@ -228,6 +228,36 @@ def test_outer_forward_reports_no_device_failure():
     assert not outer_forward_failed(ws, B, shape, 8)
 
 
+def test_device_failure_reports_can_be_seen():
+    """The host side of the bounded-wait contract: a set flag is what the accessors report. Nothing here makes a
+    kernel's wait run out; the flag in the workspace and the library's status word are written by hand."""
+    import gridnet_b200 as gb
+    from gridnet_b200._lib import lib
+
+    shape, B = (16, 16, 16), 4
+    w, b, s, gamma, beta = (dev(a) for a in model_params(29, shape))
+    x = dev(face_input(30, B, shape))
+    ws = gb.outer_forward_workspace(B, shape, 8, x.device)
+    gb.outer_forward(w, b, s, gamma, beta, x, 2, 3, 8, workspace=ws)
+    assert not gb.outer_forward_failed(ws, B, shape, 8)
+    off = int(lib.gn_outer_forward_error_flag_offset(B, *shape, 8))
+    ws[off:off + 4].view(torch.int32).fill_(1)  # what a kernel does when its wait gives up
+    assert gb.outer_forward_failed(ws, B, shape, 8)
+    gb.outer_forward(w, b, s, gamma, beta, x, 2, 3, 8, workspace=ws)  # the next call clears it
+    assert not gb.outer_forward_failed(ws, B, shape, 8)
+
+    # the status word of the entry points that have no workspace
+    gb.device_status(clear=True)
+    y = gb.GridnetCudaOp.apply(w, b, s, x, 2, 8, 1e-5, False, "silu")  # tuned forward, bulk tile copies
+    y2 = gb.GatedGridnetCudaOp.apply(torch.stack([w, w], 1).contiguous(), torch.stack([b, b]).contiguous(), x, 2, 8, "tanh")
+    assert torch.isfinite(y).all() and torch.isfinite(y2).all()
+    assert gb.device_status(clear=False) is False
+    assert lib.gn_device_status_set(1) == 0
+    assert gb.device_status(clear=False) is True  # not cleared by reading with clear=False
+    assert gb.device_status(clear=True) is True
+    assert gb.device_status(clear=True) is False
+
+
 @pytest.mark.parametrize("name,shape,B,bs,inner", [("C3", (128, 128, 128), 16, 8, 2), ("C4", (64, 64, 64), 128, 4, 8)])
 def test_full_size_step_gradients(name, shape, B, bs, inner):
     """One outer step of the forward + backward configurations on their full grids (C4 at its full batch,

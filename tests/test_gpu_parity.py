@@ -288,6 +288,28 @@ def test_grad_equivalence_gated(shape, inner_iters, block_size):
         assert err < 1e-9 * (1 + np.abs(r).max()), name
 
 
+@pytest.mark.parametrize("block_size", [8, 4])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_gated_gradients_with_zero_inner_iterations(block_size, dtype):
+    """inner_iters = 0 is the identity: grad_x = grad_y exactly (every cell, also the ones other threads own),
+    parameter gradients zero. Checked repeatedly, since the fault this guards against was a race."""
+    _, Gated = ops()
+    shape = (16, 16, 24)
+    w, b, x = rng_inputs(19, 3, shape, gated=True, dtype=dtype)
+    gy = np.random.default_rng(20).standard_normal(x.shape).astype(dtype)
+    want = orc.gated_backward(w.astype(np.float64), b.astype(np.float64), x.astype(np.float64), gy.astype(np.float64), 0,
+                              block_size, "tanh")
+    for _ in range(5):
+        tw, tb, tx = (dev(a).requires_grad_(True) for a in (w, b, x))
+        out = Gated.apply(tw, tb, tx, 0, block_size, "tanh")
+        assert torch.equal(out, tx)
+        gw, gb, gx = torch.autograd.grad(out, (tw, tb, tx), dev(gy))
+        assert torch.equal(gx, dev(gy))
+        assert not gw.any() and not gb.any()
+        for g, r in zip((gw, gb, gx), want):
+            assert np.array_equal(g.cpu().numpy().astype(np.float64), r)
+
+
 def test_golden_gated_vectors():
     _, Gated = ops()
     z = np.load(os.path.join(GOLDEN, "gated.npz"))

@@ -54,6 +54,22 @@ def test_static_scratch_norm_matches_workspace_norm_twice():
         assert torch.allclose(got, ref, rtol=1e-4, atol=1e-5)
 
 
+def test_static_scratch_norm_with_several_slices_per_sample():
+    """Grids of 16384 positions and more are summed in several slices per sample, so the [sample][slice] layout
+    inside the built-in scratch is in use; two calls in a row, bit-for-bit against the workspace entry point."""
+    from gridnet_b200._lib import lib
+
+    g = torch.Generator().manual_seed(11)
+    shape = (32, 32, 64)  # 65536 positions
+    gamma = (1 + 0.2 * torch.randn(shape, generator=g)).cuda()
+    beta = (0.3 * torch.randn(shape, generator=g)).cuda()
+    for B in (5, 9):
+        x = (2.0 * torch.randn(B, *shape, generator=g) + 0.7).cuda()
+        got, want = _both(lib, x, gamma, beta)
+        assert torch.equal(got, want)
+        assert torch.allclose(got, torch.nn.functional.layer_norm(x, shape, gamma, beta, 1e-5), rtol=1e-4, atol=1e-5)
+
+
 def test_static_scratch_norm_limits():
     from gridnet_b200._lib import lib
 

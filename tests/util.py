@@ -29,7 +29,7 @@ def rng_inputs(seed, B, shape, gated=False, dtype=np.float32, unit_scale=False):
     return w, b, s, x
 
 
-def assert_close(ours, ref64, ref32=None, what="", rtol=RTOL, atol=ATOL):
+def assert_close(ours, ref64, ref32=None, what="", rtol=RTOL, atol=ATOL, noise_factor=2.0):
     """Elementwise 1e-4 relative / 1e-5 absolute against the float64 oracle.
 
     Deep inner loops amplify float32 rounding noise, and gradients that are sums with
@@ -37,9 +37,10 @@ def assert_close(ours, ref64, ref32=None, what="", rtol=RTOL, atol=ATOL):
     the float32 ORACLE itself then shows errors against float64 of the size of our miss
     (measured for the reference's own float32 path at 8 and more inner iterations). Only
     when ``ref32`` is given, elements outside the bar are accepted if our worst error is at
-    most 3x the float32 oracle's worst error on the same tensor, at most 0.1 % of the
-    elements (plus 3x the oracle's own share) are outside, and the worst error stays below
-    3e-4 of max|ref|."""
+    most ``noise_factor`` (2) times the float32 oracle's worst error on the same tensor, at most
+    0.1 % of the elements (plus that factor times the oracle's own share) are outside, and the
+    worst error stays below 3e-4 of max|ref|. A test that needs a larger factor passes it and
+    says why."""
     ours = np.asarray(ours, dtype=np.float64)
     ref64 = np.asarray(ref64, dtype=np.float64)
     assert ours.shape == ref64.shape, (what, ours.shape, ref64.shape)
@@ -54,7 +55,8 @@ def assert_close(ours, ref64, ref32=None, what="", rtol=RTOL, atol=ATOL):
         noise = np.abs(np.asarray(ref32, dtype=np.float64) - ref64)
         bad32 = noise > tol
         scale = np.abs(ref64).max() + 1e-30
-        if err.max() <= 3 * noise.max() and bad.mean() <= 3 * bad32.mean() + 1e-3 and err.max() / scale < 3e-4:
+        if (err.max() <= noise_factor * noise.max() and bad.mean() <= noise_factor * bad32.mean() + 1e-3
+                and err.max() / scale < 3e-4):
             return
         detail = (f" [float32 oracle: {int(bad32.sum())} outside, worst {noise.max():.3e};"
                   f" ours worst {err.max():.3e}, max|ref| {scale:.3e}]")
