@@ -348,14 +348,13 @@ def bench_c2(ctx: Ctx):
         from gridnet_b200.backend_cuda import pair64_interleave, pair64_pack_weights, pair64_step
 
         kernel_name = "step_fwd_pair64<silu, fuse_in, stats_out>"
-        packed = pair64_pack_weights(w, b, s)
+        packed = pair64_pack_weights(w, b, s, gamma, beta)
         xi = [pair64_interleave(x) for x in xs]
         yi = [torch.empty_like(x) for x in xi]
         flag = torch.zeros(1, dtype=torch.int32, device=device)
 
         def kernel(i):
-            pair64_step(packed, xi[i % NSETS], yi[(i + 1) % NSETS], BATCH, GRID, INNER, ACT, gamma, beta, stats,
-                        partials, flag)
+            pair64_step(packed, xi[i % NSETS], yi[(i + 1) % NSETS], BATCH, GRID, INNER, ACT, stats, partials, flag)
     else:
         kernel_name = "step_fwd_fast8<silu, fuse_in, stats_out>"
 

@@ -50,10 +50,10 @@ SIGNATURES = {
     "gn_probe_fp32_fma": (c_int, [_P, c_int, _P, _P]),
     "gn_pair64_supported": (c_int, [c_int] * 5),
     "gn_pair64_packed_weight_bytes": (c_size_t, [c_int] * 3),
-    "gn_pair64_pack_weights_f32": (c_int, [_P] * 4 + [c_int] * 3 + [_P]),
+    "gn_pair64_pack_weights_f32": (c_int, [_P] * 6 + [c_int] * 3 + [_P]),
     "gn_pair64_interleave_f32": (c_int, [_P] * 2 + _geom + [_P]),
     "gn_pair64_deinterleave_f32": (c_int, [_P] * 5 + _geom + [_P]),
-    "gn_step_forward_pair64_f32": (c_int, [_P] * 7 + [c_int] + _geom + [c_int, c_int, _P, _P]),
+    "gn_step_forward_pair64_f32": (c_int, [_P] * 5 + [c_int] + _geom + [c_int, c_int, _P, _P]),
     "gn_step_forward_slab_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P]),
     "gn_step_forward_slab_faces_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P, _P, _P]),
     "gn_slab_unpack_faces_f32": (c_int, [_P] * 3 + _geom + [c_int, c_int, _P]),

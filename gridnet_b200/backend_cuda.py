@@ -286,10 +286,12 @@ def _il64_groups(batch: int) -> int:
 
 
 @torch.no_grad()
-def pair64_pack_weights(weight, bias, residual_scale) -> torch.Tensor:
-    """weight [27,M,N,K], bias, residual_scale [M,N,K] (float32, M, N, K multiples of 8) -> the parameters in
-    the order the large-batch step kernel reads them (one flat float32 tensor)."""
+def pair64_pack_weights(weight, bias, residual_scale, norm_weight=None, norm_bias=None) -> torch.Tensor:
+    """weight [27,M,N,K], bias, residual_scale [M,N,K] (float32, M, N, K multiples of 8) and, if steps are to
+    normalise their input on load, the whole-grid norm's weight and bias [M,N,K] -> the parameters in the order
+    the large-batch step kernel reads them (one flat float32 tensor)."""
     _require_f32_cuda(weight=weight, bias=bias, residual_scale=residual_scale)
+    ptr = lambda t: None if t is None else t.data_ptr()
     M, N, K = bias.shape
     nbytes = int(lib.gn_pair64_packed_weight_bytes(M, N, K))
     if nbytes == 0:
@@ -297,7 +299,8 @@ def pair64_pack_weights(weight, bias, residual_scale) -> torch.Tensor:
     packed = torch.empty(nbytes // 4, dtype=torch.float32, device=weight.device)
     with torch.cuda.device(weight.device):
         check(lib.gn_pair64_pack_weights_f32(weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(),
-                                             packed.data_ptr(), M, N, K, torch.cuda.current_stream().cuda_stream))
+                                             ptr(norm_weight), ptr(norm_bias), packed.data_ptr(), M, N, K,
+                                             torch.cuda.current_stream().cuda_stream))
     return packed
 
 
@@ -334,15 +337,16 @@ def pair64_deinterleave(x_il64, batch: int, shape, mean_rstd=None, norm_weight=N
 
 @torch.no_grad()
 def pair64_step(packed, x_il64, y_il64, batch: int, shape, inner_iters: int, activation: str = "silu",
-                norm_weight=None, norm_bias=None, in_mean_rstd=None, out_partials=None, error_flag=None) -> torch.Tensor:
+                in_mean_rstd=None, out_partials=None, error_flag=None) -> torch.Tensor:
     """One step of the large-batch kernel on interleaved activations (``gn_step_forward_pair64_f32``); the
-    optional arguments have the meaning they have in :func:`fused_step`, with ``64 * ceil(B/64)`` rows."""
+    optional arguments have the meaning they have in :func:`fused_step`, with ``64 * ceil(B/64)`` rows (the
+    norm's weight and bias that ``in_mean_rstd`` goes with are the ones given to :func:`pair64_pack_weights`)."""
     M, N, K = shape
     ptr = lambda t: None if t is None else t.data_ptr()
     nparts = 0 if out_partials is None else int(out_partials.shape[1])
     with torch.cuda.device(x_il64.device):
-        check(lib.gn_step_forward_pair64_f32(packed.data_ptr(), x_il64.data_ptr(), y_il64.data_ptr(), ptr(norm_weight),
-                                             ptr(norm_bias), ptr(in_mean_rstd), ptr(out_partials), nparts, int(batch),
+        check(lib.gn_step_forward_pair64_f32(packed.data_ptr(), x_il64.data_ptr(), y_il64.data_ptr(),
+                                             ptr(in_mean_rstd), ptr(out_partials), nparts, int(batch),
                                              M, N, K, int(inner_iters), activation_id(activation), ptr(error_flag),
                                              torch.cuda.current_stream().cuda_stream))
     return y_il64

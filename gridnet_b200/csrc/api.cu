@@ -625,14 +625,15 @@ GN_API size_t gn_pair64_packed_weight_bytes(int M, int N, int K)
     return sizeof(float) * pair64_packed_floats(M, N, K);
 }
 
-GN_API int gn_pair64_pack_weights_f32(const float *w, const float *b, const float *s, float *packed, int M, int N, int K,
-                                      void *stream)
+GN_API int gn_pair64_pack_weights_f32(const float *w, const float *b, const float *s, const float *gamma,
+                                      const float *beta, float *packed, int M, int N, int K, void *stream)
 {
     if (M <= 0 || N <= 0 || K <= 0) return GN_ERR_BAD_SHAPE;
     if (M % 8 || N % 8 || K % 8) return GN_ERR_BAD_BLOCK;
     if (!w || !b || !s || !packed) return GN_ERR_NULL_POINTER;
+    if ((gamma == nullptr) != (beta == nullptr)) return GN_ERR_NULL_POINTER;
     if (reinterpret_cast<uintptr_t>(packed) % 16) return GN_ERR_UNSUPPORTED;
-    return launch_pair64_pack(w, b, s, packed, M, N, K, (cudaStream_t)stream);
+    return launch_pair64_pack(w, b, s, gamma, beta, packed, M, N, K, (cudaStream_t)stream);
 }
 
 GN_API int gn_pair64_interleave_f32(const float *x, float *x_il64, int B, int M, int N, int K, void *stream)
@@ -654,8 +655,8 @@ GN_API int gn_pair64_deinterleave_f32(const float *y_il64, const float *mean_rst
                             (long long)M * N * K, (cudaStream_t)stream);
 }
 
-GN_API int gn_step_forward_pair64_f32(const float *packed, const float *x_il64, float *y_il64, const float *gamma,
-                                      const float *beta, const float *in_mean_rstd, double *out_partials,
+GN_API int gn_step_forward_pair64_f32(const float *packed, const float *x_il64, float *y_il64,
+                                      const float *in_mean_rstd, double *out_partials,
                                       int partials_per_sample, int B, int M, int N, int K, int inner, int act,
                                       int *error_flag, void *stream)
 {
@@ -663,7 +664,6 @@ GN_API int gn_step_forward_pair64_f32(const float *packed, const float *x_il64, 
     if (rc != GN_OK) return rc;
     if (B == 0) return GN_OK;
     if (!packed || !x_il64 || !y_il64) return GN_ERR_NULL_POINTER;
-    if (in_mean_rstd && (!gamma || !beta)) return GN_ERR_NULL_POINTER;
     if (!pair64_applicable(M, N, K, 8, inner)) return GN_ERR_UNSUPPORTED;
     const int nblocks = (M / 8) * (N / 8) * (K / 8);
     if (out_partials && partials_per_sample < nblocks * 4) return GN_ERR_BAD_SHAPE;
@@ -673,7 +673,7 @@ GN_API int gn_step_forward_pair64_f32(const float *packed, const float *x_il64, 
         (out_partials && reinterpret_cast<uintptr_t>(out_partials) % 16))
         return GN_ERR_UNSUPPORTED;
     Pair64Step a{};
-    a.packed = packed; a.gamma = gamma; a.beta = beta;
+    a.packed = packed;
     a.in_il64 = x_il64; a.out_il64 = y_il64;
     a.in_stats = reinterpret_cast<const float2 *>(in_mean_rstd);
     a.out_partials = reinterpret_cast<double2 *>(out_partials);
@@ -729,13 +729,13 @@ GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, 
             record_cuda_error(e, "cudaMemsetAsync");
             return GN_ERR_CUDA;
         }
-        rc = launch_pair64_pack(w, b, s, ws.packed, M, N, K, st);
+        rc = launch_pair64_pack(w, b, s, gamma, beta, ws.packed, M, N, K, st);
         if (rc != GN_OK) return rc;
         rc = launch_to_il64(x, ws.buf[0], B, G, P, st);
         if (rc != GN_OK) return rc;
         for (int o = 0; o < outer; ++o) {
             Pair64Step a{};
-            a.packed = ws.packed; a.gamma = gamma; a.beta = beta;
+            a.packed = ws.packed;
             a.in_il64 = ws.buf[o & 1];
             a.out_il64 = ws.buf[(o + 1) & 1];
             a.in_stats = o > 0 ? ws.stats : nullptr;

@@ -77,8 +77,7 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
 // ---- step_pair64.cu ("lanes = samples" kernel for large batches; activations in the IL64 layout
 // [group][z][y][x][64 samples], weights pre-packed per block half)
 struct Pair64Step {
-    const float *packed;      // pair64_packed_floats(M, N, K) floats from launch_pair64_pack
-    const float *gamma, *beta;
+    const float *packed;      // pair64_packed_floats(M, N, K) floats from launch_pair64_pack (holds gamma, beta too)
     const float *in_il64;
     float *out_il64;
     const float2 *in_stats;   // [G*64] or nullptr
@@ -89,7 +88,8 @@ struct Pair64Step {
 };
 bool pair64_applicable(int M, int N, int K, int block, int inner);
 size_t pair64_packed_floats(int M, int N, int K);
-int launch_pair64_pack(const float *w, const float *b, const float *s, float *packed, int M, int N, int K, cudaStream_t st);
+int launch_pair64_pack(const float *w, const float *b, const float *s, const float *gamma, const float *beta, float *packed,
+                       int M, int N, int K, cudaStream_t st);
 int launch_step_fwd_pair64(const Pair64Step &a, int act, cudaStream_t st);
 int launch_to_il64(const float *x, float *il, int B, int G, long long P, cudaStream_t st);
 // stats == nullptr: plain layout conversion; otherwise y = (v - mean) * rstd * gamma + beta

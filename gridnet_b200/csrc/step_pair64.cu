@@ -59,10 +59,15 @@ constexpr int TILE_BYTES = TILE_F * 4;       // 153600
 // alternate buffer of the exchange plane: alt[x column][y row][64 samples]
 constexpr int AXS = 10 * NS;
 constexpr int PLANE_BYTES = 100 * NS * 4;    // 25600
-constexpr int WPK_W = 6912;                  // packed weights of half a block
-constexpr int WPK_F = WPK_W + 512;           // + bias[256] + scale[256]
+// packed parameters of half a block: 8 chunks (x half h, output column xo), each 3 x-taps x 8 units x 36
+// weights, then 8 units x 4 biases, then 8 units x 4 scales; a chunk is fetched by one bulk copy
+constexpr int WCH_W = 864, WCH_F = WCH_W + 64, WCH_BYTES = WCH_F * 4;  // 3712 bytes
+constexpr int WPK_F = 8 * WCH_F;             // 7424
 constexpr int WPK_BYTES = WPK_F * 4;         // 29696
 constexpr int GB_CELLS = 600;
+// after the chunks: (gamma, beta) of the 600 tile cells of the block half, zero outside the grid
+constexpr int GB_BYTES = GB_CELLS * 8;       // 4800
+constexpr int PK_F = WPK_F + 2 * GB_CELLS;   // floats per block half in the packed buffer: 8624
 constexpr unsigned kSpinLimit = 1u << 20;    // bounded waits on mbarriers
 
 constexpr int OFF_TILE = 0;
@@ -71,14 +76,13 @@ constexpr int OFF_W = OFF_ALT + PLANE_BYTES;
 constexpr int OFF_GB = OFF_W + WPK_BYTES;
 constexpr int OFF_RED = OFF_GB + GB_CELLS * 8;
 constexpr int OFF_BAR = OFF_RED + 16 * NS * 16;  // 16 contributors x 64 samples x double2
-constexpr int SMEM_BYTES = OFF_BAR + 192;
+constexpr int SMEM_BYTES = OFF_BAR + 256;
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of one SM");
 }  // namespace pair64
 
 struct Pair64Params {
-    const float *wpk;            // [blocks][2][WPK_F] from pair64_pack_k
-    const float *gamma, *beta;   // [M,N,K] (FUSE_IN)
-    const float2 *in_stats;      // [G*64] (mean, rstd) of the input (FUSE_IN)
+    const float *wpk;            // [blocks][2][PK_F] from pair64_pack_k
+        const float2 *in_stats;      // [G*64] (mean, rstd) of the input (FUSE_IN)
     double2 *out_partials;       // [G*64][nparts]; this kernel fills slots block*4 .. block*4+3 (STATS_OUT)
     int nparts;
     float *y;                    // IL64 output
@@ -105,6 +109,48 @@ __device__ __forceinline__ void unpack2(u64 v, float &a, float &b)
 __device__ __forceinline__ void ffma2(u64 &acc, u64 a, u64 w)
 {
     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(w));
+}
+__device__ __forceinline__ u64 fmul2(u64 a, u64 b)
+{
+    u64 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 fadd2(u64 a, u64 b)
+{
+    u64 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 ffma2r(u64 a, u64 b, u64 c)
+{
+    u64 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// cen + sc * act(h) for a pair of samples. silu is done on the pair: the multiplies and adds are packed, only the
+// two MUFU operations per value are scalar. 2^t overflows to +inf for very negative h; the reciprocal is then 0
+// and h * 0 = -0, the right limit, so no clamp is needed.
+template <int ACT>
+__device__ __forceinline__ u64 act_residual2(u64 h, float sc, u64 cen)
+{
+    const u64 sc2 = pack2(sc, sc);
+    if (ACT == GN_ACT_SILU) {
+        const u64 t = fmul2(h, pack2(-1.4426950408889634f, -1.4426950408889634f));
+        float t0, t1, e0, e1, r0, r1;
+        unpack2(t, t0, t1);
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(t0));
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(t1));
+        const u64 d = fadd2(pack2(e0, e1), pack2(1.0f, 1.0f));
+        float d0, d1;
+        unpack2(d, d0, d1);
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(d0));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(d1));
+        return ffma2r(fmul2(h, pack2(r0, r1)), sc2, cen);
+    }
+    float h0, h1;
+    unpack2(h, h0, h1);
+    return ffma2r(pack2(Act<ACT, float>::fwd(h0), Act<ACT, float>::fwd(h1)), sc2, cen);
 }
 __device__ __forceinline__ Quad lds_quad(const float *p)
 {
@@ -166,10 +212,11 @@ __device__ __forceinline__ void bulk_load_1d(unsigned dst, const void *src, unsi
 
 // ---- the kernel ----------------------------------------------------------------------------
 // Barriers in shared memory (8 bytes each, from OFF_BAR): C[0..4] column pair (j, 9-j) of the tile has
-// landed; W weights have landed; R1, R2, R3, R5 every warp has finished step 1 / 2 / 3 / 5 (and every
-// tile write it does before that point); D[0..4] in a work item's last iteration every warp has read
-// column pair j for the last time (pairs 0..3 in step j, pair 4 = columns 4 and 5 in step 5), so the
-// columns can be re-filled for the next item.
+// landed; W[0..3] the parameter chunks of output column xo (both x halves) have landed; R1, R2, R3, R5
+// every warp has finished step 1 / 2 / 3 / 5 (and every tile write it does before that point); D[0..4] in
+// a work item's last iteration every warp has read column pair j for the last time (pairs 0..3 in step j,
+// pair 4 = columns 4 and 5 in step 5), so the columns can be re-filled for the next item; E[0..3] likewise
+// for the parameter chunks of output column xo, last used in step xo + 2; G the (gamma, beta) table has landed.
 template <int ACT, bool FUSE_IN, bool STATS_OUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
     step_fwd_pair64(const __grid_constant__ CUtensorMap in_map, const Pair64Params p)
@@ -182,7 +229,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
     float2 *const gbt = reinterpret_cast<float2 *>(smem + OFF_GB);
     double2 *const red = reinterpret_cast<double2 *>(smem + OFF_RED);
     const unsigned bar0 = smem_u32(smem + OFF_BAR);
-    const unsigned bar_c = bar0, bar_w = bar0 + 48, bar_r = bar0 + 56, bar_d = bar0 + 88;
+    const unsigned bar_c = bar0, bar_w = bar0 + 40, bar_r = bar0 + 72, bar_d = bar0 + 104, bar_e = bar0 + 144,
+                   bar_g = bar0 + 176;
 
     const int tid = threadIdx.x, lane = tid & 31, u = tid >> 5;
     const int h = lane >> 4, li = lane & 15;  // x half (0: columns 0..5 upwards, 1: columns 9..4 downwards), sample quad
@@ -194,7 +242,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
 
     if (tid == 0) {
         for (int i = 0; i < 5; ++i) mbar_init(bar_c + 8 * i, 1);
-        mbar_init(bar_w, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(bar_w + 8 * i, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(bar_e + 8 * i, 8);
+        mbar_init(bar_g, 1);
         for (int i = 0; i < 4; ++i) mbar_init(bar_r + 8 * i, 8);
         for (int i = 0; i < 5; ++i) mbar_init(bar_d + 8 * i, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -214,12 +264,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
     const int pez = partner ? 0 : 5;
     const unsigned rem_tile = map_to_rank(smem_u32(tile + pez * ZS), partner), rem_alt = map_to_rank(smem_u32(alt), partner);
     const int col0 = h ? 9 : 0;
-    const float *const wp = wsm + (h * 96 + u) * 36;
-    const float *const bp = wsm + WPK_W + (h * 32 + u) * 4;
+    const float *const wp = wsm + h * 4 * WCH_F + u * 36;          // + xo * WCH_F + c * 288 + 4 * tap
+    const float *const bp = wsm + h * 4 * WCH_F + WCH_W + u * 4;   // + xo * WCH_F: biases; 32 floats further: scales
 
-    unsigned ph_w = 0, ph1 = 0, ph2 = 0, ph3 = 0, ph5 = 0;
+    unsigned ph_w = 0, ph_g = 0, ph1 = 0, ph2 = 0, ph3 = 0, ph5 = 0;
     bool failed = false;
     auto wait_bar = [&](unsigned bar, unsigned &ph) {
+#ifdef GN_PAIR64_NOSYNC  // timing experiment only (racy): skip the waits on the R barriers
+        if (bar >= bar_r && bar < bar_d) {
+            ph ^= 1;
+            return;
+        }
+#endif
         if (!mbar_wait_bounded(bar, ph, kSpinLimit)) failed = true;
         ph ^= 1;
     };
@@ -246,43 +302,48 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
         tma_load_5d(smem_u32(tile + j * XS), &in_map, bar_c + 8 * j, 0, o.x + j, o.y, o.z, o.g);
         tma_load_5d(smem_u32(tile + (9 - j) * XS), &in_map, bar_c + 8 * j, 0, o.x + 9 - j, o.y, o.z, o.g);
     };
-    auto issue_weights = [&](int brick) {
+    // thread 0: fetch the parameter chunks of output column xo (one per x half) of a block
+    auto issue_weights = [&](int brick, int xo) {
+        const float *src = p.wpk + ((size_t)brick * 2 + rank) * PK_F;
         fence_proxy_async();
-        mbar_expect_tx(bar_w, WPK_BYTES);
-        bulk_load_1d(smem_u32(wsm), p.wpk + ((size_t)brick * 2 + rank) * WPK_F, WPK_BYTES, bar_w);
+        mbar_expect_tx(bar_w + 8 * xo, 2 * WCH_BYTES);
+        bulk_load_1d(smem_u32(wsm + xo * WCH_F), src + xo * WCH_F, WCH_BYTES, bar_w + 8 * xo);
+        bulk_load_1d(smem_u32(wsm + (4 + xo) * WCH_F), src + (4 + xo) * WCH_F, WCH_BYTES, bar_w + 8 * xo);
     };
 
-    // (gamma, beta) of the tile cells of a block half, zero outside the grid (there the zero fill must stay zero)
-    auto build_gb_table = [&](int brick) {
-        const int bx = brick % nbx, by = (brick / nbx) % nby, bz = brick / nbx / nby;
-        for (int c = tid; c < GB_CELLS; c += THREADS) {
-            const int cy = c % 10, cz = (c / 10) % 6, cx = c / 60;
-            const int gz = bz * 8 + 4 * (int)rank - 1 + cz, gy = by * 8 - 1 + cy, gx = bx * 8 - 1 + cx;
-            float2 gb = make_float2(0.0f, 0.0f);
-            if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < p.K) {
-                const size_t gi = ((size_t)gz * p.N + gy) * p.K + gx;
-                gb = make_float2(p.gamma[gi], p.beta[gi]);
-            }
-            gbt[c] = gb;
-        }
+    // thread 0: fetch the (gamma, beta) table of a block half
+    auto issue_gb_table = [&](int brick) {
+        fence_proxy_async();
+        mbar_expect_tx(bar_g, GB_BYTES);
+        bulk_load_1d(smem_u32(gbt), p.wpk + ((size_t)brick * 2 + rank) * PK_F + WPK_F, GB_BYTES, bar_g);
     };
-    if (FUSE_IN && it0 < it1) build_gb_table(it0 / p.G);
-    __syncthreads();  // barriers initialised, table complete
+    __syncthreads();  // barriers initialised
 
     if (tid == 0 && it0 < it1) {
         const TileOrigin o = tile_origin(it0);
         for (int j = 0; j < 5; ++j) issue_cols(o, j);
-        issue_weights(it0 / p.G);
+        for (int xo = 0; xo < 4; ++xo) issue_weights(it0 / p.G, xo);
+        if (FUSE_IN) issue_gb_table(it0 / p.G);
     }
 
+#ifdef GN_PAIR64_TRACE
+    long long *trace = reinterpret_cast<long long *>(p.error_flag);
+    int tr = 0;
+#define TRACE_() do { if (blockIdx.x == 0 && tid == 0 && tr < 120) trace[tr++] = clock64(); } while (0)
+#else
+#define TRACE_() do { } while (0)
+#endif
     int cur_brick = -1;
     for (int item = it0; item < it1; ++item) {
+        TRACE_();
         const int brick = item / p.G, g = item - brick * p.G;
         const int bx = brick % nbx, by = (brick / nbx) % nby, bz = brick / nbx / nby;
         const bool new_brick = brick != cur_brick;
         cur_brick = brick;
         const bool has_next = item + 1 < it1;
         unsigned ph_item = (unsigned)(item - it0) & 1u;  // C and D barriers complete once per item
+        const int next_brick = has_next ? (item + 1) / p.G : brick;
+        const bool next_is_new_brick = next_brick != brick;
         float na[4], nb[4];  // normalise: v * na + nb, then * gamma + beta
         if (FUSE_IN) {
 #pragma unroll
@@ -292,7 +353,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                 nb[q] = -mr.x * mr.y;
             }
         }
-        // normalise the columns in place as they land
+        if (FUSE_IN && new_brick) wait_bar(bar_g, ph_g);
+        // normalise the columns in place as they land: 16 lanes per cell, 16 cells at a time, four rounds per column
         for (int j = 0; j < 5; ++j) {
             unsigned phc = ph_item;
             wait_bar(bar_c + 8 * j, phc);
@@ -300,23 +362,44 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     const int cx = half ? 9 - j : j;
-                    float4 *cp = reinterpret_cast<float4 *>(tile + cx * XS + 4 * li);
-                    const float2 *gp = gbt + cx * 60;
-                    for (int r = tid >> 4; r < 60; r += THREADS / 16) {
-                        float4 v = cp[r * (NS / 4)];
-                        const float2 gb = gp[r];
-                        v.x = fmaf(fmaf(v.x, na[0], nb[0]), gb.x, gb.y);
-                        v.y = fmaf(fmaf(v.y, na[1], nb[1]), gb.x, gb.y);
-                        v.z = fmaf(fmaf(v.z, na[2], nb[2]), gb.x, gb.y);
-                        v.w = fmaf(fmaf(v.w, na[3], nb[3]), gb.x, gb.y);
-                        cp[r * (NS / 4)] = v;
+                    float4 *cp = reinterpret_cast<float4 *>(tile + cx * XS + 4 * li) + (tid >> 4) * (NS / 4);
+                    const float2 *gp = gbt + cx * 60 + (tid >> 4);
+                    const bool tail = (tid >> 4) < 12;  // rows 48 .. 59 of the column
+                    float4 v[4];
+                    float2 gb[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (k < 3 || tail) {
+                            v[k] = cp[k * 16 * (NS / 4)];
+                            gb[k] = gp[k * 16];
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (k < 3 || tail) {
+                            v[k].x = fmaf(fmaf(v[k].x, na[0], nb[0]), gb[k].x, gb[k].y);
+                            v[k].y = fmaf(fmaf(v[k].y, na[1], nb[1]), gb[k].x, gb[k].y);
+                            v[k].z = fmaf(fmaf(v[k].z, na[2], nb[2]), gb[k].x, gb[k].y);
+                            v[k].w = fmaf(fmaf(v[k].w, na[3], nb[3]), gb[k].x, gb[k].y);
+                            cp[k * 16 * (NS / 4)] = v[k];
+                        }
                     }
                 }
             }
         }
-        if (new_brick) wait_bar(bar_w, ph_w);
+        if (new_brick) {
+            for (int xo = 0; xo < 4; ++xo) {
+                unsigned phw = ph_w;
+                wait_bar(bar_w + 8 * xo, phw);
+            }
+            ph_w ^= 1;
+        }
+        TRACE_();
         __syncthreads();
+        TRACE_();
+        if (FUSE_IN && tid == 0 && next_is_new_brick) issue_gb_table(next_brick);  // the table is not read again in this item
         cluster_wait();  // the partner has finished the previous item: its exchange buffers may be written
+        TRACE_();
         // The rim of the exchange plane (stale halo cells) also goes to the plane's alternate buffer, which is first
         // read in iteration 1: the arrive / wait chain of iteration 0 orders these stores before those loads.
         for (int k = tid >> 4; k < 36; k += THREADS / 16) {
@@ -373,10 +456,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                     // this warp is done with column pair j of the item's tile (columns 4 and 5: after step 5)
                     if (j <= 3) arrive(bar_d + 8 * j);
                     if (j == 5) arrive(bar_d + 32);
+                    // ... and with the parameters of output column j - 3 (last used in step j - 1)
+                    if (j >= 3) arrive(bar_e + 8 * (j - 3));
                     if (tid == 0 && j >= 1 && j <= 4 && has_next) {
                         unsigned phd = ph_item;
                         wait_bar(bar_d + 8 * (j - 1), phd);
                         issue_cols(nxt, j - 1);
+                    }
+                    if (tid == 0 && j >= 4 && next_is_new_brick) {
+                        unsigned phe = ph_item;
+                        wait_bar(bar_e + 8 * (j - 4), phe);
+                        issue_weights(next_brick, j - 4);
                     }
                 }
                 if (j >= 1 && j <= 4) {
@@ -384,7 +474,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                     for (int jn = 0; jn < 4; ++jn) cen[j - 1][jn] = col[1 + (jn >> 1)][1 + (jn & 1)];
                 }
                 if (j <= 3) {
-                    const float4 b4 = *reinterpret_cast<const float4 *>(bp + j * 32);
+                    const float4 b4 = *reinterpret_cast<const float4 *>(bp + j * WCH_F);
                     acc[j][0].lo = acc[j][0].hi = pack2(b4.x, b4.x);
                     acc[j][1].lo = acc[j][1].hi = pack2(b4.y, b4.y);
                     acc[j][2].lo = acc[j][2].hi = pack2(b4.z, b4.z);
@@ -398,7 +488,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                     for (int c = 0; c < 3; ++c) {
                         const int xo = j - c;
                         if (xo < 0 || xo > 3) continue;
-                        const float4 w4 = *reinterpret_cast<const float4 *>(wp + (xo * 3 + c) * 288 + 4 * ab);
+                        const float4 w4 = *reinterpret_cast<const float4 *>(wp + xo * WCH_F + c * 288 + 4 * ab);
                         const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                         for (int jn = 0; jn < 4; ++jn) {
@@ -412,19 +502,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                 float4 o[4];
                 if (j >= 2) {
                     const int xo = j - 2;
-                    const float4 s4 = *reinterpret_cast<const float4 *>(bp + 256 + xo * 32);
+                    const float4 s4 = *reinterpret_cast<const float4 *>(bp + 32 + xo * WCH_F);
                     const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
                     for (int jn = 0; jn < 4; ++jn) {
-                        float a0, a1, a2, a3, c0, c1, c2, c3;
-                        unpack2(acc[xo][jn].lo, a0, a1);
-                        unpack2(acc[xo][jn].hi, a2, a3);
-                        unpack2(cen[xo][jn].lo, c0, c1);
-                        unpack2(cen[xo][jn].hi, c2, c3);
-                        o[jn].x = fmaf(Act<ACT, float>::fwd(a0), sv[jn], c0);
-                        o[jn].y = fmaf(Act<ACT, float>::fwd(a1), sv[jn], c1);
-                        o[jn].z = fmaf(Act<ACT, float>::fwd(a2), sv[jn], c2);
-                        o[jn].w = fmaf(Act<ACT, float>::fwd(a3), sv[jn], c3);
+                        const u64 lo = act_residual2<ACT>(acc[xo][jn].lo, sv[jn], cen[xo][jn].lo);
+                        const u64 hi = act_residual2<ACT>(acc[xo][jn].hi, sv[jn], cen[xo][jn].hi);
+                        unpack2(lo, o[jn].x, o[jn].y);
+                        unpack2(hi, o[jn].z, o[jn].w);
                     }
                     if (LAST) {
 #pragma unroll
@@ -473,12 +558,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                 }
             }
         };
-        for (int t = 0; t + 1 < p.inner; ++t) iteration(std::false_type{}, t);
+        for (int t = 0; t + 1 < p.inner; ++t) {
+            iteration(std::false_type{}, t);
+            TRACE_();
+        }
         iteration(std::true_type{}, p.inner - 1);
+        TRACE_();
         if (tid == 0 && has_next) {
             unsigned phd = ph_item;
             wait_bar(bar_d + 32, phd);
             issue_cols(nxt, 4);
+        }
+        // the parameters of output columns 2 and 3 are last used in steps 4 and 5
+        arrive(bar_e + 24);
+        if (tid == 0 && next_is_new_brick) {
+            for (int xo = 2; xo < 4; ++xo) {
+                unsigned phe = ph_item;
+                wait_bar(bar_e + 8 * xo, phe);
+                issue_weights(next_brick, xo);
+            }
         }
 
         if (STATS_OUT) {
@@ -487,10 +585,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
             for (int q = 0; q < 4; ++q) red[(u * 2 + h) * NS + 4 * li + q] = make_double2((double)ssum[q], (double)ssq[q]);
         }
         cluster_arrive_relaxed();  // this CTA no longer reads its exchange buffers of this item
-        const bool next_is_new_brick = has_next && (item + 1) / p.G != brick;
-        if (FUSE_IN && next_is_new_brick) build_gb_table((item + 1) / p.G);  // not read before the next item's normalisation
-        __syncthreads();  // every read of the weights is done; the partials and the table are in place
-        if (tid == 0 && next_is_new_brick) issue_weights((item + 1) / p.G);
+        TRACE_();
+        __syncthreads();  // the partials are in place
+        TRACE_();
         if (STATS_OUT && tid < NS) {
             double s = 0.0, q = 0.0;
 #pragma unroll
@@ -505,19 +602,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
         }
     }
     cluster_wait();  // no CTA leaves while its partner may still store into its shared memory
+#ifndef GN_PAIR64_TRACE
     if (failed && p.error_flag) *p.error_flag = 1;
+#endif
 }
 
 // ---- weight packing ---------------------------------------------------------------------------
 // One CTA per block: the block's 27 x 512 weights, biases and scales are staged in shared memory with
 // coalesced reads and written out in the order the step kernel reads them:
-//   [block][rank][ (h, xo, c, unit) x 36 floats ((a * 3 + b) * 4 + jn) | bias (h, xo, unit, jn) | scale (same) ]
+//   [block][rank][chunk (h, xo)][ (c, unit) x 36 floats ((a * 3 + b) * 4 + jn) | bias (unit, jn) | scale (unit, jn) ]
 // rank = z half of the block, h = x half, xo = output column counted from the half's outer end,
 // c = x tap in sweep order (h = 1 sweeps downwards, so its taps are mirrored), unit = (zp, yp) patch,
 // jn = (dz, dy) inside the patch, (a, b) = (z, y) tap. Tap numbering a * 9 + b * 3 + c follows
 // gridnet/backend_torch.py:283-298.
 __global__ void __launch_bounds__(256) pair64_pack_k(const float *__restrict__ w, const float *__restrict__ b,
-                                                     const float *__restrict__ s, float *__restrict__ out, int M, int N,
+                                                     const float *__restrict__ s, const float *__restrict__ gamma,
+                                                     const float *__restrict__ beta, float *__restrict__ out, int M, int N,
                                                      int K)
 {
     extern __shared__ float stage[];  // [29][512]: 27 taps, bias, scale
@@ -532,30 +632,39 @@ __global__ void __launch_bounds__(256) pair64_pack_k(const float *__restrict__ w
         stage[idx] = t < 27 ? w[(size_t)t * P + gi] : (t == 27 ? b[gi] : s[gi]);
     }
     __syncthreads();
-    float *o = out + (size_t)brick * 2 * pair64::WPK_F;
+    float *o = out + (size_t)brick * 2 * pair64::PK_F;
+    // (gamma, beta) of the 6 x 10 x 10 tile cells of each block half, in the tile's order [x][z][y]; cells outside
+    // the grid get (0, 0), which keeps the zero fill of the bulk copies at zero through the normalisation
+    for (int idx = threadIdx.x; idx < 2 * pair64::GB_CELLS; idx += 256) {
+        const int rank = idx / pair64::GB_CELLS, c = idx - rank * pair64::GB_CELLS;
+        const int cy = c % 10, cz = (c / 10) % 6, cx = c / 60;
+        const int gz = bz * 8 + 4 * rank - 1 + cz, gy = by * 8 - 1 + cy, gx = bx * 8 - 1 + cx;
+        float2 gb = make_float2(0.0f, 0.0f);
+        if (gamma && gz >= 0 && gz < M && gy >= 0 && gy < N && gx >= 0 && gx < K) {
+            const size_t gi = ((size_t)gz * N + gy) * K + gx;
+            gb = make_float2(gamma[gi], beta[gi]);
+        }
+        reinterpret_cast<float2 *>(o + rank * pair64::PK_F + pair64::WPK_F)[c] = gb;
+    }
     for (int idx = threadIdx.x; idx < 2 * pair64::WPK_F; idx += 256) {
         const int rank = idx / pair64::WPK_F, e = idx - rank * pair64::WPK_F;
-        int h, xo, un, jn, src_t, cc = 0, ab = 0;
-        if (e < pair64::WPK_W) {
-            const int grp = e / 36, k = e - grp * 36;
-            un = grp & 7;
-            const int c = (grp >> 3) % 3, hx = (grp >> 3) / 3;
-            h = hx >> 2;
-            xo = hx & 3;
-            ab = k >> 2;
-            jn = k & 3;
-            cc = h ? 2 - c : c;
-            src_t = (ab / 3) * 9 + (ab % 3) * 3 + cc;
+        const int chunk = e / pair64::WCH_F, k = e - chunk * pair64::WCH_F;  // chunk = h * 4 + xo
+        const int h = chunk >> 2, xo = chunk & 3;
+        int un, jn, src_t;
+        if (k < pair64::WCH_W) {
+            const int c = k / 288, r = k - c * 288;  // x tap in sweep order, then [unit][tap (a, b)][jn]
+            un = r / 36;
+            const int ab = (r - un * 36) >> 2;
+            jn = r & 3;
+            src_t = (ab / 3) * 9 + (ab % 3) * 3 + (h ? 2 - c : c);
         } else {
-            const int k = (e - pair64::WPK_W) & 255;
-            src_t = e - pair64::WPK_W < 256 ? 27 : 28;
-            jn = k & 3;
-            un = (k >> 2) & 7;
-            xo = (k >> 5) & 3;
-            h = k >> 7;
+            const int r = (k - pair64::WCH_W) & 31;
+            src_t = k - pair64::WCH_W < 32 ? 27 : 28;
+            un = r >> 2;
+            jn = r & 3;
         }
         const int z = 4 * rank + 2 * (un >> 2) + (jn >> 1), y = 2 * (un & 3) + (jn & 1), x = h ? 7 - xo : xo;
-        o[idx] = stage[src_t * 512 + (z * 8 + y) * 8 + x];
+        o[rank * pair64::PK_F + e] = stage[src_t * 512 + (z * 8 + y) * 8 + x];
     }
 }
 
@@ -632,7 +741,7 @@ EncodeTiledFn encode_tiled_fn()
 
 size_t pair64_packed_floats(int M, int N, int K)
 {
-    return (size_t)(M / 8) * (N / 8) * (K / 8) * 2 * pair64::WPK_F;
+    return (size_t)(M / 8) * (N / 8) * (K / 8) * 2 * pair64::PK_F;
 }
 
 bool pair64_applicable(int M, int N, int K, int block, int inner)
@@ -660,7 +769,8 @@ static int make_il64_map(CUtensorMap *map, const float *il, int M, int N, int K,
     return GN_OK;
 }
 
-int launch_pair64_pack(const float *w, const float *b, const float *s, float *packed, int M, int N, int K, cudaStream_t st)
+int launch_pair64_pack(const float *w, const float *b, const float *s, const float *gamma, const float *beta, float *packed,
+                       int M, int N, int K, cudaStream_t st)
 {
     static bool attr_set = false;
     const int smem = 29 * 512 * 4;
@@ -673,7 +783,7 @@ int launch_pair64_pack(const float *w, const float *b, const float *s, float *pa
         attr_set = true;
     }
     const int nblocks = (M / 8) * (N / 8) * (K / 8);
-    pair64_pack_k<<<nblocks, 256, smem, st>>>(w, b, s, packed, M, N, K);
+    pair64_pack_k<<<nblocks, 256, smem, st>>>(w, b, s, gamma, beta, packed, M, N, K);
     return check_launch("pair64_pack");
 }
 
@@ -698,7 +808,7 @@ int launch_step_fwd_pair64(const Pair64Step &a, int act, cudaStream_t st)
     int rc = make_il64_map(&map, a.in_il64, a.M, a.N, a.K, a.G);
     if (rc != GN_OK) return rc;
     Pair64Params p{};
-    p.wpk = a.packed; p.gamma = a.gamma; p.beta = a.beta;
+    p.wpk = a.packed;
     p.in_stats = a.in_stats; p.out_partials = a.out_partials; p.nparts = a.nparts;
     p.y = a.out_il64;
     p.error_flag = a.error_flag ? a.error_flag : device_status_ptr();
