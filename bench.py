@@ -337,7 +337,7 @@ def bench_c2(ctx: Ctx):
     failed = gb.outer_forward_failed(ws, BATCH, GRID, BLOCK)
 
     # ---------------- the dominant kernel alone (roofline)
-    nparts = gb.step_stats_partials(GRID, BLOCK)
+    nparts = int(lib.gn_pair64_stats_partials(*GRID)) if large_batch else gb.step_stats_partials(GRID, BLOCK)
     partials = torch.empty(BATCH, nparts, 2, dtype=torch.float64, device=device)
     stats = torch.empty(BATCH, 2, device=device)
     # any finite statistics do for timing: mean 0, rstd 1
@@ -610,9 +610,11 @@ def bench_train(ctx: Ctx, name: str, stash=None, microbatches=None, steps_cap: i
     G, block, inner, outer, batch, desc = TRAIN_WORKLOADS[name]
     if args.batch:
         batch = args.batch
-    stash = args.stash if stash is None else stash
-    # keep the inner iterations' intermediate results from the forward pass (memory for time)
-    previous_stash = gb.keep_forward_stash(bool(stash))
+    if stash is None and args.stash:
+        stash = True
+    # keep the inner iterations' intermediate results from the forward pass (memory for time): True / False force
+    # it, None leaves the package's default (kept whenever they fit comfortably in the free device memory)
+    previous_stash = gb.keep_forward_stash(stash)
     dist = ctx.need_group() if world > 1 else None
     if batch % world:
         raise SystemExit(f"batch {batch} does not divide over {world} ranks")
@@ -704,7 +706,10 @@ def bench_train(ctx: Ctx, name: str, stash=None, microbatches=None, steps_cap: i
                              "alone are %.0f MB, larger than the 126 MB L2"
                              % (b_loc * G ** 3 * 4 / 1e6, 2 * outer, 2 * outer * b_loc * G ** 3 * 4 / 1e6),
                        "forward_ms": t_fwd / steps, "backward_ms": t_bwd / steps, "finite": finite,
-                       "intermediate_results": "kept from the forward pass" if stash else "recomputed in the backward pass",
+                       "intermediate_results": ("kept from the forward pass" if stash else "recomputed in the backward pass"
+                                                if stash is not None else
+                                                "kept from the forward pass where they take at most a tenth of the free "
+                                                "device memory, else recomputed (package default)"),
                        "microbatches": nmb,
                        "samples_per_sec": batch / sec},
             "roofline": {"bound": "fp32", "achieved": flops / sec / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",

@@ -49,6 +49,7 @@ SIGNATURES = {
     "gn_device_status_set": (c_int, [c_int]),
     "gn_probe_fp32_fma": (c_int, [_P, c_int, _P, _P]),
     "gn_pair64_supported": (c_int, [c_int] * 5),
+    "gn_pair64_stats_partials": (c_int, [c_int] * 3),
     "gn_pair64_packed_weight_bytes": (c_size_t, [c_int] * 3),
     "gn_pair64_pack_weights_f32": (c_int, [_P] * 6 + [c_int] * 3 + [_P]),
     "gn_pair64_interleave_f32": (c_int, [_P] * 2 + _geom + [_P]),

@@ -38,18 +38,34 @@ def _assert_step_args(weight, bias, residual_scale, init_activations, block_size
     return batch_size
 
 
-_keep_forward_stash = False
+_keep_forward_stash = None  # None: decide per call from the free device memory
 
 
-def keep_forward_stash(enabled: bool) -> bool:
-    """Trade memory for time in training: when on, a :class:`GridnetCudaOp` forward that will be
-    differentiated (float32, per-block normalisation off, tuned path) also keeps every inner iteration's
-    pre-activations and intermediate activations, ``(2 * inner_iters - 1)`` extra activation tensors per
-    call, and its backward skips recomputing them (about a quarter of the backward time). Off by default:
-    the reference recomputes, and so does this package unless asked. Returns the previous setting."""
+def keep_forward_stash(enabled):
+    """Trade memory for time in training: a :class:`GridnetCudaOp` forward that will be differentiated
+    (float32, per-block normalisation off, tuned path) can also keep every inner iteration's pre-activations
+    and intermediate activations, ``(2 * inner_iters - 1)`` extra activation tensors per call, so that its
+    backward skips recomputing them (about a quarter of the backward time; same gradient bits). The reference
+    always recomputes. ``True`` / ``False`` force the choice; ``None`` (the default) keeps them whenever they
+    take at most a tenth of the device memory that is free at that moment, and recomputes otherwise, call by
+    call. Returns the previous setting."""
     global _keep_forward_stash
-    previous, _keep_forward_stash = _keep_forward_stash, bool(enabled)
+    previous, _keep_forward_stash = _keep_forward_stash, (None if enabled is None else bool(enabled))
     return previous
+
+
+def _stash_wanted(weight, init_activations, inner_iters: int, block_size: int) -> bool:
+    if _keep_forward_stash is not None:
+        return _keep_forward_stash
+    B, M, N, K = init_activations.shape
+    need = int(lib.gn_step_stash_bytes(B, M, N, K, int(inner_iters), int(block_size)))
+    if need <= 0:
+        return False
+    dev = weight.device
+    free, _ = torch.cuda.mem_get_info(dev)
+    # what torch's caching allocator holds but has not handed out counts as free too
+    free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+    return need * 10 <= free
 
 
 class GridnetCudaOp(torch.autograd.Function):
@@ -65,8 +81,8 @@ class GridnetCudaOp(torch.autograd.Function):
         ctx.cfg = (inner_iters, block_size, eps, normalize, activation)
         ctx.stash = None
         outputs = torch.empty_like(init_activations)
-        if (_keep_forward_stash and not normalize and weight.dtype == torch.float32
-                and any(ctx.needs_input_grad[:4])):
+        if (not normalize and weight.dtype == torch.float32 and any(ctx.needs_input_grad[:4])
+                and _stash_wanted(weight, init_activations, inner_iters, block_size)):
             ctx.stash = gridnet_cuda.forward_with_stash(weight, bias, residual_scale, init_activations, outputs,
                                                         inner_iters, block_size, activation)
             return outputs

@@ -619,6 +619,12 @@ GN_API int gn_pair64_supported(int M, int N, int K, int block, int inner)
     return pair64_applicable(M, N, K, block, inner) ? 1 : 0;
 }
 
+GN_API int gn_pair64_stats_partials(int M, int N, int K)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || M % 8 || N % 8 || K % 8) return 0;
+    return 2 * (M / 8) * (N / 8) * (K / 8);
+}
+
 GN_API size_t gn_pair64_packed_weight_bytes(int M, int N, int K)
 {
     if (M <= 0 || N <= 0 || K <= 0 || M % 8 || N % 8 || K % 8) return 0;
@@ -666,7 +672,7 @@ GN_API int gn_step_forward_pair64_f32(const float *packed, const float *x_il64, 
     if (!packed || !x_il64 || !y_il64) return GN_ERR_NULL_POINTER;
     if (!pair64_applicable(M, N, K, 8, inner)) return GN_ERR_UNSUPPORTED;
     const int nblocks = (M / 8) * (N / 8) * (K / 8);
-    if (out_partials && partials_per_sample < nblocks * 4) return GN_ERR_BAD_SHAPE;
+    if (out_partials && partials_per_sample < nblocks * 2) return GN_ERR_BAD_SHAPE;
     if ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(x_il64) | reinterpret_cast<uintptr_t>(y_il64)) % 16)
         return GN_ERR_UNSUPPORTED;
     if ((in_mean_rstd && reinterpret_cast<uintptr_t>(in_mean_rstd) % 8) ||
@@ -740,12 +746,12 @@ GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, 
             a.out_il64 = ws.buf[(o + 1) & 1];
             a.in_stats = o > 0 ? ws.stats : nullptr;
             a.out_partials = ws.partials;
-            a.nparts = nblocks * 4;
+            a.nparts = nblocks * 2;
             a.error_flag = ws.error_flag;
             a.M = M; a.N = N; a.K = K; a.G = G; a.inner = inner;
             rc = launch_step_fwd_pair64(a, act, st);
             if (rc != GN_OK) return rc;
-            rc = launch_norm_finalize(ws.partials, nblocks * 4, ws.stats, Bp, P, ln_eps, st);
+            rc = launch_norm_finalize(ws.partials, nblocks * 2, ws.stats, Bp, P, ln_eps, st);
             if (rc != GN_OK) return rc;
         }
         return launch_from_il64(ws.buf[outer & 1], ws.stats, gamma, beta, y, B, G, P, st);

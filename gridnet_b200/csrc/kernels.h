@@ -81,7 +81,7 @@ struct Pair64Step {
     const float *in_il64;
     float *out_il64;
     const float2 *in_stats;   // [G*64] or nullptr
-    double2 *out_partials;    // [G*64][nparts] or nullptr; slots block*4 .. block*4+3 are written
+    double2 *out_partials;    // [G*64][nparts] or nullptr; slots 0 .. 2*blocks-1 of every row are written
     int nparts;
     int *error_flag;          // device int, set when a bounded wait gave up
     int M, N, K, G, inner;

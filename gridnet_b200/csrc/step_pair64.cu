@@ -83,7 +83,7 @@ static_assert(SMEM_BYTES <= 232448, "shared memory budget of one SM");
 struct Pair64Params {
     const float *wpk;            // [blocks][2][PK_F] from pair64_pack_k
         const float2 *in_stats;      // [G*64] (mean, rstd) of the input (FUSE_IN)
-    double2 *out_partials;       // [G*64][nparts]; this kernel fills slots block*4 .. block*4+3 (STATS_OUT)
+    double2 *out_partials;       // [G*64][nparts]; this kernel fills slots 0 .. 2*blocks-1 of every row (STATS_OUT)
     int nparts;
     float *y;                    // IL64 output
     int *error_flag;             // set to 1 if a bounded wait gave up
@@ -596,9 +596,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair64::THREADS, 1)
                 s += v.x;
                 q += v.y;
             }
-            double2 *dst = p.out_partials + (size_t)(g * NS + tid) * p.nparts + (size_t)brick * 4 + 2 * rank;
-            dst[0] = make_double2(s, q);
-            dst[1] = make_double2(0.0, 0.0);
+            p.out_partials[(size_t)(g * NS + tid) * p.nparts + (size_t)brick * 2 + rank] = make_double2(s, q);
         }
     }
     cluster_wait();  // no CTA leaves while its partner may still store into its shared memory

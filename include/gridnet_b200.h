@@ -249,6 +249,7 @@ GN_API int gn_step_forward_fused_f32(const float *weight, const float *bias, con
  * ("IL64": [ceil(B/64)][M][N][K][64] floats, samples beyond B zero) and the parameters re-ordered
  * per block half. No counterpart in the reference.
  *   gn_pair64_supported            1 if this device and shape can run it
+ *   gn_pair64_stats_partials       (sum, sum of squares) pairs per sample that a step writes: 2 per block
  *   gn_pair64_packed_weight_bytes  size of the re-ordered parameters (weights, bias, scale, gamma, beta)
  *   gn_pair64_pack_weights_f32     weight [27,M,N,K], bias, scale [M,N,K] and the whole-grid norm's gamma, beta
  *                                  [M,N,K] (both NULL if no step will normalise its input) -> packed
@@ -256,13 +257,15 @@ GN_API int gn_step_forward_fused_f32(const float *weight, const float *bias, con
  *   gn_pair64_interleave_f32       x [B,M,N,K] -> x_il64
  *   gn_step_forward_pair64_f32     one step, IL64 in, IL64 out; in_mean_rstd ([64*ceil(B/64)][2]; the gamma
  *                                  and beta it goes with are the packed ones) and out_partials
- *                                  ([64*ceil(B/64)][partials_per_sample][2] doubles, partials_per_sample >=
- *                                  gn_step_stats_partials(M,N,K,8)) as in gn_step_forward_fused_f32;
+ *                                  ([64*ceil(B/64)][partials_per_sample][2] doubles; the first
+ *                                  gn_pair64_stats_partials(M,N,K) pairs of every row are written) as in
+ *                                  gn_step_forward_fused_f32;
  *                                  error_flag (device int, may be NULL) is set to 1 if a bounded wait on a
  *                                  bulk copy gave up
  *   gn_pair64_deinterleave_f32     y_il64 -> y [B,M,N,K]; with mean_rstd != NULL y = (v - mean) * rstd *
  *                                  gamma + beta */
 GN_API int gn_pair64_supported(int M, int N, int K, int block, int inner);
+GN_API int gn_pair64_stats_partials(int M, int N, int K);
 GN_API size_t gn_pair64_packed_weight_bytes(int M, int N, int K);
 GN_API int gn_pair64_pack_weights_f32(const float *weight, const float *bias, const float *scale, const float *gamma,
                                const float *beta, float *packed, int M, int N, int K, void *stream);

@@ -172,3 +172,28 @@ def outer_forward(weight, bias, scale, gamma, beta, x, inner, outer, block_size,
         h = step_forward(weight, bias, scale, h, inner, block_size, eps, normalize, activation)
         h = layernorm_forward(h, gamma, beta, ln_eps)
     return h
+
+
+def outer_backward(weight, bias, scale, gamma, beta, x, gy, inner, outer, block_size, eps=1e-5, normalize=False,
+                   activation="silu", ln_eps=1e-5):
+    """Gradient of :func:`outer_forward` for an upstream gradient ``gy`` on its result: the composition
+    ``step_backward o layernorm_backward`` walked from the last outer step to the first, parameter gradients
+    summed over the steps (shared parameters). Returns (grad_weight, grad_bias, grad_scale, grad_gamma,
+    grad_beta, grad_x)."""
+    h = np.asarray(x)
+    step_in, norm_in = [], []
+    for _ in range(outer):
+        step_in.append(h)
+        s = step_forward(weight, bias, scale, h, inner, block_size, eps, normalize, activation)
+        norm_in.append(s)
+        h = layernorm_forward(s, gamma, beta, ln_eps)
+    g = np.asarray(gy, dtype=h.dtype)
+    gw = gb = gs = gg = gbt = None
+    for k in reversed(range(outer)):
+        g, dg, dbt = layernorm_backward(norm_in[k], gamma, g, ln_eps)
+        dw, db, ds, g = step_backward(weight, bias, scale, step_in[k], g, inner, block_size, eps, normalize, activation)
+        if gw is None:
+            gw, gb, gs, gg, gbt = dw, db, ds, dg, dbt
+        else:
+            gw, gb, gs, gg, gbt = gw + dw, gb + db, gs + ds, gg + dg, gbt + dbt
+    return gw, gb, gs, gg, gbt, g

@@ -34,11 +34,21 @@ def test_model_fused_inference_equals_training_path_and_oracle():
                              sd["norm.bias"], x.cpu().numpy().astype(np.float64), 2, 3, 8)
     err = np.abs(fused.cpu().numpy() - want)
     assert (err <= 1e-5 + 1e-4 * np.abs(want)).all()
-    # a training step: gradients reach every parameter and match finite differences of the oracle loss
-    loss = (stepwise * torch.linspace(-1, 1, stepwise.numel(), device=dev).view_as(stepwise)).sum()
-    loss.backward()
-    for name, p in model.named_parameters():
-        assert p.grad is not None and torch.isfinite(p.grad).all() and p.grad.abs().sum() > 0, name
+    # a training step: the gradients of all five parameters and of the input against the oracle's chain
+    # step_backward o layernorm_backward over the three outer steps (float64 oracle, float32 oracle for the noise)
+    from util import assert_close
+
+    gy = torch.linspace(-1, 1, stepwise.numel(), device=dev).view_as(stepwise).contiguous()
+    xg = x.clone().requires_grad_(True)
+    out = model(xg)
+    names = ["network.weight", "network.bias", "network.residual_scale", "norm.weight", "norm.bias"]
+    params = dict(model.named_parameters())
+    grads = torch.autograd.grad(out, [params[n] for n in names] + [xg], gy)
+    args64 = [sd[n] for n in names] + [x.cpu().numpy().astype(np.float64), gy.cpu().numpy().astype(np.float64)]
+    want64 = orc.outer_backward(*args64, 2, 3, 8)
+    want32 = orc.outer_backward(*(a.astype(np.float32) for a in args64), 2, 3, 8)
+    for name, g, r64, r32 in zip(names + ["input"], grads, want64, want32):
+        assert_close(g.cpu().numpy(), r64, r32, f"model gradient of {name}")
 
 
 def test_gated_model_and_readout_run():

@@ -118,3 +118,24 @@ def test_empty_batch_and_bad_block():
     assert y.shape == (0, *shape)
     with pytest.raises(AssertionError):
         orc.step_forward(w, b, b, np.zeros((1, *shape), np.float32), 2, 3)
+
+
+def test_outer_backward_matches_finite_differences():
+    """The oracle's chain rule over the model loop (step_backward o layernorm_backward, shared parameters summed)
+    against central differences of outer_forward, float64, one random entry of every argument."""
+    r = np.random.default_rng(0)
+    shape, B = (8, 8, 8), 2
+    w = r.standard_normal((27, *shape)) / np.sqrt(27)
+    b, s = 0.1 * r.standard_normal(shape), 1 + 0.1 * r.standard_normal(shape)
+    ga, be = 1 + 0.1 * r.standard_normal(shape), 0.1 * r.standard_normal(shape)
+    x, gy = r.standard_normal((B, *shape)), r.standard_normal((B, *shape))
+    args = [w, b, s, ga, be, x]
+    grads = orc.outer_backward(*args, gy, 2, 2, 4)
+    eps = 1e-6
+    for ai in range(6):
+        idx = tuple(int(r.integers(0, d)) for d in args[ai].shape)
+        ap, am = [a.copy() for a in args], [a.copy() for a in args]
+        ap[ai][idx] += eps
+        am[ai][idx] -= eps
+        fd = float(((orc.outer_forward(*ap, 2, 2, 4) - orc.outer_forward(*am, 2, 2, 4)) * gy).sum()) / (2 * eps)
+        assert abs(fd - grads[ai][idx]) <= 1e-6 * (1 + abs(fd)), (ai, fd, grads[ai][idx])
