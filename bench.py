@@ -226,7 +226,24 @@ class Ctx:
         torch.cuda.set_device(local_rank)
         self.device = torch.device("cuda", local_rank)
         self.dist = None
-        self._own_group = False
+        self.affinity = self._pin_cores()
+
+    def _pin_cores(self):
+        """With several ranks on one host, give each its own share of the cores this job may use, so that the
+        threads that feed a GPU (and the pages of its pinned buffers, first touched by them) stay put. No GPU or
+        driver setting is involved."""
+        if self.world <= 1:
+            return None
+        try:
+            cores = sorted(os.sched_getaffinity(0))
+            per = len(cores) // self.world
+            if per < 1:
+                return None
+            mine = cores[self.local_rank * per:(self.local_rank + 1) * per]
+            os.sched_setaffinity(0, mine)
+            return f"{len(mine)} of {len(cores)} cores: {mine[0]}-{mine[-1]}"
+        except (AttributeError, OSError):
+            return None
 
     def need_group(self):
         """A process group, also at one rank (the slab driver issues collectives either way)."""
@@ -421,10 +438,33 @@ def bench_c2(ctx: Ctx):
     ok = bool(torch.isfinite(hy[0]).all().item())
     e2e_value = neuron_updates(BATCH) * world * n_e2e / (ems * 1e-3)
     nbytes = xs[0].numel() * 4
+    # The ceiling the host side sets: the same host->device and device->host copies with no compute at all, on two
+    # streams, all ranks at once. End to end cannot be faster than this, whatever the kernels do.
+    cs_in, cs_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    ctx.barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    cs_in.wait_stream(torch.cuda.current_stream())
+    cs_out.wait_stream(torch.cuda.current_stream())
+    for i in range(n_e2e):
+        with torch.cuda.stream(cs_in):
+            xs[i % 2].copy_(hx[i % 2], non_blocking=True)
+        with torch.cuda.stream(cs_out):
+            hy[i % 2].copy_(ys[i % 2], non_blocking=True)
+    torch.cuda.current_stream().wait_stream(cs_in)
+    torch.cuda.current_stream().wait_stream(cs_out)
+    c1.record()
+    ctx.barrier()
+    cms = ctx.max_over_ranks(c0.elapsed_time(c1))
     e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
            "ms_per_step": ems / n_e2e, "steps": n_e2e,
            "finite": ok,
            "host_gbs_per_rank": 2 * nbytes * n_e2e / (ems * 1e-3) / 1e9,
+           "copies_alone": {"ms_per_step": cms / n_e2e, "host_gbs_per_rank": 2 * nbytes * n_e2e / (cms * 1e-3) / 1e9,
+                            "value_ceiling": neuron_updates(BATCH) * world * n_e2e / (cms * 1e-3),
+                            "note": "the same pinned-host copies both ways with no compute, all ranks at once: the "
+                                    "ceiling that host memory and PCIe set for the end-to-end figure"},
+           "cpu_affinity": ctx.affinity,
            "note": "full [B,M,N,K] activations in and out through HostPipelinedForward (pinned host memory; copies of one "
                    "step overlap the compute of its neighbours on separate streams)"}
 

@@ -444,7 +444,7 @@ GN_API size_t gn_norm_workspace_bytes(int B, long long P)
 GN_API int gn_norm_forward_f32(const float *x, const float *gamma, const float *beta, float *y, float *mean_rstd, int B,
                         long long P, float eps, void *workspace, size_t workspace_bytes, void *stream)
 {
-    if (B < 0 || P <= 0 || B > 65535) return GN_ERR_BAD_SHAPE;
+    if (B < 0 || P <= 0 || (long long)B * ((P + 1023) / 1024) > 0x7fffffffLL) return GN_ERR_BAD_SHAPE;
     if (B == 0) return GN_OK;
     if (!x || !gamma || !beta || !y) return GN_ERR_NULL_POINTER;
     int rc = check_ws(workspace, workspace_bytes, gn_norm_workspace_bytes(B, P));
@@ -473,7 +473,7 @@ GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float 
                          float *gbeta, int B, long long P, float eps, void *workspace, size_t workspace_bytes,
                          void *stream)
 {
-    if (B < 0 || P <= 0 || B > 65535) return GN_ERR_BAD_SHAPE;
+    if (B < 0 || P <= 0 || (long long)B * ((P + 1023) / 1024) > 0x7fffffffLL) return GN_ERR_BAD_SHAPE;
     if (!gamma || !ggamma || !gbeta) return GN_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;
     if (B == 0) {
@@ -600,7 +600,7 @@ GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_
 GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *beta, const float *mean_rstd, float *y,
                       int B, long long P, void *stream)
 {
-    if (B < 0 || P <= 0 || B > 65535) return GN_ERR_BAD_SHAPE;
+    if (B < 0 || P <= 0 || (long long)B * ((P + 1023) / 1024) > 0x7fffffffLL) return GN_ERR_BAD_SHAPE;
     if (B == 0) return GN_OK;
     if (!x || !gamma || !beta || !mean_rstd || !y) return GN_ERR_NULL_POINTER;
     return launch_norm_apply(x, gamma, beta, reinterpret_cast<const float2 *>(mean_rstd), y, B, P,
@@ -709,7 +709,7 @@ GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, 
     int rc = check_geometry(B, M, N, K, inner, block, act);
     if (rc != GN_OK) return rc;
     if (outer < 0) return GN_ERR_BAD_SHAPE;
-    if (B > 65535) return GN_ERR_BAD_SHAPE;
+    if ((long long)B * (((long long)M * N * K + 1023) / 1024) > 0x7fffffffLL) return GN_ERR_BAD_SHAPE;
     if (B == 0) return GN_OK;
     if (!w || !b || !s || !gamma || !beta || !x || !y) return GN_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;

@@ -11,7 +11,8 @@
 
 namespace gn {
 
-constexpr int kNumSMs = 148;  // B200
+constexpr int kNumSMs = 148;  // B200; only the fallback where the device cannot be asked
+int sm_count();                // multiprocessor count of the current device (status.cu)
 
 // Set by every launcher that sees a CUDA error; read by gn_last_cuda_error().
 void record_cuda_error(cudaError_t e, const char *where);
@@ -143,7 +144,7 @@ __device__ __forceinline__ float2 ld_pinned2(const float *ptr)  // 8-byte aligne
 // How many ways to split the batch across CTAs so that the grid fills the GPU.
 inline int pick_batch_chunks(long long grid_blocks, int B, int ctas_per_sm, int min_samples_per_cta = 1)
 {
-    long long want = 2LL * kNumSMs * ctas_per_sm;  // about two waves
+    long long want = 2LL * sm_count() * ctas_per_sm;  // about two waves
     long long c = (want + grid_blocks - 1) / grid_blocks;
     long long cmax = B / min_samples_per_cta;
     if (cmax < 1) cmax = 1;
@@ -159,7 +160,7 @@ inline int pick_batch_chunks(long long grid_blocks, int B, int ctas_per_sm, int 
 inline int pick_batch_chunks_balanced(long long grid_blocks, int B, int ctas_per_sm, double overhead_samples,
                                       int max_chunks)
 {
-    const long long slots = (long long)kNumSMs * ctas_per_sm;
+    const long long slots = (long long)sm_count() * ctas_per_sm;
     int best = 1;
     double best_cost = 1e300;
     for (int c = 1; c <= max_chunks && c <= B; ++c) {

@@ -99,6 +99,19 @@ int launch_from_il64(const float *il, const float2 *stats, const float *gamma, c
 // ---- status.cu: device address of the per-device status word that kernels set when a bounded wait gives up
 // and the caller passed no flag of its own (nullptr if it cannot be resolved)
 int *device_status_ptr();
+// multiprocessor count of the current device, cached
+int sm_count();
+// For once-per-device set-up of a kernel (cudaFuncSetAttribute is per device): true the first time it is called
+// with this mask while a given device is current, false afterwards. One mask per kernel instantiation.
+bool first_use_on_device(unsigned long long *mask);
+// cache of tensor maps keyed on (kind of map, device, base pointer, four extents)
+struct MapKey {
+    const void *ptr;
+    int kind, dev;
+    int d[4];
+};
+bool tensor_map_cache_get(const MapKey &key, CUtensorMap *out);
+void tensor_map_cache_put(const MapKey &key, const CUtensorMap &map);
 int launch_propagate_flag(const int *flag, cudaStream_t st);
 
 // ---- probe.cu (FFMA-only kernel for the measured FP32 peak)

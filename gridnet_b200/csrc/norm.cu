@@ -16,13 +16,14 @@ static __device__ __forceinline__ bool aligned16(const void *p)
     return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
 }
 
-// grid (parts, B); slice length is a multiple of 4 so that slices stay float4-aligned
+// grid B * parts (one dimension: the batch is not limited by the 65535 of gridDim.y); slice length is a multiple
+// of 4 so that slices stay float4-aligned
 __global__ void __launch_bounds__(256) norm_partial_stats_k(const float *__restrict__ x,
                                                             double2 *__restrict__ partials, long long P,
-                                                            long long slice)
+                                                            long long slice, int parts)
 {
     __shared__ double red[33];
-    const int b = blockIdx.y, part = blockIdx.x;
+    const int b = blockIdx.x / parts, part = blockIdx.x - b * parts;
     const float *xs = x + (size_t)b * P;
     const long long lo = (long long)part * slice;
     const long long hi = min(P, lo + slice);
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(256) norm_partial_stats_k(const float *__restr
     }
     s = block_sum(s, red);
     q = block_sum(q, red);
-    if (threadIdx.x == 0) partials[(size_t)b * gridDim.x + part] = make_double2(s, q);
+    if (threadIdx.x == 0) partials[(size_t)b * parts + part] = make_double2(s, q);
 }
 
 // grid B; adds nparts partials in a fixed order
@@ -72,17 +73,18 @@ __global__ void __launch_bounds__(256) norm_finalize_k(const double2 *__restrict
     }
 }
 
-// grid (ceil(P / 1024), B)
+// grid B * ceil(P / 1024), one dimension
 __global__ void __launch_bounds__(256) norm_apply_k(const float *__restrict__ x, const float *__restrict__ gamma,
                                                     const float *__restrict__ beta,
                                                     const float2 *__restrict__ stats, float *__restrict__ y,
-                                                    long long P)
+                                                    long long P, unsigned chunks)
 {
-    const int b = blockIdx.y;
+    const int b = blockIdx.x / chunks;
+    const unsigned chunk = blockIdx.x - (unsigned)b * chunks;
     const float2 mr = stats[b];
     const float *xs = x + (size_t)b * P;
     float *ys = y + (size_t)b * P;
-    const long long i0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const long long i0 = ((long long)chunk * blockDim.x + threadIdx.x) * 4;
     if (i0 >= P) return;
     if ((P & 3) == 0 && aligned16(xs) && aligned16(ys) && aligned16(gamma) && aligned16(beta)) {
         const float4 v = *reinterpret_cast<const float4 *>(xs + i0);
@@ -99,16 +101,16 @@ __global__ void __launch_bounds__(256) norm_apply_k(const float *__restrict__ x,
     }
 }
 
-// per-sample partial sums of a = sum(gy * gamma) and c = sum(gy * gamma * xhat); grid (parts, B)
+// per-sample partial sums of a = sum(gy * gamma) and c = sum(gy * gamma * xhat); grid B * parts
 __global__ void __launch_bounds__(256) norm_bwd_partial_k(const float *__restrict__ x,
                                                           const float *__restrict__ gamma,
                                                           const float *__restrict__ gy,
                                                           const float2 *__restrict__ stats,
                                                           double2 *__restrict__ partials, long long P,
-                                                          long long slice)
+                                                          long long slice, int parts)
 {
     __shared__ double red[33];
-    const int b = blockIdx.y, part = blockIdx.x;
+    const int b = blockIdx.x / parts, part = blockIdx.x - b * parts;
     const float2 mr = stats[b];
     const float *xs = x + (size_t)b * P;
     const float *gs = gy + (size_t)b * P;
@@ -123,7 +125,7 @@ __global__ void __launch_bounds__(256) norm_bwd_partial_k(const float *__restric
     }
     a = block_sum(a, red);
     c = block_sum(c, red);
-    if (threadIdx.x == 0) partials[(size_t)b * gridDim.x + part] = make_double2(a, c);
+    if (threadIdx.x == 0) partials[(size_t)b * parts + part] = make_double2(a, c);
 }
 
 // grid B: ac[b] = (a / P, c / P)
@@ -183,8 +185,7 @@ static long long slice_len(long long P, int parts)
 
 int launch_norm_partial_stats(const float *x, double2 *partials, int B, long long P, int parts, cudaStream_t st)
 {
-    dim3 grid(parts, B);
-    norm_partial_stats_k<<<grid, 256, 0, st>>>(x, partials, P, slice_len(P, parts));
+    norm_partial_stats_k<<<(unsigned)B * (unsigned)parts, 256, 0, st>>>(x, partials, P, slice_len(P, parts), parts);
     return check_launch("norm_partial_stats");
 }
 
@@ -198,8 +199,8 @@ int launch_norm_finalize(const double2 *partials, int nparts, float2 *stats, int
 int launch_norm_apply(const float *x, const float *gamma, const float *beta, const float2 *stats, float *y,
                       int B, long long P, cudaStream_t st)
 {
-    dim3 grid((unsigned)((P + 1023) / 1024), B);
-    norm_apply_k<<<grid, 256, 0, st>>>(x, gamma, beta, stats, y, P);
+    const unsigned chunks = (unsigned)((P + 1023) / 1024);
+    norm_apply_k<<<(unsigned)B * chunks, 256, 0, st>>>(x, gamma, beta, stats, y, P, chunks);
     return check_launch("norm_apply");
 }
 
@@ -207,8 +208,8 @@ int launch_norm_backward(const float *x, const float *gamma, const float *gy, co
                          double2 *partials, float2 *ac, float *gx, float *ggamma, float *gbeta, int B,
                          long long P, int parts, cudaStream_t st)
 {
-    dim3 grid(parts, B);
-    norm_bwd_partial_k<<<grid, 256, 0, st>>>(x, gamma, gy, stats, partials, P, slice_len(P, parts));
+    norm_bwd_partial_k<<<(unsigned)B * (unsigned)parts, 256, 0, st>>>(x, gamma, gy, stats, partials, P, slice_len(P, parts),
+                                                                     parts);
     norm_bwd_finalize_k<<<B, 64, 0, st>>>(partials, parts, ac, P);
     norm_bwd_apply_k<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(x, gamma, gy, stats, ac, gx, ggamma, gbeta, B, P);
     return check_launch("norm_backward");

@@ -24,9 +24,7 @@ __global__ void __launch_bounds__(256) ffma_probe_k(float *sink, int iters)
 
 int launch_ffma_probe(float *sink, int iters, long long *fma_count, cudaStream_t st)
 {
-    int dev = 0, sms = kNumSMs;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int ctas = sms * 8;  // 2048 threads per SM: every scheduler has warps to pick from
+    const int ctas = sm_count() * 8;  // 2048 threads per SM: every scheduler has warps to pick from
     ffma_probe_k<<<ctas, 256, 0, st>>>(sink, iters);
     if (fma_count) *fma_count = (long long)ctas * 256 * 16 * iters;
     return check_launch("ffma_probe");

@@ -37,6 +37,67 @@ int *device_status_ptr()
     return g_status_ptr[dev];
 }
 
+// Multiprocessor count of the CURRENT device (148 on B200), looked up once per device.
+int sm_count()
+{
+    static int cached[kMaxDevices] = {0};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kNumSMs;
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = kNumSMs;
+        }
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+bool first_use_on_device(unsigned long long *mask)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    const unsigned long long bit = 1ULL << dev;
+    if (*mask & bit) return false;
+    *mask |= bit;
+    return true;
+}
+
+// A few recently built tensor maps, so that a loop of launches on the same buffers does not encode the same
+// descriptor again and again (the encoding is a driver call of a microsecond or two).
+struct MapSlot {
+    MapKey key;
+    CUtensorMap map;
+    bool used;
+};
+static MapSlot g_maps[16];
+static int g_map_next = 0;
+
+bool tensor_map_cache_get(const MapKey &key, CUtensorMap *out)
+{
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    for (const MapSlot &s : g_maps)
+        if (s.used && s.key.ptr == key.ptr && s.key.kind == key.kind && s.key.dev == key.dev && s.key.d[0] == key.d[0] &&
+            s.key.d[1] == key.d[1] && s.key.d[2] == key.d[2] && s.key.d[3] == key.d[3]) {
+            *out = s.map;
+            return true;
+        }
+    return false;
+}
+
+void tensor_map_cache_put(const MapKey &key, const CUtensorMap &map)
+{
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    MapSlot &s = g_maps[g_map_next];
+    g_map_next = (g_map_next + 1) % 16;
+    s.key = key;
+    s.map = map;
+    s.used = true;
+}
+
 __global__ void propagate_flag_k(const int *flag, int *status)
 {
     if (*flag) *status = 1;

@@ -817,7 +817,7 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     {
         // One CTA per region covers the batch when the grid already fills the GPU; otherwise the batch
         // is split into at most 8 chunks that form a cluster and combine their sums on chip.
-        const int want = nb >= 4LL * kNumSMs * 3 ? 1 : pick_batch_chunks_balanced(nb, B, 3, 2.0, 8);
+        const int want = nb >= 4LL * sm_count() * 3 ? 1 : pick_batch_chunks_balanced(nb, B, 3, 2.0, 8);
         p.spc = (B + want - 1) / want;
         const unsigned chunks = (unsigned)((B + p.spc - 1) / p.spc);
         p.cluster_reduce = chunks > 1;

@@ -330,9 +330,11 @@ bool fast8_applicable(const FastFwdParams &p, int block, int normalize)
     if ((block != 8 && block != 4) || normalize || p.inner < 1) return false;
     if (p.M % 8 || p.N % 8 || p.K % 8) return false;  // a CTA owns an 8 x 8 x 8 region also with block 4
     if ((long long)p.M * p.N * p.K >= (1LL << 31)) return false;
-    // the per-cell descriptor holds offsets relative to the tile origin in 20 bits
-    if ((9LL * p.N + 9) * p.K + 9 >= fast8::kMaxRel) return false;
     auto al = [](const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; };
+    // Without bulk tensor copies the per-cell descriptor holds global offsets relative to the tile origin in 20
+    // bits, which limits the size of an (N, K) plane; with them the offsets point into the staging buffer.
+    const bool bulk = encode_tiled_fn() && al(p.x, 16) && (p.K & 3) == 0;
+    if (!bulk && (9LL * p.N + 9) * p.K + 9 >= fast8::kMaxRel) return false;
     if (!(al(p.w, 8) && al(p.b, 8) && al(p.s, 8) && al(p.x, 4) && al(p.y, 8) && al(p.save_h, 8) && al(p.save_x, 8)))
         return false;
     // block 4 tiles are fetched by bulk tensor copy only
@@ -357,13 +359,19 @@ bool fast8_make_tile_map(CUtensorMap *map, const float *base, int B, int M, int 
 {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc || (reinterpret_cast<uintptr_t>(base) & 15) || (K & 3)) return false;
+    MapKey key{base, 16, 0, {B, M, N, K}};
+    (void)cudaGetDevice(&key.dev);
+    if (tensor_map_cache_get(key, map)) return true;
     const cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)B};
     const cuuint64_t strides[3] = {(cuuint64_t)K * 4, (cuuint64_t)N * K * 4, (cuuint64_t)M * N * K * 4};
     const cuuint32_t box[4] = {16, 10, 10, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    tensor_map_cache_put(key, *map);
+    return true;
 }
 
 int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
@@ -386,10 +394,13 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
     do {                                                                                                  \
         auto kern = step_fwd_fast8<4, A, FI, SO, true, IT>;                                               \
         const size_t dyn = sizeof(float) * 4 * PatchGeo<4>::TS;                                           \
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn); \
-        if (e != cudaSuccess) {                                                                           \
-            record_cuda_error(e, "cudaFuncSetAttribute");                                                 \
-            return GN_ERR_CUDA;                                                                           \
+        static unsigned long long attr_set = 0; /* one mask per instantiation: the macro body is its own scope */ \
+        if (first_use_on_device(&attr_set)) {                                                             \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn); \
+            if (e != cudaSuccess) {                                                                       \
+                record_cuda_error(e, "cudaFuncSetAttribute");                                             \
+                return GN_ERR_CUDA;                                                                       \
+            }                                                                                             \
         }                                                                                                 \
         kern<<<grid, fast8::THREADS, dyn, st>>>(map, p);                                                  \
     } while (0)

@@ -753,6 +753,9 @@ bool pair64_applicable(int M, int N, int K, int block, int inner)
 // Tensor map over an IL64 buffer: dims (fastest first) {64, K, N, M, G}, box {64, 1, 10, 6, 1}: one tile column.
 static int make_il64_map(CUtensorMap *map, const float *il, int M, int N, int K, int G)
 {
+    MapKey key{il, 64, 0, {M, N, K, G}};
+    (void)cudaGetDevice(&key.dev);
+    if (tensor_map_cache_get(key, map)) return GN_OK;
     const cuuint64_t dims[5] = {64, (cuuint64_t)K, (cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)G};
     const cuuint64_t strides[4] = {256, (cuuint64_t)K * 256, (cuuint64_t)N * K * 256, (cuuint64_t)M * N * K * 256};
     const cuuint32_t box[5] = {64, 1, 10, 6, 1};
@@ -764,21 +767,21 @@ static int make_il64_map(CUtensorMap *map, const float *il, int M, int N, int K,
         record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
         return GN_ERR_CUDA;
     }
+    tensor_map_cache_put(key, *map);
     return GN_OK;
 }
 
 int launch_pair64_pack(const float *w, const float *b, const float *s, const float *gamma, const float *beta, float *packed,
                        int M, int N, int K, cudaStream_t st)
 {
-    static bool attr_set = false;
+    static unsigned long long attr_set = 0;
     const int smem = 29 * 512 * 4;
-    if (!attr_set) {
+    if (first_use_on_device(&attr_set)) {
         cudaError_t e = cudaFuncSetAttribute(pair64_pack_k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
             record_cuda_error(e, "cudaFuncSetAttribute(pair64_pack_k)");
             return GN_ERR_CUDA;
         }
-        attr_set = true;
     }
     const int nblocks = (M / 8) * (N / 8) * (K / 8);
     pair64_pack_k<<<nblocks, 256, smem, st>>>(w, b, s, gamma, beta, packed, M, N, K);
@@ -813,25 +816,22 @@ int launch_step_fwd_pair64(const Pair64Step &a, int act, cudaStream_t st)
     p.M = a.M; p.N = a.N; p.K = a.K; p.G = a.G; p.inner = a.inner;
     p.nblocks = (a.M / 8) * (a.N / 8) * (a.K / 8);
     p.nitems = p.nblocks * a.G;
-    int dev = 0, sms = kNumSMs;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int ncl = sms / 2;
+    int ncl = sm_count() / 2;
     if (ncl > p.nitems) ncl = p.nitems;
     // evenly filled rounds: with r = ceil(items / clusters) rounds, use just as many clusters as r rounds need
     const int rounds = (p.nitems + ncl - 1) / ncl;
     ncl = (p.nitems + rounds - 1) / rounds;
     const bool fin = a.in_stats != nullptr, sout = a.out_partials != nullptr;
-    static bool attr_done[4][2][2] = {};
+    static unsigned long long attr_done[4][2][2] = {};
 #define ONE_(A, FI, SO)                                                                                    \
     do {                                                                                                   \
         auto kern = step_fwd_pair64<A, FI, SO>;                                                            \
-        if (!attr_done[A][FI][SO]) {                                                                       \
+        if (first_use_on_device(&attr_done[A][FI][SO])) {                                                  \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair64::SMEM_BYTES); \
             if (e != cudaSuccess) {                                                                        \
                 record_cuda_error(e, "cudaFuncSetAttribute(step_fwd_pair64)");                            \
                 return GN_ERR_CUDA;                                                                        \
             }                                                                                              \
-            attr_done[A][FI][SO] = true;                                                                   \
         }                                                                                                  \
         kern<<<2 * ncl, pair64::THREADS, pair64::SMEM_BYTES, st>>>(map, p);                                \
     } while (0)

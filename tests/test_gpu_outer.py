@@ -228,6 +228,48 @@ def test_outer_forward_reports_no_device_failure():
     assert not outer_forward_failed(ws, B, shape, 8)
 
 
+def test_grid_norm_with_more_than_65535_samples():
+    """The batch sits in the first grid dimension of the norm kernels, so it is not capped at 65535."""
+    from gridnet_b200 import GridNormOp
+
+    B, shape = 70001, (4, 4, 4)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = 2 * torch.randn(B, *shape, device="cuda", generator=g) + 0.5
+    gamma = 1 + 0.1 * torch.randn(shape, device="cuda", generator=g)
+    beta = 0.1 * torch.randn(shape, device="cuda", generator=g)
+    y = GridNormOp.apply(x, gamma, beta, 1e-5)
+    ref = torch.nn.functional.layer_norm(x, shape, gamma, beta, 1e-5)
+    assert torch.allclose(y, ref, rtol=1e-4, atol=1e-5)
+    idx = [0, 1, 65535, 65536, B - 1]
+    want = orc.layernorm_forward(x[idx].cpu().numpy().astype(np.float64), gamma.cpu().numpy().astype(np.float64),
+                                 beta.cpu().numpy().astype(np.float64))
+    assert_close(y[idx].cpu().numpy(), want, None, "norm, large batch")
+
+
+def test_forward_on_planes_beyond_the_register_prefetch_limit():
+    """A grid whose (N, K) plane is too large for the 20-bit offsets of the plain-load path still takes the tuned
+    forward kernel when bulk tensor copies apply (and stays correct): 8 x 344 x 344, one sample."""
+    from gridnet_b200 import GridnetCudaOp
+    from gridnet_b200._lib import lib
+
+    shape = (8, 344, 344)
+    r = np.random.default_rng(41)
+    w = (r.standard_normal((27, *shape)) / np.sqrt(27)).astype(np.float32)
+    b = (0.1 * r.standard_normal(shape)).astype(np.float32)
+    s = (1 + 0.1 * r.standard_normal(shape)).astype(np.float32)
+    x = r.standard_normal((1, *shape)).astype(np.float32)
+    tw, tb, ts, tx = (dev(a) for a in (w, b, s, x))
+    got = GridnetCudaOp.apply(tw, tb, ts, tx, 2, 8, 1e-5, False, "silu")
+    # the fused entry point only exists on the tuned path: it must accept this shape now
+    y2 = torch.empty_like(tx)
+    rc = lib.gn_step_forward_fused_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), y2.data_ptr(), None, None,
+                                       None, None, 1, *shape, 2, 8, 2, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.gn_status_string(rc)
+    assert torch.equal(got, y2)
+    ref = orc.step_forward(*(a.astype(np.float64) for a in (w, b, s, x)), 2, 8, normalize=False, activation="silu")
+    assert_close(got.cpu().numpy(), ref, None, "large plane")
+
+
 def test_device_failure_reports_can_be_seen():
     """The host side of the bounded-wait contract: a set flag is what the accessors report. Nothing here makes a
     kernel's wait run out; the flag in the workspace and the library's status word are written by hand."""
