@@ -544,7 +544,41 @@ def slab_parity_on_ranks(ctx: Ctx) -> dict:
         verdict = torch.tensor([1.0 if ok else 0.0, float(e_direct.max().item()), float(e_nccl.max().item())], device=device)
     dist.broadcast(verdict, src=0)
     del peers
-    return {"slab_parity_ok": bool(verdict[0].item() > 0.5), "grid": [M, N, K], "batch": B,
+
+    # training on the real ranks: forward + backward with the reverse face exchange and both all-reduces over NCCL,
+    # gathered and compared with rank 0's single-GPU autograd through the package's ops
+    from gridnet_b200.slab import make_cuda_trainer, train_distributed
+
+    gy = torch.randn(B, M, N, K, generator=g)
+    trainer = make_cuda_trainer(lay, w, b, s, gamma, beta, x, inner, ACT, device=device)
+    _, res = train_distributed(trainer, outer, lambda o: gy[..., lay.k0:lay.k0 + lay.k_loc].to(device))
+    gathered = []
+    for t in res:
+        parts = [torch.empty_like(t) for _ in range(world)] if rank == 0 else None
+        dist.gather(t.contiguous(), parts, dst=0)
+        gathered.append(torch.cat(parts, dim=-1) if rank == 0 else None)
+    bverdict = torch.zeros(2, device=device)
+    if rank == 0:
+        leaves = [t.to(device).requires_grad_(True) for t in (w, b, s, gamma, beta, x)]
+        h = leaves[5]
+        for _ in range(outer):
+            h = gb.GridNormOp.apply(gb.GridnetCudaOp.apply(leaves[0], leaves[1], leaves[2], h, inner, 8, 1e-5, False, ACT),
+                                    leaves[3], leaves[4], 1e-5)
+        single = torch.autograd.grad(h, leaves, gy.to(device))
+        worst, okb = 0.0, True
+        for a, c in zip(gathered, single):
+            e = float((a - c).abs().max().item())
+            worst = max(worst, e / (1.0 + float(c.abs().max().item())))
+            okb = okb and bool(((a - c).abs() <= 1e-4 * (1 + c.abs().max()) + 1e-3 * c.abs()).all().item())
+        bverdict = torch.tensor([1.0 if okb else 0.0, worst], device=device)
+    dist.broadcast(bverdict, src=0)
+    return {"slab_parity_ok": bool(verdict[0].item() > 0.5) and bool(bverdict[0].item() > 0.5),
+            "slab_forward_parity_ok": bool(verdict[0].item() > 0.5),
+            "slab_backward_parity_ok": bool(bverdict[0].item() > 0.5),
+            "backward_worst_err_over_max": float(bverdict[1].item()),
+            "backward_tolerance": "|slab - single GPU| <= 1e-4 (1 + max|ref|) + 1e-3 |ref| for all six gradients (two float32 "
+                                  "implementations with different summation orders; the oracle comparison is in tests/test_slab.py)",
+            "grid": [M, N, K], "batch": B,
             "max_abs_err_direct": float(verdict[1].item()), "max_abs_err_nccl": float(verdict[2].item()),
             "same_bits_both_paths": None if rank != 0 else bool(torch.equal(outs["direct"], outs["nccl"])),
             "tolerance": "1e-5 + 1e-4 |ref| against outer_forward on the whole grid on rank 0"}

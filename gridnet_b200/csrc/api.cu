@@ -497,6 +497,61 @@ GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float 
     return launch_norm_backward(x, gamma, gy, ws.stats, ws.partials, ws.ac, gx, ggamma, gbeta, B, P, parts, st);
 }
 
+GN_API int gn_norm_local_sums_f32(const float *x, double *sums, int B, long long P, void *workspace,
+                                  size_t workspace_bytes, void *stream)
+{
+    if (B < 0 || P <= 0) return GN_ERR_BAD_SHAPE;
+    if (B == 0) return GN_OK;
+    if (!x || !sums) return GN_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(sums) % 16) return GN_ERR_UNSUPPORTED;
+    int rc = check_ws(workspace, workspace_bytes, gn_norm_workspace_bytes(B, P));
+    if (rc != GN_OK) return rc;
+    const NormWs ws = carve_norm(workspace, B);
+    return launch_norm_local_sums(x, ws.partials, reinterpret_cast<double2 *>(sums), B, P, norm_pick_parts(P),
+                                  (cudaStream_t)stream);
+}
+
+GN_API int gn_norm_backward_local_sums_f32(const float *x, const float *gamma, const float *gy, const float *mean_rstd,
+                                           double *sums, int B, long long P, void *workspace, size_t workspace_bytes,
+                                           void *stream)
+{
+    if (B < 0 || P <= 0) return GN_ERR_BAD_SHAPE;
+    if (B == 0) return GN_OK;
+    if (!x || !gamma || !gy || !mean_rstd || !sums) return GN_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(sums) % 16 || reinterpret_cast<uintptr_t>(mean_rstd) % 8) return GN_ERR_UNSUPPORTED;
+    int rc = check_ws(workspace, workspace_bytes, gn_norm_workspace_bytes(B, P));
+    if (rc != GN_OK) return rc;
+    const NormWs ws = carve_norm(workspace, B);
+    return launch_norm_backward_local_sums(x, gamma, gy, reinterpret_cast<const float2 *>(mean_rstd), ws.partials,
+                                           reinterpret_cast<double2 *>(sums), B, P, norm_pick_parts(P),
+                                           (cudaStream_t)stream);
+}
+
+GN_API int gn_norm_backward_apply_f32(const float *x, const float *gamma, const float *gy, const float *mean_rstd,
+                                      const double *sums, long long P_total, float *gx, float *ggamma, float *gbeta,
+                                      int B, long long P, void *workspace, size_t workspace_bytes, void *stream)
+{
+    if (B < 0 || P <= 0 || P_total < P) return GN_ERR_BAD_SHAPE;
+    if (!gamma || !ggamma || !gbeta) return GN_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (B == 0) {
+        cudaError_t e = cudaMemsetAsync(ggamma, 0, sizeof(float) * (size_t)P, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gbeta, 0, sizeof(float) * (size_t)P, st);
+        if (e != cudaSuccess) {
+            record_cuda_error(e, "cudaMemsetAsync");
+            return GN_ERR_CUDA;
+        }
+        return GN_OK;
+    }
+    if (!x || !gy || !mean_rstd || !sums || !gx) return GN_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(sums) % 16 || reinterpret_cast<uintptr_t>(mean_rstd) % 8) return GN_ERR_UNSUPPORTED;
+    int rc = check_ws(workspace, workspace_bytes, gn_norm_workspace_bytes(B, P));
+    if (rc != GN_OK) return rc;
+    const NormWs ws = carve_norm(workspace, B);
+    return launch_norm_backward_apply(x, gamma, gy, reinterpret_cast<const float2 *>(mean_rstd),
+                                      reinterpret_cast<const double2 *>(sums), P_total, ws.ac, gx, ggamma, gbeta, B, P, st);
+}
+
 GN_API int gn_step_stats_partials(int M, int N, int K, int block)
 {
     if (M <= 0 || N <= 0 || K <= 0 || (block != 8 && block != 4) || M % 8 || N % 8 || K % 8) return 0;

@@ -130,5 +130,14 @@ int launch_norm_backward(const float *x, const float *gamma, const float *gy, co
                          double2 *partials, float2 *ac, float *gx, float *ggamma, float *gbeta, int B,
                          long long P, int parts, cudaStream_t st);
 int norm_pick_parts(long long P);
+// The same normalisation in pieces, for a grid that is sharded over several ranks: per-sample sums over the local
+// part (the caller adds them up over the ranks), then the element-wise passes with the global figures.
+int launch_norm_local_sums(const float *x, double2 *partials, double2 *sums, int B, long long P, int parts,
+                           cudaStream_t st);
+int launch_norm_backward_local_sums(const float *x, const float *gamma, const float *gy, const float2 *stats,
+                                    double2 *partials, double2 *sums, int B, long long P, int parts, cudaStream_t st);
+int launch_norm_backward_apply(const float *x, const float *gamma, const float *gy, const float2 *stats,
+                               const double2 *sums, long long P_total, float2 *ac, float *gx, float *ggamma, float *gbeta,
+                               int B, long long P, cudaStream_t st);
 
 }  // namespace gn

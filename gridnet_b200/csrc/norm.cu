@@ -168,6 +168,29 @@ __global__ void __launch_bounds__(256) norm_bwd_apply_k(const float *__restrict_
     gbeta[i] = dbt;
 }
 
+// grid B: sums[b] = sum over the nparts partials of sample b, in a fixed order (one thread per sample is plenty)
+__global__ void __launch_bounds__(64) norm_sum_partials_k(const double2 *__restrict__ partials, int nparts,
+                                                          double2 *__restrict__ sums)
+{
+    if (threadIdx.x != 0) return;
+    const double2 *ps = partials + (size_t)blockIdx.x * nparts;
+    double a = 0.0, c = 0.0;
+    for (int i = 0; i < nparts; ++i) {
+        a += ps[i].x;
+        c += ps[i].y;
+    }
+    sums[blockIdx.x] = make_double2(a, c);
+}
+
+// grid B: ac[b] = sums[b] / P (the sums may come from an all-reduce over the ranks that share a grid)
+__global__ void __launch_bounds__(64) norm_scale_sums_k(const double2 *__restrict__ sums, float2 *__restrict__ ac,
+                                                        long long P)
+{
+    if (threadIdx.x != 0) return;
+    const double2 v = sums[blockIdx.x];
+    ac[blockIdx.x] = make_float2((float)(v.x / (double)P), (float)(v.y / (double)P));
+}
+
 // ------------------------------------------------------------------ launchers
 int norm_pick_parts(long long P)
 {
@@ -202,6 +225,32 @@ int launch_norm_apply(const float *x, const float *gamma, const float *beta, con
     const unsigned chunks = (unsigned)((P + 1023) / 1024);
     norm_apply_k<<<(unsigned)B * chunks, 256, 0, st>>>(x, gamma, beta, stats, y, P, chunks);
     return check_launch("norm_apply");
+}
+
+int launch_norm_local_sums(const float *x, double2 *partials, double2 *sums, int B, long long P, int parts,
+                           cudaStream_t st)
+{
+    norm_partial_stats_k<<<(unsigned)B * (unsigned)parts, 256, 0, st>>>(x, partials, P, slice_len(P, parts), parts);
+    norm_sum_partials_k<<<B, 64, 0, st>>>(partials, parts, sums);
+    return check_launch("norm_local_sums");
+}
+
+int launch_norm_backward_local_sums(const float *x, const float *gamma, const float *gy, const float2 *stats,
+                                    double2 *partials, double2 *sums, int B, long long P, int parts, cudaStream_t st)
+{
+    norm_bwd_partial_k<<<(unsigned)B * (unsigned)parts, 256, 0, st>>>(x, gamma, gy, stats, partials, P, slice_len(P, parts),
+                                                                     parts);
+    norm_sum_partials_k<<<B, 64, 0, st>>>(partials, parts, sums);
+    return check_launch("norm_backward_local_sums");
+}
+
+int launch_norm_backward_apply(const float *x, const float *gamma, const float *gy, const float2 *stats,
+                               const double2 *sums, long long P_total, float2 *ac, float *gx, float *ggamma, float *gbeta,
+                               int B, long long P, cudaStream_t st)
+{
+    norm_scale_sums_k<<<B, 64, 0, st>>>(sums, ac, P_total);
+    norm_bwd_apply_k<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(x, gamma, gy, stats, ac, gx, ggamma, gbeta, B, P);
+    return check_launch("norm_backward_apply");
 }
 
 int launch_norm_backward(const float *x, const float *gamma, const float *gy, const float2 *stats,

@@ -11,6 +11,10 @@ parameter. Per outer step there is exactly one exchange:
 * the per-sample (sum, sum of squares) of the step's raw output are all-reduced, because the
   LayerNorm between steps spans the whole grid.
 
+Training (:class:`SlabTrainer`) adds the two exchanges of the backward pass: the all-reduce of the
+LayerNorm backward's per-sample sums, and the reverse face exchange in which the gradient found in a
+rank's ghost columns goes back to the neighbour that owns those columns.
+
 Local layout: ``[..., 8 + K_loc + 8]`` — one ghost block of 8 columns on each side keeps
 block alignment; only ghost column 7 (left) and ``8 + K_loc`` (right) are ever read.
 
@@ -93,6 +97,12 @@ class SlabLayout:
     def put_from_right(self, padded, face):
         padded[..., GHOST + self.k_loc] = face
 
+    def zero_ghosts(self, padded):
+        """Clears both ghost blocks in place (the real columns are untouched)."""
+        padded[..., :GHOST] = 0
+        padded[..., GHOST + self.k_loc:] = 0
+        return padded
+
 
 class CudaSlabBackend:
     """Runs the local arithmetic of one rank through the C ABI (float32, block 8, normalize off)."""
@@ -107,6 +117,7 @@ class CudaSlabBackend:
             assert t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.shape[-1] == layout.k_pad
         self.w, self.b, self.s, self.gamma, self.beta = weight, bias, scale, gamma, beta
         self.inner, self.act, self.ln_eps = int(inner), activation_id(activation), float(ln_eps)
+        self._act_name = activation
         self.M, self.N = bias.shape[0], bias.shape[1]
         self.nparts = 4 * (self.M // 8) * (self.N // 8) * (layout.k_loc // 8)
         self._partials = None
@@ -185,6 +196,60 @@ class CudaSlabBackend:
         self.check(self.lib.gn_norm_apply_f32(x.data_ptr(), self.gamma.data_ptr(), self.beta.data_ptr(),
                                               stats.data_ptr(), y.data_ptr(), B, P, self._stream()))
         return y
+
+
+    # ---- training: the step op and the whole-grid norm on the padded slab, forward and backward ----------------
+    def _norm_ws(self, B, P):
+        n = max(int(self.lib.gn_norm_workspace_bytes(B, P)), 256)
+        return torch.empty(n, dtype=torch.uint8, device=self.w.device)
+
+    def train_step(self, xp):
+        """One step of the op on the whole padded slab (``gn_step_forward_f32``). The ghost blocks are computed
+        too and mean nothing: their weights are zero, and the caller clears them."""
+        from . import gridnet_cuda
+
+        yp = torch.empty_like(xp)
+        gridnet_cuda.forward(self.w, self.b, self.s, xp, yp, self.inner, 8, 1e-5, False, self._act_name)
+        return yp
+
+    def train_step_backward(self, xp, gyp):
+        """Backward of :meth:`train_step` for an upstream gradient that is zero in the ghost blocks: parameter
+        gradients (zero in the ghost blocks) and the gradient of the padded input, whose two ghost columns next
+        to the real ones carry what belongs to the neighbours."""
+        from . import gridnet_cuda
+
+        gw, gb, gs, gxp = (torch.empty_like(t) for t in (self.w, self.b, self.s, xp))
+        gridnet_cuda.backward(self.w, self.b, self.s, xp, gyp.contiguous(), gw, gb, gs, gxp, self.inner, 8, 1e-5, False,
+                              self._act_name)
+        return gw, gb, gs, gxp
+
+    def ln_local_sums(self, sp):
+        B, P = sp.shape[0], sp[0].numel()
+        sums = torch.empty(B, 2, dtype=torch.float64, device=sp.device)
+        ws = self._norm_ws(B, P)
+        self.check(self.lib.gn_norm_local_sums_f32(sp.data_ptr(), sums.data_ptr(), B, P, ws.data_ptr(), ws.numel(),
+                                                   self._stream()))
+        return sums
+
+    def ln_backward_sums(self, sp, gp, stats):
+        B, P = sp.shape[0], sp[0].numel()
+        sums = torch.empty(B, 2, dtype=torch.float64, device=sp.device)
+        ws = self._norm_ws(B, P)
+        self.check(self.lib.gn_norm_backward_local_sums_f32(sp.data_ptr(), self.gamma.data_ptr(), gp.data_ptr(),
+                                                            stats.data_ptr(), sums.data_ptr(), B, P, ws.data_ptr(),
+                                                            ws.numel(), self._stream()))
+        return sums
+
+    def ln_backward_apply(self, sp, gp, stats, sums, count: int):
+        B, P = sp.shape[0], sp[0].numel()
+        gsp, gg, gbt = torch.empty_like(sp), torch.empty_like(self.gamma), torch.empty_like(self.gamma)
+        ws = self._norm_ws(B, P)
+        sums = sums.contiguous()
+        self.check(self.lib.gn_norm_backward_apply_f32(sp.data_ptr(), self.gamma.data_ptr(), gp.data_ptr(),
+                                                       stats.data_ptr(), sums.data_ptr(), int(count), gsp.data_ptr(),
+                                                       gg.data_ptr(), gbt.data_ptr(), B, P, ws.data_ptr(), ws.numel(),
+                                                       self._stream()))
+        return gsp, gg, gbt
 
 
 class SlabRunner:
@@ -427,3 +492,165 @@ def make_cuda_runner(layout: SlabLayout, weight, bias, scale, gamma, beta, x, in
                               sh(beta, True), inner, activation, ln_eps)
     M, N, K = bias.shape
     return SlabRunner(layout, backend, sh(x, True), M * N * K)
+
+
+class SlabTrainer:
+    """One rank's part of a TRAINING step of the model loop on a slab-sharded grid: the forward pass of
+    ``outer`` x (step, whole-grid LayerNorm) keeping what the backward pass needs, then the backward pass.
+
+    What crosses rank boundaries, per outer step (gridnet/scripts/train_mnist.py:62-64 on one device; the
+    single-device semantics of the halo gradient are the tile-gradient scatter of
+    src/gridnet_cuda_kernels.cu:424-435):
+
+    * forward: the two boundary faces of the step's input (into the neighbours' ghost columns) and the
+      per-sample (sum, sum of squares) of the step's output (all-reduce), as in inference;
+    * backward: the all-reduce of the LayerNorm backward's two per-sample sums, and the REVERSE face
+      exchange: the gradient that a rank's boundary blocks leave in its ghost columns belongs to the
+      neighbour's boundary column, which adds it to its own gradient.
+
+    Parameters and their gradients are local to a rank (no weight all-reduce). Like :class:`SlabRunner` this
+    is a state machine; :func:`train_distributed` and :func:`train_emulated` drive it."""
+
+    def __init__(self, layout: SlabLayout, backend, x_padded: torch.Tensor, grid_size: int):
+        self.layout, self.backend, self.grid_size = layout, backend, int(grid_size)
+        self.h = layout.zero_ghosts(x_padded.clone())   # current activations, padded, ghosts clear until faces arrive
+        self.saved = []                                 # per outer step: (step input with faces, step output, stats)
+        self._pending = None
+        self.grads = None                               # (gw, gb, gs, ggamma, gbeta), padded, summed over the steps
+        self.g = None                                   # gradient w.r.t. the current activations, padded, ghosts clear
+
+    # ---- forward
+    def faces_out(self):
+        return self.layout.face_to_left(self.h), self.layout.face_to_right(self.h)
+
+    def faces_in(self, from_left, from_right):
+        if from_left is not None:
+            self.layout.put_from_left(self.h, from_left)
+        if from_right is not None:
+            self.layout.put_from_right(self.h, from_right)
+
+    def forward_step(self):
+        """The step on the padded slab; returns the local (sum, sum of squares) of its real output."""
+        s = self.layout.zero_ghosts(self.backend.train_step(self.h))
+        self._pending = (self.h, s)
+        return self.backend.ln_local_sums(s)
+
+    def forward_norm(self, global_sums):
+        xin, s = self._pending
+        stats = self.backend.finalize(global_sums, self.grid_size)
+        self.saved.append((xin, s, stats))
+        self.h = self.layout.zero_ghosts(self.backend.apply(s, stats, torch.empty_like(s)))
+
+    def output(self):
+        return self.layout.real(self.h).contiguous()
+
+    # ---- backward
+    def backward_begin(self, grad_output_real):
+        self.g = torch.zeros_like(self.h)
+        self.layout.real(self.g).copy_(grad_output_real)
+        self.grads = None
+
+    def backward_norm_sums(self):
+        _, s, stats = self.saved[-1]
+        return self.backend.ln_backward_sums(s, self.g, stats)
+
+    def backward_step(self, global_sums):
+        """LayerNorm backward with the global sums, then the step's backward; returns the gradients that landed in
+        the two ghost columns (for the left and the right neighbour)."""
+        xin, s, stats = self.saved.pop()
+        gs_, gg, gbt = self.backend.ln_backward_apply(s, self.g, stats, global_sums, self.grid_size)
+        self.layout.zero_ghosts(gs_)
+        gw, gb, gsc, gx = self.backend.train_step_backward(xin, gs_)
+        new = (gw, gb, gsc, gg, gbt)
+        self.grads = new if self.grads is None else tuple(a + b for a, b in zip(self.grads, new))
+        lay = self.layout
+        to_left = gx[..., GHOST - 1].contiguous() if lay.left is not None else None
+        to_right = gx[..., GHOST + lay.k_loc].contiguous() if lay.right is not None else None
+        self.g = lay.zero_ghosts(gx)
+        return to_left, to_right
+
+    def backward_faces_in(self, from_left, from_right):
+        """Adds what the neighbours found in their ghost copies of this rank's boundary columns."""
+        lay = self.layout
+        if from_left is not None:
+            self.g[..., GHOST] += from_left
+        if from_right is not None:
+            self.g[..., GHOST + lay.k_loc - 1] += from_right
+
+    def result(self):
+        """(grad_weight, grad_bias, grad_scale, grad_gamma, grad_beta, grad_input) of the real columns."""
+        lay = self.layout
+        return tuple(lay.real(t).contiguous() for t in self.grads) + (lay.real(self.g).contiguous(),)
+
+
+def _swap_with_neighbours(layout: SlabLayout, to_left, to_right, like, group=None):
+    """Grouped send/recv: ``to_left`` / ``to_right`` go to the neighbours, returns what they sent this way."""
+    import torch.distributed as dist
+
+    from_left = torch.empty_like(like) if layout.left is not None else None
+    from_right = torch.empty_like(like) if layout.right is not None else None
+    ops = []
+    if layout.left is not None:
+        ops += [dist.P2POp(dist.isend, to_left, layout.left, group), dist.P2POp(dist.irecv, from_left, layout.left, group)]
+    if layout.right is not None:
+        ops += [dist.P2POp(dist.isend, to_right, layout.right, group), dist.P2POp(dist.irecv, from_right, layout.right, group)]
+    for r in (dist.batch_isend_irecv(ops) if ops else []):
+        r.wait()
+    return from_left, from_right
+
+
+def train_distributed(trainer: SlabTrainer, outer: int, grad_output_fn, group=None):
+    """Forward and backward of the model loop for one rank over torch.distributed (NCCL on GPUs, gloo on CPU).
+    ``grad_output_fn(output_real)`` gives the upstream gradient of this rank's part of the final activations.
+    Returns ``(output_real, gradients)`` with the gradients as in :meth:`SlabTrainer.result`."""
+    import torch.distributed as dist
+
+    lay = trainer.layout
+    for _ in range(outer):
+        to_left, to_right = trainer.faces_out()
+        trainer.faces_in(*_swap_with_neighbours(lay, to_left, to_right, to_left, group))
+        sums = trainer.forward_step()
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
+        trainer.forward_norm(sums)
+    out = trainer.output()
+    trainer.backward_begin(grad_output_fn(out))
+    for _ in range(outer):
+        sums = trainer.backward_norm_sums()
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
+        to_left, to_right = trainer.backward_step(sums)
+        like = to_left if to_left is not None else to_right
+        if like is not None:
+            trainer.backward_faces_in(*_swap_with_neighbours(lay, to_left, to_right, like, group))
+    return out, trainer.result()
+
+
+def train_emulated(trainers, outer: int, grad_output_fn):
+    """:func:`train_distributed` with all ranks in one process, taking turns (tests on one device).
+    ``grad_output_fn(rank, output_real)`` gives each rank's upstream gradient."""
+    world = len(trainers)
+    for _ in range(outer):
+        faces = [t.faces_out() for t in trainers]
+        for i, t in enumerate(trainers):
+            t.faces_in(faces[i - 1][1] if i > 0 else None, faces[i + 1][0] if i + 1 < world else None)
+        total = torch.stack([t.forward_step() for t in trainers]).sum(0)
+        for t in trainers:
+            t.forward_norm(total.clone())
+    outs = [t.output() for t in trainers]
+    for i, t in enumerate(trainers):
+        t.backward_begin(grad_output_fn(i, outs[i]))
+    for _ in range(outer):
+        total = torch.stack([t.backward_norm_sums() for t in trainers]).sum(0)
+        ghost = [t.backward_step(total.clone()) for t in trainers]
+        for i, t in enumerate(trainers):
+            t.backward_faces_in(ghost[i - 1][1] if i > 0 else None, ghost[i + 1][0] if i + 1 < world else None)
+    return outs, [t.result() for t in trainers]
+
+
+def make_cuda_trainer(layout: SlabLayout, weight, bias, scale, gamma, beta, x, inner: int, activation: str = "silu",
+                      ln_eps: float = 1e-5, device=None) -> SlabTrainer:
+    """Shard FULL tensors (any device) for this rank and build its trainer on ``device``."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    sh = lambda t: layout.shard(t, False).to(device)
+    backend = CudaSlabBackend(layout, sh(weight), sh(bias), sh(scale), sh(gamma), sh(beta), inner, activation, ln_eps)
+    M, N, K = bias.shape
+    return SlabTrainer(layout, backend, sh(x), M * N * K)

@@ -203,6 +203,25 @@ GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float 
                          float *grad_gamma, float *grad_beta, int B, long long P, float eps,
                          void *workspace, size_t workspace_bytes, void *stream);
 
+/* The same normalisation in pieces, for a grid whose positions are spread over several ranks (slab sharding:
+ * each rank holds P of the P_total positions of every sample). The caller adds the [B][2] double sums of the
+ * ranks (an all-reduce) between the calls; no counterpart in the reference, which is single-device.
+ *   forward:  gn_norm_local_sums_f32 -> (sum x, sum x^2) per sample over the local part; all-reduce;
+ *             gn_norm_finalize_f32(sums, 1, mean_rstd, B, P_total, eps); gn_norm_apply_f32 on the local part.
+ *   backward: gn_norm_backward_local_sums_f32 -> (sum gy gamma, sum gy gamma xhat) per sample, local; all-reduce;
+ *             gn_norm_backward_apply_f32 with the global sums and P_total: grad_x, grad_gamma, grad_beta of the
+ *             local part (overwritten).
+ * workspace: gn_norm_workspace_bytes(B, P). */
+GN_API int gn_norm_local_sums_f32(const float *x, double *sums, int B, long long P, void *workspace,
+                           size_t workspace_bytes, void *stream);
+GN_API int gn_norm_backward_local_sums_f32(const float *x, const float *gamma, const float *grad_y,
+                                    const float *mean_rstd, double *sums, int B, long long P, void *workspace,
+                                    size_t workspace_bytes, void *stream);
+GN_API int gn_norm_backward_apply_f32(const float *x, const float *gamma, const float *grad_y, const float *mean_rstd,
+                               const double *sums, long long P_total, float *grad_x, float *grad_gamma,
+                               float *grad_beta, int B, long long P, void *workspace, size_t workspace_bytes,
+                               void *stream);
+
 /* gn_norm_forward_static_f32: gn_norm_forward_f32 without a workspace argument and without
  * any allocation, for callers that are not allowed to allocate device memory (a host
  * application that has frozen its memory plan, a plug-in running inside another program's

@@ -10,7 +10,8 @@ import torch
 
 from oracle import gridnet_oracle as orc
 
-from gridnet_b200.slab import SlabLayout, SlabRunner, run_distributed, run_emulated
+from gridnet_b200.slab import (SlabLayout, SlabRunner, SlabTrainer, run_distributed, run_emulated, train_distributed,
+                               train_emulated)
 from slab_checker_backend import OracleSlabBackend
 
 
@@ -93,6 +94,107 @@ def test_two_gloo_ranks_match_single_grid_oracle():
     shape, B, inner, outer = (8, 8, 32), 2, 2, 3
     want = orc.outer_forward(*(t.numpy() for t in problem(31, B, shape)), inner, outer, 8)
     assert np.abs(got - want).max() < 1e-10 * (1 + np.abs(want).max())
+
+
+# ---- training: forward + backward with the reverse face exchange --------------------------------------------------
+def oracle_trainer(layout, prob, inner):
+    w, b, s, gamma, beta, x = prob
+    sh = lambda t: layout.shard(t, False)
+    be = OracleSlabBackend(layout, sh(w), sh(b), sh(s), sh(gamma), sh(beta), inner)
+    return SlabTrainer(layout, be, sh(x), b.numel())
+
+
+def upstream(seed, B, shape):
+    return torch.randn(B, *shape, generator=torch.Generator().manual_seed(seed), dtype=torch.float64)
+
+
+def check_training_result(world, shape, outs, results, prob, gy, inner, outer, tol):
+    """R-rank output and gradients (concatenated along K) against the single-grid oracle chain."""
+    want_y = orc.outer_forward(*(t.numpy() for t in prob), inner, outer, 8)
+    want = orc.outer_backward(*(t.numpy() for t in prob), gy.numpy(), inner, outer, 8)
+    got_y = np.concatenate([np.asarray(o, dtype=np.float64) for o in outs], -1)
+    assert np.abs(got_y - want_y).max() <= tol * (1 + np.abs(want_y).max())
+    for i, name in enumerate(("weight", "bias", "scale", "gamma", "beta", "input")):
+        got = np.concatenate([np.asarray(r[i], dtype=np.float64) for r in results], -1)
+        assert got.shape == want[i].shape, name
+        assert np.abs(got - want[i]).max() <= tol * (1 + np.abs(want[i]).max()), (name, np.abs(got - want[i]).max())
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_emulated_training_ranks_match_single_grid_oracle(world):
+    shape, B, inner, outer = (8, 8, 32), 2, 2, 3
+    prob = problem(40, B, shape)
+    gy = upstream(41, B, shape)
+    lays = [SlabLayout(shape[2], world, r) for r in range(world)]
+    trainers = [oracle_trainer(l, prob, inner) for l in lays]
+    outs, results = train_emulated(trainers, outer, lambda r, out: gy[..., lays[r].k0:lays[r].k0 + lays[r].k_loc])
+    check_training_result(world, shape, [o.numpy() for o in outs], [[t.numpy() for t in r] for r in results], prob, gy,
+                          inner, outer, 1e-10)
+
+
+def _gloo_train_worker(rank, world, port, tmpdir):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        shape, B, inner, outer = (8, 8, 32), 2, 2, 3
+        lay = SlabLayout(shape[2], world, rank)
+        gy = upstream(43, B, shape)
+        out, res = train_distributed(oracle_trainer(lay, problem(42, B, shape), inner), outer,
+                                     lambda o: gy[..., lay.k0:lay.k0 + lay.k_loc])
+        np.savez(os.path.join(tmpdir, f"train{rank}.npz"), out=out.numpy(), **{f"g{i}": t.numpy() for i, t in enumerate(res)})
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_train_like_the_single_grid_oracle():
+    import torch.multiprocessing as mp
+
+    world = 2
+    port = 29900 + os.getpid() % 90
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_gloo_train_worker, args=(world, port, tmp), nprocs=world, join=True)
+        zs = [np.load(os.path.join(tmp, f"train{r}.npz")) for r in range(world)]
+        outs = [z["out"] for z in zs]
+        results = [[z[f"g{i}"] for i in range(6)] for z in zs]
+    shape, B, inner, outer = (8, 8, 32), 2, 2, 3
+    check_training_result(world, shape, outs, results, problem(42, B, shape), upstream(43, B, shape), inner, outer, 1e-10)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,shape", [(2, (16, 16, 32)), (4, (8, 16, 64)), (1, (16, 8, 16))])
+def test_cuda_slab_training_matches_single_device(world, shape):
+    """The CUDA backend, ranks emulated on one device: output and all six gradients against the float64 oracle
+    chain (1e-4 relative / 1e-5 absolute, with the float32 oracle's own noise as the allowance) and against the
+    single-device autograd ops of the package."""
+    import gridnet_b200 as gb
+    from gridnet_b200.slab import make_cuda_trainer
+    from util import assert_close
+
+    B, inner, outer = 3, 2, 3
+    prob = [t.float() for t in problem(44, B, shape)]
+    gy = upstream(45, B, shape).float()
+    lays = [SlabLayout(shape[2], world, r) for r in range(world)]
+    trainers = [make_cuda_trainer(l, *prob, inner) for l in lays]
+    outs, results = train_emulated(trainers, outer, lambda r, out: gy[..., lays[r].k0:lays[r].k0 + lays[r].k_loc].cuda())
+    got_y = torch.cat(outs, -1)
+    got = [torch.cat([r[i] for r in results], -1) for i in range(6)]
+    # single device, autograd through the package's ops
+    w, b, s, gamma, beta, x = (t.cuda().requires_grad_(True) for t in prob)
+    h = x
+    for _ in range(outer):
+        h = gb.GridNormOp.apply(gb.GridnetCudaOp.apply(w, b, s, h, inner, 8, 1e-5, False, "silu"), gamma, beta, 1e-5)
+    single = torch.autograd.grad(h, (w, b, s, gamma, beta, x), gy.cuda())
+    assert torch.allclose(got_y, h.detach(), rtol=1e-5, atol=1e-6)
+    for name, a, c in zip(("weight", "bias", "scale", "gamma", "beta", "input"), got, single):
+        assert torch.allclose(a, c, rtol=1e-3, atol=1e-4 * (1 + c.abs().max().item())), (name, (a - c).abs().max().item())
+    args64 = [t.double().numpy() for t in prob] + [gy.double().numpy()]
+    want64 = orc.outer_backward(*args64, inner, outer, 8)
+    want32 = orc.outer_backward(*(a.astype(np.float32) for a in args64), inner, outer, 8)
+    for name, a, r64, r32 in zip(("weight", "bias", "scale", "gamma", "beta", "input"), got, want64, want32):
+        assert_close(a.cpu().numpy(), r64, r32, f"slab training, world {world}: gradient of {name}")
 
 
 @pytest.mark.gpu
