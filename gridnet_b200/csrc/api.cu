@@ -531,7 +531,7 @@ GN_API int gn_norm_backward_apply_f32(const float *x, const float *gamma, const 
                                       const double *sums, long long P_total, float *gx, float *ggamma, float *gbeta,
                                       int B, long long P, void *workspace, size_t workspace_bytes, void *stream)
 {
-    if (B < 0 || P <= 0 || P_total < P) return GN_ERR_BAD_SHAPE;
+    if (B < 0 || P <= 0 || P_total <= 0) return GN_ERR_BAD_SHAPE;  // P may count padding cells whose grad_y is zero
     if (!gamma || !ggamma || !gbeta) return GN_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;
     if (B == 0) {
