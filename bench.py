@@ -415,14 +415,14 @@ def bench_c2(ctx: Ctx):
 
     # ---------------- end to end through the public op with pinned host buffers
     # Host batches go through HostPipelinedForward: host->device copy, the fused loop and the
-    # device->host copy of each batch run on three streams, two device buffer sets deep, so the
+    # device->host copy of each batch run on three streams, three device buffer sets deep, so the
     # copies of one step overlap the compute of its neighbours. All copies are inside the timed region.
-    hx = [x.pin_memory() for x in xs_host[:2]]
+    hx = [x.pin_memory() for x in xs_host[:3]]
     hy = [torch.empty_like(h).pin_memory() for h in hx]
     pipe = gb.HostPipelinedForward(w, b, s, gamma, beta, BATCH, INNER, OUTER, BLOCK, ACT)
 
-    for i in range(3):
-        pipe.submit(hx[i % 2], hy[i % 2])
+    for i in range(4):
+        pipe.submit(hx[i % 3], hy[i % 3])
     pipe.synchronize()
     ctx.barrier()
     n_e2e = max(3, args.steps)  # the same K as the device-resident figure; includes filling and draining the pipeline
@@ -430,7 +430,7 @@ def bench_c2(ctx: Ctx):
     t0.record()
     pipe.join()  # nothing of the pipeline starts before the start event
     for i in range(n_e2e):
-        pipe.submit(hx[i % 2], hy[i % 2])
+        pipe.submit(hx[i % 3], hy[i % 3])
     pipe.join()  # the current stream waits for the last device->host copy
     t1.record()
     ctx.barrier()

@@ -374,11 +374,13 @@ class HostPipelinedForward:
     ``submit(host_x, host_y)`` queues host->device copy, :func:`outer_forward` and device->host
     copy of one batch on three streams with ``depth`` device buffer sets, so the copies of one
     batch overlap the compute of its neighbours; ``synchronize()`` waits for everything queued.
+    A buffer set is busy for copy-in + compute + copy-out, so three sets (the default) are what
+    keeps all three stages running at once; with two, a step takes half of that sum.
     ``host_x`` / ``host_y`` are ``[B, M, N, K]`` float32 CPU tensors (pinned for real overlap).
     """
 
     def __init__(self, weight, bias, residual_scale, norm_weight, norm_bias, batch: int, inner_iters: int,
-                 outer_iters: int, block_size: int, activation: str = "silu", ln_eps: float = 1e-5, depth: int = 2):
+                 outer_iters: int, block_size: int, activation: str = "silu", ln_eps: float = 1e-5, depth: int = 3):
         self.params = (weight, bias, residual_scale, norm_weight, norm_bias)
         self.cfg = (int(inner_iters), int(outer_iters), int(block_size), activation, float(ln_eps))
         dev = weight.device

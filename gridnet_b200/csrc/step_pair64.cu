@@ -618,16 +618,27 @@ __global__ void __launch_bounds__(256) pair64_pack_k(const float *__restrict__ w
                                                      const float *__restrict__ beta, float *__restrict__ out, int M, int N,
                                                      int K)
 {
-    extern __shared__ float stage[];  // [29][512]: 27 taps, bias, scale
+    extern __shared__ __align__(16) float stage[];  // [29][512]: 27 taps, bias, scale
     const int nbx = K >> 3, nby = N >> 3;
     const int brick = blockIdx.x;
     const int bx = brick % nbx, by = (brick / nbx) % nby, bz = brick / nbx / nby;
     const size_t P = (size_t)M * N * K;
-    for (int idx = threadIdx.x; idx < 29 * 512; idx += 256) {
-        const int t = idx >> 9, n = idx & 511;
-        const int z = n >> 6, y = (n >> 3) & 7, x = n & 7;
-        const size_t gi = ((size_t)(bz * 8 + z) * N + (by * 8 + y)) * K + (bx * 8 + x);
-        stage[idx] = t < 27 ? w[(size_t)t * P + gi] : (t == 27 ? b[gi] : s[gi]);
+    const bool vec = ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(s)) & 15) == 0;
+    if (vec) {  // K is a multiple of 8, so half a block row is an aligned float4
+        for (int idx = threadIdx.x; idx < 29 * 128; idx += 256) {
+            const int t = idx >> 7, n = (idx & 127) * 4;
+            const int z = n >> 6, y = (n >> 3) & 7, x = n & 7;
+            const size_t gi = ((size_t)(bz * 8 + z) * N + (by * 8 + y)) * K + (bx * 8 + x);
+            const float *src = t < 27 ? w + (size_t)t * P + gi : (t == 27 ? b + gi : s + gi);
+            *reinterpret_cast<float4 *>(stage + t * 512 + n) = *reinterpret_cast<const float4 *>(src);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < 29 * 512; idx += 256) {
+            const int t = idx >> 9, n = idx & 511;
+            const int z = n >> 6, y = (n >> 3) & 7, x = n & 7;
+            const size_t gi = ((size_t)(bz * 8 + z) * N + (by * 8 + y)) * K + (bx * 8 + x);
+            stage[idx] = t < 27 ? w[(size_t)t * P + gi] : (t == 27 ? b[gi] : s[gi]);
+        }
     }
     __syncthreads();
     float *o = out + (size_t)brick * 2 * pair64::PK_F;
