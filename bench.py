@@ -509,7 +509,8 @@ def slab_parity_on_ranks(ctx: Ctx) -> dict:
     import torch
 
     import gridnet_b200 as gb
-    from gridnet_b200.slab import PeerFaceBuffers, SlabLayout, make_cuda_runner, run_direct, run_distributed
+    from gridnet_b200.slab import (PeerFaceBuffers, PeerStatsMailboxes, SlabLayout, make_cuda_runner, run_direct,
+                                   run_distributed)
 
     dist = ctx.need_group()
     world, rank, device = ctx.world, ctx.rank, ctx.device
@@ -526,10 +527,11 @@ def slab_parity_on_ranks(ctx: Ctx) -> dict:
     x[..., 0] = torch.randn(B, M, N, generator=g)
     lay = SlabLayout(K, world, rank)
     peers = PeerFaceBuffers(lay, B, M, N, device)
+    boxes = PeerStatsMailboxes(lay, B, device)
     outs = {}
     for name in ("direct", "nccl"):
         runner = make_cuda_runner(lay, w, b, s, gamma, beta, x, inner, ACT, device=device)
-        local = run_direct(runner, outer, peers) if name == "direct" else run_distributed(runner, outer)
+        local = run_direct(runner, outer, peers, mailboxes=boxes) if name == "direct" else run_distributed(runner, outer)
         parts = [torch.empty_like(local) for _ in range(world)] if rank == 0 else None
         dist.gather(local.contiguous(), parts, dst=0)
         if rank == 0:
@@ -543,7 +545,8 @@ def slab_parity_on_ranks(ctx: Ctx) -> dict:
         ok = bool((e_direct <= tol).all().item()) and bool((e_nccl <= tol).all().item())
         verdict = torch.tensor([1.0 if ok else 0.0, float(e_direct.max().item()), float(e_nccl.max().item())], device=device)
     dist.broadcast(verdict, src=0)
-    del peers
+    mailbox_wait_failed = boxes.failed()
+    del peers, boxes
 
     # training on the real ranks: forward + backward with the reverse face exchange and both all-reduces over NCCL,
     # gathered and compared with rank 0's single-GPU autograd through the package's ops
@@ -572,7 +575,8 @@ def slab_parity_on_ranks(ctx: Ctx) -> dict:
             okb = okb and bool(((a - c).abs() <= 1e-4 * (1 + c.abs().max()) + 1e-3 * c.abs()).all().item())
         bverdict = torch.tensor([1.0 if okb else 0.0, worst], device=device)
     dist.broadcast(bverdict, src=0)
-    return {"slab_parity_ok": bool(verdict[0].item() > 0.5) and bool(bverdict[0].item() > 0.5),
+    return {"slab_parity_ok": bool(verdict[0].item() > 0.5) and bool(bverdict[0].item() > 0.5) and not mailbox_wait_failed,
+            "mailbox_wait_failed": mailbox_wait_failed,
             "slab_forward_parity_ok": bool(verdict[0].item() > 0.5),
             "slab_backward_parity_ok": bool(bverdict[0].item() > 0.5),
             "backward_worst_err_over_max": float(bverdict[1].item()),
@@ -589,8 +593,8 @@ def bench_slab(ctx: Ctx):
     slab-sharded along K over all ranks (strong scaling: the total work is fixed)."""
     import torch
 
-    from gridnet_b200.slab import (GHOST, CudaSlabBackend, PeerFaceBuffers, SlabLayout, SlabRunner, run_direct,
-                                   run_distributed)
+    from gridnet_b200.slab import (GHOST, CudaSlabBackend, PeerFaceBuffers, PeerStatsMailboxes, SlabLayout, SlabRunner,
+                                   run_direct, run_distributed)
 
     args, rank, world, device = ctx.args, ctx.rank, ctx.world, ctx.device
     dist = ctx.need_group()
@@ -619,10 +623,11 @@ def bench_slab(ctx: Ctx):
     # with NCCL send/recv (--slab-exchange nccl)
     direct = args.slab_exchange == "direct" and world > 1
     peers = PeerFaceBuffers(lay, B, G, G, device) if direct else None
+    boxes = PeerStatsMailboxes(lay, B, device) if direct else None
 
     def one_pass():
         runner = SlabRunner(lay, backend, x, G * G * G)
-        return run_direct(runner, outer, peers) if direct else run_distributed(runner, outer)
+        return run_direct(runner, outer, peers, mailboxes=boxes) if direct else run_distributed(runner, outer)
 
     warm = max(1, min(args.warmup, 2))
     for _ in range(warm):
@@ -649,14 +654,17 @@ def bench_slab(ctx: Ctx):
         "config": {"workload": "C5: 256^3 grid, block 8, 2 inner x 32 outer, batch 32, fp32, forward + whole-grid "
                                "LayerNorm, slab-sharded along K", "parallelism": f"slab x{world}",
                    "exchange": ("per outer step: the step kernel stores 2 faces [32,256,256] fp32 into the neighbours' memory "
-                                "over NVLink; all-reduce of [32,2] f64" if direct else
+                                "over NVLink; the [32,2] f64 sums go to every rank's mailbox by peer stores and flags "
+                                "(no collective call)" if direct else
                                 "per outer step: 2 faces [32,256,256] fp32 send/recv per neighbour + all-reduce of [32,2] f64"),
                    "samples_per_sec": B * steps / (ms * 1e-3), "finite": finite, "output_checksum": float(chk.item())},
-        "gpu_launches": (outer * 2 + 1) * steps,
+        "gpu_launches": (outer * 3 + 1) * steps if direct else (outer * 2 + 1) * steps,
     }
+    if boxes is not None:
+        rec["mailbox_wait_failed"] = boxes.failed()
     if parity is not None:
         rec.update(parity)
-    del backend, peers, w, x, out
+    del backend, peers, boxes, w, x, out
     ctx.release()
     return rec
 

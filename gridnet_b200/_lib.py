@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_double, c_float, c_int, c_longlong, c_size_t, c_void_p
+from ctypes import c_char_p, c_double, c_float, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libgridnet_b200.so")
@@ -61,6 +61,10 @@ SIGNATURES = {
     "gn_step_forward_slab_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P]),
     "gn_step_forward_slab_faces_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P, _P, _P]),
     "gn_slab_unpack_faces_f32": (c_int, [_P] * 3 + _geom + [c_int, c_int, _P]),
+    "gn_slab_mailbox_bytes": (c_size_t, [c_int, c_int]),
+    "gn_slab_publish_sums_f32": (c_int, [_P, c_int, c_int, c_int, c_int, _P, c_int, c_ulonglong, _P]),
+    "gn_slab_finalize_unpack_f32": (c_int, [_P, c_int, c_int, c_int, c_ulonglong, c_longlong, c_float, _P, _P, _P, _P,
+                                            c_int, c_int, c_int, c_int, c_int, _P, _P]),
     "gn_norm_finalize_f32": (c_int, [_P, c_int, _P, c_int, c_longlong, c_float, _P]),
     "gn_norm_apply_f32": (c_int, [_P] * 5 + [c_int, c_longlong, _P]),
     "gn_outer_forward_workspace_bytes": (c_size_t, [c_int] * 5),

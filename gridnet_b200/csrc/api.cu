@@ -642,6 +642,38 @@ GN_API int gn_slab_unpack_faces_f32(const float *from_left, const float *from_ri
     return launch_slab_unpack_faces(from_left, from_right, x, B, M, N, K, col_left, col_right, (cudaStream_t)stream);
 }
 
+GN_API size_t gn_slab_mailbox_bytes(int world, int B)
+{
+    if (world < 1 || world > 16 || B <= 0) return 0;
+    return slab_mailbox_bytes(world, B);
+}
+
+GN_API int gn_slab_publish_sums_f32(const double *partials, int partials_per_sample, int B, int rank, int world,
+                                    void *const *mailboxes, int parity, unsigned long long step, void *stream)
+{
+    if (B <= 0 || partials_per_sample <= 0 || (parity != 0 && parity != 1) || step == 0) return GN_ERR_BAD_SHAPE;
+    if (!partials || !mailboxes) return GN_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(partials) % 16) return GN_ERR_UNSUPPORTED;
+    return launch_slab_publish_sums(reinterpret_cast<const double2 *>(partials), partials_per_sample, B, rank, world, mailboxes,
+                                    parity, step, (cudaStream_t)stream);
+}
+
+GN_API int gn_slab_finalize_unpack_f32(const void *mailbox, int world, int B, int parity, unsigned long long step,
+                                       long long count, float eps, float *mean_rstd, const float *from_left,
+                                       const float *from_right, float *x, int M, int N, int K, int col_left, int col_right,
+                                       int *error_flag, void *stream)
+{
+    if (B <= 0 || count <= 0 || (parity != 0 && parity != 1) || step == 0) return GN_ERR_BAD_SHAPE;
+    if ((from_left || from_right) && (M <= 0 || N <= 0 || K <= 0 || col_left < 0 || col_left >= K || col_right < 0 || col_right >= K))
+        return GN_ERR_BAD_SHAPE;
+    if (!mailbox || !mean_rstd) return GN_ERR_NULL_POINTER;
+    if ((from_left || from_right) && !x) return GN_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(mailbox) % 16 || reinterpret_cast<uintptr_t>(mean_rstd) % 8) return GN_ERR_UNSUPPORTED;
+    return launch_slab_finalize_unpack(mailbox, world, B, parity, step, count, eps, reinterpret_cast<float2 *>(mean_rstd),
+                                       from_left, from_right, x, M, N, K, col_left, col_right,
+                                       error_flag ? error_flag : device_status_ptr(), (cudaStream_t)stream);
+}
+
 GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_rstd, int B, long long P, float eps,
                          void *stream)
 {

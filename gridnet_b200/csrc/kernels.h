@@ -64,6 +64,14 @@ int launch_gated_fwd_fast8(const float *w, const float *b, const float *x, float
 int launch_slab_unpack_faces(const float *from_left, const float *from_right, float *x, int B, int M, int N, int K,
                              int col_left, int col_right, cudaStream_t st);
 
+// statistics exchange of the slab mode through mailboxes in peer-mapped memory (no collective call)
+size_t slab_mailbox_bytes(int world, int B);
+int launch_slab_publish_sums(const double2 *partials, int nparts, int B, int rank, int world, void *const *mailboxes,
+                             int parity, unsigned long long step, cudaStream_t st);
+int launch_slab_finalize_unpack(const void *mailbox, int world, int B, int parity, unsigned long long step, long long count,
+                                float eps, float2 *stats, const float *from_left, const float *from_right, float *x, int M,
+                                int N, int K, int col_left, int col_right, int *error_flag, cudaStream_t st);
+
 // ---- step_bwd_fast.cu (tuned float backward, block 8, normalize off; needs a workspace)
 size_t bwd_fast8_stash_floats(int B, int M, int N, int K, int inner);
 size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner, bool with_stash);

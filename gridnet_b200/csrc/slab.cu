@@ -27,4 +27,154 @@ int launch_slab_unpack_faces(const float *from_left, const float *from_right, fl
     return check_launch("slab_unpack_faces");
 }
 
+// ---- the statistics exchange without a collective call ------------------------------------------------------
+// Every rank owns a "mailbox" (normally in memory that all ranks have mapped): for each of two step parities and
+// each source rank, [B] (sum, sum of squares) in double and a 64-bit flag. After its step kernel a rank adds up
+// its own partials per sample and stores the sums into slot [parity][its rank] of EVERY rank's mailbox (plain
+// peer stores), fences, and then stores the step number into the matching flags. The receiving side waits, with
+// an iteration limit, until the flags of all ranks show the step number, adds the sums in rank order (so every
+// rank gets the same bits), finishes the statistics and unpacks the two faces that the neighbours' step kernels
+// stored before they published. A flag only ever grows, so nothing has to be cleared between steps; two parities
+// suffice because a rank cannot be more than one step ahead of a neighbour it needs sums from.
+
+constexpr int kMaxSlabWorld = 16;
+constexpr unsigned kMailboxSpinLimit = 1u << 22;  // x ~100 ns of sleep between polls: well under a second
+
+struct SlabMailboxes {
+    unsigned char *base[kMaxSlabWorld];  // every rank's mailbox (own rank included)
+};
+
+// layout of one mailbox, in bytes
+__host__ __device__ inline size_t mailbox_sums_offset(int parity, int src, int world, int B)
+{
+    return ((size_t)(parity * world + src) * B) * sizeof(double2);
+}
+__host__ __device__ inline size_t mailbox_flags_offset(int world, int B)
+{
+    return (size_t)2 * world * B * sizeof(double2);
+}
+size_t slab_mailbox_bytes(int world, int B)
+{
+    return mailbox_flags_offset(world, B) + (size_t)2 * world * sizeof(unsigned long long) + 64;  // + the CTA counter
+}
+
+// grid B: one CTA adds up a sample's partials (fixed order) and stores the pair into every mailbox; the CTA that
+// finishes last publishes the flags
+__global__ void __launch_bounds__(256) slab_publish_sums_k(const double2 *__restrict__ partials, int nparts, int B,
+                                                           int rank, int world, SlabMailboxes boxes, int parity,
+                                                           unsigned long long step)
+{
+    __shared__ double red[33];
+    __shared__ bool last;
+    const int b = blockIdx.x;
+    const double2 *ps = partials + (size_t)b * nparts;
+    double s = 0.0, q = 0.0;
+    for (int i = threadIdx.x; i < nparts; i += blockDim.x) {
+        const double2 v = ps[i];
+        s += v.x;
+        q += v.y;
+    }
+    s = block_sum(s, red);
+    q = block_sum(q, red);
+    if (threadIdx.x < world) {
+        double2 *dst = reinterpret_cast<double2 *>(boxes.base[threadIdx.x] + mailbox_sums_offset(parity, rank, world, B));
+        dst[b] = make_double2(s, q);
+    }
+    __threadfence_system();  // the sums are out before this CTA counts itself as done
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned *counter = reinterpret_cast<unsigned *>(boxes.base[rank] + mailbox_flags_offset(world, B) +
+                                                         (size_t)2 * world * sizeof(unsigned long long));
+        last = atomicAdd(counter, 1u) == (unsigned)B - 1;
+        if (last) *counter = 0;  // ready for the next step (launches on a stream do not overlap)
+    }
+    __syncthreads();
+    if (last && threadIdx.x < world) {
+        __threadfence_system();  // order the other CTAs' stores, seen through the counter, before the flags
+        unsigned long long *flag = reinterpret_cast<unsigned long long *>(boxes.base[threadIdx.x] + mailbox_flags_offset(world, B)) +
+                                   parity * world + rank;
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flag), "l"(step) : "memory");
+    }
+}
+
+// Waits for the step's flags of all ranks in this rank's mailbox, then: CTAs 0 .. B-1 finish the statistics of one
+// sample each; all CTAs unpack the two faces (as slab_unpack_faces_k). A wait that runs out sets *error_flag and
+// carries on.
+__global__ void __launch_bounds__(256) slab_finalize_unpack_k(const unsigned char *__restrict__ box, int world, int B,
+                                                              int parity, unsigned long long step, long long count, float eps,
+                                                              float2 *__restrict__ stats, const float *__restrict__ from_left,
+                                                              const float *__restrict__ from_right, float *__restrict__ x,
+                                                              size_t cells, int K, int col_left, int col_right,
+                                                              int *error_flag)
+{
+    __shared__ bool ok;
+    if (threadIdx.x == 0) {
+        const unsigned long long *flags =
+            reinterpret_cast<const unsigned long long *>(box + mailbox_flags_offset(world, B)) + parity * world;
+        bool all = true;
+        for (int r = 0; r < world; ++r) {
+            unsigned spins = 0;
+            unsigned long long v;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flags + r) : "memory");
+                if (v >= step) break;
+                if (++spins > kMailboxSpinLimit) {
+                    all = false;
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        ok = all;
+        if (!all && error_flag) *error_flag = 1;
+    }
+    __syncthreads();
+    if ((int)blockIdx.x < B && threadIdx.x == 0) {
+        const int b = blockIdx.x;
+        double s = 0.0, q = 0.0;
+        for (int r = 0; r < world; ++r) {
+            const double2 v = reinterpret_cast<const double2 *>(box + mailbox_sums_offset(parity, r, world, B))[b];
+            s += v.x;
+            q += v.y;
+        }
+        const double mean = s / (double)count;
+        double var = q / (double)count - mean * mean;
+        if (var < 0.0) var = 0.0;
+        stats[b] = make_float2((float)mean, (float)(1.0 / sqrt(var + (double)eps)));
+    }
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < cells; i += (size_t)gridDim.x * blockDim.x) {
+        if (from_left) x[i * K + col_left] = from_left[i];
+        if (from_right) x[i * K + col_right] = from_right[i];
+    }
+}
+
+int launch_slab_publish_sums(const double2 *partials, int nparts, int B, int rank, int world, void *const *mailboxes,
+                             int parity, unsigned long long step, cudaStream_t st)
+{
+    if (world < 1 || world > kMaxSlabWorld || rank < 0 || rank >= world) return GN_ERR_BAD_SHAPE;
+    SlabMailboxes boxes{};
+    for (int r = 0; r < world; ++r) {
+        if (!mailboxes[r]) return GN_ERR_NULL_POINTER;
+        boxes.base[r] = static_cast<unsigned char *>(mailboxes[r]);
+    }
+    slab_publish_sums_k<<<B, 256, 0, st>>>(partials, nparts, B, rank, world, boxes, parity, step);
+    return check_launch("slab_publish_sums");
+}
+
+int launch_slab_finalize_unpack(const void *mailbox, int world, int B, int parity, unsigned long long step, long long count,
+                                float eps, float2 *stats, const float *from_left, const float *from_right, float *x, int M,
+                                int N, int K, int col_left, int col_right, int *error_flag, cudaStream_t st)
+{
+    if (world < 1 || world > kMaxSlabWorld) return GN_ERR_BAD_SHAPE;
+    const size_t cells = (from_left || from_right) ? (size_t)B * M * N : 0;
+    size_t ctas = (cells + 255) / 256;
+    if (ctas < (size_t)B) ctas = B;
+    const size_t cap = (size_t)sm_count() * 8;
+    if (ctas > cap) ctas = cap > (size_t)B ? cap : (size_t)B;
+    slab_finalize_unpack_k<<<(unsigned)ctas, 256, 0, st>>>(static_cast<const unsigned char *>(mailbox), world, B, parity, step,
+                                                           count, eps, stats, from_left, from_right, x, cells, K, col_left,
+                                                           col_right, error_flag);
+    return check_launch("slab_finalize_unpack");
+}
+
 }  // namespace gn

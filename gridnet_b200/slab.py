@@ -145,7 +145,7 @@ class CudaSlabBackend:
         self._launch(x, y, in_stats, 1, self.layout.k_loc // 8, 0)
         return self.sums()
 
-    def step_with_faces(self, x, y, in_stats, face_to_left: int, face_to_right: int):
+    def step_with_faces(self, x, y, in_stats, face_to_left: int, face_to_right: int, reduce: bool = True):
         """:meth:`step` whose boundary K-blocks also store their faces, packed ``[B, M, N]``, to the two
         device addresses (0 = no neighbour on that side; normally peer memory)."""
         B = x.shape[0]
@@ -157,7 +157,7 @@ class CudaSlabBackend:
             self._partials.data_ptr(), self.nparts, B, self.M, self.N, self.layout.k_pad,
             1, self.layout.k_loc // 8, self.inner, self.act, face_to_left or None, face_to_right or None,
             self._stream()))
-        return self.sums()
+        return self.sums() if reduce else None
 
     def unpack_faces(self, from_left, from_right, x):
         """Packed faces ``[B, M, N]`` (or None) -> the two ghost columns of the padded slab ``x``."""
@@ -165,6 +165,28 @@ class CudaSlabBackend:
         self.check(self.lib.gn_slab_unpack_faces_f32(
             None if from_left is None else from_left.data_ptr(), None if from_right is None else from_right.data_ptr(),
             x.data_ptr(), B, self.M, self.N, self.layout.k_pad, GHOST - 1, GHOST + self.layout.k_loc, self._stream()))
+
+    def publish_sums(self, mailbox_ptrs, rank: int, world: int, step: int):
+        """Adds up the partials of the last step per sample and stores them, then the step number, into every
+        rank's mailbox (``gn_slab_publish_sums_f32``)."""
+        import ctypes
+
+        B = self._partials.shape[0]
+        arr = (ctypes.c_void_p * world)(*mailbox_ptrs)
+        self.check(self.lib.gn_slab_publish_sums_f32(self._partials.data_ptr(), self.nparts, B, rank, world, arr, step & 1,
+                                                     step, self._stream()))
+
+    def finalize_unpack(self, mailbox, world: int, step: int, count: int, from_left, from_right, x, error_flag=None):
+        """Waits (bounded) for the step's sums of all ranks, finishes the statistics and moves the faces into the
+        ghost columns of ``x`` (``gn_slab_finalize_unpack_f32``); returns ``[B, 2]`` (mean, rstd)."""
+        B = x.shape[0]
+        stats = torch.empty(B, 2, dtype=torch.float32, device=x.device)
+        ptr = lambda t: None if t is None else t.data_ptr()
+        self.check(self.lib.gn_slab_finalize_unpack_f32(
+            mailbox.data_ptr(), world, B, step & 1, step, int(count), self.ln_eps, stats.data_ptr(), ptr(from_left),
+            ptr(from_right), x.data_ptr(), self.M, self.N, self.layout.k_pad, GHOST - 1, GHOST + self.layout.k_loc,
+            ptr(error_flag), self._stream()))
+        return stats
 
     # The same step in two parts, so that the faces can travel while the interior computes:
     # the K-blocks that touch a neighbour slab first, the rest afterwards.
@@ -279,6 +301,13 @@ class SlabRunner:
 
     def unpack(self, from_left, from_right):
         self.backend.unpack_faces(from_left, from_right, self.bufs[self.cur])
+
+    def compute_direct_no_sums(self, face_to_left: int, face_to_right: int):
+        """:meth:`compute_direct` that leaves the partials in the backend (for :class:`PeerStatsMailboxes`)."""
+        nxt = 1 if self.cur != 1 else 2
+        self.backend.step_with_faces(self.bufs[self.cur], self.bufs[nxt], self.stats, face_to_left, face_to_right,
+                                     reduce=False)
+        self.cur = nxt
 
     def can_split(self) -> bool:
         return hasattr(self.backend, "step_boundary")
@@ -424,11 +453,61 @@ class PeerFaceBuffers:
                 self.buf[parity, 1] if lay.right is not None else None)
 
 
-def run_direct(runner: SlabRunner, outer: int, peers: PeerFaceBuffers, group=None) -> torch.Tensor:
+class PeerStatsMailboxes:
+    """One mailbox per rank for the per-sample statistics of a step, allocated in torch's symmetric memory so that
+    every rank can store into every other rank's (plain peer stores; NVLink multicast switched off). With them a
+    step of the slab loop needs no collective call at all: see :func:`run_direct`."""
+
+    def __init__(self, layout: SlabLayout, B: int, device, group=None):
+        import os
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from ._lib import lib
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = layout.world, layout.rank
+        nbytes = int(lib.gn_slab_mailbox_bytes(self.world, B))
+        assert nbytes > 0, "at most 16 ranks"
+        self.buf = symm.empty((nbytes + 7) // 8, dtype=torch.int64, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.step = 0  # outer steps published so far over the life of the mailboxes (flags only ever grow)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def failed(self) -> bool:
+        """True if a wait for the other ranks' sums has run out since the mailboxes were made. Synchronises."""
+        return bool(self.error_flag.item())
+
+
+def run_direct(runner: SlabRunner, outer: int, peers: PeerFaceBuffers, group=None,
+               mailboxes: "PeerStatsMailboxes | None" = None) -> torch.Tensor:
     """Drive one rank for ``outer`` steps with the faces delivered by the step kernel itself
     (:class:`PeerFaceBuffers`): per step one kernel, the all-reduce of the sums, the finalisation of the
-    statistics and the unpacking of the received faces - no pack kernels, no send/recv calls."""
+    statistics and the unpacking of the received faces - no pack kernels, no send/recv calls.
+
+    With ``mailboxes`` the all-reduce goes too: the sums travel by peer stores and flags
+    (:class:`PeerStatsMailboxes`), so a step is three launches and no collective call; the flag that says "this
+    rank's sums have landed" also says "its face stores have landed", since both come from the same stream."""
     import torch.distributed as dist
+
+    if mailboxes is not None:
+        be, lay = runner.backend, runner.layout
+        for k in range(outer):
+            mailboxes.step += 1
+            step = mailboxes.step
+            q = step & 1
+            runner.compute_direct_no_sums(*peers.target(q))
+            be.publish_sums(mailboxes.ptrs, lay.rank, lay.world, step)
+            from_left, from_right = peers.received(q)
+            runner.stats = be.finalize_unpack(mailboxes.buf, lay.world, step, runner.grid_size, from_left, from_right,
+                                              runner.bufs[runner.cur], mailboxes.error_flag)
+        return runner.result()
 
     for k in range(outer):
         q = k & 1
@@ -457,6 +536,35 @@ def run_emulated_direct(runners, outer: int):
         for i, r in enumerate(runners):
             r.set_global_sums(total.clone())
             r.unpack(recv[i][q, 0] if i > 0 else None, recv[i][q, 1] if i + 1 < world else None)
+    return [r.result() for r in runners]
+
+
+def run_emulated_mailboxes(runners, outer: int):
+    """:func:`run_direct` with mailboxes, all ranks in one process on one GPU: every rank's step and publish
+    kernels are launched before any rank's finalize kernel, so the waits find their flags already set."""
+    from ._lib import lib
+
+    world = len(runners)
+    first = runners[0].bufs[0]
+    B, M, N = first.shape[0], first.shape[1], first.shape[2]
+    dev = first.device
+    recv = [torch.zeros(2, 2, B, M, N, dtype=torch.float32, device=dev) for _ in range(world)]
+    nbytes = int(lib.gn_slab_mailbox_bytes(world, B))
+    boxes = [torch.zeros((nbytes + 7) // 8, dtype=torch.int64, device=dev) for _ in range(world)]
+    ptrs = [b.data_ptr() for b in boxes]
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    for k in range(outer):
+        step = k + 1
+        q = step & 1
+        for i, r in enumerate(runners):
+            to_left = recv[i - 1][q, 1].data_ptr() if i > 0 else 0
+            to_right = recv[i + 1][q, 0].data_ptr() if i + 1 < world else 0
+            r.compute_direct_no_sums(to_left, to_right)
+            r.backend.publish_sums(ptrs, i, world, step)
+        for i, r in enumerate(runners):
+            r.stats = r.backend.finalize_unpack(boxes[i], world, step, r.grid_size, recv[i][q, 0] if i > 0 else None,
+                                                recv[i][q, 1] if i + 1 < world else None, r.bufs[r.cur], flag)
+    assert not bool(flag.item()), "a wait for the ranks' sums ran out"
     return [r.result() for r in runners]
 
 

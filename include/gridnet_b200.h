@@ -331,6 +331,27 @@ GN_API int gn_step_forward_slab_faces_f32(const float *weight, const float *bias
  * float array x [B, M, N, K]; either source may be NULL. */
 GN_API int gn_slab_unpack_faces_f32(const float *from_left, const float *from_right, float *x, int B,
                              int M, int N, int K, int col_left, int col_right, void *stream);
+/* The statistics exchange of the slab mode without a collective call. Every rank owns a mailbox of
+ * gn_slab_mailbox_bytes(world, B) bytes, zero-filled once, in memory that all ranks have mapped (world <= 16).
+ * After the step kernel of outer step number `step` (1, 2, 3, ...; parity = step & 1):
+ *   gn_slab_publish_sums_f32     adds this rank's partials per sample and stores the [B][2] double sums into
+ *                                every rank's mailbox (mailboxes[r] = rank r's mailbox as mapped here), then
+ *                                publishes them by storing `step` into the mailboxes' flags (release, system scope);
+ *   gn_slab_finalize_unpack_f32  waits, with an iteration limit, until this rank's mailbox shows `step` from all
+ *                                ranks, adds the sums in rank order, writes mean_rstd [B][2] over `count` values
+ *                                per sample, and moves the two faces (as gn_slab_unpack_faces_f32; either may be
+ *                                NULL). If the wait runs out it sets *error_flag (NULL: the library's status word,
+ *                                gn_device_status) and returns garbage statistics rather than hang.
+ * The waiting kernel and the publishing kernels of the other ranks must be able to run at the same time: one rank
+ * per GPU (or, with all ranks on one GPU, every rank's publish launched before any finalize). No counterpart in
+ * the reference (it is single-GPU). */
+GN_API size_t gn_slab_mailbox_bytes(int world, int B);
+GN_API int gn_slab_publish_sums_f32(const double *partials, int partials_per_sample, int B, int rank, int world,
+                             void *const *mailboxes, int parity, unsigned long long step, void *stream);
+GN_API int gn_slab_finalize_unpack_f32(const void *mailbox, int world, int B, int parity, unsigned long long step,
+                                long long count, float eps, float *mean_rstd, const float *from_left,
+                                const float *from_right, float *x, int M, int N, int K, int col_left,
+                                int col_right, int *error_flag, void *stream);
 GN_API int gn_norm_finalize_f32(const double *partials, int nparts, float *mean_rstd, int B,
                          long long P, float eps, void *stream);
 GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *beta,
