@@ -16,6 +16,7 @@ from .backend_cuda import (GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, HostPi
 from .modules import (GatedGridnet, Gridnet, GridnetModel, GridNorm, Readout, gated_gridnet_step,
                       gridnet_step)
 from .script_models import ImageNetModel, MnistModel
+from .web_checkpoint import read_web_checkpoint, write_web_checkpoint
 
 __all__ = [
     "Gridnet",
@@ -41,6 +42,8 @@ __all__ = [
     "norm_apply",
     "step_stats_partials",
     "gridnet_cuda",
+    "write_web_checkpoint",
+    "read_web_checkpoint",
     "GridnetB200Error",
     "LIB_PATH",
 ]
