@@ -58,6 +58,7 @@ SIGNATURES = {
     "gn_pair64_interleave_f32": (c_int, [_P] * 2 + _geom + [_P]),
     "gn_pair64_deinterleave_f32": (c_int, [_P] * 5 + _geom + [_P]),
     "gn_step_forward_pair64_f32": (c_int, [_P] * 5 + [c_int] + _geom + [c_int, c_int, _P, _P]),
+    "gn_step_forward_train_f32": (c_int, [_P] * 9 + _geom + [c_int, c_int, c_int, _P, c_size_t, _P]),
     "gn_step_forward_slab_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P]),
     "gn_step_forward_slab_faces_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P, _P, _P]),
     "gn_slab_unpack_faces_f32": (c_int, [_P] * 3 + _geom + [c_int, c_int, _P]),

@@ -189,6 +189,136 @@ class GridNormOp(torch.autograd.Function):
         return gx, gg, gb, None
 
 
+class FusedLoopTrainOp(torch.autograd.Function):
+    """The model loop of the reference's scripts with gradients:
+
+        h = x
+        for _ in range(outer_iters):
+            h = layer_norm(gridnet_step(weight, bias, residual_scale, h, ..., normalize=False), norm_weight, norm_bias)
+
+    (gridnet/scripts/train_mnist.py:62-64) as ONE autograd node, float32, shared parameters. The forward pass is the
+    fused loop of :func:`outer_forward`: every step kernel reduces the statistics of what it writes and normalises
+    its input while loading it, so between steps only the RAW step outputs (and [B, 2] statistics) exist and are
+    saved - half the activations that the step-by-step composition saves, and two passes over the grid fewer per
+    outer step. The backward pass walks the steps in reverse with the library's LayerNorm backward (reusing the
+    saved statistics) and the tuned step backward, whose normalised input is rebuilt from the saved raw tensor.
+    With the memory-for-time setting (:func:`keep_forward_stash`) the step kernels also keep their inner
+    iterations for the backward, as :class:`GridnetCudaOp` does.
+
+    ``FusedLoopTrainOp.apply(weight, bias, residual_scale, norm_weight, norm_bias, x, inner_iters, outer_iters,
+    block_size, activation, ln_eps)``."""
+
+    @staticmethod
+    def supported(weight, x, inner_iters: int, block_size: int) -> bool:
+        if weight.dtype != torch.float32 or not weight.is_cuda or inner_iters < 1 or x.shape[0] == 0:
+            return False
+        B, M, N, K = x.shape
+        # the tuned forward (needed for the fusion) and the tuned backward both want whole 8^3 regions
+        return block_size in (4, 8) and M % 8 == 0 and N % 8 == 0 and K % 8 == 0 and \
+            int(lib.gn_step_backward_workspace_bytes(B, M, N, K, int(inner_iters), int(block_size), 0, 4)) > 0
+
+    @staticmethod
+    def forward(ctx, weight, bias, residual_scale, norm_weight, norm_bias, x, inner_iters: int, outer_iters: int,
+                block_size: int, activation: str, ln_eps: float):
+        _assert_step_args(weight, bias, residual_scale, x, block_size, False)
+        assert norm_weight.shape == bias.shape == norm_bias.shape, f"{norm_weight.shape=} invalid for {bias.shape=}"
+        x = x.contiguous()
+        _require_f32_cuda(weight=weight, bias=bias, residual_scale=residual_scale, norm_weight=norm_weight,
+                          norm_bias=norm_bias, x=x)
+        B, M, N, K = x.shape
+        P = M * N * K
+        act = activation_id(activation)
+        dev = weight.device
+        nparts = int(lib.gn_step_stats_partials(M, N, K, block_size))
+        partials = torch.empty(B, nparts, 2, dtype=torch.float64, device=dev)
+        need_grad = any(ctx.needs_input_grad[:6])
+        raws, stats, stashes = [], [], []
+        src, src_stats = x, None
+        with torch.cuda.device(dev):
+            st = torch.cuda.current_stream().cuda_stream
+            for _ in range(outer_iters):
+                dst = torch.empty_like(x)
+                stash = None
+                if need_grad and _stash_wanted(weight, x, inner_iters, block_size):
+                    stash = torch.empty(int(lib.gn_step_stash_bytes(B, M, N, K, int(inner_iters), int(block_size))),
+                                        dtype=torch.uint8, device=dev)
+                check(lib.gn_step_forward_train_f32(
+                    weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(), src.data_ptr(), dst.data_ptr(),
+                    norm_weight.data_ptr(), norm_bias.data_ptr(), None if src_stats is None else src_stats.data_ptr(),
+                    partials.data_ptr(), B, M, N, K, int(inner_iters), int(block_size), act,
+                    None if stash is None else stash.data_ptr(), 0 if stash is None else stash.numel(), st))
+                mr = torch.empty(B, 2, dtype=torch.float32, device=dev)
+                check(lib.gn_norm_finalize_f32(partials.data_ptr(), nparts, mr.data_ptr(), B, P, float(ln_eps), st))
+                raws.append(dst)
+                stats.append(mr)
+                stashes.append(stash)
+                src, src_stats = dst, mr
+            y = torch.empty_like(x)
+            if outer_iters:
+                check(lib.gn_norm_apply_f32(src.data_ptr(), norm_weight.data_ptr(), norm_bias.data_ptr(),
+                                            src_stats.data_ptr(), y.data_ptr(), B, P, st))
+            else:
+                y.copy_(x)
+        ctx.save_for_backward(weight, bias, residual_scale, norm_weight, norm_bias, x, *raws, *stats)
+        ctx.stashes = stashes
+        ctx.cfg = (int(inner_iters), int(outer_iters), int(block_size), activation, float(ln_eps))
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        inner, outer, block, activation, ln_eps = ctx.cfg
+        saved = ctx.saved_tensors
+        weight, bias, scale, gamma, beta, x = saved[:6]
+        raws, stats = saved[6:6 + outer], saved[6 + outer:6 + 2 * outer]
+        stashes, ctx.stashes = ctx.stashes, None
+        B, M, N, K = x.shape
+        P = M * N * K
+        dev = weight.device
+        g = grad_y.contiguous()
+        gw = gb = gs = gg = gbt = None
+        with torch.cuda.device(dev):
+            st = torch.cuda.current_stream().cuda_stream
+            nws = _workspace(lib.gn_norm_workspace_bytes(B, P), dev)
+            sums = torch.empty(B, 2, dtype=torch.float64, device=dev)
+            for k in reversed(range(outer)):
+                # LayerNorm backward of step k with the statistics saved by the forward pass
+                gs_k, dg, dbt = torch.empty_like(x), torch.empty_like(gamma), torch.empty_like(gamma)
+                check(lib.gn_norm_backward_local_sums_f32(raws[k].data_ptr(), gamma.data_ptr(), g.data_ptr(),
+                                                          stats[k].data_ptr(), sums.data_ptr(), B, P, nws.data_ptr(),
+                                                          nws.numel(), st))
+                check(lib.gn_norm_backward_apply_f32(raws[k].data_ptr(), gamma.data_ptr(), g.data_ptr(), stats[k].data_ptr(),
+                                                     sums.data_ptr(), P, gs_k.data_ptr(), dg.data_ptr(), dbt.data_ptr(), B, P,
+                                                     nws.data_ptr(), nws.numel(), st))
+                # the step's input: x itself for the first step, else the normalised output of the step before
+                if k == 0:
+                    xin = x
+                else:
+                    xin = torch.empty_like(x)
+                    check(lib.gn_norm_apply_f32(raws[k - 1].data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                                stats[k - 1].data_ptr(), xin.data_ptr(), B, P, st))
+                dw, db, ds, gx = (torch.empty_like(t) for t in (weight, bias, scale, x))
+                if stashes[k] is not None:
+                    gridnet_cuda.backward_with_stash(weight, bias, scale, xin, gs_k, dw, db, ds, gx, inner, block, activation,
+                                                     stashes[k])
+                    stashes[k] = None
+                else:
+                    gridnet_cuda.backward(weight, bias, scale, xin, gs_k, dw, db, ds, gx, inner, block, 1e-5, False,
+                                          activation)
+                if gw is None:
+                    gw, gb, gs, gg, gbt = dw, db, ds, dg, dbt
+                else:
+                    gw += dw
+                    gb += db
+                    gs += ds
+                    gg += dg
+                    gbt += dbt
+                g = gx
+        if outer == 0:
+            z = torch.zeros_like
+            return z(weight), z(bias), z(scale), z(gamma), z(beta), g, None, None, None, None, None
+        return gw, gb, gs, gg, gbt, g, None, None, None, None, None
+
+
 def device_status(clear: bool = True, device=None) -> bool:
     """True if, since the last clear, a kernel on ``device`` gave up a bounded wait on a bulk tile copy and had
     no workspace flag to report it in (the results of that call are invalid). Synchronises the device."""

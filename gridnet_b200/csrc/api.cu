@@ -582,6 +582,36 @@ GN_API int gn_step_forward_fused_f32(const float *w, const float *b, const float
     return launch_step_fwd_fast8(p, act, (cudaStream_t)stream);
 }
 
+GN_API int gn_step_forward_train_f32(const float *w, const float *b, const float *s, const float *x, float *y,
+                                     const float *gamma, const float *beta, const float *in_mean_rstd,
+                                     double *out_partials, int B, int M, int N, int K, int inner, int block, int act,
+                                     void *stash, size_t stash_bytes, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (B == 0) return GN_OK;
+    if (!w || !b || !s || !x || !y) return GN_ERR_NULL_POINTER;
+    if (in_mean_rstd && (!gamma || !beta)) return GN_ERR_NULL_POINTER;
+    FastFwdParams p{};
+    p.w = w; p.b = b; p.s = s; p.x = x; p.y = y; p.gamma = gamma; p.beta = beta;
+    p.in_stats = reinterpret_cast<const float2 *>(in_mean_rstd);
+    p.out_partials = reinterpret_cast<double2 *>(out_partials);
+    p.nparts = gn_step_stats_partials(M, N, K, block);
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner; p.sub = block;
+    if (stash) {
+        const size_t need = gn_step_stash_bytes(B, M, N, K, inner, block);
+        if (need == 0) return GN_ERR_UNSUPPORTED;
+        if (stash_bytes < need || reinterpret_cast<uintptr_t>(stash) % 16) return GN_ERR_WORKSPACE;
+        p.save_h = static_cast<float *>(stash);
+        p.save_x = p.save_h + (size_t)inner * B * M * N * K;
+    }
+    if (!fast8_applicable(p, block, 0)) return GN_ERR_UNSUPPORTED;
+    if ((in_mean_rstd && reinterpret_cast<uintptr_t>(in_mean_rstd) % 8) ||
+        (out_partials && reinterpret_cast<uintptr_t>(out_partials) % 16))
+        return GN_ERR_UNSUPPORTED;
+    return launch_step_fwd_fast8(p, act, (cudaStream_t)stream);
+}
+
 static int slab_forward(const float *w, const float *b, const float *s, const float *x, float *y,
                              const float *gamma, const float *beta, const float *in_mean_rstd,
                              double *out_partials, int partials_per_sample, int B, int M, int N, int K,

@@ -13,7 +13,7 @@ from typing import Tuple
 import torch
 import torch.nn as nn
 
-from .backend_cuda import GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, outer_forward
+from .backend_cuda import FusedLoopTrainOp, GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, outer_forward
 
 
 def _need_cuda(t: torch.Tensor, what: str) -> None:
@@ -101,8 +101,10 @@ class GridnetModel(nn.Module):
     """The loop of the reference's scripts: ``for _ in range(outer_iters): h = network(h); h = norm(h)``
     (gridnet/scripts/train_mnist.py:62-64), with submodules named ``network`` and ``norm`` as there.
 
-    With gradients disabled, a plain float32 network with per-block normalisation off runs as ONE fused
-    call (:func:`outer_forward`); otherwise the two autograd ops are composed step by step."""
+    A plain float32 network with per-block normalisation off runs fused: with gradients disabled as ONE call
+    (:func:`outer_forward`), with gradients as one autograd node over the whole loop (:class:`FusedLoopTrainOp`:
+    statistics out of the step kernels, normalisation on load, only raw step outputs saved). Everything else is
+    the step-by-step composition of the two autograd ops."""
 
     def __init__(self, shape: Tuple[int, int, int], inner_iters: int, outer_iters: int, block_size: int, device,
                  init_scale: float = 1.0, residual_scale: float = 1.0, activation: str = "silu", gated: bool = False,
@@ -119,12 +121,16 @@ class GridnetModel(nn.Module):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         net = self.network
-        fusable = (isinstance(net, Gridnet) and not net.normalize and h.dtype == torch.float32
-                   and not (torch.is_grad_enabled() and (h.requires_grad or any(p.requires_grad for p in self.parameters()))))
-        if fusable:
+        plain = isinstance(net, Gridnet) and not net.normalize and h.dtype == torch.float32
+        with_grad = torch.is_grad_enabled() and (h.requires_grad or any(p.requires_grad for p in self.parameters()))
+        if plain and not with_grad:
             return outer_forward(net.weight, net.bias, net.residual_scale, self.norm.weight, self.norm.bias,
                                  h.contiguous(), net.inner_iterations, self.outer_iters, net.block_size, net.activation,
                                  self.norm.eps)
+        if plain and FusedLoopTrainOp.supported(net.weight, h, net.inner_iterations, net.block_size):
+            return FusedLoopTrainOp.apply(net.weight, net.bias, net.residual_scale, self.norm.weight, self.norm.bias, h,
+                                          net.inner_iterations, self.outer_iters, net.block_size, net.activation,
+                                          self.norm.eps)
         for _ in range(self.outer_iters):
             h = self.norm(net(h))
         return h

@@ -16,7 +16,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from .backend_cuda import outer_forward
+from .backend_cuda import FusedLoopTrainOp, outer_forward
 from .modules import GatedGridnet, Gridnet, GridNorm, Readout
 
 
@@ -26,12 +26,17 @@ def _wants_grad(module: nn.Module, *tensors: torch.Tensor) -> bool:
 
 
 def _plain_loop(network: nn.Module, norm: GridNorm, h: torch.Tensor, outer_iters: int, owner: nn.Module) -> torch.Tensor:
-    """``for _ in range(outer_iters): h = norm(network(h))``, as one fused call when nothing needs a gradient."""
-    if (isinstance(network, Gridnet) and not network.normalize and h.dtype == torch.float32
-            and not _wants_grad(owner, h)):
+    """``for _ in range(outer_iters): h = norm(network(h))``: one fused call when nothing needs a gradient, one
+    autograd node over the whole loop when something does and the tuned kernels apply."""
+    plain = isinstance(network, Gridnet) and not network.normalize and h.dtype == torch.float32
+    if plain and not _wants_grad(owner, h):
         return outer_forward(network.weight, network.bias, network.residual_scale, norm.weight, norm.bias,
                              h.contiguous(), network.inner_iterations, outer_iters, network.block_size,
                              network.activation, norm.eps)
+    if plain and FusedLoopTrainOp.supported(network.weight, h, network.inner_iterations, network.block_size):
+        return FusedLoopTrainOp.apply(network.weight, network.bias, network.residual_scale, norm.weight, norm.bias, h,
+                                      network.inner_iterations, outer_iters, network.block_size, network.activation,
+                                      norm.eps)
     for _ in range(outer_iters):
         h = norm(network(h))
     return h

@@ -262,6 +262,14 @@ GN_API int gn_step_forward_fused_f32(const float *weight, const float *bias, con
                               const float *x, float *y, const float *gamma, const float *beta,
                               const float *in_mean_rstd, double *out_partials, int B, int M,
                               int N, int K, int inner, int block, int activation, void *stream);
+/* gn_step_forward_fused_f32 for the forward pass of TRAINING (block 8 or 4): the same fusion with the
+ * normalisation, and with stash != NULL (gn_step_stash_bytes bytes, 16-byte aligned) it also keeps what
+ * gn_step_backward_stash_f32 needs, like gn_step_forward_stash_f32. The x that the matching backward wants is the
+ * NORMALISED input: gn_norm_apply_f32(x, gamma, beta, in_mean_rstd). No counterpart in the reference. */
+GN_API int gn_step_forward_train_f32(const float *weight, const float *bias, const float *scale, const float *x,
+                              float *y, const float *gamma, const float *beta, const float *in_mean_rstd,
+                              double *out_partials, int B, int M, int N, int K, int inner, int block,
+                              int activation, void *stash, size_t stash_bytes, void *stream);
 /* Large-batch form of gn_step_forward_fused_f32 (block 8, normalize = 0, inner >= 1, M, N, K
  * multiples of 8): same arithmetic as src/gridnet_cuda_kernels.cu:101-200, but a thread owns
  * samples instead of neurons, which needs the activations interleaved by groups of 64 samples

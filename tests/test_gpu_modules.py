@@ -49,6 +49,55 @@ def test_model_fused_inference_equals_training_path_and_oracle():
     want32 = orc.outer_backward(*(a.astype(np.float32) for a in args64), 2, 3, 8)
     for name, g, r64, r32 in zip(names + ["input"], grads, want64, want32):
         assert_close(g.cpu().numpy(), r64, r32, f"model gradient of {name}")
+    # the fused training node against the step-by-step composition of the two autograd ops (same library kernels
+    # underneath, different order of a few float32 operations), with the forward stash on and off
+    for keep in (False, True):
+        previous = gb.keep_forward_stash(keep)
+        try:
+            xs = x.clone().requires_grad_(True)
+            h = xs
+            for _ in range(3):
+                h = model.norm(model.network(h))
+            want = torch.autograd.grad(h, [params[n] for n in names] + [xs], gy)
+            xf = x.clone().requires_grad_(True)
+            outf = model(xf)
+            got = torch.autograd.grad(outf, [params[n] for n in names] + [xf], gy)
+        finally:
+            gb.keep_forward_stash(previous)
+        assert torch.allclose(outf, h, rtol=1e-5, atol=1e-6)
+        for name, a, c in zip(names + ["input"], got, want):
+            assert torch.allclose(a, c, rtol=1e-3, atol=1e-4 * (1 + c.abs().max().item())), (name, keep, (a - c).abs().max().item())
+
+
+@pytest.mark.parametrize("block,shape,B", [(8, (16, 8, 24), 5), (4, (8, 16, 8), 3)])
+def test_fused_training_loop_op(block, shape, B):
+    """FusedLoopTrainOp directly: both block sizes, odd batch, a non-cubic grid, zero outer iterations, and
+    gradients against the float64 oracle chain."""
+    import gridnet_b200 as gb
+    from util import assert_close
+
+    r = np.random.default_rng(61)
+    f = np.float32
+    w = (r.standard_normal((27, *shape)) / np.sqrt(27)).astype(f)
+    b = (0.1 * r.standard_normal(shape)).astype(f)
+    s = (1 + 0.1 * r.standard_normal(shape)).astype(f)
+    ga = (1 + 0.1 * r.standard_normal(shape)).astype(f)
+    be = (0.1 * r.standard_normal(shape)).astype(f)
+    x = r.standard_normal((B, *shape)).astype(f)
+    gy = r.standard_normal((B, *shape)).astype(f)
+    inner, outer = 2, 3
+    leaves = [torch.from_numpy(a).cuda().requires_grad_(True) for a in (w, b, s, ga, be, x)]
+    assert gb.FusedLoopTrainOp.supported(leaves[0], leaves[5], inner, block)
+    y = gb.FusedLoopTrainOp.apply(*leaves, inner, outer, block, "silu", 1e-5)
+    grads = torch.autograd.grad(y, leaves, torch.from_numpy(gy).cuda())
+    a64 = [a.astype(np.float64) for a in (w, b, s, ga, be, x)]
+    assert_close(y.detach().cpu().numpy(), orc.outer_forward(*a64, inner, outer, block), None, "fused training forward")
+    want64 = orc.outer_backward(*a64, gy.astype(np.float64), inner, outer, block)
+    want32 = orc.outer_backward(w, b, s, ga, be, x, gy, inner, outer, block)
+    for name, g, r64, r32 in zip(("weight", "bias", "scale", "gamma", "beta", "input"), grads, want64, want32):
+        assert_close(g.cpu().numpy(), r64, r32, f"fused training gradient of {name} (block {block})")
+    y0 = gb.FusedLoopTrainOp.apply(*leaves, inner, 0, block, "silu", 1e-5)
+    assert torch.equal(y0, leaves[5])
 
 
 def test_gated_model_and_readout_run():
