@@ -71,6 +71,7 @@ SIGNATURES = {
     "gn_outer_forward_workspace_bytes": (c_size_t, [c_int] * 5),
     "gn_outer_forward_error_flag_offset": (c_size_t, [c_int] * 5),
     "gn_outer_forward_f32": (c_int, [_P] * 7 + _geom + [c_int, c_int, c_int, c_float, c_int, _P, c_size_t, _P]),
+    "gn_outer_forward_flags_f32": (c_int, [_P] * 7 + _geom + [c_int, c_int, c_int, c_float, c_int, _P, c_size_t, c_int, _P]),
 }
 
 

@@ -369,13 +369,23 @@ def outer_forward(weight, bias, residual_scale, norm_weight, norm_bias, init_act
     y = torch.empty_like(init_activations) if out is None else out
     need = lib.gn_outer_forward_workspace_bytes(B, M, N, K, block_size)
     ws = workspace if workspace is not None else _workspace(need, weight.device)
+    # A caller-owned workspace keeps the parameters re-ordered for the large-batch kernel between calls. They are
+    # rebuilt unless this very workspace tensor was used by the previous call with the same parameter tensors and
+    # neither they nor the workspace have been written to through torch since (torch counts in-place writes).
+    params = (weight, bias, residual_scale, norm_weight, norm_bias)
+    key = (tuple((t.data_ptr(), t._version) for t in params), (B, M, N, K, int(block_size)))
+    flags = 0
+    if workspace is not None and getattr(ws, "_gn_packed_for", None) == (key, ws._version):
+        flags = 1  # GN_OUTER_PARAMS_UNCHANGED
     with torch.cuda.device(weight.device):
-        check(lib.gn_outer_forward_f32(weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(),
-                                       norm_weight.data_ptr(), norm_bias.data_ptr(),
-                                       init_activations.data_ptr(), y.data_ptr(), B, M, N, K, int(inner_iters),
-                                       int(outer_iters), int(block_size), float(ln_eps),
-                                       activation_id(activation), ws.data_ptr(), ws.numel(),
-                                       torch.cuda.current_stream().cuda_stream))
+        check(lib.gn_outer_forward_flags_f32(weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(),
+                                             norm_weight.data_ptr(), norm_bias.data_ptr(),
+                                             init_activations.data_ptr(), y.data_ptr(), B, M, N, K, int(inner_iters),
+                                             int(outer_iters), int(block_size), float(ln_eps),
+                                             activation_id(activation), ws.data_ptr(), ws.numel(), flags,
+                                             torch.cuda.current_stream().cuda_stream))
+    if workspace is not None:
+        ws._gn_packed_for = (key, ws._version)
     return y
 
 

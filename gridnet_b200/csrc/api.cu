@@ -819,9 +819,32 @@ GN_API size_t gn_outer_forward_error_flag_offset(int B, int M, int N, int K, int
     return (size_t)((unsigned char *)w.error_flag - (unsigned char *)nullptr);
 }
 
+static int outer_forward_impl(const float *w, const float *b, const float *s, const float *gamma, const float *beta,
+                              const float *x, float *y, int B, int M, int N, int K, int inner, int outer, int block,
+                              float ln_eps, int act, void *workspace, size_t workspace_bytes, int flags, void *stream);
+
 GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, const float *gamma, const float *beta,
                          const float *x, float *y, int B, int M, int N, int K, int inner, int outer, int block,
                          float ln_eps, int act, void *workspace, size_t workspace_bytes, void *stream)
+{
+    return outer_forward_impl(w, b, s, gamma, beta, x, y, B, M, N, K, inner, outer, block, ln_eps, act, workspace,
+                              workspace_bytes, 0, stream);
+}
+
+GN_API int gn_outer_forward_flags_f32(const float *w, const float *b, const float *s, const float *gamma, const float *beta,
+                                      const float *x, float *y, int B, int M, int N, int K, int inner, int outer, int block,
+                                      float ln_eps, int act, void *workspace, size_t workspace_bytes, int flags, void *stream)
+{
+    if (flags & ~GN_OUTER_PARAMS_UNCHANGED) return GN_ERR_UNSUPPORTED;
+    return outer_forward_impl(w, b, s, gamma, beta, x, y, B, M, N, K, inner, outer, block, ln_eps, act, workspace,
+                              workspace_bytes, flags, stream);
+}
+
+}  // extern "C"
+
+static int outer_forward_impl(const float *w, const float *b, const float *s, const float *gamma, const float *beta,
+                              const float *x, float *y, int B, int M, int N, int K, int inner, int outer, int block,
+                              float ln_eps, int act, void *workspace, size_t workspace_bytes, int flags, void *stream)
 {
     int rc = check_geometry(B, M, N, K, inner, block, act);
     if (rc != GN_OK) return rc;
@@ -852,8 +875,10 @@ GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, 
             record_cuda_error(e, "cudaMemsetAsync");
             return GN_ERR_CUDA;
         }
-        rc = launch_pair64_pack(w, b, s, gamma, beta, ws.packed, M, N, K, st);
-        if (rc != GN_OK) return rc;
+        if (!(flags & GN_OUTER_PARAMS_UNCHANGED)) {  // else the workspace still holds them from the previous call
+            rc = launch_pair64_pack(w, b, s, gamma, beta, ws.packed, M, N, K, st);
+            if (rc != GN_OK) return rc;
+        }
         rc = launch_to_il64(x, ws.buf[0], B, G, P, st);
         if (rc != GN_OK) return rc;
         for (int o = 0; o < outer; ++o) {
@@ -913,5 +938,3 @@ GN_API int gn_outer_forward_f32(const float *w, const float *b, const float *s, 
     if (fused) return launch_norm_apply(src, gamma, beta, ws.stats, y, B, P, st);
     return GN_OK;
 }
-
-}  // extern "C"

@@ -386,6 +386,16 @@ GN_API int gn_outer_forward_f32(const float *weight, const float *bias, const fl
                          int B, int M, int N, int K, int inner, int outer, int block,
                          float ln_eps, int activation, void *workspace,
                          size_t workspace_bytes, void *stream);
+/* gn_outer_forward_f32 with flags. GN_OUTER_PARAMS_UNCHANGED: the previous call with this workspace had the same
+ * weight, bias, scale, gamma and beta (same values, same shape) and nothing else has written to the workspace
+ * since, so the re-ordered copy of the parameters that the large-batch kernel keeps there is still good and is
+ * not rebuilt (an inference server calls the loop many times between weight updates). */
+#define GN_OUTER_PARAMS_UNCHANGED 1
+GN_API int gn_outer_forward_flags_f32(const float *weight, const float *bias, const float *scale,
+                               const float *norm_weight, const float *norm_bias, const float *x, float *y,
+                               int B, int M, int N, int K, int inner, int outer, int block, float ln_eps,
+                               int activation, void *workspace, size_t workspace_bytes, int flags,
+                               void *stream);
 
 #ifdef __cplusplus
 }

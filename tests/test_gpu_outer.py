@@ -191,6 +191,30 @@ def test_large_batch_kernel_matches_patch_kernel_and_oracle(B, shape, inner, out
                  f"large-batch kernel B={B}")
 
 
+def test_packed_parameters_are_rebuilt_when_parameters_change():
+    """A reused workspace keeps the re-ordered parameters of the large-batch kernel; changing a parameter in place,
+    passing another parameter tensor, or scribbling over the workspace must all lead to a rebuild."""
+    from gridnet_b200 import outer_forward, outer_forward_workspace
+
+    shape, B, inner, outer = (16, 16, 16), 64, 2, 2
+    w, b, s, gamma, beta = (dev(a) for a in model_params(71, shape))
+    x = dev(face_input(72, B, shape))
+    ws = outer_forward_workspace(B, shape, 8, x.device)
+    fresh = lambda *p: outer_forward(*p, x, inner, outer, 8)  # no workspace given: always rebuilt
+    y1 = outer_forward(w, b, s, gamma, beta, x, inner, outer, 8, workspace=ws)
+    assert torch.equal(y1, outer_forward(w, b, s, gamma, beta, x, inner, outer, 8, workspace=ws))  # reused
+    with torch.no_grad():
+        w.mul_(1.5)  # in place: same tensor, new version
+    y2 = outer_forward(w, b, s, gamma, beta, x, inner, outer, 8, workspace=ws)
+    assert torch.equal(y2, fresh(w, b, s, gamma, beta)) and not torch.equal(y2, y1)
+    gamma2 = gamma * 0.5  # another tensor
+    y3 = outer_forward(w, b, s, gamma2, beta, x, inner, outer, 8, workspace=ws)
+    assert torch.equal(y3, fresh(w, b, s, gamma2, beta)) and not torch.equal(y3, y2)
+    ws.fill_(7)  # the caller used the memory for something else in between
+    y4 = outer_forward(w, b, s, gamma2, beta, x, inner, outer, 8, workspace=ws)
+    assert torch.equal(y4, y3)
+
+
 def test_large_batch_step_building_blocks():
     """gn_pair64_* through the C ABI: interleave -> one step without normalisation -> de-interleave equals the
     plain step op; interleave -> de-interleave is the identity."""
