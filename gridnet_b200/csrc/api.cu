@@ -218,9 +218,10 @@ static OuterWs carve_outer(void *base, int B, int M, int N, int K, int block)
     return w;
 }
 
-// 0 = choose automatically (the large-batch kernel of step_pair64.cu when the batch fills its groups of
-// 64 samples well, else the register-patch kernel of step_fast.cu), 1 = always the register-patch
-// kernel, 2 = always the large-batch kernel
+// 0 = choose automatically (the one persistent kernel of outer_small.cu for problems so small that launches are
+// what they cost; the large-batch kernel of step_pair64.cu when the batch fills its groups of 64 samples well; else
+// the register-patch kernel of step_fast.cu, one launch per outer step), 1 = always the register-patch kernel,
+// 2 = always the large-batch kernel, 3 = always the persistent kernel
 static int g_outer_kernel = 0;
 
 // The large-batch kernel computes whole groups of 64 samples: worth it when at most a quarter of the
@@ -274,7 +275,7 @@ GN_API int gn_config_set(const char *key, int value)
 {
     if (!key) return GN_ERR_NULL_POINTER;
     if (!strcmp(key, "outer_kernel")) {
-        if (value < 0 || value > 2) return GN_ERR_UNSUPPORTED;
+        if (value < 0 || value > 3) return GN_ERR_UNSUPPORTED;
         g_outer_kernel = value;
         return GN_OK;
     }
@@ -866,6 +867,21 @@ static int outer_forward_impl(const float *w, const float *b, const float *s, co
     const bool fused = fast8_applicable(p, block, 0);
     const int nparts_fused = (int)((long long)(M / 8) * (N / 8) * (K / 8) * 4);
 
+    if (g_outer_kernel == 0 || g_outer_kernel == 3) {
+        const int spc = outer_small_spc(B, M, N, K, block, inner, outer, w, b, s, gamma, beta, x, y);
+        if (spc > 0) {
+            // the int after the error flag is the counter of the kernel's grid-wide barrier
+            const cudaError_t e = cudaMemsetAsync(ws.error_flag, 0, 2 * sizeof(int), st);
+            if (e != cudaSuccess) {
+                record_cuda_error(e, "cudaMemsetAsync");
+                return GN_ERR_CUDA;
+            }
+            return launch_outer_small(w, b, s, gamma, beta, x, y, ws.buf[0], ws.buf[1], ws.partials,
+                                      reinterpret_cast<unsigned *>(ws.error_flag + 1), ws.error_flag, B, M, N, K, inner, outer,
+                                      spc, ln_eps, act, st);
+        }
+        if (g_outer_kernel == 3) return GN_ERR_UNSUPPORTED;
+    }
     const bool pair_ok = pair64_applicable(M, N, K, block, inner);
     if (pair_ok && (g_outer_kernel == 2 || (g_outer_kernel == 0 && pair64_fills_groups(B)))) {
         const int Bp = round_up64(B), G = Bp / 64;

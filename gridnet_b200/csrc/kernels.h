@@ -125,6 +125,13 @@ int launch_propagate_flag(const int *flag, cudaStream_t st);
 // ---- probe.cu (FFMA-only kernel for the measured FP32 peak)
 int launch_ffma_probe(float *sink, int iters, long long *fma_count, cudaStream_t st);
 
+// ---- outer_small.cu (the whole fused loop as one persistent cooperative kernel, for launch-bound problems)
+int outer_small_spc(int B, int M, int N, int K, int block, int inner, int outer, const void *w, const void *b, const void *s,
+                    const void *gamma, const void *beta, const void *x, const void *y);
+int launch_outer_small(const float *w, const float *b, const float *s, const float *gamma, const float *beta, const float *x,
+                       float *y, float *buf0, float *buf1, double2 *partials, unsigned *barrier, int *error_flag, int B, int M,
+                       int N, int K, int inner, int outer, int spc, float eps, int act, cudaStream_t st);
+
 // ---- norm.cu
 constexpr int kNormMaxParts = 64;
 // per-sample (sum, sum of squares) of x in double, `parts` slices per sample

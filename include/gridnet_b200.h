@@ -68,11 +68,12 @@ GN_API const char *gn_last_cuda_error(void);
 GN_API int gn_activation_from_name(const char *name);
 GN_API int gn_version(void);
 /* Process-wide tuning switches (not needed for normal use). Keys:
- *   "outer_kernel": which step kernel gn_outer_forward_f32 uses: 0 = automatic (default: the
- *                   large-batch kernel when at most a quarter of the last group of 64 samples
- *                   would be padding, else the register-patch kernel), 1 = the register-patch
- *                   kernel, 2 = the large-batch kernel (GN_ERR_UNSUPPORTED from
- *                   gn_outer_forward_f32 when it does not apply).
+ *   "outer_kernel": which kernel gn_outer_forward_f32 uses: 0 = automatic (default: the whole
+ *                   loop as one persistent kernel when the problem is so small that launches are
+ *                   what it costs; the large-batch kernel when at most a quarter of the last group
+ *                   of 64 samples would be padding; else the register-patch kernel), 1 = the
+ *                   register-patch kernel, 2 = the large-batch kernel, 3 = the persistent kernel
+ *                   (GN_ERR_UNSUPPORTED from gn_outer_forward_f32 when the forced one does not apply).
  *   "forward_samples_per_cta": samples one CTA of the tuned float forward kernel walks through;
  *                   0 = chosen from the grid and batch size (default). */
 GN_API int gn_config_set(const char *key, int value);

@@ -191,6 +191,39 @@ def test_large_batch_kernel_matches_patch_kernel_and_oracle(B, shape, inner, out
                  f"large-batch kernel B={B}")
 
 
+@pytest.mark.parametrize("B,shape,inner,outer,act", [
+    (8, (32, 32, 32), 2, 8, "silu"),       # the MNIST-shaped configuration in full
+    (5, (16, 16, 16), 3, 2, "tanh"),       # samples that do not divide over the CTAs
+    (1, (8, 8, 8), 1, 1, "relu"),          # one block, one sample, one step
+    (3, (8, 24, 16), 2, 5, "leaky_relu"),  # non-cubic grid
+])
+def test_persistent_kernel_matches_step_by_step_loop_and_oracle(B, shape, inner, outer, act):
+    """The whole loop as one cooperative kernel (what small problems get by default) against the loop of one
+    launch per outer step and against the oracle; two runs give the same bits."""
+    from gridnet_b200 import outer_forward, outer_forward_failed, outer_forward_workspace
+    from gridnet_b200._lib import lib
+
+    w, b, s, gamma, beta = model_params(81, shape)
+    x = face_input(82, B, shape)
+    args = [dev(a) for a in (w, b, s, gamma, beta, x)]
+    ws = outer_forward_workspace(B, shape, 8, args[0].device)
+    try:
+        assert lib.gn_config_set(b"outer_kernel", 1) == 0
+        base = outer_forward(*args, inner, outer, 8, act)
+        assert lib.gn_config_set(b"outer_kernel", 3) == 0
+        got = outer_forward(*args, inner, outer, 8, act, workspace=ws)
+        again = outer_forward(*args, inner, outer, 8, act, workspace=ws)
+    finally:
+        lib.gn_config_set(b"outer_kernel", 0)
+    assert not outer_forward_failed(ws, B, shape, 8)
+    assert torch.equal(got, again)
+    assert torch.allclose(got, base, rtol=2e-5, atol=2e-6), (got - base).abs().max().item()
+    auto = outer_forward(*args, inner, outer, 8, act)  # small problems take the persistent kernel by themselves
+    assert torch.equal(auto, got)
+    a64 = [a.astype(np.float64) for a in (w, b, s, gamma, beta, x)]
+    assert_close(got.cpu().numpy(), orc.outer_forward(*a64, inner, outer, 8, activation=act), None, f"persistent kernel B={B}")
+
+
 def test_packed_parameters_are_rebuilt_when_parameters_change():
     """A reused workspace keeps the re-ordered parameters of the large-batch kernel; changing a parameter in place,
     passing another parameter tensor, or scribbling over the workspace must all lead to a rebuild."""
