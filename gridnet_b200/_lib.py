@@ -68,6 +68,7 @@ SIGNATURES = {
                                             c_int, c_int, c_int, c_int, c_int, _P, _P]),
     "gn_norm_finalize_f32": (c_int, [_P, c_int, _P, c_int, c_longlong, c_float, _P]),
     "gn_norm_apply_f32": (c_int, [_P] * 5 + [c_int, c_longlong, _P]),
+    "gn_outer_forward_plan": (c_int, [c_int] * 7),
     "gn_outer_forward_workspace_bytes": (c_size_t, [c_int] * 5),
     "gn_outer_forward_error_flag_offset": (c_size_t, [c_int] * 5),
     "gn_outer_forward_f32": (c_int, [_P] * 7 + _geom + [c_int, c_int, c_int, c_float, c_int, _P, c_size_t, _P]),

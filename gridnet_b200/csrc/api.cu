@@ -807,6 +807,23 @@ GN_API int gn_step_forward_pair64_f32(const float *packed, const float *x_il64, 
     return launch_step_fwd_pair64(a, act, (cudaStream_t)stream);
 }
 
+GN_API int gn_outer_forward_plan(int B, int M, int N, int K, int inner, int outer, int block)
+{
+    if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || inner < 1 || outer < 1 || (block != 4 && block != 8)) return 0;
+    static const double aligned[2] = {0.0, 0.0};  // any 16-byte aligned address: the choice below only looks at alignment
+    const void *a = aligned;
+    if ((g_outer_kernel == 0 || g_outer_kernel == 3) && outer_small_spc(B, M, N, K, block, inner, outer, a, a, a, a, a, a, a) > 0)
+        return 3;
+    if (g_outer_kernel == 3) return 0;
+    if (pair64_applicable(M, N, K, block, inner) && (g_outer_kernel == 2 || (g_outer_kernel == 0 && pair64_fills_groups(B))))
+        return 2;
+    if (g_outer_kernel == 2) return 0;
+    FastFwdParams p{};
+    p.w = p.b = p.s = p.x = reinterpret_cast<const float *>(a);
+    p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner; p.sub = block;
+    return fast8_applicable(p, block, 0) ? 1 : 4;
+}
+
 GN_API size_t gn_outer_forward_workspace_bytes(int B, int M, int N, int K, int block)
 {
     if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || (block != 4 && block != 8)) return 256;

@@ -23,7 +23,7 @@ namespace gn {
 
 namespace small8 {
 constexpr int THREADS = 128;
-constexpr int MAX_SPC = 16;                   // samples per CTA at most
+constexpr int MAX_SPC = 2;                    // samples per CTA at most: both tiles are fetched up front
 constexpr unsigned kSpinLimit = 1u << 22;     // polls of the grid barrier, ~50 ns apart
 }  // namespace small8
 
@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(small8::THREADS, 2) outer_small_k(const OuterS
     using namespace small8;
     using Geo = PatchGeo<8>;
     constexpr int RS = Geo::RS, PS = Geo::PS, TS = Geo::TS;
-    __shared__ __align__(16) float tiles[2][TS];
+    __shared__ __align__(16) float tiles[MAX_SPC][2][TS];  // [sample of the CTA][ping-pong]
     __shared__ float2 gbtab[Geo::CELLS];
     __shared__ float2 mstats[MAX_SPC];
     __shared__ double red[33];
@@ -108,27 +108,38 @@ __global__ void __launch_bounds__(small8::THREADS, 2) outer_small_k(const OuterS
     for (int o = 0; o < p.outer; ++o) {
         const float *src = o == 0 ? p.x : p.buf[(o - 1) & 1];
         float *dst = p.buf[o & 1];
-        for (int smp = s0; smp < s1; ++smp) {
-            const float2 mr = o > 0 ? mstats[smp - s0] : make_float2(0.0f, 1.0f);
-            const float *xs = src + (size_t)smp * P + origin;
+        // fetch the tiles of all of this CTA's samples first: the loads of the second overlap the first one's arithmetic
 #pragma unroll
-            for (int j = 0; j < Geo::SLOTS; ++j) {
-                if (soff[j] >= 0) {
-                    // __ldcg: the neighbours' blocks were written by other CTAs in the previous step
-                    float v = rel[j] >= 0 ? __ldcg(xs + rel[j]) : 0.0f;
-                    if (o > 0) {
-                        const float2 gb = gbtab[tid + j * THREADS];
-                        v = fmaf((v - mr.x) * mr.y, gb.x, gb.y);
+        for (int q = 0; q < MAX_SPC; ++q) {
+            const int smp = s0 + q;
+            if (smp < s1) {
+                const float2 mr = o > 0 ? mstats[q] : make_float2(0.0f, 1.0f);
+                const float *xs = src + (size_t)smp * P + origin;
+                float v[Geo::SLOTS];
+#pragma unroll
+                for (int j = 0; j < Geo::SLOTS; ++j)  // __ldcg: the neighbours' blocks were written by other CTAs
+                    v[j] = (soff[j] >= 0 && rel[j] >= 0) ? __ldcg(xs + rel[j]) : 0.0f;
+#pragma unroll
+                for (int j = 0; j < Geo::SLOTS; ++j) {
+                    if (soff[j] >= 0) {
+                        float u = v[j];
+                        if (o > 0) {
+                            const float2 gb = gbtab[tid + j * THREADS];
+                            u = fmaf((u - mr.x) * mr.y, gb.x, gb.y);
+                        }
+                        tiles[q][0][soff[j]] = u;
+                        if (halo[j]) tiles[q][1][soff[j]] = u;
                     }
-                    tiles[0][soff[j]] = v;
-                    if (halo[j]) tiles[1][soff[j]] = v;
                 }
             }
-            __syncthreads();
+        }
+        __syncthreads();
+        for (int smp = s0; smp < s1; ++smp) {
+            float(*tl2)[TS] = tiles[smp - s0];
             for (int it = 0; it < p.inner; ++it) {
                 const bool last = it + 1 == p.inner;
                 const int cur = it & 1;
-                const float *tl = tiles[cur] + toff;
+                const float *tl = tl2[cur] + toff;
                 float acc[2][2] = {{bias[0][0], bias[0][1]}, {bias[1][0], bias[1][1]}};
                 float old[2][2];
 #pragma unroll
@@ -160,7 +171,7 @@ __global__ void __launch_bounds__(small8::THREADS, 2) outer_small_k(const OuterS
 #pragma unroll
                     for (int i = 0; i < 2; ++i) nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
                 if (!last) {
-                    float *to = tiles[cur ^ 1] + toff + PS + RS + 1;
+                    float *to = tl2[cur ^ 1] + toff + PS + RS + 1;
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         to[j * RS] = nv[j][0];
@@ -187,7 +198,6 @@ __global__ void __launch_bounds__(small8::THREADS, 2) outer_small_k(const OuterS
                         __stcg(&p.partials[(size_t)smp * p.nparts + (size_t)blk * 4 + (tid >> 5)], make_double2(sm, sq));
                 }
             }
-            __syncthreads();  // the tiles are free for the next sample
         }
 
         // ---- grid-wide barrier: every CTA's outputs and partials of step o are in global memory
@@ -204,7 +214,7 @@ __global__ void __launch_bounds__(small8::THREADS, 2) outer_small_k(const OuterS
                     if (p.error_flag) *p.error_flag = 1;
                     break;
                 }
-                __nanosleep(50);
+                if (spins > 64) __nanosleep(40);
             }
         }
         __syncthreads();

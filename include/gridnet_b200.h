@@ -377,6 +377,11 @@ GN_API int gn_norm_apply_f32(const float *x, const float *gamma, const float *be
  * block 8, the weights re-ordered for the large-batch kernel (29/27 of the weight tensor).
  * With the large-batch kernel (see gn_step_forward_pair64_f32 below) the activations stay
  * interleaved by groups of 64 samples between steps, [group][M][N][K][64], and are read by TMA. */
+/* Which kernel gn_outer_forward_f32 would take for this problem with suitably aligned buffers: 3 = the whole loop
+ * as one persistent kernel (1 launch), 2 = the large-batch kernel (2 launches per outer step + 3), 1 = the
+ * register-patch kernel (2 per outer step + 1), 4 = the step-by-step composition of the generic kernels,
+ * 0 = bad arguments or the kernel forced with gn_config_set does not apply. */
+GN_API int gn_outer_forward_plan(int B, int M, int N, int K, int inner, int outer, int block);
 GN_API size_t gn_outer_forward_workspace_bytes(int B, int M, int N, int K, int block);
 /* Byte offset, inside the workspace, of an int that gn_outer_forward_f32 sets to 1 when a bounded
  * wait on a bulk tile copy gave up (the results of that call are then invalid). It is cleared at
