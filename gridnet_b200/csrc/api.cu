@@ -810,7 +810,7 @@ GN_API int gn_step_forward_pair64_f32(const float *packed, const float *x_il64, 
 GN_API int gn_outer_forward_plan(int B, int M, int N, int K, int inner, int outer, int block)
 {
     if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || inner < 1 || outer < 1 || (block != 4 && block != 8)) return 0;
-    static const double aligned[2] = {0.0, 0.0};  // any 16-byte aligned address: the choice below only looks at alignment
+    alignas(16) static const double aligned[2] = {0.0, 0.0};  // any 16-byte aligned address: only alignment is looked at
     const void *a = aligned;
     if ((g_outer_kernel == 0 || g_outer_kernel == 3) && outer_small_spc(B, M, N, K, block, inner, outer, a, a, a, a, a, a, a) > 0)
         return 3;
