@@ -53,43 +53,75 @@ __host__ __device__ inline size_t mailbox_flags_offset(int world, int B)
 {
     return (size_t)2 * world * B * sizeof(double2);
 }
+constexpr int kPublishSlices = 8;  // CTAs that share the partials of one sample
+
+// after the flags: the CTA counter of the whole launch, per-sample counters, per-sample slice sums (own use only)
+__host__ __device__ inline size_t mailbox_scratch_offset(int world, int B)
+{
+    return mailbox_flags_offset(world, B) + (size_t)2 * world * sizeof(unsigned long long);
+}
 size_t slab_mailbox_bytes(int world, int B)
 {
-    return mailbox_flags_offset(world, B) + (size_t)2 * world * sizeof(unsigned long long) + 64;  // + the CTA counter
+    size_t n = mailbox_scratch_offset(world, B) + 16 + (size_t)B * sizeof(unsigned);
+    n = (n + 15) / 16 * 16;
+    return n + (size_t)B * kPublishSlices * sizeof(double2);
 }
 
-// grid B: one CTA adds up a sample's partials (fixed order) and stores the pair into every mailbox; the CTA that
-// finishes last publishes the flags
+// grid B * kPublishSlices: a CTA adds up one slice of a sample's partials (fixed order); the CTA of a sample that
+// finishes last adds the slice sums in slice order and stores the pair into every mailbox; the CTA that finishes
+// last of all publishes the flags
 __global__ void __launch_bounds__(256) slab_publish_sums_k(const double2 *__restrict__ partials, int nparts, int B,
                                                            int rank, int world, SlabMailboxes boxes, int parity,
                                                            unsigned long long step)
 {
     __shared__ double red[33];
-    __shared__ bool last;
-    const int b = blockIdx.x;
+    __shared__ bool last_of_sample, last_of_all;
+    const int b = blockIdx.x / kPublishSlices, slice = blockIdx.x - b * kPublishSlices;
+    unsigned char *own = boxes.base[rank] + mailbox_scratch_offset(world, B);
+    unsigned *all_counter = reinterpret_cast<unsigned *>(own);
+    unsigned *sample_counter = reinterpret_cast<unsigned *>(own + 16) + b;
+    double2 *slice_sums = reinterpret_cast<double2 *>(own + (16 + (size_t)B * sizeof(unsigned) + 15) / 16 * 16) + (size_t)b * kPublishSlices;
+    const int per = (nparts + kPublishSlices - 1) / kPublishSlices;
+    const int lo = slice * per, hi = min(nparts, lo + per);
     const double2 *ps = partials + (size_t)b * nparts;
     double s = 0.0, q = 0.0;
-    for (int i = threadIdx.x; i < nparts; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
         const double2 v = ps[i];
         s += v.x;
         q += v.y;
     }
     s = block_sum(s, red);
     q = block_sum(q, red);
-    if (threadIdx.x < world) {
-        double2 *dst = reinterpret_cast<double2 *>(boxes.base[threadIdx.x] + mailbox_sums_offset(parity, rank, world, B));
-        dst[b] = make_double2(s, q);
+    if (threadIdx.x == 0) {
+        __stcg(&slice_sums[slice], make_double2(s, q));
+        __threadfence();
+        last_of_sample = atomicAdd(sample_counter, 1u) == (unsigned)kPublishSlices - 1;
+        last_of_all = false;
+        if (last_of_sample) {
+            *sample_counter = 0;
+            __threadfence();
+        }
     }
-    __threadfence_system();  // the sums are out before this CTA counts itself as done
+    __syncthreads();
+    if (!last_of_sample) return;
+    if (threadIdx.x < world) {
+        double ts = 0.0, tq = 0.0;
+        for (int k = 0; k < kPublishSlices; ++k) {
+            const double2 v = __ldcg(&slice_sums[k]);
+            ts += v.x;
+            tq += v.y;
+        }
+        double2 *dst = reinterpret_cast<double2 *>(boxes.base[threadIdx.x] + mailbox_sums_offset(parity, rank, world, B));
+        dst[b] = make_double2(ts, tq);
+    }
+    __threadfence_system();  // the sums are out before this sample counts as done
     __syncthreads();
     if (threadIdx.x == 0) {
-        unsigned *counter = reinterpret_cast<unsigned *>(boxes.base[rank] + mailbox_flags_offset(world, B) +
-                                                         (size_t)2 * world * sizeof(unsigned long long));
-        last = atomicAdd(counter, 1u) == (unsigned)B - 1;
-        if (last) *counter = 0;  // ready for the next step (launches on a stream do not overlap)
+        last_of_all = atomicAdd(all_counter, 1u) == (unsigned)B - 1;
+        if (last_of_all) *all_counter = 0;  // ready for the next step (launches on a stream do not overlap)
     }
     __syncthreads();
-    if (last && threadIdx.x < world) {
+    if (last_of_all && threadIdx.x < world) {
         __threadfence_system();  // order the other CTAs' stores, seen through the counter, before the flags
         unsigned long long *flag = reinterpret_cast<unsigned long long *>(boxes.base[threadIdx.x] + mailbox_flags_offset(world, B)) +
                                    parity * world + rank;
@@ -157,7 +189,7 @@ int launch_slab_publish_sums(const double2 *partials, int nparts, int B, int ran
         if (!mailboxes[r]) return GN_ERR_NULL_POINTER;
         boxes.base[r] = static_cast<unsigned char *>(mailboxes[r]);
     }
-    slab_publish_sums_k<<<B, 256, 0, st>>>(partials, nparts, B, rank, world, boxes, parity, step);
+    slab_publish_sums_k<<<B * kPublishSlices, 256, 0, st>>>(partials, nparts, B, rank, world, boxes, parity, step);
     return check_launch("slab_publish_sums");
 }
 
