@@ -697,6 +697,7 @@ def bench_train(ctx: Ctx, name: str, stash=None, microbatches=None, steps_cap: i
     # keep the inner iterations' intermediate results from the forward pass (memory for time): True / False force
     # it, None leaves the package's default (kept whenever they fit comfortably in the free device memory)
     previous_stash = gb.keep_forward_stash(stash)
+    ctx.release()  # what the configuration before this one held goes back to the driver first
     dist = ctx.need_group() if world > 1 else None
     if batch % world:
         raise SystemExit(f"batch {batch} does not divide over {world} ranks")
@@ -752,6 +753,8 @@ def bench_train(ctx: Ctx, name: str, stash=None, microbatches=None, steps_cap: i
         return total + gxs
 
     warm = max(3, args.warmup)  # the first steps also grow torch's allocator cache
+    torch.cuda.reset_peak_memory_stats(device)
+    free0 = torch.cuda.mem_get_info(device)[0] / 1e9
     for _ in range(warm):
         grads = step(False)
     barrier()
@@ -760,11 +763,17 @@ def bench_train(ctx: Ctx, name: str, stash=None, microbatches=None, steps_cap: i
         sampler.start()
     steps = max(1, min(args.steps, steps_cap))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    mem0 = torch.cuda.memory_stats(device)
     e0.record()
     for _ in range(steps):
         grads = step(True)
     e1.record()
     barrier()
+    mem1 = torch.cuda.memory_stats(device)
+    # calls of the caching allocator into the driver inside the timed region (0 once its cache is warm)
+    driver_allocs = int(mem1.get("num_device_alloc", 0) - mem0.get("num_device_alloc", 0))
+    alloc_retries = int(mem1.get("num_alloc_retries", 0) - mem0.get("num_alloc_retries", 0))
+    peak_gb = mem1.get("allocated_bytes.all.peak", 0) / 1e9
     clocks = sampler.stop() if rank == 0 else None
     ms = ctx.max_over_ranks(e0.elapsed_time(e1))
     finite = all(bool(torch.isfinite(t_).all().item()) for t_ in grads)
@@ -793,6 +802,9 @@ def bench_train(ctx: Ctx, name: str, stash=None, microbatches=None, steps_cap: i
                                                 "kept from the forward pass where they take at most a tenth of the free "
                                                 "device memory, else recomputed (package default)"),
                        "microbatches": nmb,
+                       "allocator": {"driver_allocations_in_timed_region": driver_allocs,
+                                     "out_of_memory_retries_in_timed_region": alloc_retries,
+                                     "peak_allocated_gb": peak_gb, "free_before_gb": free0},
                        "samples_per_sec": batch / sec},
             "roofline": {"bound": "fp32", "achieved": flops / sec / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
                          "frac": flops / sec / 1e12 / fp32_peak,
