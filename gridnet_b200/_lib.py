@@ -41,6 +41,7 @@ SIGNATURES = {
     "gn_norm_workspace_bytes": (c_size_t, [c_int, c_longlong]),
     "gn_norm_forward_f32": (c_int, [_P] * 5 + [c_int, c_longlong, c_float, _P, c_size_t, _P]),
     "gn_norm_backward_f32": (c_int, [_P] * 6 + [c_int, c_longlong, c_float, _P, c_size_t, _P]),
+    "gn_norm_residual_combine_f32": (c_int, [_P] * 7 + [c_int, c_longlong, c_float, _P, c_size_t, _P]),
     "gn_norm_local_sums_f32": (c_int, [_P, _P, c_int, c_longlong, _P, c_size_t, _P]),
     "gn_norm_backward_local_sums_f32": (c_int, [_P] * 5 + [c_int, c_longlong, _P, c_size_t, _P]),
     "gn_norm_backward_apply_f32": (c_int, [_P] * 5 + [c_longlong] + [_P] * 3 + [c_int, c_longlong, _P, c_size_t, _P]),

@@ -220,45 +220,11 @@ class FusedLoopTrainOp(torch.autograd.Function):
     @staticmethod
     def forward(ctx, weight, bias, residual_scale, norm_weight, norm_bias, x, inner_iters: int, outer_iters: int,
                 block_size: int, activation: str, ln_eps: float):
-        _assert_step_args(weight, bias, residual_scale, x, block_size, False)
-        assert norm_weight.shape == bias.shape == norm_bias.shape, f"{norm_weight.shape=} invalid for {bias.shape=}"
-        x = x.contiguous()
-        _require_f32_cuda(weight=weight, bias=bias, residual_scale=residual_scale, norm_weight=norm_weight,
-                          norm_bias=norm_bias, x=x)
-        B, M, N, K = x.shape
-        P = M * N * K
-        act = activation_id(activation)
-        dev = weight.device
-        nparts = int(lib.gn_step_stats_partials(M, N, K, block_size))
-        partials = torch.empty(B, nparts, 2, dtype=torch.float64, device=dev)
         need_grad = any(ctx.needs_input_grad[:6])
-        raws, stats, stashes = [], [], []
-        src, src_stats = x, None
-        with torch.cuda.device(dev):
-            st = torch.cuda.current_stream().cuda_stream
-            for _ in range(outer_iters):
-                dst = torch.empty_like(x)
-                stash = None
-                if need_grad and _stash_wanted(weight, x, inner_iters, block_size):
-                    stash = torch.empty(int(lib.gn_step_stash_bytes(B, M, N, K, int(inner_iters), int(block_size))),
-                                        dtype=torch.uint8, device=dev)
-                check(lib.gn_step_forward_train_f32(
-                    weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(), src.data_ptr(), dst.data_ptr(),
-                    norm_weight.data_ptr(), norm_bias.data_ptr(), None if src_stats is None else src_stats.data_ptr(),
-                    partials.data_ptr(), B, M, N, K, int(inner_iters), int(block_size), act,
-                    None if stash is None else stash.data_ptr(), 0 if stash is None else stash.numel(), st))
-                mr = torch.empty(B, 2, dtype=torch.float32, device=dev)
-                check(lib.gn_norm_finalize_f32(partials.data_ptr(), nparts, mr.data_ptr(), B, P, float(ln_eps), st))
-                raws.append(dst)
-                stats.append(mr)
-                stashes.append(stash)
-                src, src_stats = dst, mr
-            y = torch.empty_like(x)
-            if outer_iters:
-                check(lib.gn_norm_apply_f32(src.data_ptr(), norm_weight.data_ptr(), norm_bias.data_ptr(),
-                                            src_stats.data_ptr(), y.data_ptr(), B, P, st))
-            else:
-                y.copy_(x)
+        x = x.contiguous()
+        y, raws, stats, stashes = _fused_loop_forward([(weight, bias, residual_scale)] * int(outer_iters), norm_weight,
+                                                      norm_bias, x, int(inner_iters), int(block_size), activation,
+                                                      float(ln_eps), need_grad)
         ctx.save_for_backward(weight, bias, residual_scale, norm_weight, norm_bias, x, *raws, *stats)
         ctx.stashes = stashes
         ctx.cfg = (int(inner_iters), int(outer_iters), int(block_size), activation, float(ln_eps))
@@ -271,52 +237,203 @@ class FusedLoopTrainOp(torch.autograd.Function):
         weight, bias, scale, gamma, beta, x = saved[:6]
         raws, stats = saved[6:6 + outer], saved[6 + outer:6 + 2 * outer]
         stashes, ctx.stashes = ctx.stashes, None
-        B, M, N, K = x.shape
-        P = M * N * K
-        dev = weight.device
-        g = grad_y.contiguous()
-        gw = gb = gs = gg = gbt = None
-        with torch.cuda.device(dev):
-            st = torch.cuda.current_stream().cuda_stream
-            nws = _workspace(lib.gn_norm_workspace_bytes(B, P), dev)
-            sums = torch.empty(B, 2, dtype=torch.float64, device=dev)
-            for k in reversed(range(outer)):
-                # LayerNorm backward of step k with the statistics saved by the forward pass
-                gs_k, dg, dbt = torch.empty_like(x), torch.empty_like(gamma), torch.empty_like(gamma)
-                check(lib.gn_norm_backward_local_sums_f32(raws[k].data_ptr(), gamma.data_ptr(), g.data_ptr(),
-                                                          stats[k].data_ptr(), sums.data_ptr(), B, P, nws.data_ptr(),
-                                                          nws.numel(), st))
-                check(lib.gn_norm_backward_apply_f32(raws[k].data_ptr(), gamma.data_ptr(), g.data_ptr(), stats[k].data_ptr(),
-                                                     sums.data_ptr(), P, gs_k.data_ptr(), dg.data_ptr(), dbt.data_ptr(), B, P,
-                                                     nws.data_ptr(), nws.numel(), st))
-                # the step's input: x itself for the first step, else the normalised output of the step before
-                if k == 0:
-                    xin = x
-                else:
-                    xin = torch.empty_like(x)
-                    check(lib.gn_norm_apply_f32(raws[k - 1].data_ptr(), gamma.data_ptr(), beta.data_ptr(),
-                                                stats[k - 1].data_ptr(), xin.data_ptr(), B, P, st))
-                dw, db, ds, gx = (torch.empty_like(t) for t in (weight, bias, scale, x))
-                if stashes[k] is not None:
-                    gridnet_cuda.backward_with_stash(weight, bias, scale, xin, gs_k, dw, db, ds, gx, inner, block, activation,
-                                                     stashes[k])
-                    stashes[k] = None
-                else:
-                    gridnet_cuda.backward(weight, bias, scale, xin, gs_k, dw, db, ds, gx, inner, block, 1e-5, False,
-                                          activation)
-                if gw is None:
-                    gw, gb, gs, gg, gbt = dw, db, ds, dg, dbt
-                else:
-                    gw += dw
-                    gb += db
-                    gs += ds
-                    gg += dg
-                    gbt += dbt
-                g = gx
+        total = []
+
+        def add(k, grads):  # the steps share one parameter set: their gradients are summed as they appear
+            if not total:
+                total.extend(grads)
+            else:
+                for acc, g in zip(total, grads):
+                    acc += g
+
+        gg, gbt, g = _fused_loop_backward([(weight, bias, scale)] * outer, gamma, beta, x, raws, stats, stashes,
+                                          grad_y, inner, block, activation, add)
         if outer == 0:
             z = torch.zeros_like
             return z(weight), z(bias), z(scale), z(gamma), z(beta), g, None, None, None, None, None
-        return gw, gb, gs, gg, gbt, g, None, None, None, None, None
+        return total[0], total[1], total[2], gg, gbt, g, None, None, None, None, None
+
+
+class FusedLoopSeparateTrainOp(torch.autograd.Function):
+    """:class:`FusedLoopTrainOp` for a loop in which every outer step has its own network
+    (``separate_params`` of gridnet/scripts/train_imagenet.py:54-58,76-79): the same fused forward and the same
+    reverse walk, each step's parameter gradients going to that step's parameters.
+
+    ``FusedLoopSeparateTrainOp.apply(norm_weight, norm_bias, x, inner_iters, block_size, activation, ln_eps,
+    weight_0, bias_0, residual_scale_0, weight_1, ...)``: three tensors per outer step."""
+
+    @staticmethod
+    def forward(ctx, norm_weight, norm_bias, x, inner_iters: int, block_size: int, activation: str, ln_eps: float,
+                *step_params):
+        assert len(step_params) % 3 == 0, "three tensors (weight, bias, residual_scale) per outer step"
+        plist = [tuple(step_params[i:i + 3]) for i in range(0, len(step_params), 3)]
+        need_grad = any(ctx.needs_input_grad)
+        x = x.contiguous()
+        y, raws, stats, stashes = _fused_loop_forward(plist, norm_weight, norm_bias, x, int(inner_iters),
+                                                      int(block_size), activation, float(ln_eps), need_grad)
+        ctx.save_for_backward(norm_weight, norm_bias, x, *step_params, *raws, *stats)
+        ctx.stashes = stashes
+        ctx.cfg = (int(inner_iters), len(plist), int(block_size), activation)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        inner, outer, block, activation = ctx.cfg
+        saved = ctx.saved_tensors
+        gamma, beta, x = saved[:3]
+        flat = saved[3:3 + 3 * outer]
+        plist = [tuple(flat[i:i + 3]) for i in range(0, 3 * outer, 3)]
+        raws, stats = saved[3 + 3 * outer:3 + 4 * outer], saved[3 + 4 * outer:3 + 5 * outer]
+        stashes, ctx.stashes = ctx.stashes, None
+        per_step = [None] * outer
+
+        def keep(k, grads):
+            per_step[k] = grads
+
+        gg, gbt, g = _fused_loop_backward(plist, gamma, beta, x, raws, stats, stashes, grad_y, inner, block, activation,
+                                          keep)
+        if outer == 0:
+            return torch.zeros_like(gamma), torch.zeros_like(beta), g, None, None, None, None
+        return (gg, gbt, g, None, None, None, None) + tuple(t for grads in per_step for t in grads)
+
+
+def _fused_loop_forward(plist, norm_weight, norm_bias, x, inner_iters, block_size, activation, ln_eps, need_grad):
+    """The fused forward of the model loop with one (weight, bias, residual_scale) per outer step: every step kernel
+    normalises its input while loading it and reduces the statistics of what it writes. Returns the normalised
+    final grid, the raw step outputs, their (mean, rstd) and the kept inner iterations (or None) per step."""
+    B, M, N, K = x.shape
+    P = M * N * K
+    act = activation_id(activation)
+    dev = x.device
+    for weight, bias, residual_scale in plist:
+        _assert_step_args(weight, bias, residual_scale, x, block_size, False)
+        assert norm_weight.shape == bias.shape == norm_bias.shape, f"{norm_weight.shape=} invalid for {bias.shape=}"
+        _require_f32_cuda(weight=weight, bias=bias, residual_scale=residual_scale)
+    _require_f32_cuda(norm_weight=norm_weight, norm_bias=norm_bias, x=x)
+    nparts = int(lib.gn_step_stats_partials(M, N, K, block_size))
+    partials = torch.empty(B, nparts, 2, dtype=torch.float64, device=dev)
+    raws, stats, stashes = [], [], []
+    src, src_stats = x, None
+    with torch.cuda.device(dev):
+        st = torch.cuda.current_stream().cuda_stream
+        for weight, bias, residual_scale in plist:
+            dst = torch.empty_like(x)
+            stash = None
+            if need_grad and _stash_wanted(weight, x, inner_iters, block_size):
+                stash = torch.empty(int(lib.gn_step_stash_bytes(B, M, N, K, int(inner_iters), int(block_size))),
+                                    dtype=torch.uint8, device=dev)
+            check(lib.gn_step_forward_train_f32(
+                weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(), src.data_ptr(), dst.data_ptr(),
+                norm_weight.data_ptr(), norm_bias.data_ptr(), None if src_stats is None else src_stats.data_ptr(),
+                partials.data_ptr(), B, M, N, K, int(inner_iters), int(block_size), act,
+                None if stash is None else stash.data_ptr(), 0 if stash is None else stash.numel(), st))
+            mr = torch.empty(B, 2, dtype=torch.float32, device=dev)
+            check(lib.gn_norm_finalize_f32(partials.data_ptr(), nparts, mr.data_ptr(), B, P, float(ln_eps), st))
+            if need_grad:
+                raws.append(dst)
+                stats.append(mr)
+                stashes.append(stash)
+            src, src_stats = dst, mr
+        y = torch.empty_like(x)
+        if plist:
+            check(lib.gn_norm_apply_f32(src.data_ptr(), norm_weight.data_ptr(), norm_bias.data_ptr(),
+                                        src_stats.data_ptr(), y.data_ptr(), B, P, st))
+        else:
+            y.copy_(x)
+    return y, raws, stats, stashes
+
+
+def _fused_loop_backward(plist, gamma, beta, x, raws, stats, stashes, grad_y, inner, block, activation, sink):
+    """The reverse walk over the steps of :func:`_fused_loop_forward`: the library's LayerNorm backward with the
+    saved statistics, then the tuned step backward on the step's normalised input rebuilt from the saved raw
+    tensor. ``sink(k, (dw, db, ds))`` receives step k's parameter gradients; returns the gradients of the norm
+    weight and bias (summed over the steps) and of x."""
+    outer = len(plist)
+    B, M, N, K = x.shape
+    P = M * N * K
+    dev = x.device
+    g = grad_y.contiguous()
+    gg = gbt = None
+    stashes = list(stashes)
+    with torch.cuda.device(dev):
+        st = torch.cuda.current_stream().cuda_stream
+        nws = _workspace(lib.gn_norm_workspace_bytes(B, P), dev)
+        sums = torch.empty(B, 2, dtype=torch.float64, device=dev)
+        for k in reversed(range(outer)):
+            weight, bias, scale = plist[k]
+            # LayerNorm backward of step k with the statistics saved by the forward pass
+            gs_k, dg, dbt = torch.empty_like(x), torch.empty_like(gamma), torch.empty_like(gamma)
+            check(lib.gn_norm_backward_local_sums_f32(raws[k].data_ptr(), gamma.data_ptr(), g.data_ptr(),
+                                                      stats[k].data_ptr(), sums.data_ptr(), B, P, nws.data_ptr(),
+                                                      nws.numel(), st))
+            check(lib.gn_norm_backward_apply_f32(raws[k].data_ptr(), gamma.data_ptr(), g.data_ptr(), stats[k].data_ptr(),
+                                                 sums.data_ptr(), P, gs_k.data_ptr(), dg.data_ptr(), dbt.data_ptr(), B, P,
+                                                 nws.data_ptr(), nws.numel(), st))
+            # the step's input: x itself for the first step, else the normalised output of the step before
+            if k == 0:
+                xin = x
+            else:
+                xin = torch.empty_like(x)
+                check(lib.gn_norm_apply_f32(raws[k - 1].data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                            stats[k - 1].data_ptr(), xin.data_ptr(), B, P, st))
+            dw, db, ds, gx = (torch.empty_like(t) for t in (weight, bias, scale, x))
+            if stashes[k] is not None:
+                gridnet_cuda.backward_with_stash(weight, bias, scale, xin, gs_k, dw, db, ds, gx, inner, block, activation,
+                                                 stashes[k])
+                stashes[k] = None
+            else:
+                gridnet_cuda.backward(weight, bias, scale, xin, gs_k, dw, db, ds, gx, inner, block, 1e-5, False,
+                                      activation)
+            sink(k, (dw, db, ds))
+            if gg is None:
+                gg, gbt = dg, dbt
+            else:
+                gg += dg
+                gbt += dbt
+            g = gx
+    return gg, gbt, g
+
+
+def fused_loop_forward(step_params, norm_weight, norm_bias, x, inner_iters: int, block_size: int,
+                       activation: str = "silu", ln_eps: float = 1e-5, outer_residual: bool = False) -> torch.Tensor:
+    """The model loop of gridnet/scripts/train_imagenet.py:76-86 without gradients, for the variants that
+    :func:`outer_forward` does not take: ``step_params`` is one ``(weight, bias, residual_scale)`` per outer step
+    (``separate_params``; repeat one tuple for shared parameters), and with ``outer_residual`` a step is
+    ``n = norm(h); h = h + (net(n) - n)`` instead of ``h = norm(net(h))``. Float32, tuned step kernel
+    (whole 8^3 regions, block 4 or 8). The normalised tensor is never stored: the step kernel normalises while it
+    loads, and either it (plain form) or the combining pass (residual form) reduces the next statistics."""
+    x = x.contiguous()
+    if not outer_residual:
+        with torch.no_grad():
+            return _fused_loop_forward(list(step_params), norm_weight, norm_bias, x, int(inner_iters), int(block_size),
+                                       activation, float(ln_eps), False)[0]
+    B, M, N, K = x.shape
+    P = M * N * K
+    act = activation_id(activation)
+    dev = x.device
+    _require_f32_cuda(norm_weight=norm_weight, norm_bias=norm_bias, x=x)
+    with torch.cuda.device(dev), torch.no_grad():
+        st = torch.cuda.current_stream().cuda_stream
+        nws = _workspace(lib.gn_norm_workspace_bytes(B, P), dev)
+        sums = torch.empty(B, 2, dtype=torch.float64, device=dev)
+        mr = [torch.empty(B, 2, dtype=torch.float32, device=dev) for _ in range(2)]
+        h, y = x, torch.empty_like(x)
+        out = torch.empty_like(x)
+        check(lib.gn_norm_local_sums_f32(h.data_ptr(), sums.data_ptr(), B, P, nws.data_ptr(), nws.numel(), st))
+        check(lib.gn_norm_finalize_f32(sums.data_ptr(), 1, mr[0].data_ptr(), B, P, float(ln_eps), st))
+        for k, (weight, bias, residual_scale) in enumerate(step_params):
+            _assert_step_args(weight, bias, residual_scale, x, block_size, False)
+            _require_f32_cuda(weight=weight, bias=bias, residual_scale=residual_scale)
+            cur, nxt = mr[k & 1], mr[(k + 1) & 1]
+            check(lib.gn_step_forward_train_f32(
+                weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(), h.data_ptr(), y.data_ptr(),
+                norm_weight.data_ptr(), norm_bias.data_ptr(), cur.data_ptr(), None, B, M, N, K, int(inner_iters),
+                int(block_size), act, None, 0, st))
+            check(lib.gn_norm_residual_combine_f32(h.data_ptr(), y.data_ptr(), norm_weight.data_ptr(),
+                                                   norm_bias.data_ptr(), cur.data_ptr(), out.data_ptr(), nxt.data_ptr(),
+                                                   B, P, float(ln_eps), nws.data_ptr(), nws.numel(), st))
+            h = out  # the combining pass may write over its own h
+        return h.clone() if h is x else h
 
 
 def device_status(clear: bool = True, device=None) -> bool:

@@ -71,7 +71,9 @@ int step_forward<float>(const float *w, const float *b, const float *s, const fl
     FastFwdParams p{};
     p.w = w; p.b = b; p.s = s; p.x = x; p.y = y;
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner; p.sub = block;
-    if (fast8_applicable(p, block, normalize)) return launch_step_fwd_fast8(p, act, st);
+    p.normalize = normalize ? 1 : 0;
+    p.norm_eps = eps;
+    if (fast8_applicable(p, block, p.normalize)) return launch_step_fwd_fast8(p, act, st);
     return launch_step_fwd_generic<float>(w, b, s, x, y, B, M, N, K, inner, block, eps, normalize, act, st);
 }
 
@@ -496,6 +498,26 @@ GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float 
     rc = launch_norm_finalize(ws.partials, parts, ws.stats, B, P, eps, st);
     if (rc != GN_OK) return rc;
     return launch_norm_backward(x, gamma, gy, ws.stats, ws.partials, ws.ac, gx, ggamma, gbeta, B, P, parts, st);
+}
+
+GN_API int gn_norm_residual_combine_f32(const float *h, const float *y, const float *gamma, const float *beta,
+                                        const float *mean_rstd_h, float *out, float *mean_rstd_out, int B, long long P,
+                                        float eps, void *workspace, size_t workspace_bytes, void *stream)
+{
+    if (B < 0 || P <= 0) return GN_ERR_BAD_SHAPE;
+    if (B == 0) return GN_OK;
+    if (!h || !y || !gamma || !beta || !mean_rstd_h || !out || !mean_rstd_out) return GN_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(mean_rstd_h) % 8 || reinterpret_cast<uintptr_t>(mean_rstd_out) % 8)
+        return GN_ERR_UNSUPPORTED;
+    int rc = check_ws(workspace, workspace_bytes, gn_norm_workspace_bytes(B, P));
+    if (rc != GN_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const NormWs ws = carve_norm(workspace, B);
+    const int parts = norm_pick_parts(P);
+    rc = launch_norm_residual_combine(h, y, gamma, beta, reinterpret_cast<const float2 *>(mean_rstd_h), out, ws.partials,
+                                      B, P, parts, st);
+    if (rc != GN_OK) return rc;
+    return launch_norm_finalize(ws.partials, parts, reinterpret_cast<float2 *>(mean_rstd_out), B, P, eps, st);
 }
 
 GN_API int gn_norm_local_sums_f32(const float *x, double *sums, int B, long long P, void *workspace,

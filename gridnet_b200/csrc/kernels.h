@@ -46,6 +46,10 @@ struct FastFwdParams {
     // first / last column, packed as [B][M][N], to these addresses (normally a buffer in the neighbouring
     // GPU's memory, written over NVLink); nullptr = no neighbour on that side.
     float *face_left, *face_right;
+    // Per-block normalisation (the reference's normalize=True): block 8 only, and none of the fusions, the
+    // replay mode or the slab mode above. norm_eps is added to the tile's standard deviation.
+    int normalize;
+    float norm_eps;
 };
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize);
 extern int g_fast8_spc_override;  // tuning knob: samples per CTA of the tuned forward kernel, 0 = automatic
@@ -147,6 +151,9 @@ int launch_norm_backward(const float *x, const float *gamma, const float *gy, co
 int norm_pick_parts(long long P);
 // The same normalisation in pieces, for a grid that is sharded over several ranks: per-sample sums over the local
 // part (the caller adds them up over the ranks), then the element-wise passes with the global figures.
+int launch_norm_residual_combine(const float *h, const float *y, const float *gamma, const float *beta,
+                                 const float2 *stats, float *out, double2 *partials, int B, long long P, int parts,
+                                 cudaStream_t st);
 int launch_norm_local_sums(const float *x, double2 *partials, double2 *sums, int B, long long P, int parts,
                            cudaStream_t st);
 int launch_norm_backward_local_sums(const float *x, const float *gamma, const float *gy, const float2 *stats,

@@ -101,6 +101,56 @@ __global__ void __launch_bounds__(256) norm_apply_k(const float *__restrict__ x,
     }
 }
 
+// The residual form of the model loop (gridnet/scripts/train_imagenet.py:81-83): n = LayerNorm(h);
+// h' = h + (net(n) - n). Given h, y = net(n) and the statistics of h, writes h' (out may be h or y) and the
+// per-sample partial sums of h' for the next step's statistics. grid B * parts, slices as in norm_partial_stats_k.
+__global__ void __launch_bounds__(256) norm_residual_combine_k(const float *__restrict__ h, const float *__restrict__ y,
+                                                               const float *__restrict__ gamma,
+                                                               const float *__restrict__ beta,
+                                                               const float2 *__restrict__ stats, float *out,
+                                                               double2 *__restrict__ partials, long long P,
+                                                               long long slice, int parts)
+{
+    __shared__ double red[33];
+    const int b = blockIdx.x / parts, part = blockIdx.x - b * parts;
+    const float2 mr = stats[b];
+    const float *hs = h + (size_t)b * P;
+    const float *ys = y + (size_t)b * P;
+    float *os = out + (size_t)b * P;
+    const long long lo = (long long)part * slice;
+    const long long hi = min(P, lo + slice);
+    double s = 0.0, q = 0.0;
+    if ((P & 3) == 0 && aligned16(hs) && aligned16(ys) && aligned16(os) && aligned16(gamma) && aligned16(beta)) {
+        for (long long i = lo / 4 + threadIdx.x; i < hi / 4; i += blockDim.x) {
+            const float4 a = reinterpret_cast<const float4 *>(hs)[i];
+            const float4 v = reinterpret_cast<const float4 *>(ys)[i];
+            const float4 g = reinterpret_cast<const float4 *>(gamma)[i];
+            const float4 c = reinterpret_cast<const float4 *>(beta)[i];
+            float4 o;
+            o.x = a.x + (v.x - fmaf((a.x - mr.x) * mr.y, g.x, c.x));
+            o.y = a.y + (v.y - fmaf((a.y - mr.x) * mr.y, g.y, c.y));
+            o.z = a.z + (v.z - fmaf((a.z - mr.x) * mr.y, g.z, c.z));
+            o.w = a.w + (v.w - fmaf((a.w - mr.x) * mr.y, g.w, c.w));
+            reinterpret_cast<float4 *>(os)[i] = o;
+            const float ls = (o.x + o.y) + (o.z + o.w);
+            const float lq = fmaf(o.x, o.x, o.y * o.y) + fmaf(o.z, o.z, o.w * o.w);
+            s += (double)ls;
+            q += (double)lq;
+        }
+    } else {
+        for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            const float a = hs[i];
+            const float o = a + (ys[i] - fmaf((a - mr.x) * mr.y, gamma[i], beta[i]));
+            os[i] = o;
+            s += (double)o;
+            q = fma((double)o, (double)o, q);
+        }
+    }
+    s = block_sum(s, red);
+    q = block_sum(q, red);
+    if (threadIdx.x == 0) partials[(size_t)b * parts + part] = make_double2(s, q);
+}
+
 // per-sample partial sums of a = sum(gy * gamma) and c = sum(gy * gamma * xhat); grid B * parts
 __global__ void __launch_bounds__(256) norm_bwd_partial_k(const float *__restrict__ x,
                                                           const float *__restrict__ gamma,
@@ -225,6 +275,15 @@ int launch_norm_apply(const float *x, const float *gamma, const float *beta, con
     const unsigned chunks = (unsigned)((P + 1023) / 1024);
     norm_apply_k<<<(unsigned)B * chunks, 256, 0, st>>>(x, gamma, beta, stats, y, P, chunks);
     return check_launch("norm_apply");
+}
+
+int launch_norm_residual_combine(const float *h, const float *y, const float *gamma, const float *beta,
+                                 const float2 *stats, float *out, double2 *partials, int B, long long P, int parts,
+                                 cudaStream_t st)
+{
+    norm_residual_combine_k<<<(unsigned)B * (unsigned)parts, 256, 0, st>>>(h, y, gamma, beta, stats, out, partials, P,
+                                                                          slice_len(P, parts), parts);
+    return check_launch("norm_residual_combine");
 }
 
 int launch_norm_local_sums(const float *x, double2 *partials, double2 *sums, int B, long long P, int parts,

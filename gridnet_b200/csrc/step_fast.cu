@@ -63,7 +63,18 @@ constexpr long long kMaxRel = 1LL << 20;
 // INNER_T > 0: the inner iteration count is a compile-time constant (loop unrolled, tile parity
 // folded into addresses); INNER_T == 0: taken from the parameters.
 // SUB: the block size (8: the CTA's region is one block; 4: eight blocks, each with its own tile).
-template <int SUB, int ACT, bool FUSE_IN, bool STATS_OUT, bool USE_TMA, int INNER_T>
+// NORM: per-block normalisation (the reference's normalize=True, gridnet/backend_torch.py:92-97,
+// src/gridnet_cuda_kernels.cu:164-170): before every inner iteration the stencil input is
+// (tile - mean) / (std + eps) over the 1000 cells of the tile (halo and cells outside the grid included), the
+// residual stays un-normalised. The sums come from where the values are produced, and the iteration never waits
+// for them: the tile commit reduces the halo and the interior of a fresh tile once per sample (double precision);
+// the fresh tile's mean c becomes the sample's pivot; every iteration stores each thread's sums of (v - c) and
+// (v - c)^2 over the four values it writes, the barrier that publishes the tile publishes them, and after it
+// every warp adds the 128 partial sums (two loads and ten shuffles) WHILE the stencil runs on sum w (v - c),
+// which needs neither the mean nor the deviation. They enter at the end: h = (acc - (mean - c) sum w) / (std +
+// eps) + bias, with the per-neuron sum of the weights in a register. Shifting by c keeps the float sums and the
+// subtraction free of cancellation whatever the tile's offset.
+template <int SUB, int ACT, bool FUSE_IN, bool STATS_OUT, bool USE_TMA, int INNER_T, bool NORM = false>
 __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
     step_fwd_fast8(const __grid_constant__ CUtensorMap x_map, const FastFwdParams p)
 {
@@ -82,6 +93,16 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
     __shared__ __align__(128) float staging[USE_TMA ? 2 : 1][USE_TMA ? STG : 4];
     __shared__ __align__(8) unsigned long long bars[2];
     __shared__ float2 gbtab[FUSE_IN ? SLOTS * THREADS : 1];  // (gamma, beta) per tile cell
+    static_assert(!NORM || (SUB == 8 && !FUSE_IN && !STATS_OUT), "per-block normalisation: block 8, plain input and output");
+    // NORM: (sum, sum of squares) per warp: of the halo and of the interior of a freshly committed tile
+    // [sample parity][halo | interior][warp], and of the interior an iteration wrote [iteration parity][warp]
+    __shared__ double2 fresh_sums[NORM ? 2 : 1][2][4];
+    __shared__ __align__(16) float2 part_sums[2][NORM ? THREADS : 1];
+    // NORM: bias, scale and weight sum of the thread's four neurons (kept out of the registers: used once per
+    // iteration), and per warp the sample's (halo sum, halo sum of squares, fresh interior sum, ... of squares)
+    // relative to the pivot, then the pivot
+    __shared__ float4 tconst[3][NORM ? THREADS : 1];
+    __shared__ float4 wnorm[2][NORM ? 4 : 1];
 
     const int tid = threadIdx.x;
     const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
@@ -147,6 +168,20 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
         scl[j][1] = vs.y;
     }
 
+    if (NORM) {
+        float wsum[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};  // sum of each neuron's 27 weights
+#pragma unroll
+        for (int t = 0; t < 27; ++t)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                wsum[j][0] += w[t][j][0];
+                wsum[j][1] += w[t][j][1];
+            }
+        tconst[0][tid] = make_float4(bias[0][0], bias[0][1], bias[1][0], bias[1][1]);
+        tconst[1][tid] = make_float4(scl[0][0], scl[0][1], scl[1][0], scl[1][1]);
+        tconst[2][tid] = make_float4(wsum[0][0], wsum[0][1], wsum[1][0], wsum[1][1]);
+    }
+
     const int s0 = blockIdx.y * p.spc;
     const int s1 = min(p.B, s0 + p.spc);
     const int toff = Geo::window_origin(xp, yp, z);  // window origin of this thread inside a tile
@@ -186,6 +221,7 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                 if (!mbar_wait_bounded(bar_base + 8 * par, ((smp - s0) >> 1) & 1, kSpinLimit) && p.error_flag)
                     *p.error_flag = 1;
             }
+            double hs = 0.0, hq = 0.0, is = 0.0, iq = 0.0;
 #pragma unroll
             for (int j = 0; j < SLOTS; ++j) {
                 const unsigned ci = cinfo[j];
@@ -197,6 +233,26 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                     }
                     tiles[set][0][ci & SOFF_MASK] = v;
                     if (ci & HALO_BIT) tiles[set][1][ci & SOFF_MASK] = v;
+                    if (NORM) {
+                        const double d = (double)v;
+                        if (ci & HALO_BIT) {
+                            hs += d;
+                            hq = fma(d, d, hq);
+                        } else {
+                            is += d;
+                            iq = fma(d, d, iq);
+                        }
+                    }
+                }
+            }
+            if (NORM) {
+                hs = warp_sum(hs);
+                hq = warp_sum(hq);
+                is = warp_sum(is);
+                iq = warp_sum(iq);
+                if ((tid & 31) == 0) {
+                    fresh_sums[set][0][tid >> 5] = make_double2(hs, hq);
+                    fresh_sums[set][1][tid >> 5] = make_double2(is, iq);
                 }
             }
         }
@@ -234,6 +290,30 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
         commit(smp + 1, set ^ 1);
         if (!USE_TMA) prefetch(smp + 2);
         load_stats(smp + 2);
+        // NORM: the sample's pivot and, relative to it, the sums of the halo (fixed for the sample) and of the
+        // fresh interior; every thread adds the same per-warp sums in the same order
+        float pivot = 0.0f;
+        if (NORM) {
+            if ((tid & 31) == 0) {  // one lane per warp; every warp adds the same sums in the same order
+                double hs = 0.0, hq = 0.0, is = 0.0, iq = 0.0;
+#pragma unroll
+                for (int wq = 0; wq < 4; ++wq) {
+                    const double2 h2 = fresh_sums[set][0][wq], i2 = fresh_sums[set][1][wq];
+                    hs += h2.x;
+                    hq += h2.y;
+                    is += i2.x;
+                    iq += i2.y;
+                }
+                const float pv = (float)((hs + is) * (1.0 / Geo::CELLS));
+                const double c = (double)pv;
+                constexpr double NI = 512.0, NH = Geo::CELLS - 512.0;
+                wnorm[0][tid >> 5] = make_float4((float)(hs - NH * c), (float)(hq - 2.0 * c * hs + NH * c * c),
+                                                 (float)(is - NI * c), (float)(iq - 2.0 * c * is + NI * c * c));
+                wnorm[1][tid >> 5] = make_float4(pv, 0.0f, 0.0f, 0.0f);
+            }
+            __syncwarp();
+            pivot = wnorm[1][tid >> 5].x;
+        }
 #pragma unroll
         for (int it = 0; it < (INNER_T > 0 ? INNER_T : inner); ++it) {
             const bool last = it + 1 == inner;
@@ -241,16 +321,37 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
             const float *tl = tiles[set][cur] + toff;
             float acc[2][2] = {{bias[0][0], bias[0][1]}, {bias[1][0], bias[1][1]}};
             float old[2][2];
+            // NORM: the interior sums of this tile relative to the pivot: this lane's share of the 128 partial
+            // sums; the five shuffle rounds that add them over the warp sit between the first stencil rows
+            float red_s = 0.0f, red_q = 0.0f;
+            if (NORM) {
+                if (it > 0) {
+                    const float4 a = *reinterpret_cast<const float4 *>(&part_sums[it & 1][(tid & 31) * 4]);
+                    const float4 c = *reinterpret_cast<const float4 *>(&part_sums[it & 1][(tid & 31) * 4 + 2]);
+                    red_s = (a.x + a.z) + (c.x + c.z);
+                    red_q = (a.y + a.w) + (c.y + c.w);
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j) acc[j][0] = acc[j][1] = 0.0f;
+            }
 #pragma unroll
             for (int a = 0; a < 3; ++a)
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const float2 v01 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS);
                     const float2 v23 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS + 2);
-                    const float v[4] = {v01.x, v01.y, v23.x, v23.y};
+                    float v[4] = {v01.x, v01.y, v23.x, v23.y};
                     if (a == 1 && (r == 1 || r == 2)) {
                         old[r - 1][0] = v[1];
                         old[r - 1][1] = v[2];
+                    }
+                    if (NORM) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) v[c] -= pivot;
+                        if (a * 4 + r < 5) {  // one shuffle round per row (uniform: every lane takes part)
+                            red_s += __shfl_xor_sync(0xffffffffu, red_s, 16 >> (a * 4 + r));
+                            red_q += __shfl_xor_sync(0xffffffffu, red_q, 16 >> (a * 4 + r));
+                        }
                     }
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
@@ -265,10 +366,32 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                     }
                 }
             float nv[2][2];
+            if (NORM) {
+                const float4 wn = wnorm[0][tid >> 5];
+                const float is = it > 0 ? red_s : wn.z, iq = it > 0 ? red_q : wn.w;
+                // the tile's mean relative to the pivot and 1 / (std + eps); approximate square root and reciprocal
+                // (a few ulp, far inside the tolerance of the comparison with the reference)
+                const float tmean = (wn.x + is) * (1.0f / Geo::CELLS);
+                const float var = fmaxf(fmaf(-tmean, tmean, (wn.y + iq) * (1.0f / Geo::CELLS)), 0.0f);
+                float sd, trs;
+                asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(sd) : "f"(var));
+                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(trs) : "f"(sd + p.norm_eps));
+                const float4 cb = tconst[0][tid], cs = tconst[1][tid], cw = tconst[2][tid];
+                const float bb[2][2] = {{cb.x, cb.y}, {cb.z, cb.w}}, ss[2][2] = {{cs.x, cs.y}, {cs.z, cs.w}};
+                const float ww[2][2] = {{cw.x, cw.y}, {cw.z, cw.w}};
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
+                for (int j = 0; j < 2; ++j)
 #pragma unroll
-                for (int i = 0; i < 2; ++i) nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
+                    for (int i = 0; i < 2; ++i) {
+                        acc[j][i] = fmaf(fmaf(-tmean, ww[j][i], acc[j][i]), trs, bb[j][i]);
+                        nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), ss[j][i], old[j][i]);
+                    }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), scl[j][i], old[j][i]);
+            }
             if (p.save_h) {  // replay for the backward pass: pre-activations, and activations between iterations
                 const size_t o = ((size_t)it * p.B + smp) * P + g00;
 #pragma unroll
@@ -287,6 +410,11 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                 for (int j = 0; j < 2; ++j) {
                     to[j * RS] = (z & 1) ? nv[j][1] : nv[j][0];
                     to[j * RS + step] = (z & 1) ? nv[j][0] : nv[j][1];
+                }
+                if (NORM) {
+                    const float d0 = nv[0][0] - pivot, d1 = nv[0][1] - pivot, d2 = nv[1][0] - pivot, d3 = nv[1][1] - pivot;
+                    part_sums[(it + 1) & 1][tid] =
+                        make_float2((d0 + d1) + (d2 + d3), fmaf(d0, d0, d1 * d1) + fmaf(d2, d2, d3 * d3));
                 }
                 __syncthreads();  // the other tile is complete; this one may be overwritten next
             } else {
@@ -327,7 +455,11 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
 // ------------------------------------------------------------------ launcher
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize)
 {
-    if ((block != 8 && block != 4) || normalize || p.inner < 1) return false;
+    if ((block != 8 && block != 4) || p.inner < 1) return false;
+    if (normalize != p.normalize) return false;  // the caller says which; the parameters must agree
+    if (normalize && (block != 8 || p.in_stats || p.out_partials || p.save_h || p.save_x || p.face_left || p.face_right ||
+                      p.kbn > 0))
+        return false;
     if (p.M % 8 || p.N % 8 || p.K % 8) return false;  // a CTA owns an 8 x 8 x 8 region also with block 4
     if ((long long)p.M * p.N * p.K >= (1LL << 31)) return false;
     auto al = [](const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; };
@@ -422,6 +554,23 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
         else if (sout) ONE_(A, false, true);    \
         else ONE_(A, false, false);             \
     } while (0)
+#define NORM_(A)                                                                                                  \
+    do {                                                                                                          \
+        if (tma && p.inner == 2) step_fwd_fast8<8, A, false, false, true, 2, true><<<grid, fast8::THREADS, 0, st>>>(map, p); \
+        else if (tma && p.inner == 4) step_fwd_fast8<8, A, false, false, true, 4, true><<<grid, fast8::THREADS, 0, st>>>(map, p); \
+        else if (tma) step_fwd_fast8<8, A, false, false, true, 0, true><<<grid, fast8::THREADS, 0, st>>>(map, p); \
+        else step_fwd_fast8<8, A, false, false, false, 0, true><<<grid, fast8::THREADS, 0, st>>>(map, p);         \
+    } while (0)
+    if (p.normalize) {
+        switch (act) {
+        case GN_ACT_RELU: NORM_(GN_ACT_RELU); break;
+        case GN_ACT_LEAKY_RELU: NORM_(GN_ACT_LEAKY_RELU); break;
+        case GN_ACT_SILU: NORM_(GN_ACT_SILU); break;
+        default: NORM_(GN_ACT_TANH); break;
+        }
+        return check_launch("step_fwd_fast8 (per-block normalisation)");
+    }
+#undef NORM_
     switch (act) {
     case GN_ACT_RELU: LAUNCH_(GN_ACT_RELU); break;
     case GN_ACT_LEAKY_RELU: LAUNCH_(GN_ACT_LEAKY_RELU); break;

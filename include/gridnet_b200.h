@@ -204,6 +204,15 @@ GN_API int gn_norm_backward_f32(const float *x, const float *gamma, const float 
                          float *grad_gamma, float *grad_beta, int B, long long P, float eps,
                          void *workspace, size_t workspace_bytes, void *stream);
 
+/* The residual form of the model loop, gridnet/scripts/train_imagenet.py:81-83: n = LayerNorm(h); h' = h + (net(n) - n).
+ * Given h [B,P], y = net(n) [B,P] and the (mean, rstd) of h, writes out = h + (y - LayerNorm(h)) (out may alias h or
+ * y) and the (mean, rstd) of out for the next step, so the normalised tensor itself is never stored: the step
+ * kernel normalises h while loading it (gn_step_forward_train_f32 with in_mean_rstd). workspace:
+ * gn_norm_workspace_bytes(B, P). */
+GN_API int gn_norm_residual_combine_f32(const float *h, const float *y, const float *gamma, const float *beta,
+                                        const float *mean_rstd_h, float *out, float *mean_rstd_out, int B, long long P,
+                                        float eps, void *workspace, size_t workspace_bytes, void *stream);
+
 /* The same normalisation in pieces, for a grid whose positions are spread over several ranks (slab sharding:
  * each rank holds P of the P_total positions of every sample). The caller adds the [B][2] double sums of the
  * ranks (an all-reduce) between the calls; no counterpart in the reference, which is single-device.

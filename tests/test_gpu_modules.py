@@ -135,3 +135,55 @@ def test_host_pipelined_forward_matches_outer_forward():
     for xi, yi in zip(hx, hy):
         want = gb.outer_forward(w, b, s, gamma, beta, xi.cuda(), 2, 3, 8).cpu()
         assert torch.equal(yi, want)
+
+
+@pytest.mark.parametrize("block", [8, 4])
+def test_fused_loop_variants_equal_the_step_by_step_composition(block):
+    """Per-step parameters (with gradients, through FusedLoopSeparateTrainOp) and the residual form (without,
+    through fused_loop_forward) against the composition of the step op and the norm op, which the other tests pin
+    to the oracle (gridnet/scripts/train_imagenet.py:76-86)."""
+    import gridnet_b200 as gb
+
+    g = torch.Generator().manual_seed(17)
+    shape, B, inner, outer = (16, 8, 16), 3, 2, 3
+    dev = "cuda"
+    mk = lambda *sz, scale=1.0, shift=0.0: (shift + scale * torch.randn(*sz, generator=g)).to(dev)
+    plist = [(mk(27, *shape, scale=27 ** -0.5), mk(*shape, scale=0.1), mk(*shape, scale=0.1, shift=1.0))
+             for _ in range(outer)]
+    gamma, beta = mk(*shape, scale=0.1, shift=1.0), mk(*shape, scale=0.1)
+    x, gy = mk(B, *shape), mk(B, *shape)
+
+    def composition(leaves_p, ga, be, xin, residual):
+        h = xin
+        for w, b, s in leaves_p:
+            if residual:
+                n = gb.GridNormOp.apply(h, ga, be, 1e-5)
+                h = h + (gb.GridnetCudaOp.apply(w, b, s, n, inner, block, 1e-5, False, "silu") - n)
+            else:
+                h = gb.GridNormOp.apply(gb.GridnetCudaOp.apply(w, b, s, h, inner, block, 1e-5, False, "silu"), ga, be, 1e-5)
+        return h
+
+    # inference, both forms
+    with torch.no_grad():
+        for residual in (False, True):
+            want = composition(plist, gamma, beta, x, residual)
+            got = gb.fused_loop_forward(plist, gamma, beta, x, inner, block, "silu", 1e-5, outer_residual=residual)
+            assert torch.allclose(got, want, rtol=1e-4, atol=1e-5), (residual, (got - want).abs().max().item())
+        assert torch.equal(gb.fused_loop_forward([], gamma, beta, x, inner, block, "silu", 1e-5, outer_residual=True), x)
+
+    # training with per-step parameters
+    def leaves():
+        ps = [tuple(t.clone().requires_grad_(True) for t in p) for p in plist]
+        return ps, gamma.clone().requires_grad_(True), beta.clone().requires_grad_(True), x.clone().requires_grad_(True)
+
+    ps, ga, be, xl = leaves()
+    flat = [t for p in ps for t in p]
+    want_y = composition(ps, ga, be, xl, False)
+    want = torch.autograd.grad(want_y, [ga, be, xl] + flat, gy)
+    ps, ga, be, xl = leaves()
+    flat = [t for p in ps for t in p]
+    got_y = gb.FusedLoopSeparateTrainOp.apply(ga, be, xl, inner, block, "silu", 1e-5, *flat)
+    got = torch.autograd.grad(got_y, [ga, be, xl] + flat, gy)
+    assert torch.allclose(got_y, want_y, rtol=1e-4, atol=1e-5)
+    for i, (a, c) in enumerate(zip(got, want)):
+        assert torch.allclose(a, c, rtol=1e-3, atol=1e-4 * (1 + c.abs().max().item())), (i, (a - c).abs().max().item())
