@@ -319,10 +319,12 @@ GN_API int gn_step_backward_f64(const double *w, const double *b, const double *
 GN_API size_t gn_step_backward_workspace_bytes(int B, int M, int N, int K, int inner, int block, int normalize,
                                                int elem_size)
 {
-    if (elem_size != 4 || (block != 8 && block != 4) || normalize || inner < 1 || B <= 0 || M <= 0 || N <= 0 || K <= 0)
-        return 0;
+    if (elem_size != 4 || (block != 8 && block != 4) || inner < 1 || B <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+    if (normalize && block != 8) return 0;  // per-block normalisation: the tuned path covers block 8
     if (M % 8 || N % 8 || K % 8) return 0;
-    return align_up(sizeof(float) * bwd_fast8_workspace_floats(B, M, N, K, inner, true), 256);
+    // with per-block normalisation the tile statistics and halo terms follow the ordinary workspace
+    const size_t extra = normalize ? bwd_fast8_norm_extra_floats(B, M, N, K, inner) : 0;
+    return align_up(sizeof(float) * (bwd_fast8_workspace_floats(B, M, N, K, inner, true) + extra), 256);
 }
 
 GN_API size_t gn_step_backward_error_flag_offset(int B, int M, int N, int K, int inner)
@@ -343,7 +345,7 @@ GN_API int gn_step_backward_ws_f32(const float *w, const float *b, const float *
         w && b && s && x && gy && gw && gb && gs && gx &&
         bwd_fast8_applicable(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, normalize))
         return launch_step_bwd_fast8(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, act, nullptr,
-                                     (float *)workspace, (cudaStream_t)stream);
+                                     (float *)workspace, (cudaStream_t)stream, normalize ? 1 : 0, eps);
     return api_step_backward<float>(w, b, s, x, gy, gw, gb, gs, gx, B, M, N, K, inner, block, eps, normalize, act,
                                     stream);
 }

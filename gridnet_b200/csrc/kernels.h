@@ -50,6 +50,9 @@ struct FastFwdParams {
     // replay mode or the slab mode above. norm_eps is added to the tile's standard deviation.
     int normalize;
     float norm_eps;
+    // Replay mode with per-block normalisation: [inner][B][regions] (mean, 1 / (std + eps), std, std + eps) of the
+    // tile every iteration normalised, for the backward kernels; nullptr = not wanted.
+    float4 *tile_stats;
 };
 bool fast8_applicable(const FastFwdParams &p, int block, int normalize);
 extern int g_fast8_spc_override;  // tuning knob: samples per CTA of the tuned forward kernel, 0 = automatic
@@ -84,7 +87,8 @@ bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const 
                           int normalize);
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
-                          const float *stash, float *ws, cudaStream_t st);
+                          const float *stash, float *ws, cudaStream_t st, int normalize = 0, float eps = 0.0f);
+size_t bwd_fast8_norm_extra_floats(int B, int M, int N, int K, int inner);
 
 // ---- step_pair64.cu ("lanes = samples" kernel for large batches; activations in the IL64 layout
 // [group][z][y][x][64 samples], weights pre-packed per block half)

@@ -52,17 +52,37 @@ struct BwdParams {
     int B, M, N, K, inner, spc;
     int *error_flag;     // set to 1 if a bounded wait on a bulk copy gave up
     int cluster_reduce;  // wgrad: the batch chunks of a block are one cluster and reduce through shared memory
+    // Per-block normalisation (block 8): the bias, the replay's per-tile statistics [inner][B][regions]
+    // (mean, 1 / (std + eps), std, std + eps), and per sample and region the two sums that every cell of the
+    // region's tile owes to the statistics ([B][regions] (F, E): grad_x[c] -= F + x[c] * E).
+    const float *b;
+    const float4 *tile_stats;
+    float2 *hterm;
 };
 
 // ---------------------------------------------------------------------------- reverse sweep
 // INNER_T > 0: the inner iteration count is a compile-time constant (loop unrolled); 0: from the parameters.
-template <int SUB, int ACT, int INNER_T>
+//
+// NORM (per-block normalisation, gridnet/backend_torch.py:92-97): the stencil input of iteration t was
+// in = (tile - mean_t) * inv_t with inv_t = 1 / (std_t + eps) over all 1000 tile cells. With Gin[c] the gradient
+// of the stencil inputs, the tile gradient is inv Gin[c] - P1 - P2 (x[c] - mean), P1 = inv sum(Gin) / 1000,
+// P2 = inv sum(Gin in) / (1000 std). Both sums are sums over the block's NEURONS, no halo gradient needed:
+// sum(Gin) = sum_n delta[n] W[n] (W = the neuron's 27 weights added up) and sum(Gin in) = sum_n delta[n] (h[n] -
+// bias[n]). So the kernel scales delta by inv (tile, stored deltas and their sum: the other kernels then see
+// inv Gin), reduces the two sums over the CTA while the gather runs (per-thread partial sums published by the
+// barrier that publishes the delta tile; every warp adds the 128 of them between its first stencil rows), and
+// subtracts P1 + P2 (x_t[n] - mean) from its own cells. What the halo cells owe, F = sum_t (P1 - P2 mean) and
+// E = sum_t P2, goes to hterm for the cross-block kernel.
+template <int SUB, int ACT, int INNER_T, bool NORM = false>
 __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams p)
 {
     using namespace bwd8;
     using Geo = PatchGeo<SUB>;
     constexpr int RS = Geo::RS, PS = Geo::PS, TS = Geo::TS;
+    static_assert(!NORM || SUB == 8, "per-block normalisation: block 8");
     __shared__ __align__(16) float D[2][TS];
+    __shared__ __align__(16) float2 part_sums[2][NORM ? THREADS : 1];
+    __shared__ float4 tconst[3][NORM ? THREADS : 1];  // bias, weight sum, scale of the thread's four neurons
     const int tid = threadIdx.x;
     const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
     const int nbx = p.K >> 3, nby = p.N >> 3;
@@ -98,6 +118,20 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
         scl[j][0] = v.x;
         scl[j][1] = v.y;
     }
+    if (NORM) {
+        float ws[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+        for (int t = 0; t < 27; ++t)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float2 v = *reinterpret_cast<const float2 *>(p.w + (size_t)t * P + g00 + (size_t)j * K);
+                ws[j][0] += v.x;
+                ws[j][1] += v.y;
+            }
+        const float2 b0 = *reinterpret_cast<const float2 *>(p.b + g00), b1 = *reinterpret_cast<const float2 *>(p.b + g00 + K);
+        tconst[0][tid] = make_float4(b0.x, b0.y, b1.x, b1.y);
+        tconst[1][tid] = make_float4(ws[0][0], ws[0][1], ws[1][0], ws[1][1]);
+        tconst[2][tid] = make_float4(scl[0][0], scl[0][1], scl[1][0], scl[1][1]);
+    }
     for (int i = tid; i < 2 * TS; i += THREADS) (&D[0][0])[i] = 0.0f;  // the halo of both tiles stays zero
     __syncthreads();
 
@@ -107,12 +141,24 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
     // pre-activations of the iteration handled next and the next sample's output gradient are
     // fetched one iteration early
     float2 hn[2], gn[2];
+    // NORM: the tile statistics and this thread's activations x_t of the iteration handled next
+    float4 tsn = make_float4(0.0f, 1.0f, 1.0f, 1.0f);
+    float2 xn[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+    auto fetch_norm = [&](int smp, int it) {
+        if (NORM) {
+            tsn = p.tile_stats[((size_t)it * p.B + smp) * gridDim.x + blk];
+            const float *src = it > 0 ? p.save_x + ((size_t)(it - 1) * p.B + smp) * P : p.x + (size_t)smp * P;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) xn[j] = ld_pinned2(src + g00 + (size_t)j * K);
+        }
+    };
     if (s0 < s1) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             hn[j] = ld_pinned2(p.save_h + ((size_t)((INNER_T > 0 ? INNER_T : p.inner) - 1) * p.B + s0) * P + g00 + (size_t)j * K);
             gn[j] = ld_pinned2(p.gy + (size_t)s0 * P + g00 + (size_t)j * K);
         }
+        fetch_norm(s0, (INNER_T > 0 ? INNER_T : p.inner) - 1);
     }
     for (int smp = s0; smp < s1; ++smp) {
         const size_t so = (size_t)smp * P + g00;
@@ -123,6 +169,7 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
             g[j][1] = gn[j].y;
             dsum[j][0] = dsum[j][1] = dsacc[j][0] = dsacc[j][1] = 0.0f;
         }
+        float hF = 0.0f, hE = 0.0f;  // NORM: what every cell of the tile owes to the statistics, summed over t
         const int inner = INNER_T > 0 ? INNER_T : p.inner;
 #pragma unroll
         for (int it = (INNER_T > 0 ? INNER_T : inner) - 1; it >= 0; --it, ++step) {
@@ -130,30 +177,58 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
             float *Dt = D[step & 1];
             float dl[2][2];
             const float2 hc[2] = {hn[0], hn[1]};
+            const float4 ts = tsn;
+            const float2 xc[2] = {xn[0], xn[1]};
             if (it > 0) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
                     hn[j] = ld_pinned2(p.save_h + ho - (size_t)p.B * P + (size_t)j * K);
+                fetch_norm(smp, it - 1);
             } else if (smp + 1 < s1) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     hn[j] = ld_pinned2(p.save_h + ((size_t)(inner - 1) * p.B + smp + 1) * P + g00 + (size_t)j * K);
                     gn[j] = ld_pinned2(p.gy + so + P + (size_t)j * K);
                 }
+                fetch_norm(smp + 1, inner - 1);
             }
+            if (NORM) {
+                const float4 cb = tconst[0][tid], cw = tconst[1][tid], cs = tconst[2][tid];
+                const float bb[2][2] = {{cb.x, cb.y}, {cb.z, cb.w}}, ww[2][2] = {{cw.x, cw.y}, {cw.z, cw.w}};
+                const float ss[2][2] = {{cs.x, cs.y}, {cs.z, cs.w}};
+                float pa = 0.0f, pc = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const float2 h = hc[j];
-                float f0, d0, f1, d1;
-                Act<ACT, float>::both(h.x, f0, d0);
-                Act<ACT, float>::both(h.y, f1, d1);
-                dsacc[j][0] = fmaf(f0, g[j][0], dsacc[j][0]);
-                dsacc[j][1] = fmaf(f1, g[j][1], dsacc[j][1]);
-                dl[j][0] = d0 * g[j][0] * scl[j][0];
-                dl[j][1] = d1 * g[j][1] * scl[j][1];
-                dsum[j][0] += dl[j][0];
-                dsum[j][1] += dl[j][1];
-                *reinterpret_cast<float2 *>(p.delta + ho + (size_t)j * K) = make_float2(dl[j][0], dl[j][1]);
+                for (int j = 0; j < 2; ++j) {
+                    const float hv[2] = {hc[j].x, hc[j].y};
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        float f, d;
+                        Act<ACT, float>::both(hv[i], f, d);
+                        dsacc[j][i] = fmaf(f, g[j][i], dsacc[j][i]);
+                        const float raw = d * g[j][i] * ss[j][i];
+                        pa = fmaf(raw, ww[j][i], pa);
+                        pc = fmaf(raw, hv[i] - bb[j][i], pc);
+                        dl[j][i] = raw * ts.y;  // everything downstream sees delta / (std + eps)
+                        dsum[j][i] += dl[j][i];
+                    }
+                    *reinterpret_cast<float2 *>(p.delta + ho + (size_t)j * K) = make_float2(dl[j][0], dl[j][1]);
+                }
+                part_sums[step & 1][tid] = make_float2(pa, pc);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float2 h = hc[j];
+                    float f0, d0, f1, d1;
+                    Act<ACT, float>::both(h.x, f0, d0);
+                    Act<ACT, float>::both(h.y, f1, d1);
+                    dsacc[j][0] = fmaf(f0, g[j][0], dsacc[j][0]);
+                    dsacc[j][1] = fmaf(f1, g[j][1], dsacc[j][1]);
+                    dl[j][0] = d0 * g[j][0] * scl[j][0];
+                    dl[j][1] = d1 * g[j][1] * scl[j][1];
+                    dsum[j][0] += dl[j][0];
+                    dsum[j][1] += dl[j][1];
+                    *reinterpret_cast<float2 *>(p.delta + ho + (size_t)j * K) = make_float2(dl[j][0], dl[j][1]);
+                }
             }
             {
                 float *to = Dt + toff + PS + RS + 1 + (z & 1);
@@ -165,6 +240,13 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
                 }
             }
             __syncthreads();
+            float red_a = 0.0f, red_c = 0.0f;  // NORM: this lane's share of the 128 partial sums
+            if (NORM) {
+                const float4 a = *reinterpret_cast<const float4 *>(&part_sums[step & 1][(tid & 31) * 4]);
+                const float4 c = *reinterpret_cast<const float4 *>(&part_sums[step & 1][(tid & 31) * 4 + 2]);
+                red_a = (a.x + a.z) + (c.x + c.z);
+                red_c = (a.y + a.w) + (c.y + c.w);
+            }
             const float *tl = Dt + toff;
 #pragma unroll
             for (int a = 0; a < 3; ++a)
@@ -173,6 +255,10 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
                     const float2 v01 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS);
                     const float2 v23 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS + 2);
                     const float v[4] = {v01.x, v01.y, v23.x, v23.y};
+                    if (NORM && a * 4 + r < 5) {  // one shuffle round per row (uniform: every lane takes part)
+                        red_a += __shfl_xor_sync(0xffffffffu, red_a, 16 >> (a * 4 + r));
+                        red_c += __shfl_xor_sync(0xffffffffu, red_c, 16 >> (a * 4 + r));
+                    }
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const int bb = r - j;
@@ -185,7 +271,19 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
                         }
                     }
                 }
+            if (NORM) {
+                const float p1 = ts.y * red_a * (1.0f / Geo::CELLS);
+                const float p2 = red_c * ts.y / ((float)Geo::CELLS * ts.z);
+                hF += fmaf(-p2, ts.x, p1);
+                hE += p2;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    g[j][0] -= fmaf(p2, xc[j].x - ts.x, p1);
+                    g[j][1] -= fmaf(p2, xc[j].y - ts.x, p1);
+                }
+            }
         }
+        if (NORM && tid == 0) p.hterm[(size_t)smp * gridDim.x + blk] = make_float2(hF, hE);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             *reinterpret_cast<float2 *>(p.gx + so + (size_t)j * K) = make_float2(g[j][0], g[j][1]);
@@ -196,7 +294,10 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
 }
 
 // ------------------------------------------------------------------------- weight gradients
-template <int SUB, bool USE_TMA>
+// NORM (per-block normalisation): the stencil input was (tile - mean_t) / (std_t + eps) and the stored deltas
+// are already divided by (std_t + eps), so the tile mean is subtracted from each window value and the bias
+// gradient multiplies the stored delta by (std_t + eps) again.
+template <int SUB, bool USE_TMA, bool NORM = false>
 __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_constant__ CUtensorMap x_map, const BwdParams p)
 {
     using namespace bwd8;
@@ -292,8 +393,10 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
         __syncthreads();
     }
     float2 xn[2], dn[2];  // own activations and deltas of the step handled next
+    float4 tsn = make_float4(0.0f, 1.0f, 1.0f, 1.0f);  // NORM: and its tile statistics
     auto fetch_step = [&](int smp, int it) {
         if (smp < s1) {
+            if (NORM) tsn = p.tile_stats[((size_t)it * p.B + smp) * gridDim.x + blk];
             const size_t o = ((size_t)it * p.B + smp) * P + g00;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -327,6 +430,7 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
         if (!USE_TMA) fetch_tile(smp + 1);
         for (int it = 0; it < p.inner; ++it) {
             float dl[2][2] = {{dn[0].x, dn[0].y}, {dn[1].x, dn[1].y}};
+            const float tmean = tsn.x, tsd = tsn.w;
             float *tl_w = tiles[it & 1];
             if (it > 0) {
                 float *to = tl_w + toff + PS + RS + 1;
@@ -340,8 +444,8 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
             else fetch_step(smp + 1, 0);
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                db[j][0] += dl[j][0];
-                db[j][1] += dl[j][1];
+                db[j][0] = NORM ? fmaf(dl[j][0], tsd, db[j][0]) : db[j][0] + dl[j][0];
+                db[j][1] = NORM ? fmaf(dl[j][1], tsd, db[j][1]) : db[j][1] + dl[j][1];
             }
             __syncthreads();  // tile complete (the other tile may still be read by slower threads)
             if (USE_TMA && it == 0) fetch_tile(smp + 2);  // everyone has copied this sample's staging buffer
@@ -352,7 +456,11 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
                 for (int r = 0; r < 4; ++r) {
                     const float2 v01 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS);
                     const float2 v23 = *reinterpret_cast<const float2 *>(tl + a * PS + r * RS + 2);
-                    const float v[4] = {v01.x, v01.y, v23.x, v23.y};
+                    float v[4] = {v01.x, v01.y, v23.x, v23.y};
+                    if (NORM) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) v[c] -= tmean;
+                    }
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const int bb = r - j;
@@ -571,8 +679,13 @@ constexpr int TS = 1000;
 constexpr int SLOTS = 3;  // ceil(1000 / 384)
 }  // namespace border8
 
+// hterm != nullptr (per-block normalisation): every cell of a region's tile, halo included, also owes
+// F + x[c] E to that region's statistics (bwd_reverse8 has taken it from the region's own cells); a surface
+// cell lies in the tiles of the up to seven neighbouring regions across the faces it touches.
 __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *__restrict__ w, const float *__restrict__ dsum,
-                                                                  float *__restrict__ gx, int B, int M, int N, int K, int spc)
+                                                                  float *__restrict__ gx, int B, int M, int N, int K, int spc,
+                                                                  const float2 *__restrict__ hterm,
+                                                                  const float *__restrict__ x)
 {
     using namespace border8;
     __shared__ float tile[2][TS];
@@ -648,6 +761,22 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
     const int pz = (sz == 0 || sz == 7) ? (sz / 7) * 64 + sy * 8 + sx : -1;
     const int py = (sy == 0 || sy == 7) ? (sy / 7) * 64 + sz * 8 + sx : -1;
     const int px = (sx == 0 || sx == 7) ? (sx / 7) * 64 + sz * 8 + sy : -1;
+    // the neighbouring regions whose tile holds this surface cell, in a fixed order (-1: none)
+    int nbr[7];
+    {
+        const int fz = sz == 0 ? -1 : (sz == 7 ? 1 : 0), fy = sy == 0 ? -1 : (sy == 7 ? 1 : 0), fx = sx == 0 ? -1 : (sx == 7 ? 1 : 0);
+        const int nbz = M >> 3;
+#pragma unroll
+        for (int q = 1; q < 8; ++q) {
+            const int dz = (q & 4) ? fz : 0, dy = (q & 2) ? fy : 0, dx = (q & 1) ? fx : 0;
+            const bool real = ((q & 4) == 0 || fz != 0) && ((q & 2) == 0 || fy != 0) && ((q & 1) == 0 || fx != 0);
+            const int z2 = bz + dz, y2 = by + dy, x2 = bx + dx;
+            nbr[q - 1] = (hterm && active && real && z2 >= 0 && z2 < nbz && y2 >= 0 && y2 < nby && x2 >= 0 && x2 < nbx)
+                             ? (z2 * nby + y2) * nbx + x2
+                             : -1;
+        }
+    }
+    const unsigned nregions = gridDim.x;
 
     const int s0 = blockIdx.y * spc, s1 = min(B, s0 + spc);
     float pf[SLOTS];
@@ -685,6 +814,17 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
             if (pz >= 0) acc += part[par][0][pz];
             if (py >= 0) acc += part[par][1][py];
             if (px >= 0) acc += part[par][2][px];
+            if (hterm) {
+                float f = 0.0f, e = 0.0f;
+#pragma unroll
+                for (int q = 0; q < 7; ++q)
+                    if (nbr[q] >= 0) {
+                        const float2 t = hterm[(size_t)smp * nregions + nbr[q]];
+                        f += t.x;
+                        e += t.y;
+                    }
+                acc -= fmaf(x[(size_t)smp * P + c], e, f);
+            }
             gx[(size_t)smp * P + c] = acc;
         }
     }
@@ -696,6 +836,14 @@ size_t bwd_fast8_stash_floats(int B, int M, int N, int K, int inner)
     // pre-activations of every iteration and the activations between iterations
     const size_t BP = (size_t)B * M * N * K;
     return (size_t)inner * BP + (size_t)(inner > 1 ? inner - 1 : 0) * BP;
+}
+
+// floats that the per-block-normalisation backward needs after the ordinary workspace (whose last 16 bytes hold
+// the error flag): the tile statistics [inner][B][regions] float4 and the halo terms [B][regions] float2
+size_t bwd_fast8_norm_extra_floats(int B, int M, int N, int K, int inner)
+{
+    const size_t regions = (size_t)(M / 8) * (N / 8) * (K / 8);
+    return (size_t)inner * B * regions * 4 + (size_t)B * regions * 2;
 }
 
 size_t bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner, bool with_stash)
@@ -713,17 +861,18 @@ bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const 
     FastFwdParams f{};
     f.w = w; f.b = b; f.s = s; f.x = x;
     f.B = B; f.M = M; f.N = N; f.K = K; f.inner = inner;
-    if (!fast8_applicable(f, block, normalize)) return false;
+    f.normalize = normalize ? 1 : 0;  // per-block normalisation: block 8 only (fast8_applicable says so)
+    if (!fast8_applicable(f, block, f.normalize)) return false;
     auto al8 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 7) == 0; };
     return al8(gy) && al8(gw) && al8(gb) && al8(gs) && al8(gx) && al8(x);
 }
 
 // wgrad launch for one instantiation: plain when one CTA covers a block's batch, otherwise the
 // batch chunks of a block as one thread-block cluster
-template <int SUB, bool USE_TMA>
+template <int SUB, bool USE_TMA, bool NORM = false>
 static int launch_wgrad(const CUtensorMap &map, const BwdParams &p, long long nb, unsigned chunks, cudaStream_t st)
 {
-    auto kern = bwd_wgrad8<SUB, USE_TMA>;
+    auto kern = bwd_wgrad8<SUB, USE_TMA, NORM>;
     if (chunks <= 1) {
         kern<<<(unsigned)nb, bwd8::THREADS, 0, st>>>(map, p);
         return GN_OK;
@@ -771,7 +920,7 @@ static void launch_reverse(const BwdParams &p, dim3 grid, int act, cudaStream_t 
 
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
-                          const float *stash, float *ws, cudaStream_t st)
+                          const float *stash, float *ws, cudaStream_t st, int normalize, float eps)
 {
     // stash != nullptr: the forward pass kept the pre-activations and intermediate activations
     // (launch_step_fwd_fast8 with save_h / save_x), so the replay is skipped
@@ -782,6 +931,11 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     float *dsum = delta + (size_t)inner * BP;
     float *dsb = dsum + BP;
     int *error_flag = reinterpret_cast<int *>(dsb + BP);
+    // per-block normalisation: the replay's tile statistics and the halo terms follow the flag's 16 bytes
+    const long long nregions = (long long)(M / 8) * (N / 8) * (K / 8);
+    float4 *tile_stats = reinterpret_cast<float4 *>(dsb + BP + 4);
+    float2 *hterm = reinterpret_cast<float2 *>(tile_stats + (size_t)inner * B * nregions);
+    if (normalize && (stash || block != 8)) return GN_ERR_UNSUPPORTED;
     if (cudaMemsetAsync(error_flag, 0, sizeof(int), st) != cudaSuccess) {
         record_cuda_error(cudaGetLastError(), "cudaMemsetAsync");
         return GN_ERR_CUDA;
@@ -794,6 +948,9 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     f.save_h = save_h;
     f.save_x = save_x;
     f.error_flag = error_flag;
+    f.normalize = normalize ? 1 : 0;
+    f.norm_eps = eps;
+    f.tile_stats = normalize ? tile_stats : nullptr;
     if (!stash) {
         rc = launch_step_fwd_fast8(f, act, st);
         if (rc != GN_OK) return rc;
@@ -805,11 +962,21 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     p.delta = delta; p.dsum = dsum; p.dsb = dsb; p.gw = gw; p.gb = gb; p.gs = gs; p.gx = gx;
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
     p.error_flag = error_flag;
+    p.b = b;
+    p.tile_stats = tile_stats;
+    p.hterm = hterm;
     {
         const int chunks = pick_batch_chunks_balanced(nb, B, 3, 1.5, 16);
         p.spc = (B + chunks - 1) / chunks;
         dim3 grid((unsigned)nb, (unsigned)((B + p.spc - 1) / p.spc));
-        if (block == 4) launch_reverse<4>(p, grid, act, st);
+        if (normalize) {
+            switch (act) {
+            case GN_ACT_RELU: bwd_reverse8<8, GN_ACT_RELU, 0, true><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+            case GN_ACT_LEAKY_RELU: bwd_reverse8<8, GN_ACT_LEAKY_RELU, 0, true><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+            case GN_ACT_SILU: bwd_reverse8<8, GN_ACT_SILU, 0, true><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+            default: bwd_reverse8<8, GN_ACT_TANH, 0, true><<<grid, bwd8::THREADS, 0, st>>>(p); break;
+            }
+        } else if (block == 4) launch_reverse<4>(p, grid, act, st);
         else launch_reverse<8>(p, grid, act, st);
         rc = check_launch("bwd_reverse8");
         if (rc != GN_OK) return rc;
@@ -827,6 +994,8 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
         if (block == 4) {
             if (!tma) return GN_ERR_UNSUPPORTED;  // excluded by bwd_fast8_applicable
             rc = launch_wgrad<4, true>(map, p, nb, chunks, st);
+        } else if (normalize) {
+            rc = tma ? launch_wgrad<8, true, true>(map, p, nb, chunks, st) : launch_wgrad<8, false, true>(map, p, nb, chunks, st);
         } else if (tma) {
             rc = launch_wgrad<8, true>(map, p, nb, chunks, st);
         } else {
@@ -841,7 +1010,7 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
         const int spc = (B + chunks - 1) / chunks;
         dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
         if (block == 4) bwd_halo8_k<4><<<grid, HaloGeo<4>::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
-        else bwd_border8_k<<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
+        else bwd_border8_k<<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc, normalize ? hterm : nullptr, x);
     }
     rc = check_launch("bwd_halo8");
     if (rc != GN_OK) return rc;

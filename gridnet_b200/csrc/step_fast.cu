@@ -376,6 +376,9 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                 float sd, trs;
                 asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(sd) : "f"(var));
                 asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(trs) : "f"(sd + p.norm_eps));
+                if (p.tile_stats && tid == 0)  // every thread holds the same values
+                    p.tile_stats[((size_t)it * p.B + smp) * gridDim.x + blk] =
+                        make_float4(pivot + tmean, trs, sd, sd + p.norm_eps);
                 const float4 cb = tconst[0][tid], cs = tconst[1][tid], cw = tconst[2][tid];
                 const float bb[2][2] = {{cb.x, cb.y}, {cb.z, cb.w}}, ss[2][2] = {{cs.x, cs.y}, {cs.z, cs.w}};
                 const float ww[2][2] = {{cw.x, cw.y}, {cw.z, cw.w}};
@@ -457,8 +460,7 @@ bool fast8_applicable(const FastFwdParams &p, int block, int normalize)
 {
     if ((block != 8 && block != 4) || p.inner < 1) return false;
     if (normalize != p.normalize) return false;  // the caller says which; the parameters must agree
-    if (normalize && (block != 8 || p.in_stats || p.out_partials || p.save_h || p.save_x || p.face_left || p.face_right ||
-                      p.kbn > 0))
+    if (normalize && (block != 8 || p.in_stats || p.out_partials || p.face_left || p.face_right || p.kbn > 0))
         return false;
     if (p.M % 8 || p.N % 8 || p.K % 8) return false;  // a CTA owns an 8 x 8 x 8 region also with block 4
     if ((long long)p.M * p.N * p.K >= (1LL << 31)) return false;

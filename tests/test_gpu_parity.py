@@ -344,11 +344,11 @@ def test_extension_layer_errors():
         gridnet_cuda.forward(w, b, s, xt, y, 1, 8, 1e-5, False, "silu")
     from gridnet_b200._lib import lib
 
-    big = lib.gn_step_backward_max_inner(8, 4) + 1
-    tw = w.clone().requires_grad_(True)
-    # (per-block normalisation on: the one-kernel backward with its shared-memory stash; the tuned
-    # float path for normalize=False has no such limit)
-    out = Op.apply(tw, b, s, x, big, 8, 1e-5, True, "relu")
+    big = lib.gn_step_backward_max_inner(8, 8) + 1
+    tw = w.double().requires_grad_(True)
+    # (double precision: the one-kernel backward with its shared-memory stash; the tuned float paths
+    # have no such limit)
+    out = Op.apply(tw, b.double(), s.double(), x.double(), big, 8, 1e-5, True, "relu")
     with pytest.raises(RuntimeError, match="inner"):
         out.sum().backward()
     # an empty batch returns a clone without launching anything
@@ -478,8 +478,53 @@ def test_tuned_backward_equals_one_kernel_backward(block):
     assert lib.gn_step_backward_stash_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), tgy.data_ptr(),
                                           *(t.data_ptr() for t in g), B, M, N, K, inner, block, 2, stash.data_ptr(),
                                           stash.numel() - 512, ws2.data_ptr(), ws2.numel(), stream) == -6
-    # no tuned path: sides that are not multiples of 8, per-block normalisation, double precision
+    # no tuned path: sides that are not multiples of 8, per-block normalisation at block 4, double precision
     assert lib.gn_step_stash_bytes(B, 12, N, K, inner, 4) == 0
     assert lib.gn_step_backward_workspace_bytes(B, 12, N, K, inner, 4, 0, 4) == 0
-    assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, block, 1, 4) == 0
+    assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, 4, 1, 4) == 0
     assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, block, 0, 8) == 0
+
+
+@pytest.mark.parametrize("activation", ["silu", "tanh", "leaky_relu"])
+def test_tuned_backward_with_per_block_normalisation(activation):
+    """float32, normalize on, block 8: the four-kernel path (replay with tile statistics, reverse sweep with the
+    two block sums, weight gradients on mean-free tiles, cross-block kernel with the halo terms) against the
+    float64 oracle on a grid with interior, face, edge and corner blocks and an odd batch; bit-identical when
+    repeated (no floating-point atomics); and against the one-kernel path, which scatters with atomics
+    (gridnet/backend_torch.py:92-97, src/gridnet_cuda_kernels.cu:396-416)."""
+    from gridnet_b200._lib import lib
+
+    shape, B, inner = (24, 16, 32), 5, 3
+    w, b, s, x = rng_inputs(51, B, shape, unit_scale=False)
+    x = (x + 0.5).astype(np.float32)  # tiles with a mean
+    b = (0.1 * np.random.default_rng(52).standard_normal(shape)).astype(np.float32)
+    s = (1 + 0.1 * np.random.default_rng(53).standard_normal(shape)).astype(np.float32)
+    gy = np.random.default_rng(54).standard_normal(x.shape).astype(np.float32)
+    act = {"relu": 0, "leaky_relu": 1, "silu": 2, "tanh": 3}[activation]
+    assert act == lib.gn_activation_from_name(activation.encode())
+    want = orc.step_backward(*(a.astype(np.float64) for a in (w, b, s, x, gy)), inner, 8, 1e-5, True, activation)
+    noise = orc.step_backward(w, b, s, x, gy, inner, 8, 1e-5, True, activation)
+    tw, tb, ts, tx, tgy = (dev(a) for a in (w, b, s, x, gy))
+    M, N, K = shape
+    stream = torch.cuda.current_stream().cuda_stream
+    outs = {}
+    for tag in ("plain", "tuned", "tuned again"):
+        g = [torch.full_like(t, 3.0) for t in (tw, tb, ts, tx)]
+        if tag == "plain":
+            rc = lib.gn_step_backward_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), tgy.data_ptr(),
+                                          *(t.data_ptr() for t in g), B, M, N, K, inner, 8, 1e-5, 1, act, stream)
+        else:
+            need = lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, 8, 1, 4)
+            assert need > lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, 8, 0, 4) > 0
+            ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+            rc = lib.gn_step_backward_ws_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), tgy.data_ptr(),
+                                             *(t.data_ptr() for t in g), B, M, N, K, inner, 8, 1e-5, 1, act,
+                                             ws.data_ptr(), ws.numel(), stream)
+        assert rc == 0, lib.gn_status_string(rc)
+        outs[tag] = [t.cpu().numpy() for t in g]
+    for name, a, c in zip(("gw", "gb", "gs", "gx"), outs["tuned"], outs["tuned again"]):
+        assert np.array_equal(a, c), f"{name}: the tuned path is not bit-reproducible"
+    for tag in ("plain", "tuned"):
+        for name, g, r, n in zip(("gw", "gb", "gs", "gx"), outs[tag], want, noise):
+            assert_close(g, r, n, f"{tag} {name} {activation}, normalize on")
+    assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, 4, 1, 4) == 0  # block 4 keeps the one-kernel path
