@@ -38,6 +38,9 @@ SIGNATURES = {
     "gn_gated_forward_f64": (c_int, [_P] * 4 + _geom + [c_int, c_int, c_int, _P]),
     "gn_gated_backward_f32": (c_int, [_P] * 7 + _geom + [c_int, c_int, c_int, _P]),
     "gn_gated_backward_f64": (c_int, [_P] * 7 + _geom + [c_int, c_int, c_int, _P]),
+    "gn_gated_backward_workspace_bytes": (c_size_t, [c_int] * 7),
+    "gn_gated_backward_error_flag_offset": (c_size_t, [c_int] * 5),
+    "gn_gated_backward_ws_f32": (c_int, [_P] * 7 + _geom + [c_int, c_int, c_int, _P, c_size_t, _P]),
     "gn_norm_workspace_bytes": (c_size_t, [c_int, c_longlong]),
     "gn_norm_forward_f32": (c_int, [_P] * 5 + [c_int, c_longlong, c_float, _P, c_size_t, _P]),
     "gn_norm_backward_f32": (c_int, [_P] * 6 + [c_int, c_longlong, c_float, _P, c_size_t, _P]),

@@ -415,6 +415,33 @@ GN_API int gn_step_backward_stash_f32(const float *w, const float *b, const floa
                                  static_cast<const float *>(stash), static_cast<float *>(workspace), (cudaStream_t)stream);
 }
 
+GN_API size_t gn_gated_backward_workspace_bytes(int B, int M, int N, int K, int inner, int block, int elem_size)
+{
+    if (elem_size != 4 || block != 8 || inner < 1 || B <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M % 8 || N % 8 || K % 8) return 0;
+    return align_up(sizeof(float) * gated_bwd_fast8_workspace_floats(B, M, N, K, inner), 256);
+}
+
+GN_API size_t gn_gated_backward_error_flag_offset(int B, int M, int N, int K, int inner)
+{
+    if (B <= 0 || M <= 0 || N <= 0 || K <= 0 || inner < 1) return 0;
+    return sizeof(float) * (gated_bwd_fast8_workspace_floats(B, M, N, K, inner) - 4);
+}
+
+GN_API int gn_gated_backward_ws_f32(const float *w, const float *b, const float *x, const float *gy, float *gw, float *gb,
+                                    float *gx, int B, int M, int N, int K, int inner, int block, int act, void *workspace,
+                                    size_t workspace_bytes, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    const size_t need = gn_gated_backward_workspace_bytes(B, M, N, K, inner, block, 4);
+    if (B > 0 && need > 0 && workspace && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) % 16) == 0 &&
+        w && b && x && gy && gw && gb && gx && gated_bwd_fast8_applicable(w, b, x, gy, gw, gb, gx, M, N, K, inner, block))
+        return launch_gated_bwd_fast8(w, b, x, gy, gw, gb, gx, B, M, N, K, inner, act, (float *)workspace,
+                                      (cudaStream_t)stream);
+    return api_gated_backward<float>(w, b, x, gy, gw, gb, gx, B, M, N, K, inner, block, act, stream);
+}
+
 GN_API int gn_step_backward_max_inner(int block, int elem_size) { return step_backward_max_inner(block, elem_size); }
 
 GN_API int gn_gated_forward_f32(const float *w, const float *b, const float *x, float *y, int B, int M, int N, int K,

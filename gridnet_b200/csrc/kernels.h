@@ -65,7 +65,19 @@ bool fast8_make_tile_map(CUtensorMap *map, const float *base, int B, int M, int 
 bool gated_fast8_applicable(const float *w, const float *b, const float *x, const float *y, int M, int N, int K, int block,
                             int inner);
 int launch_gated_fwd_fast8(const float *w, const float *b, const float *x, float *y, int B, int M, int N, int K, int inner,
-                           int act, cudaStream_t st);
+                           int act, cudaStream_t st, float *save_hv = nullptr, float *save_hg = nullptr,
+                           float *save_x = nullptr, int *error_flag = nullptr);
+
+// ---- step_gated_bwd_fast.cu (tuned float backward of the gated update, block 8: replay, reverse sweep, weight
+// gradients, and the cross-block kernel of step_bwd_fast.cu once per branch)
+size_t gated_bwd_fast8_workspace_floats(int B, int M, int N, int K, int inner);
+bool gated_bwd_fast8_applicable(const float *w, const float *b, const float *x, const float *gy, const float *gw,
+                                const float *gb, const float *gx, int M, int N, int K, int inner, int block);
+int launch_gated_bwd_fast8(const float *w, const float *b, const float *x, const float *gy, float *gw, float *gb, float *gx,
+                           int B, int M, int N, int K, int inner, int act, float *ws, cudaStream_t st);
+// the cross-block part of grad_x for one weight set: w + tap * tap_stride + cell (step_bwd_fast.cu)
+int launch_bwd_border8(const float *w, size_t tap_stride, const float *dsum, float *gx, int B, int M, int N, int K,
+                       cudaStream_t st);
 
 // ---- slab.cu
 int launch_slab_unpack_faces(const float *from_left, const float *from_right, float *x, int B, int M, int N, int K,

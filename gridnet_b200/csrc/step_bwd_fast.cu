@@ -685,7 +685,7 @@ constexpr int SLOTS = 3;  // ceil(1000 / 384)
 __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *__restrict__ w, const float *__restrict__ dsum,
                                                                   float *__restrict__ gx, int B, int M, int N, int K, int spc,
                                                                   const float2 *__restrict__ hterm,
-                                                                  const float *__restrict__ x)
+                                                                  const float *__restrict__ x, size_t tap_stride)
 {
     using namespace border8;
     __shared__ float tile[2][TS];
@@ -740,7 +740,7 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
         const int nz = bz * 8 + l[0] - d[0], ny = by * 8 + l[1] - d[1], nx = bx * 8 + l[2] - d[2];
         const bool ok = owned && nz >= 0 && nz < M && ny >= 0 && ny < N && nx >= 0 && nx < K;
         const int t = (d[0] + 1) * 9 + (d[1] + 1) * 3 + (d[2] + 1);
-        wf[q] = ok ? w[(size_t)t * P + ((size_t)nz * N + ny) * K + nx] : 0.0f;
+        wf[q] = ok ? w[(size_t)t * tap_stride + ((size_t)nz * N + ny) * K + nx] : 0.0f;
         toff[q] = (l[0] + 1 - d[0]) * 100 + (l[1] + 1 - d[1]) * 10 + (l[2] + 1 - d[2]);
     }
 
@@ -918,6 +918,17 @@ static void launch_reverse(const BwdParams &p, dim3 grid, int act, cudaStream_t 
     else launch_reverse_inner<SUB, 0>(p, grid, act, st);
 }
 
+int launch_bwd_border8(const float *w, size_t tap_stride, const float *dsum, float *gx, int B, int M, int N, int K,
+                       cudaStream_t st)
+{
+    const long long nb = (long long)(M / 8) * (N / 8) * (K / 8);
+    const int chunks = pick_batch_chunks_balanced(nb, B, 3, 8.0, 32);
+    const int spc = (B + chunks - 1) / chunks;
+    dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
+    bwd_border8_k<<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc, nullptr, nullptr, tap_stride);
+    return check_launch("bwd_border8");
+}
+
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
                           const float *stash, float *ws, cudaStream_t st, int normalize, float eps)
@@ -1010,7 +1021,7 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
         const int spc = (B + chunks - 1) / chunks;
         dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
         if (block == 4) bwd_halo8_k<4><<<grid, HaloGeo<4>::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
-        else bwd_border8_k<<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc, normalize ? hterm : nullptr, x);
+        else bwd_border8_k<<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc, normalize ? hterm : nullptr, x, P);
     }
     rc = check_launch("bwd_halo8");
     if (rc != GN_OK) return rc;

@@ -32,6 +32,9 @@ struct GatedFastParams {
     float *y;
     int B, M, N, K, inner, spc;
     int *error_flag;  // optional: set to 1 if a bounded wait on a bulk copy gave up
+    // Replay mode of the backward pass: every iteration's two pre-activations ([inner][B][M,N,K] each) and the
+    // activations after iterations 1 .. inner-1 ([inner-1][B][M,N,K]); y may then be nullptr.
+    float *save_hv, *save_hg, *save_x;
 };
 
 template <int ACT>
@@ -150,13 +153,19 @@ __global__ void __launch_bounds__(gated8::THREADS, 1)
                 const float gate = sigmoid_(ag[i]);
                 nv[i] = gate * old[i] + (1.0f - gate) * Act<ACT, float>::fwd(av[i]);
             }
+            if (p.save_hv) {
+                const size_t o = ((size_t)it * p.B + smp) * P + g0;
+                *reinterpret_cast<float2 *>(p.save_hv + o) = make_float2(av[0], av[1]);
+                *reinterpret_cast<float2 *>(p.save_hg + o) = make_float2(ag[0], ag[1]);
+                if (!last) *reinterpret_cast<float2 *>(p.save_x + o) = make_float2(nv[0], nv[1]);
+            }
             if (!last) {
                 float *to = tiles[set][cur ^ 1] + toff + PS + RS + 1;
                 to[0] = nv[0];
                 to[1] = nv[1];
                 __syncthreads();  // the other tile is complete; this one may be overwritten next
             } else {
-                *reinterpret_cast<float2 *>(p.y + (size_t)smp * P + g0) = make_float2(nv[0], nv[1]);
+                if (p.y) *reinterpret_cast<float2 *>(p.y + (size_t)smp * P + g0) = make_float2(nv[0], nv[1]);
             }
         }
         __syncthreads();  // next sample's tiles are complete; this sample's tiles are free
@@ -173,7 +182,7 @@ bool gated_fast8_applicable(const float *w, const float *b, const float *x, cons
 }
 
 int launch_gated_fwd_fast8(const float *w, const float *b, const float *x, float *y, int B, int M, int N, int K, int inner,
-                           int act, cudaStream_t st)
+                           int act, cudaStream_t st, float *save_hv, float *save_hg, float *save_x, int *error_flag)
 {
     CUtensorMap map;
     memset(&map, 0, sizeof(map));
@@ -182,7 +191,9 @@ int launch_gated_fwd_fast8(const float *w, const float *b, const float *x, float
     GatedFastParams p{};
     p.w = w; p.b = b; p.x = x; p.y = y;
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
-    p.error_flag = device_status_ptr();  // this entry point has no workspace: report to the library's status word
+    p.save_hv = save_hv; p.save_hg = save_hg; p.save_x = save_x;
+    // the forward entry point has no workspace: it reports to the library's status word
+    p.error_flag = error_flag ? error_flag : device_status_ptr();
     const int chunks = pick_batch_chunks_balanced(nb, B, 1, 1.5, B < 64 ? B : 64);
     p.spc = (B + chunks - 1) / chunks;
     dim3 grid((unsigned)nb, (unsigned)((B + p.spc - 1) / p.spc));

@@ -147,6 +147,18 @@ def backward_gated(weight, bias, initActivations, outGrads, weightGradOut, biasG
     B, M, N, K = initActivations.shape
     fn = getattr(lib, "gn_gated_backward_" + _suffix(weight))
     with torch.cuda.device(weight.device):
+        need = 0
+        if _suffix(weight) == "f32" and B > 0:
+            need = int(lib.gn_gated_backward_workspace_bytes(B, M, N, K, int(innerIterations), int(blockSize), 4))
+        if need:
+            # scratch for the tuned four-kernel path (torch's caching allocator, stream ordered)
+            ws = torch.empty(need, dtype=torch.uint8, device=weight.device)
+            check(lib.gn_gated_backward_ws_f32(
+                weight.data_ptr(), bias.data_ptr(), initActivations.data_ptr(), outGrads.data_ptr(),
+                weightGradOut.data_ptr(), biasGradOut.data_ptr(), activationsGradOut.data_ptr(), B, M, N, K,
+                int(innerIterations), int(blockSize), activation_id(activation), ws.data_ptr(), ws.numel(),
+                _stream(weight)))
+            return
         check(fn(weight.data_ptr(), bias.data_ptr(), initActivations.data_ptr(), outGrads.data_ptr(),
                  weightGradOut.data_ptr(), biasGradOut.data_ptr(), activationsGradOut.data_ptr(), B, M, N, K,
                  int(innerIterations), int(blockSize), activation_id(activation), _stream(weight)))

@@ -187,6 +187,20 @@ GN_API int gn_gated_backward_f64(const double *weight, const double *bias, const
                           const double *grad_y, double *grad_weight, double *grad_bias,
                           double *grad_x, int B, int M, int N, int K, int inner, int block,
                           int activation, void *stream);
+/* gn_gated_backward_f32 with a caller-supplied scratch buffer (16-byte aligned, at least
+ * gn_gated_backward_workspace_bytes(...) bytes; 0 = no tuned path for these arguments: call gn_gated_backward_f32).
+ * With it the float backward at block 8 runs as four kernels with the forward kernel's register-patch mapping
+ * (replay, reverse sweep, weight gradients, cross-block part of grad_x), without floating-point atomics, so two calls
+ * return the same bits, and with no limit on `inner`; otherwise it behaves exactly like gn_gated_backward_f32. The
+ * int at gn_gated_backward_error_flag_offset(...) inside the workspace is 1 afterwards if a bounded wait on a bulk
+ * tile copy gave up (the results are then invalid). Same reference entry point as gn_gated_backward_f32
+ * (src/gridnet_cuda.cpp:159-186 -> src/gridnet_cuda_kernels.cu:538-734). */
+GN_API size_t gn_gated_backward_workspace_bytes(int B, int M, int N, int K, int inner, int block, int elem_size);
+GN_API size_t gn_gated_backward_error_flag_offset(int B, int M, int N, int K, int inner);
+GN_API int gn_gated_backward_ws_f32(const float *weight, const float *bias, const float *x, const float *grad_y,
+                             float *grad_weight, float *grad_bias, float *grad_x, int B, int M, int N, int K,
+                             int inner, int block, int activation, void *workspace, size_t workspace_bytes,
+                             void *stream);
 
 /* ------------------------------------------------- whole-grid normalisation
  * The reference's models apply torch.nn.LayerNorm over the full [M,N,K] grid

@@ -528,3 +528,48 @@ def test_tuned_backward_with_per_block_normalisation(activation):
         for name, g, r, n in zip(("gw", "gb", "gs", "gx"), outs[tag], want, noise):
             assert_close(g, r, n, f"{tag} {name} {activation}, normalize on")
     assert lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, 4, 1, 4) == 0  # block 4 keeps the one-kernel path
+
+
+@pytest.mark.parametrize("activation,inner", [("tanh", 3), ("silu", 2), ("relu", 1), ("leaky_relu", 4)])
+def test_tuned_gated_backward(activation, inner):
+    """float32 gated backward at block 8: the four-kernel path (with workspace) against the float64 oracle and
+    the one-kernel path on a grid with interior, face, edge and corner blocks and an odd batch, through the C ABI;
+    bit-identical when repeated (src/gridnet_cuda_kernels.cu:538-734, gridnet/backend_torch.py:145-267)."""
+    from gridnet_b200._lib import lib
+
+    shape, B = (24, 16, 32), 5
+    w, b, x = rng_inputs(71, B, shape, gated=True, unit_scale=True)
+    b = (0.3 * b).astype(np.float32)
+    gy = np.random.default_rng(72).standard_normal(x.shape).astype(np.float32)
+    act = lib.gn_activation_from_name(activation.encode())
+    want = orc.gated_backward(*(a.astype(np.float64) for a in (w, b, x, gy)), inner, 8, activation)
+    noise = orc.gated_backward(w, b, x, gy, inner, 8, activation)
+    tw, tb, tx, tgy = (dev(a) for a in (w, b, x, gy))
+    M, N, K = shape
+    stream = torch.cuda.current_stream().cuda_stream
+    outs = {}
+    for tag in ("plain", "tuned", "tuned again"):
+        g = [torch.full_like(t, 3.0) for t in (tw, tb, tx)]
+        if tag == "plain":
+            rc = lib.gn_gated_backward_f32(tw.data_ptr(), tb.data_ptr(), tx.data_ptr(), tgy.data_ptr(),
+                                           *(t.data_ptr() for t in g), B, M, N, K, inner, 8, act, stream)
+        else:
+            need = lib.gn_gated_backward_workspace_bytes(B, M, N, K, inner, 8, 4)
+            assert need > 0
+            ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+            rc = lib.gn_gated_backward_ws_f32(tw.data_ptr(), tb.data_ptr(), tx.data_ptr(), tgy.data_ptr(),
+                                              *(t.data_ptr() for t in g), B, M, N, K, inner, 8, act, ws.data_ptr(),
+                                              ws.numel(), stream)
+            off = lib.gn_gated_backward_error_flag_offset(B, M, N, K, inner)
+            assert int(ws.view(torch.int32)[off // 4].item()) == 0
+        assert rc == 0, lib.gn_status_string(rc)
+        outs[tag] = [t.cpu().numpy() for t in g]
+    for name, a, c in zip(("gw", "gb", "gx"), outs["tuned"], outs["tuned again"]):
+        assert np.array_equal(a, c), f"{name}: the tuned path is not bit-reproducible"
+    for tag in ("plain", "tuned"):
+        for name, g, r, n in zip(("gw", "gb", "gx"), outs[tag], want, noise):
+            assert_close(g, r, n, f"{tag} gated {name} {activation} inner={inner}")
+    # no tuned path: block 4, double precision, sides that are not multiples of 8; too small a workspace falls back
+    assert lib.gn_gated_backward_workspace_bytes(B, M, N, K, inner, 4, 4) == 0
+    assert lib.gn_gated_backward_workspace_bytes(B, M, N, K, inner, 8, 8) == 0
+    assert lib.gn_gated_backward_workspace_bytes(B, 12, N, K, inner, 8, 4) == 0
