@@ -602,21 +602,20 @@ def bench_slab(ctx: Ctx):
     ctx.release()
     G, B, inner, outer = 256, 32, 2, 32
     lay = SlabLayout(G, world, rank)
-    g = torch.Generator(device=device).manual_seed(100 + rank)
-    kp = lay.k_pad
-    w = torch.randn(27, G, G, kp, generator=g, device=device) / 27 ** 0.5
-    b = torch.zeros(G, G, kp, device=device)
-    s = torch.ones(G, G, kp, device=device)
-    gamma = torch.ones(G, G, kp, device=device)
-    beta = torch.zeros(G, G, kp, device=device)
-    for t in (gamma, beta):  # ghost columns beyond the ends of the grid stay zero after normalise-on-load
-        if lay.left is None:
-            t[..., :GHOST] = 0
-        if lay.right is None:
-            t[..., GHOST + lay.k_loc:] = 0
-    x = torch.zeros(B, G, G, kp, device=device)
-    if rank == 0:
-        x[..., GHOST] = torch.randn(B, G, G, generator=g, device=device)
+    # The same full-grid problem on every rank and for every world size (same seed, same generator), each rank
+    # keeping its slab of it: the result can then be compared with the single-GPU loop on the whole grid, and
+    # the output checksum is the same number whatever N is.
+    g = torch.Generator(device=device).manual_seed(100)
+    w_full = torch.randn(27, G, G, G, generator=g, device=device) / 27 ** 0.5
+    x_full = torch.zeros(B, G, G, G, device=device)
+    x_full[..., 0] = torch.randn(B, G, G, generator=g, device=device)
+    b_full = torch.zeros(G, G, G, device=device)
+    s_full = torch.ones(G, G, G, device=device)
+    gamma_full = torch.ones(G, G, G, device=device)
+    beta_full = torch.zeros(G, G, G, device=device)
+    # shard(): the rank's columns plus a ghost block either side whose adjacent column holds the neighbour's
+    # boundary values (zeros beyond the ends of the grid, which normalise-on-load keeps zero)
+    w, b, s, gamma, beta, x = (lay.shard(t) for t in (w_full, b_full, s_full, gamma_full, beta_full, x_full))
     backend = CudaSlabBackend(lay, w, b, s, gamma, beta, inner, ACT)
 
     # faces: stored by the step kernel straight into the neighbours' memory (default), or packed and sent
@@ -644,8 +643,21 @@ def bench_slab(ctx: Ctx):
     torch.cuda.synchronize()
     ms = ctx.max_over_ranks(e0.elapsed_time(e1))
     finite = bool(torch.isfinite(out).all().item())
-    chk = out.double().sum().reshape(1)  # the same bits whichever way the faces travel: compare between runs
+    chk = out.double().sum().reshape(1)  # the same bits whichever way the faces travel and whatever N is
     dist.all_reduce(chk)
+    # parity at the configuration's own size, on the real ranks: every rank runs the single-GPU fused loop on the
+    # whole grid and compares its slab of the result
+    import gridnet_b200 as gb
+
+    ref = gb.outer_forward(w_full, b_full, s_full, gamma_full, beta_full, x_full, inner, outer, 8, ACT)
+    mine = ref[..., lay.k0:lay.k0 + lay.k_loc]
+    err = (mine - out).abs()
+    full_ok = torch.tensor([float(bool((err <= 1e-5 + 1e-4 * mine.abs()).all().item())),
+                            float(bool(torch.equal(mine, out)))], device=device)
+    worst = err.max().reshape(1)
+    dist.all_reduce(full_ok, op=dist.ReduceOp.MIN)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    del ref, mine, err
     nu = float(B) * G ** 3 * inner * outer
     rec = {
         "metric": METRIC, "value": nu * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
@@ -660,11 +672,17 @@ def bench_slab(ctx: Ctx):
                    "samples_per_sec": B * steps / (ms * 1e-3), "finite": finite, "output_checksum": float(chk.item())},
         "gpu_launches": (outer * 3 + 1) * steps if direct else (outer * 2 + 1) * steps,
     }
+    rec["full_size_parity"] = {"ok": bool(full_ok[0].item()), "bit_identical": bool(full_ok[1].item()),
+                               "max_abs_err": float(worst.item()),
+                               "against": "the single-GPU fused loop (gn_outer_forward_f32) on the whole 256^3 grid, run on "
+                                          "every rank; tolerance 1e-5 + 1e-4 |ref|"}
     if boxes is not None:
         rec["mailbox_wait_failed"] = boxes.failed()
     if parity is not None:
         rec.update(parity)
-    del backend, peers, boxes, w, x, out
+    if not rec["full_size_parity"]["ok"]:
+        rec["slab_parity_ok"] = False  # fails the run like the small-grid parity check
+    del backend, peers, boxes, w, x, out, w_full, x_full
     ctx.release()
     return rec
 
