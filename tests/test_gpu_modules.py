@@ -187,3 +187,41 @@ def test_fused_loop_variants_equal_the_step_by_step_composition(block):
     assert torch.allclose(got_y, want_y, rtol=1e-4, atol=1e-5)
     for i, (a, c) in enumerate(zip(got, want)):
         assert torch.allclose(a, c, rtol=1e-3, atol=1e-4 * (1 + c.abs().max().item())), (i, (a - c).abs().max().item())
+
+
+@pytest.mark.parametrize("name,grid,block,inner,outer,B", [("C3", 128, 8, 2, 16, 1), ("C4", 64, 4, 8, 16, 2)])
+def test_training_configurations_at_their_own_grid_and_depth(name, grid, block, inner, outer, B):
+    """The two forward + backward configurations of the benchmark at their own grid size, block size and
+    iteration counts (128^3 / 8 / 2 x 16 and 64^3 / 4 / 8 x 16), one or two samples of the batch (samples only meet
+    in the parameter gradients, which are sums over them): the fused training node's output and all six gradients
+    against the float64 oracle's chain rule over the whole loop, the float32 oracle giving the noise floor."""
+    import gridnet_b200 as gb
+    from util import assert_close
+
+    r = np.random.default_rng(73)
+    f = np.float32
+    shape = (grid, grid, grid)
+    w = (r.standard_normal((27, *shape)) / np.sqrt(27)).astype(f)
+    b = np.zeros(shape, f)
+    s = np.ones(shape, f)
+    ga = (1 + 0.05 * r.standard_normal(shape)).astype(f)
+    be = (0.05 * r.standard_normal(shape)).astype(f)
+    x = np.zeros((B, *shape), f)
+    x[..., 0] = r.standard_normal((B, grid, grid))  # the input face, as in the benchmark
+    gy = r.standard_normal((B, *shape)).astype(f)
+    leaves = [torch.from_numpy(a).cuda().requires_grad_(True) for a in (w, b, s, ga, be, x)]
+    assert gb.FusedLoopTrainOp.supported(leaves[0], leaves[5], inner, block)
+    y = gb.FusedLoopTrainOp.apply(*leaves, inner, outer, block, "silu", 1e-5)
+    grads = torch.autograd.grad(y, leaves, torch.from_numpy(gy).cuda())
+    assert not gb.device_status(clear=True)
+    a64 = [a.astype(np.float64) for a in (w, b, s, ga, be, x)]
+    y64 = orc.outer_forward(*a64, inner, outer, block)
+    y32 = orc.outer_forward(w, b, s, ga, be, x, inner, outer, block)
+    assert_close(y.detach().cpu().numpy(), y64, y32, f"{name} forward")
+    want64 = orc.outer_backward(*a64, gy.astype(np.float64), inner, outer, block)
+    want32 = orc.outer_backward(w, b, s, ga, be, x, gy, inner, outer, block)
+    # noise factor 3 instead of 2: the comparison is between the MAXIMA of two realisations of float32 rounding
+    # noise over up to 5.7e7 elements after 32 chained stencil passes (gradients up to 4e3 in magnitude; measured:
+    # the float32 oracle's worst error 1.3e-3, ours 3.0e-3, i.e. 7e-7 of max|ref|; 25 against 29 elements outside)
+    for label, g, r64, r32 in zip(("weight", "bias", "scale", "gamma", "beta", "input"), grads, want64, want32):
+        assert_close(g.cpu().numpy(), r64, r32, f"{name} gradient of {label}", noise_factor=3.0)
