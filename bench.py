@@ -509,8 +509,8 @@ def slab_parity_on_ranks(ctx: Ctx) -> dict:
     import torch
 
     import gridnet_b200 as gb
-    from gridnet_b200.slab import (PeerFaceBuffers, PeerStatsMailboxes, SlabLayout, make_cuda_runner, run_direct,
-                                   run_distributed)
+    from gridnet_b200.slab import (PeerFaceBuffers, PeerSlabBuffers, PeerStatsMailboxes, SlabLayout, make_cuda_runner,
+                                   run_direct, run_distributed, run_in_place)
 
     dist = ctx.need_group()
     world, rank, device = ctx.world, ctx.rank, ctx.device
@@ -527,26 +527,35 @@ def slab_parity_on_ranks(ctx: Ctx) -> dict:
     x[..., 0] = torch.randn(B, M, N, generator=g)
     lay = SlabLayout(K, world, rank)
     peers = PeerFaceBuffers(lay, B, M, N, device)
+    slabs = PeerSlabBuffers(lay, B, M, N, device)
     boxes = PeerStatsMailboxes(lay, B, device)
     outs = {}
-    for name in ("direct", "nccl"):
-        runner = make_cuda_runner(lay, w, b, s, gamma, beta, x, inner, ACT, device=device)
-        local = run_direct(runner, outer, peers, mailboxes=boxes) if name == "direct" else run_distributed(runner, outer)
+    for name in ("in-place", "direct", "nccl"):
+        runner = make_cuda_runner(lay, w, b, s, gamma, beta, x, inner, ACT, device=device,
+                                  work_buffers=slabs.work_buffers() if name == "in-place" else None)
+        if name == "in-place":
+            local = run_in_place(runner, outer, slabs, boxes)
+        elif name == "direct":
+            local = run_direct(runner, outer, peers, mailboxes=boxes)
+        else:
+            local = run_distributed(runner, outer)
         parts = [torch.empty_like(local) for _ in range(world)] if rank == 0 else None
         dist.gather(local.contiguous(), parts, dst=0)
         if rank == 0:
             outs[name] = torch.cat(parts, dim=-1)
-    verdict = torch.zeros(3, device=device)
+    verdict = torch.zeros(4, device=device)
     if rank == 0:
         ref = gb.outer_forward(*(t.to(device) for t in (w, b, s, gamma, beta, x)), inner, outer, 8, ACT)
         tol = 1e-5 + 1e-4 * ref.abs()
         e_direct = (outs["direct"] - ref).abs()
         e_nccl = (outs["nccl"] - ref).abs()
-        ok = bool((e_direct <= tol).all().item()) and bool((e_nccl <= tol).all().item())
-        verdict = torch.tensor([1.0 if ok else 0.0, float(e_direct.max().item()), float(e_nccl.max().item())], device=device)
+        e_inplace = (outs["in-place"] - ref).abs()
+        ok = all(bool((e <= tol).all().item()) for e in (e_direct, e_nccl, e_inplace))
+        verdict = torch.tensor([1.0 if ok else 0.0, float(e_direct.max().item()), float(e_nccl.max().item()),
+                                float(e_inplace.max().item())], device=device)
     dist.broadcast(verdict, src=0)
     mailbox_wait_failed = boxes.failed()
-    del peers, boxes
+    del peers, boxes, slabs
 
     # training on the real ranks: forward + backward with the reverse face exchange and both all-reduces over NCCL,
     # gathered and compared with rank 0's single-GPU autograd through the package's ops
@@ -584,7 +593,9 @@ def slab_parity_on_ranks(ctx: Ctx) -> dict:
                                   "implementations with different summation orders; the oracle comparison is in tests/test_slab.py)",
             "grid": [M, N, K], "batch": B,
             "max_abs_err_direct": float(verdict[1].item()), "max_abs_err_nccl": float(verdict[2].item()),
-            "same_bits_both_paths": None if rank != 0 else bool(torch.equal(outs["direct"], outs["nccl"])),
+            "max_abs_err_in_place": float(verdict[3].item()),
+            "same_bits_all_paths": None if rank != 0 else bool(torch.equal(outs["direct"], outs["nccl"])
+                                                               and torch.equal(outs["in-place"], outs["nccl"])),
             "tolerance": "1e-5 + 1e-4 |ref| against outer_forward on the whole grid on rank 0"}
 
 
@@ -593,8 +604,8 @@ def bench_slab(ctx: Ctx):
     slab-sharded along K over all ranks (strong scaling: the total work is fixed)."""
     import torch
 
-    from gridnet_b200.slab import (GHOST, CudaSlabBackend, PeerFaceBuffers, PeerStatsMailboxes, SlabLayout, SlabRunner,
-                                   run_direct, run_distributed)
+    from gridnet_b200.slab import (GHOST, CudaSlabBackend, PeerFaceBuffers, PeerSlabBuffers, PeerStatsMailboxes, SlabLayout,
+                                   SlabRunner, run_direct, run_distributed, run_in_place)
 
     args, rank, world, device = ctx.args, ctx.rank, ctx.world, ctx.device
     dist = ctx.need_group()
@@ -618,13 +629,18 @@ def bench_slab(ctx: Ctx):
     w, b, s, gamma, beta, x = (lay.shard(t) for t in (w_full, b_full, s_full, gamma_full, beta_full, x_full))
     backend = CudaSlabBackend(lay, w, b, s, gamma, beta, inner, ACT)
 
-    # faces: stored by the step kernel straight into the neighbours' memory (default), or packed and sent
-    # with NCCL send/recv (--slab-exchange nccl)
-    direct = args.slab_exchange == "direct" and world > 1
+    # faces: stored by the step kernel straight into the neighbours' ghost columns (default), or into packed
+    # buffers in the neighbours' memory and unpacked there (--slab-exchange direct), or packed and sent with NCCL
+    # send/recv (--slab-exchange nccl)
+    mode = args.slab_exchange if world > 1 else "nccl"
+    direct = mode == "direct"
     peers = PeerFaceBuffers(lay, B, G, G, device) if direct else None
-    boxes = PeerStatsMailboxes(lay, B, device) if direct else None
+    slabs = PeerSlabBuffers(lay, B, G, G, device) if mode == "in-place" else None
+    boxes = PeerStatsMailboxes(lay, B, device) if mode != "nccl" else None
 
     def one_pass():
+        if mode == "in-place":
+            return run_in_place(SlabRunner(lay, backend, x, G * G * G, work_buffers=slabs.work_buffers()), outer, slabs, boxes)
         runner = SlabRunner(lay, backend, x, G * G * G)
         return run_direct(runner, outer, peers, mailboxes=boxes) if direct else run_distributed(runner, outer)
 
@@ -665,12 +681,15 @@ def bench_slab(ctx: Ctx):
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "C5: 256^3 grid, block 8, 2 inner x 32 outer, batch 32, fp32, forward + whole-grid "
                                "LayerNorm, slab-sharded along K", "parallelism": f"slab x{world}",
-                   "exchange": ("per outer step: the step kernel stores 2 faces [32,256,256] fp32 into the neighbours' memory "
+                   "exchange": ("per outer step: the step kernel stores 2 faces [32,256,256] fp32 straight into the "
+                                "neighbours' ghost columns over NVLink (nothing is unpacked); the [32,2] f64 sums go to every "
+                                "rank's mailbox by peer stores and flags (no collective call)" if mode == "in-place" else
+                                "per outer step: the step kernel stores 2 faces [32,256,256] fp32 into the neighbours' memory "
                                 "over NVLink; the [32,2] f64 sums go to every rank's mailbox by peer stores and flags "
                                 "(no collective call)" if direct else
                                 "per outer step: 2 faces [32,256,256] fp32 send/recv per neighbour + all-reduce of [32,2] f64"),
                    "samples_per_sec": B * steps / (ms * 1e-3), "finite": finite, "output_checksum": float(chk.item())},
-        "gpu_launches": (outer * 3 + 1) * steps if direct else (outer * 2 + 1) * steps,
+        "gpu_launches": (outer * 3 + 1) * steps if mode != "nccl" else (outer * 2 + 1) * steps,
     }
     rec["full_size_parity"] = {"ok": bool(full_ok[0].item()), "bit_identical": bool(full_ok[1].item()),
                                "max_abs_err": float(worst.item()),
@@ -682,7 +701,7 @@ def bench_slab(ctx: Ctx):
         rec.update(parity)
     if not rec["full_size_parity"]["ok"]:
         rec["slab_parity_ok"] = False  # fails the run like the small-grid parity check
-    del backend, peers, boxes, w, x, out, w_full, x_full
+    del backend, peers, slabs, boxes, w, x, out, w_full, x_full
     ctx.release()
     return rec
 
@@ -936,8 +955,10 @@ def main():
                          "line (c5_slab at every N; c1, c3, c4 at N = 1); c2: the headline alone; c5-slab: the 256^3 grid "
                          "sharded along K over all ranks; c3 / c4: the forward + backward configurations (128^3 block 8, "
                          "64^3 block 4); c1: the small launch-bound configuration, also replayed from a CUDA graph")
-    ap.add_argument("--slab-exchange", choices=["direct", "nccl"], default="direct",
-                    help="c5-slab only: how the boundary faces travel (direct = stored by the step kernel into peer memory)")
+    ap.add_argument("--slab-exchange", choices=["in-place", "direct", "nccl"], default="in-place",
+                    help="c5-slab only: how the boundary faces travel (in-place = stored by the step kernel into the "
+                         "neighbours' ghost columns; direct = into packed buffers in the neighbours' memory, unpacked there; "
+                         "nccl = packed and sent with send/recv)")
     ap.add_argument("--stash", action="store_true",
                     help="c3 / c4 only: keep the forward pass's intermediate results instead of recomputing them in the "
                          "backward pass ((2 inner - 1) extra activation tensors per outer step)")

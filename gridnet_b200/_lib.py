@@ -65,6 +65,8 @@ SIGNATURES = {
     "gn_step_forward_train_f32": (c_int, [_P] * 9 + _geom + [c_int, c_int, c_int, _P, c_size_t, _P]),
     "gn_step_forward_slab_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P]),
     "gn_step_forward_slab_faces_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P, _P, _P]),
+    "gn_step_forward_slab_faces_strided_f32": (c_int, [_P] * 9 + [c_int] + _geom + [c_int, c_int, c_int, c_int, _P, _P,
+                                                                                   c_longlong, _P]),
     "gn_slab_unpack_faces_f32": (c_int, [_P] * 3 + _geom + [c_int, c_int, _P]),
     "gn_slab_mailbox_bytes": (c_size_t, [c_int, c_int]),
     "gn_slab_publish_sums_f32": (c_int, [_P, c_int, c_int, c_int, c_int, _P, c_int, c_ulonglong, _P]),

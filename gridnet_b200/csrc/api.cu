@@ -668,7 +668,7 @@ static int slab_forward(const float *w, const float *b, const float *s, const fl
                              const float *gamma, const float *beta, const float *in_mean_rstd,
                              double *out_partials, int partials_per_sample, int B, int M, int N, int K,
                              int k_block_first, int k_block_count, int inner, int act, float *face_to_left,
-                             float *face_to_right, void *stream)
+                             float *face_to_right, void *stream, long long face_stride = 1)
 {
     const int rc = check_geometry(B, M, N, K, inner, 8, act);
     if (rc != GN_OK) return rc;
@@ -688,7 +688,11 @@ static int slab_forward(const float *w, const float *b, const float *s, const fl
     p.B = B; p.M = M; p.N = N; p.K = K; p.inner = inner;
     p.kb0 = k_block_first; p.kbn = k_block_count;
     p.face_left = face_to_left; p.face_right = face_to_right;
-    if ((reinterpret_cast<uintptr_t>(face_to_left) | reinterpret_cast<uintptr_t>(face_to_right)) & 7) return GN_ERR_UNSUPPORTED;
+    p.face_stride = face_stride;
+    if (face_stride < 0) return GN_ERR_BAD_SHAPE;
+    // packed faces are stored two floats at a time; strided ones float by float
+    if ((reinterpret_cast<uintptr_t>(face_to_left) | reinterpret_cast<uintptr_t>(face_to_right)) & (face_stride <= 1 ? 7 : 3))
+        return GN_ERR_UNSUPPORTED;
     if (!fast8_applicable(p, 8, 0)) return GN_ERR_UNSUPPORTED;
     if ((in_mean_rstd && reinterpret_cast<uintptr_t>(in_mean_rstd) % 8) ||
         (out_partials && reinterpret_cast<uintptr_t>(out_partials) % 16))
@@ -713,6 +717,17 @@ GN_API int gn_step_forward_slab_faces_f32(const float *w, const float *b, const 
 {
     return slab_forward(w, b, s, x, y, gamma, beta, in_mean_rstd, out_partials, partials_per_sample, B, M, N, K,
                         k_block_first, k_block_count, inner, act, face_to_left, face_to_right, stream);
+}
+
+GN_API int gn_step_forward_slab_faces_strided_f32(const float *w, const float *b, const float *s, const float *x, float *y,
+                                                  const float *gamma, const float *beta, const float *in_mean_rstd,
+                                                  double *out_partials, int partials_per_sample, int B, int M, int N,
+                                                  int K, int k_block_first, int k_block_count, int inner, int act,
+                                                  float *face_to_left, float *face_to_right, long long face_stride,
+                                                  void *stream)
+{
+    return slab_forward(w, b, s, x, y, gamma, beta, in_mean_rstd, out_partials, partials_per_sample, B, M, N, K,
+                        k_block_first, k_block_count, inner, act, face_to_left, face_to_right, stream, face_stride);
 }
 
 GN_API int gn_slab_unpack_faces_f32(const float *from_left, const float *from_right, float *x, int B, int M, int N, int K,

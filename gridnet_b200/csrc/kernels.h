@@ -46,6 +46,10 @@ struct FastFwdParams {
     // first / last column, packed as [B][M][N], to these addresses (normally a buffer in the neighbouring
     // GPU's memory, written over NVLink); nullptr = no neighbour on that side.
     float *face_left, *face_right;
+    // Distance, in floats, between consecutive entries of those face arrays: 0 or 1 = packed; K of the neighbour's
+    // padded slab = the entries are that slab's ghost column itself (the face lands where the neighbour's next step
+    // reads it, nothing is unpacked).
+    long long face_stride;
     // Per-block normalisation (the reference's normalize=True): block 8 only, and none of the fusions, the
     // replay mode or the slab mode above. norm_eps is added to the tile's standard deviation.
     int normalize;

@@ -428,12 +428,24 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                         *reinterpret_cast<float2 *>(ys + (size_t)j * K) = make_float2(nv[j][0], nv[j][1]);
                 }
                 // slab mode: the boundary columns go straight to the neighbours' packed face buffers
-                if (p.face_left && bx == p.kb0 && xp == 0)
-                    *reinterpret_cast<float2 *>(p.face_left + ((size_t)smp * p.M + bz * 8 + z) * p.N + by * 8 + 2 * yp) =
-                        make_float2(nv[0][0], nv[1][0]);
-                if (p.face_right && bx == p.kb0 + p.kbn - 1 && xp == 3)
-                    *reinterpret_cast<float2 *>(p.face_right + ((size_t)smp * p.M + bz * 8 + z) * p.N + by * 8 + 2 * yp) =
-                        make_float2(nv[0][1], nv[1][1]);
+                if (p.face_left && bx == p.kb0 && xp == 0) {
+                    const size_t fi = ((size_t)smp * p.M + bz * 8 + z) * p.N + by * 8 + 2 * yp;
+                    if (p.face_stride <= 1) {
+                        *reinterpret_cast<float2 *>(p.face_left + fi) = make_float2(nv[0][0], nv[1][0]);
+                    } else {
+                        p.face_left[fi * p.face_stride] = nv[0][0];
+                        p.face_left[(fi + 1) * p.face_stride] = nv[1][0];
+                    }
+                }
+                if (p.face_right && bx == p.kb0 + p.kbn - 1 && xp == 3) {
+                    const size_t fi = ((size_t)smp * p.M + bz * 8 + z) * p.N + by * 8 + 2 * yp;
+                    if (p.face_stride <= 1) {
+                        *reinterpret_cast<float2 *>(p.face_right + fi) = make_float2(nv[0][1], nv[1][1]);
+                    } else {
+                        p.face_right[fi * p.face_stride] = nv[0][1];
+                        p.face_right[(fi + 1) * p.face_stride] = nv[1][1];
+                    }
+                }
                 if (STATS_OUT) {
                     double sm = 0.0, sq = 0.0;
 #pragma unroll

@@ -145,18 +145,20 @@ class CudaSlabBackend:
         self._launch(x, y, in_stats, 1, self.layout.k_loc // 8, 0)
         return self.sums()
 
-    def step_with_faces(self, x, y, in_stats, face_to_left: int, face_to_right: int, reduce: bool = True):
-        """:meth:`step` whose boundary K-blocks also store their faces, packed ``[B, M, N]``, to the two
-        device addresses (0 = no neighbour on that side; normally peer memory)."""
+    def step_with_faces(self, x, y, in_stats, face_to_left: int, face_to_right: int, reduce: bool = True,
+                        face_stride: int = 1):
+        """:meth:`step` whose boundary K-blocks also store their faces to the two device addresses (0 = no
+        neighbour on that side; normally peer memory): packed ``[B, M, N]``, or with ``face_stride`` = the
+        neighbour's padded K straight into the ghost column of the buffer it reads next."""
         B = x.shape[0]
         if self._partials is None or self._partials.shape[0] != B:
             self._partials = torch.empty(B, self.nparts, 2, dtype=torch.float64, device=x.device)
-        self.check(self.lib.gn_step_forward_slab_faces_f32(
+        self.check(self.lib.gn_step_forward_slab_faces_strided_f32(
             self.w.data_ptr(), self.b.data_ptr(), self.s.data_ptr(), x.data_ptr(), y.data_ptr(),
             self.gamma.data_ptr(), self.beta.data_ptr(), None if in_stats is None else in_stats.data_ptr(),
             self._partials.data_ptr(), self.nparts, B, self.M, self.N, self.layout.k_pad,
             1, self.layout.k_loc // 8, self.inner, self.act, face_to_left or None, face_to_right or None,
-            self._stream()))
+            int(face_stride), self._stream()))
         return self.sums() if reduce else None
 
     def unpack_faces(self, from_left, from_right, x):
@@ -278,10 +280,12 @@ class SlabRunner:
     """State machine of one rank; the communication between its calls is done by a driver
     (:func:`run_distributed` over torch.distributed, or an in-process emulation in tests)."""
 
-    def __init__(self, layout: SlabLayout, backend, x_padded: torch.Tensor, grid_size: int):
+    def __init__(self, layout: SlabLayout, backend, x_padded: torch.Tensor, grid_size: int, work_buffers=None):
         self.layout, self.backend = layout, backend
         self.grid_size = int(grid_size)  # M * N * K of the WHOLE grid
-        self.bufs = [x_padded, torch.zeros_like(x_padded), torch.zeros_like(x_padded)]
+        # the two buffers the steps alternate between: the caller's (e.g. peer-mapped, ghost blocks zero), or fresh
+        b1, b2 = work_buffers if work_buffers is not None else (torch.zeros_like(x_padded), torch.zeros_like(x_padded))
+        self.bufs = [x_padded, b1, b2]
         self.cur = 0          # index of the buffer holding the current (raw) activations
         self.stats = None     # (mean, rstd) of the current buffer when it is a raw step output
 
@@ -302,11 +306,15 @@ class SlabRunner:
     def unpack(self, from_left, from_right):
         self.backend.unpack_faces(from_left, from_right, self.bufs[self.cur])
 
-    def compute_direct_no_sums(self, face_to_left: int, face_to_right: int):
+    def next_index(self) -> int:
+        """Index (1 or 2) of the buffer the next step writes."""
+        return 1 if self.cur != 1 else 2
+
+    def compute_direct_no_sums(self, face_to_left: int, face_to_right: int, face_stride: int = 1):
         """:meth:`compute_direct` that leaves the partials in the backend (for :class:`PeerStatsMailboxes`)."""
-        nxt = 1 if self.cur != 1 else 2
+        nxt = self.next_index()
         self.backend.step_with_faces(self.bufs[self.cur], self.bufs[nxt], self.stats, face_to_left, face_to_right,
-                                     reduce=False)
+                                     reduce=False, face_stride=face_stride)
         self.cur = nxt
 
     def can_split(self) -> bool:
@@ -453,6 +461,48 @@ class PeerFaceBuffers:
                 self.buf[parity, 1] if lay.right is not None else None)
 
 
+class PeerSlabBuffers:
+    """The two work buffers of a rank's :class:`SlabRunner` in torch's symmetric memory, so that the neighbours'
+    step kernels can store their boundary faces straight into the ghost columns the rank reads in its next step
+    (plain peer stores, one float per entry; NVLink multicast switched off). Nothing is unpacked afterwards.
+    ``work_buffers()`` goes to the runner; ``targets(nxt)`` are the two addresses for a step that writes buffer
+    ``nxt`` (1 or 2), ``stride`` the distance between face entries."""
+
+    def __init__(self, layout: SlabLayout, B: int, M: int, N: int, device, group=None):
+        import os
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.layout = layout
+        group = group if group is not None else dist.group.WORLD
+        self.buf = symm.empty(2, B, M, N, layout.k_pad, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, group)
+        self.stride = layout.k_pad
+        buf_bytes = B * M * N * layout.k_pad * 4
+        ptrs = self.handle.buffer_ptrs
+
+        def addr(rank, nxt, col):
+            return int(ptrs[rank]) + (nxt - 1) * buf_bytes + col * 4
+
+        # my first column is the left neighbour's right ghost column, my last one the right neighbour's left one
+        self._targets = {
+            nxt: (addr(layout.left, nxt, GHOST + layout.k_loc) if layout.left is not None else 0,
+                  addr(layout.right, nxt, GHOST - 1) if layout.right is not None else 0)
+            for nxt in (1, 2)
+        }
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def work_buffers(self):
+        return self.buf[0], self.buf[1]
+
+    def targets(self, nxt: int):
+        return self._targets[nxt]
+
+
 class PeerStatsMailboxes:
     """One mailbox per rank for the per-sample statistics of a step, allocated in torch's symmetric memory so that
     every rank can store into every other rank's (plain peer stores; NVLink multicast switched off). With them a
@@ -483,6 +533,24 @@ class PeerStatsMailboxes:
     def failed(self) -> bool:
         """True if a wait for the other ranks' sums has run out since the mailboxes were made. Synchronises."""
         return bool(self.error_flag.item())
+
+
+def run_in_place(runner: SlabRunner, outer: int, slabs: "PeerSlabBuffers", mailboxes: "PeerStatsMailboxes") -> torch.Tensor:
+    """Drive one rank for ``outer`` steps with the faces stored by the step kernel straight into the neighbours'
+    ghost columns (:class:`PeerSlabBuffers`; the runner must have been built on ``slabs.work_buffers()``) and the
+    sums exchanged through :class:`PeerStatsMailboxes`: per step the step kernel, the publish kernel and a kernel
+    that waits for the sums and finishes the statistics - no unpacking pass, no collective call. A neighbour
+    writes a ghost column of the buffer this rank reads NEXT while this rank still writes that buffer's real
+    columns; it cannot write again before this rank has published its next sums, i.e. finished reading."""
+    be, lay = runner.backend, runner.layout
+    for k in range(outer):
+        mailboxes.step += 1
+        step = mailboxes.step
+        runner.compute_direct_no_sums(*slabs.targets(runner.next_index()), face_stride=slabs.stride)
+        be.publish_sums(mailboxes.ptrs, lay.rank, lay.world, step)
+        runner.stats = be.finalize_unpack(mailboxes.buf, lay.world, step, runner.grid_size, None, None,
+                                          runner.bufs[runner.cur], mailboxes.error_flag)
+    return runner.result()
 
 
 def run_direct(runner: SlabRunner, outer: int, peers: PeerFaceBuffers, group=None,
@@ -539,6 +607,33 @@ def run_emulated_direct(runners, outer: int):
     return [r.result() for r in runners]
 
 
+def run_emulated_in_place(runners, outer: int):
+    """:func:`run_in_place` with all ranks in one process on one GPU: the neighbours' work buffers are ordinary
+    tensors of the other runners; every rank's step and publish kernels are launched before any rank's finalize
+    kernel, so the waits find their flags already set."""
+    from ._lib import lib
+
+    world = len(runners)
+    first = runners[0].bufs[0]
+    B, dev = first.shape[0], first.device
+    nbytes = int(lib.gn_slab_mailbox_bytes(world, B))
+    boxes = [torch.zeros((nbytes + 7) // 8, dtype=torch.int64, device=dev) for _ in range(world)]
+    ptrs = [b.data_ptr() for b in boxes]
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    for k in range(outer):
+        step = k + 1
+        for i, r in enumerate(runners):
+            nxt, lay = r.next_index(), r.layout
+            to_left = runners[i - 1].bufs[nxt][0, 0, 0, GHOST + lay.k_loc:].data_ptr() if i > 0 else 0
+            to_right = runners[i + 1].bufs[nxt][0, 0, 0, GHOST - 1:].data_ptr() if i + 1 < world else 0
+            r.compute_direct_no_sums(to_left, to_right, face_stride=lay.k_pad)
+            r.backend.publish_sums(ptrs, i, world, step)
+        for i, r in enumerate(runners):
+            r.stats = r.backend.finalize_unpack(boxes[i], world, step, r.grid_size, None, None, r.bufs[r.cur], flag)
+    assert not bool(flag.item()), "a wait for the ranks' sums ran out"
+    return [r.result() for r in runners]
+
+
 def run_emulated_mailboxes(runners, outer: int):
     """:func:`run_direct` with mailboxes, all ranks in one process on one GPU: every rank's step and publish
     kernels are launched before any rank's finalize kernel, so the waits find their flags already set."""
@@ -592,14 +687,14 @@ def run_emulated(runners, outer: int, split: bool = False):
 
 
 def make_cuda_runner(layout: SlabLayout, weight, bias, scale, gamma, beta, x, inner: int, activation: str = "silu",
-                     ln_eps: float = 1e-5, device=None) -> SlabRunner:
+                     ln_eps: float = 1e-5, device=None, work_buffers=None) -> SlabRunner:
     """Shard FULL tensors (any device) for this rank and build its runner on ``device``."""
     device = device or torch.device("cuda", torch.cuda.current_device())
     sh = lambda t, ghost: layout.shard(t, ghost).to(device)
     backend = CudaSlabBackend(layout, sh(weight, False), sh(bias, False), sh(scale, False), sh(gamma, True),
                               sh(beta, True), inner, activation, ln_eps)
     M, N, K = bias.shape
-    return SlabRunner(layout, backend, sh(x, True), M * N * K)
+    return SlabRunner(layout, backend, sh(x, True), M * N * K, work_buffers=work_buffers)
 
 
 class SlabTrainer:

@@ -359,6 +359,21 @@ GN_API int gn_step_forward_slab_faces_f32(const float *weight, const float *bias
                                    int N, int K, int k_block_first, int k_block_count, int inner,
                                    int activation, float *face_to_left, float *face_to_right,
                                    void *stream);
+/* gn_step_forward_slab_faces_f32 whose face entries are face_stride floats apart (4-byte aligned addresses;
+ * face_stride <= 1: packed, as above). With face_stride = K of the neighbour's padded slab and face_to_left /
+ * face_to_right = the address of the ghost column [0][0][0][col] of the buffer the neighbour reads in its next
+ * step, the faces land where they are read and gn_slab_unpack_faces_f32 is not needed: that pass writes four
+ * useful bytes per 32-byte sector, here the same scattered stores leave the step kernel one by one while it
+ * computes. The neighbour must not be reading or writing that column meanwhile (it does not: its own step
+ * writes only the real columns of that buffer, and it starts its next step after this rank's kernel has
+ * finished). No counterpart in the reference (it is single-GPU). */
+GN_API int gn_step_forward_slab_faces_strided_f32(const float *weight, const float *bias, const float *scale,
+                                           const float *x, float *y, const float *norm_weight,
+                                           const float *norm_bias, const float *in_mean_rstd,
+                                           double *out_partials, int partials_per_sample, int B, int M,
+                                           int N, int K, int k_block_first, int k_block_count, int inner,
+                                           int activation, float *face_to_left, float *face_to_right,
+                                           long long face_stride, void *stream);
 /* x[b][m][n][col_left] = from_left[b][m][n], x[b][m][n][col_right] = from_right[b][m][n] for a
  * float array x [B, M, N, K]; either source may be NULL. */
 GN_API int gn_slab_unpack_faces_f32(const float *from_left, const float *from_right, float *x, int B,

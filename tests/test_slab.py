@@ -221,6 +221,11 @@ def test_cuda_slabs_match_single_device(world, shape):
 
     runners4 = [make_cuda_runner(SlabLayout(shape[2], world, r), w, b, s, gamma, beta, x, inner) for r in range(world)]
     assert torch.equal(torch.cat(run_emulated_mailboxes(runners4, outer), -1), got)
+    # ... and with the faces stored straight into the neighbours' ghost columns (no packed buffers, no unpacking)
+    from gridnet_b200.slab import run_emulated_in_place
+
+    runners5 = [make_cuda_runner(SlabLayout(shape[2], world, r), w, b, s, gamma, beta, x, inner) for r in range(world)]
+    assert torch.equal(torch.cat(run_emulated_in_place(runners5, outer), -1), got)
     single = gb.outer_forward(*(t.cuda() for t in prob), inner, outer, 8)
     assert torch.allclose(got, single, rtol=1e-5, atol=1e-6), (got - single).abs().max().item()
     want = orc.outer_forward(*(t.double().numpy() for t in prob), inner, outer, 8)
