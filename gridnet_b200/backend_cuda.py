@@ -48,7 +48,8 @@ def keep_forward_stash(enabled):
     backward skips recomputing them (about a quarter of the backward time; same gradient bits). The reference
     always recomputes. ``True`` / ``False`` force the choice; ``None`` (the default) keeps them whenever they
     take at most a tenth of the device memory that is free at that moment, and recomputes otherwise, call by
-    call. Returns the previous setting."""
+    call; the fused training loop (:class:`FusedLoopTrainOp`) decides once per loop how many of its LAST outer
+    steps keep them: as many as fit into three quarters of the free memory. Returns the previous setting."""
     global _keep_forward_stash
     previous, _keep_forward_stash = _keep_forward_stash, (None if enabled is None else bool(enabled))
     return previous
@@ -66,6 +67,24 @@ def _stash_wanted(weight, init_activations, inner_iters: int, block_size: int) -
     # what torch's caching allocator holds but has not handed out counts as free too
     free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
     return need * 10 <= free
+
+
+def _stash_steps(weight, x, inner_iters: int, block_size: int, steps: int) -> int:
+    """How many of the ``steps`` outer steps of a fused training loop keep their inner iterations: all or none when
+    :func:`keep_forward_stash` forces it; otherwise as many as fit into 75 % of the device memory that is free when
+    the loop starts (a step costs its stash plus the raw output that is saved anyway). Asked once per loop: the
+    driver's memory query is not free, and a loop should not change its mind half-way for a few megabytes."""
+    if _keep_forward_stash is not None:
+        return steps if _keep_forward_stash else 0
+    B, M, N, K = x.shape
+    need = int(lib.gn_step_stash_bytes(B, M, N, K, int(inner_iters), int(block_size)))
+    if need <= 0 or steps <= 0:
+        return 0
+    dev = weight.device
+    free, _ = torch.cuda.mem_get_info(dev)
+    free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+    per_step = need + x.numel() * 4
+    return max(0, min(steps, int(0.75 * free) // per_step))
 
 
 class GridnetCudaOp(torch.autograd.Function):
@@ -316,10 +335,12 @@ def _fused_loop_forward(plist, norm_weight, norm_bias, x, inner_iters, block_siz
     src, src_stats = x, None
     with torch.cuda.device(dev):
         st = torch.cuda.current_stream().cuda_stream
-        for weight, bias, residual_scale in plist:
+        # the LAST steps keep their inner iterations: their backward comes first, so their stash is freed first
+        keep = _stash_steps(plist[0][0], x, inner_iters, block_size, len(plist)) if need_grad and plist else 0
+        for k, (weight, bias, residual_scale) in enumerate(plist):
             dst = torch.empty_like(x)
             stash = None
-            if need_grad and _stash_wanted(weight, x, inner_iters, block_size):
+            if need_grad and k >= len(plist) - keep:
                 stash = torch.empty(int(lib.gn_step_stash_bytes(B, M, N, K, int(inner_iters), int(block_size))),
                                     dtype=torch.uint8, device=dev)
             check(lib.gn_step_forward_train_f32(

@@ -48,7 +48,8 @@ __global__ void __launch_bounds__(small8::THREADS, 2) outer_small_k(const OuterS
     __shared__ __align__(16) float tiles[MAX_SPC][2][TS];  // [sample of the CTA][ping-pong]
     __shared__ float2 gbtab[Geo::CELLS];
     __shared__ float2 mstats[MAX_SPC];
-    __shared__ double red[33];
+    __shared__ double2 wsum[MAX_SPC][4];   // per-warp (sum, sum of squares) of the CTA's outputs of this step
+    __shared__ double2 rsum[4][MAX_SPC];   // per-warp sums of the samples' partials after the barrier
 
     const int tid = threadIdx.x;
     const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
@@ -194,13 +195,22 @@ __global__ void __launch_bounds__(small8::THREADS, 2) outer_small_k(const OuterS
                         }
                     sm = warp_sum(sm);
                     sq = warp_sum(sq);
-                    if ((tid & 31) == 0)
-                        __stcg(&p.partials[(size_t)smp * p.nparts + (size_t)blk * 4 + (tid >> 5)], make_double2(sm, sq));
+                    if ((tid & 31) == 0) wsum[smp - s0][tid >> 5] = make_double2(sm, sq);
                 }
             }
         }
 
         // ---- grid-wide barrier: every CTA's outputs and partials of step o are in global memory
+        __syncthreads();
+        if (tid < s1 - s0) {  // one partial per block and sample: the four warps' sums in warp order
+            double sm = 0.0, sq = 0.0;
+#pragma unroll
+            for (int wq = 0; wq < 4; ++wq) {
+                sm += wsum[tid][wq].x;
+                sq += wsum[tid][wq].y;
+            }
+            __stcg(&p.partials[(size_t)(s0 + tid) * p.nparts + (size_t)blk * 4], make_double2(sm, sq));
+        }
         __syncthreads();
         if (tid == 0) {
             __threadfence();
@@ -219,22 +229,37 @@ __global__ void __launch_bounds__(small8::THREADS, 2) outer_small_k(const OuterS
         }
         __syncthreads();
 
-        // ---- statistics of this CTA's samples (every CTA of a sample adds the same partials in the same order)
-        for (int smp = s0; smp < s1; ++smp) {
-            const double2 *ps = p.partials + (size_t)smp * p.nparts;
-            double s = 0.0, q = 0.0;
-            for (int i = tid; i < p.nparts; i += THREADS) {
-                const double2 v = __ldcg(ps + i);
-                s += v.x;
-                q += v.y;
+        // ---- statistics of this CTA's samples: one reduction for all of them (every CTA of a sample adds the
+        // same partials, one per block, in the same order)
+        {
+            double acc[MAX_SPC][2];
+#pragma unroll
+            for (int q = 0; q < MAX_SPC; ++q) {
+                acc[q][0] = acc[q][1] = 0.0;
+                if (s0 + q < s1) {
+                    const double2 *ps = p.partials + (size_t)(s0 + q) * p.nparts;
+                    for (int i = tid; i < p.nblocks; i += THREADS) {
+                        const double2 v = __ldcg(ps + (size_t)i * 4);
+                        acc[q][0] += v.x;
+                        acc[q][1] += v.y;
+                    }
+                }
+                acc[q][0] = warp_sum(acc[q][0]);
+                acc[q][1] = warp_sum(acc[q][1]);
+                if ((tid & 31) == 0) rsum[tid >> 5][q] = make_double2(acc[q][0], acc[q][1]);
             }
-            s = block_sum(s, red);
-            q = block_sum(q, red);
-            if (tid == 0) {
-                const double mean = s / (double)P;
-                double var = q / (double)P - mean * mean;
+            __syncthreads();
+            if (tid < s1 - s0) {
+                double sm = 0.0, sq = 0.0;
+#pragma unroll
+                for (int wq = 0; wq < 4; ++wq) {
+                    sm += rsum[wq][tid].x;
+                    sq += rsum[wq][tid].y;
+                }
+                const double mean = sm / (double)P;
+                double var = sq / (double)P - mean * mean;
                 if (var < 0.0) var = 0.0;
-                mstats[smp - s0] = make_float2((float)mean, (float)(1.0 / sqrt(var + (double)p.eps)));
+                mstats[tid] = make_float2((float)mean, (float)(1.0 / sqrt(var + (double)p.eps)));
             }
         }
         __syncthreads();
