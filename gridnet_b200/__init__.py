@@ -8,7 +8,7 @@ native extension module. Everything runs through ``libgridnet_b200.so`` (C ABI i
 """
 from . import gridnet_cuda
 from ._lib import LIB_PATH, GridnetB200Error
-from .backend_cuda import (FusedLoopSeparateTrainOp, FusedLoopTrainOp, fused_loop_forward, GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, HostPipelinedForward, device_status, fused_step,
+from .backend_cuda import (FusedLoopResidualTrainOp, FusedLoopSeparateTrainOp, FusedLoopTrainOp, fused_loop_forward, GatedGridnetCudaOp, GridnetCudaOp, GridNormOp, HostPipelinedForward, device_status, fused_step,
                            keep_forward_stash, norm_apply,
                            norm_finalize, outer_forward, outer_forward_failed, outer_forward_workspace,
                            step_stats_partials)
@@ -31,6 +31,7 @@ __all__ = [
     "GridnetCudaOp",
     "GatedGridnetCudaOp",
     "GridNormOp",
+    "FusedLoopResidualTrainOp",
     "FusedLoopSeparateTrainOp",
     "FusedLoopTrainOp",
     "fused_loop_forward",

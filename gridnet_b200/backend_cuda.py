@@ -316,6 +316,136 @@ class FusedLoopSeparateTrainOp(torch.autograd.Function):
         return (gg, gbt, g, None, None, None, None) + tuple(t for grads in per_step for t in grads)
 
 
+class FusedLoopResidualTrainOp(torch.autograd.Function):
+    """The residual form of the model loop with gradients (gridnet/scripts/train_imagenet.py:81-83):
+
+        for net in nets:  n = layer_norm(h);  h = h + (net(n) - n)
+
+    as one autograd node. Forward: the step kernel normalises h while loading it, one pass writes
+    ``h + (y - layer_norm(h))`` and reduces the statistics of the result (``gn_norm_residual_combine_f32``); saved
+    are the step inputs h_k and their statistics (and the inner iterations of the last steps, memory permitting).
+    Backward, per step in reverse: the tuned step backward on the rebuilt ``n``, ``grad_n = grad_step - grad``,
+    the library's LayerNorm backward with the saved statistics, ``grad = grad + grad_h``.
+
+    ``FusedLoopResidualTrainOp.apply(norm_weight, norm_bias, x, inner_iters, block_size, activation, ln_eps,
+    outer_iters, *params)`` with ``params`` either one (weight, bias, residual_scale) shared by all outer steps or
+    ``outer_iters`` of them, one after the other."""
+
+    @staticmethod
+    def forward(ctx, norm_weight, norm_bias, x, inner_iters: int, block_size: int, activation: str, ln_eps: float,
+                outer_iters: int, *params):
+        outer = int(outer_iters)
+        assert len(params) in (3, 3 * outer), "one (weight, bias, residual_scale), or one per outer step"
+        shared = len(params) == 3 and outer != 1
+        plist = [tuple(params[:3])] * outer if len(params) == 3 else [tuple(params[i:i + 3]) for i in range(0, 3 * outer, 3)]
+        x = x.contiguous()
+        B, M, N, K = x.shape
+        P = M * N * K
+        act = activation_id(activation)
+        dev = x.device
+        _require_f32_cuda(norm_weight=norm_weight, norm_bias=norm_bias, x=x)
+        need_grad = any(ctx.needs_input_grad)
+        inputs, stats, stashes = [], [], []
+        with torch.cuda.device(dev):
+            st = torch.cuda.current_stream().cuda_stream
+            nws = _workspace(lib.gn_norm_workspace_bytes(B, P), dev)
+            sums = torch.empty(B, 2, dtype=torch.float64, device=dev)
+            mr = torch.empty(B, 2, dtype=torch.float32, device=dev)
+            h = x
+            if outer:
+                check(lib.gn_norm_local_sums_f32(h.data_ptr(), sums.data_ptr(), B, P, nws.data_ptr(), nws.numel(), st))
+                check(lib.gn_norm_finalize_f32(sums.data_ptr(), 1, mr.data_ptr(), B, P, float(ln_eps), st))
+            keep = _stash_steps(plist[0][0], x, inner_iters, block_size, outer) if need_grad and outer else 0
+            y = torch.empty_like(x)
+            for k, (weight, bias, residual_scale) in enumerate(plist):
+                _assert_step_args(weight, bias, residual_scale, x, block_size, False)
+                _require_f32_cuda(weight=weight, bias=bias, residual_scale=residual_scale)
+                stash = None
+                if need_grad and k >= outer - keep:
+                    stash = torch.empty(int(lib.gn_step_stash_bytes(B, M, N, K, int(inner_iters), int(block_size))),
+                                        dtype=torch.uint8, device=dev)
+                check(lib.gn_step_forward_train_f32(
+                    weight.data_ptr(), bias.data_ptr(), residual_scale.data_ptr(), h.data_ptr(), y.data_ptr(),
+                    norm_weight.data_ptr(), norm_bias.data_ptr(), mr.data_ptr(), None, B, M, N, K, int(inner_iters),
+                    int(block_size), act, None if stash is None else stash.data_ptr(),
+                    0 if stash is None else stash.numel(), st))
+                nxt, mr_next = torch.empty_like(x), torch.empty(B, 2, dtype=torch.float32, device=dev)
+                check(lib.gn_norm_residual_combine_f32(h.data_ptr(), y.data_ptr(), norm_weight.data_ptr(),
+                                                       norm_bias.data_ptr(), mr.data_ptr(), nxt.data_ptr(),
+                                                       mr_next.data_ptr(), B, P, float(ln_eps), nws.data_ptr(),
+                                                       nws.numel(), st))
+                if need_grad:
+                    inputs.append(h)
+                    stats.append(mr)
+                    stashes.append(stash)
+                h, mr = nxt, mr_next
+            out = h if outer else x.clone()
+        ctx.save_for_backward(norm_weight, norm_bias, *params, *inputs, *stats)
+        ctx.stashes = stashes
+        ctx.cfg = (int(inner_iters), outer, int(block_size), activation, len(params), shared)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        inner, outer, block, activation, nparams, shared = ctx.cfg
+        saved = ctx.saved_tensors
+        gamma, beta = saved[:2]
+        params = saved[2:2 + nparams]
+        plist = [tuple(params[:3])] * outer if nparams == 3 else [tuple(params[i:i + 3]) for i in range(0, 3 * outer, 3)]
+        inputs, stats = saved[2 + nparams:2 + nparams + outer], saved[2 + nparams + outer:2 + nparams + 2 * outer]
+        stashes, ctx.stashes = list(ctx.stashes), None
+        g = grad_out.contiguous()
+        if outer == 0:
+            return (torch.zeros_like(gamma), torch.zeros_like(beta), g, None, None, None, None, None) + \
+                tuple(torch.zeros_like(t) for t in params)
+        B, M, N, K = g.shape
+        P = M * N * K
+        dev = g.device
+        per_step = [None] * outer
+        total = None
+        gg = gbt = None
+        with torch.cuda.device(dev):
+            st = torch.cuda.current_stream().cuda_stream
+            nws = _workspace(lib.gn_norm_workspace_bytes(B, P), dev)
+            sums = torch.empty(B, 2, dtype=torch.float64, device=dev)
+            for k in reversed(range(outer)):
+                weight, bias, scale = plist[k]
+                h, mr = inputs[k], stats[k]
+                n = torch.empty_like(h)  # the step's input, rebuilt from h and its statistics
+                check(lib.gn_norm_apply_f32(h.data_ptr(), gamma.data_ptr(), beta.data_ptr(), mr.data_ptr(), n.data_ptr(), B, P, st))
+                dw, db, ds, gn = (torch.empty_like(t) for t in (weight, bias, scale, h))
+                if stashes[k] is not None:
+                    gridnet_cuda.backward_with_stash(weight, bias, scale, n, g, dw, db, ds, gn, inner, block, activation,
+                                                     stashes[k])
+                    stashes[k] = None
+                else:
+                    gridnet_cuda.backward(weight, bias, scale, n, g, dw, db, ds, gn, inner, block, 1e-5, False, activation)
+                del n
+                gn -= g  # h' = h + net(n) - n: n also enters with a minus sign
+                gh, dg, dbt = torch.empty_like(h), torch.empty_like(gamma), torch.empty_like(gamma)
+                check(lib.gn_norm_backward_local_sums_f32(h.data_ptr(), gamma.data_ptr(), gn.data_ptr(), mr.data_ptr(),
+                                                          sums.data_ptr(), B, P, nws.data_ptr(), nws.numel(), st))
+                check(lib.gn_norm_backward_apply_f32(h.data_ptr(), gamma.data_ptr(), gn.data_ptr(), mr.data_ptr(),
+                                                     sums.data_ptr(), P, gh.data_ptr(), dg.data_ptr(), dbt.data_ptr(), B, P,
+                                                     nws.data_ptr(), nws.numel(), st))
+                g = g + gh
+                if nparams == 3:
+                    if total is None:
+                        total = [dw, db, ds]
+                    else:
+                        for acc, t in zip(total, (dw, db, ds)):
+                            acc += t
+                else:
+                    per_step[k] = (dw, db, ds)
+                if gg is None:
+                    gg, gbt = dg, dbt
+                else:
+                    gg += dg
+                    gbt += dbt
+        pgrads = tuple(total) if nparams == 3 else tuple(t for grads in per_step for t in grads)
+        return (gg, gbt, g, None, None, None, None, None) + pgrads
+
+
 def _fused_loop_forward(plist, norm_weight, norm_bias, x, inner_iters, block_size, activation, ln_eps, need_grad):
     """The fused forward of the model loop with one (weight, bias, residual_scale) per outer step: every step kernel
     normalises its input while loading it and reduces the statistics of what it writes. Returns the normalised

@@ -16,7 +16,8 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from .backend_cuda import FusedLoopSeparateTrainOp, FusedLoopTrainOp, fused_loop_forward, outer_forward
+from .backend_cuda import (FusedLoopResidualTrainOp, FusedLoopSeparateTrainOp, FusedLoopTrainOp, fused_loop_forward,
+                           outer_forward)
 from .modules import GatedGridnet, Gridnet, GridNorm, Readout
 
 
@@ -111,17 +112,22 @@ class ImageNetModel(nn.Module):
         first = nets[0] if nets else None
         if first is not None and h.dtype == torch.float32 and not first.normalize and \
                 FusedLoopTrainOp.supported(first.weight, h, first.inner_iterations, first.block_size):
-            # the loop variants run fused too: per-step parameters, and the residual form without gradients
+            # the loop variants run fused too: per-step parameters and the residual form, with and without gradients
             plist = [(n.weight, n.bias, n.residual_scale) for n in nets]
             if not _wants_grad(self, h):
                 return self.readout(fused_loop_forward(plist, self.norm.weight, self.norm.bias, h, first.inner_iterations,
                                                        first.block_size, first.activation, self.norm.eps,
                                                        outer_residual=self.outer_residual))
-            if not self.outer_residual:
-                flat = [t for ps in plist for t in ps]
-                return self.readout(FusedLoopSeparateTrainOp.apply(self.norm.weight, self.norm.bias, h,
+            flat = [t for ps in (plist if self.separate_params else plist[:1]) for t in ps]
+            if self.outer_residual:
+                return self.readout(FusedLoopResidualTrainOp.apply(self.norm.weight, self.norm.bias, h,
                                                                    first.inner_iterations, first.block_size,
-                                                                   first.activation, self.norm.eps, *flat))
+                                                                   first.activation, self.norm.eps, self.outer_iters,
+                                                                   *flat))
+            return self.readout(FusedLoopSeparateTrainOp.apply(self.norm.weight, self.norm.bias, h,
+                                                               first.inner_iterations, first.block_size,
+                                                               first.activation, self.norm.eps,
+                                                               *[t for ps in plist for t in ps]))
         for i in range(self.outer_iters):
             net = self.networks[i] if self.separate_params else self.network
             if self.outer_residual:

@@ -188,6 +188,32 @@ def test_fused_loop_variants_equal_the_step_by_step_composition(block):
     for i, (a, c) in enumerate(zip(got, want)):
         assert torch.allclose(a, c, rtol=1e-3, atol=1e-4 * (1 + c.abs().max().item())), (i, (a - c).abs().max().item())
 
+    # training in the residual form: per-step parameters, then one shared set, with the stash forced on and off
+    for shared in (False, True):
+        for keep in (True, False):
+            previous = gb.keep_forward_stash(keep)
+            try:
+                ps, ga, be, xl = leaves()
+                if shared:
+                    ps = [ps[0]] * outer
+                uniq = list(ps[0]) if shared else [t for p in ps for t in p]
+                want_y = composition(ps, ga, be, xl, True)
+                want = torch.autograd.grad(want_y, [ga, be, xl] + uniq, gy)
+                ps, ga, be, xl = leaves()
+                if shared:
+                    ps = [ps[0]] * outer
+                uniq = list(ps[0]) if shared else [t for p in ps for t in p]
+                got_y = gb.FusedLoopResidualTrainOp.apply(ga, be, xl, inner, block, "silu", 1e-5, outer, *uniq)
+                got = torch.autograd.grad(got_y, [ga, be, xl] + uniq, gy)
+            finally:
+                gb.keep_forward_stash(previous)
+            assert torch.allclose(got_y, want_y, rtol=1e-4, atol=1e-5), (shared, keep)
+            for i, (a, c) in enumerate(zip(got, want)):
+                assert torch.allclose(a, c, rtol=1e-3, atol=1e-4 * (1 + c.abs().max().item())), \
+                    (shared, keep, i, (a - c).abs().max().item())
+    y0 = gb.FusedLoopResidualTrainOp.apply(gamma, beta, x, inner, block, "silu", 1e-5, 0, *plist[0])
+    assert torch.equal(y0, x)
+
 
 @pytest.mark.parametrize("name,grid,block,inner,outer,B", [("C3", 128, 8, 2, 16, 1), ("C4", 64, 4, 8, 16, 2)])
 def test_training_configurations_at_their_own_grid_and_depth(name, grid, block, inner, outer, B):
