@@ -139,7 +139,6 @@ __global__ void __launch_bounds__(256) slab_finalize_unpack_k(const unsigned cha
                                                               size_t cells, int K, int col_left, int col_right,
                                                               int *error_flag)
 {
-    __shared__ bool ok;
     if (threadIdx.x == 0) {
         const unsigned long long *flags =
             reinterpret_cast<const unsigned long long *>(box + mailbox_flags_offset(world, B)) + parity * world;
@@ -157,7 +156,6 @@ __global__ void __launch_bounds__(256) slab_finalize_unpack_k(const unsigned cha
                 __nanosleep(100);
             }
         }
-        ok = all;
         if (!all && error_flag) *error_flag = 1;
     }
     __syncthreads();

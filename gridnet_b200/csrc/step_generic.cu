@@ -40,7 +40,6 @@ struct BlockPos {
 template <int BS>
 __device__ __forceinline__ BlockPos block_pos(int N, int K)
 {
-    constexpr int E = Geo<BS>::E;
     BlockPos p;
     const int tid = threadIdx.x;
     if (BS == 8) {  // a warp = 8 x-positions x 4 z-planes of one row
