@@ -80,8 +80,9 @@ bool gated_bwd_fast8_applicable(const float *w, const float *b, const float *x, 
 int launch_gated_bwd_fast8(const float *w, const float *b, const float *x, const float *gy, float *gw, float *gb, float *gx,
                            int B, int M, int N, int K, int inner, int act, float *ws, cudaStream_t st);
 // the cross-block part of grad_x for one weight set: w + tap * tap_stride + cell (step_bwd_fast.cu)
+// (w2, dsum2: a second weight set with its own delta sums, added in the same pass)
 int launch_bwd_border8(const float *w, size_t tap_stride, const float *dsum, float *gx, int B, int M, int N, int K,
-                       cudaStream_t st);
+                       cudaStream_t st, const float *w2 = nullptr, const float *dsum2 = nullptr);
 
 // ---- slab.cu
 int launch_slab_unpack_faces(const float *from_left, const float *from_right, float *x, int B, int M, int N, int K,

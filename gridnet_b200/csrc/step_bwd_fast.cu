@@ -682,13 +682,19 @@ constexpr int SLOTS = 3;  // ceil(1000 / 384)
 // hterm != nullptr (per-block normalisation): every cell of a region's tile, halo included, also owes
 // F + x[c] E to that region's statistics (bwd_reverse8 has taken it from the region's own cells); a surface
 // cell lies in the tiles of the up to seven neighbouring regions across the faces it touches.
+// TWO (the gated update): a second weight set w2 with its own delta sums dsum2 is added in the same pass, so the
+// surface cells of grad_x are read and written once for both branches.
+template <bool TWO>
 __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *__restrict__ w, const float *__restrict__ dsum,
                                                                   float *__restrict__ gx, int B, int M, int N, int K, int spc,
                                                                   const float2 *__restrict__ hterm,
-                                                                  const float *__restrict__ x, size_t tap_stride)
+                                                                  const float *__restrict__ x, size_t tap_stride,
+                                                                  const float *__restrict__ w2,
+                                                                  const float *__restrict__ dsum2)
 {
     using namespace border8;
     __shared__ float tile[2][TS];
+    __shared__ float tile2[TWO ? 2 : 1][TWO ? TS : 1];
     __shared__ float part[2][3][128];  // [sample parity][axis][face cell]
     const int tid = threadIdx.x;
     const int nbx = K >> 3, nby = N >> 3;
@@ -697,7 +703,10 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
     const size_t P = (size_t)M * N * K;
     const long long origin = ((long long)(bz * 8 - 1) * N + (by * 8 - 1)) * K + (bx * 8 - 1);
 
-    for (int i = tid; i < 2 * TS; i += THREADS) (&tile[0][0])[i] = 0.0f;
+    for (int i = tid; i < 2 * TS; i += THREADS) {
+        (&tile[0][0])[i] = 0.0f;
+        if (TWO) (&tile2[0][0])[i] = 0.0f;
+    }
 
     // shell cells this thread fetches: bits 0..9 tile offset, bits 10.. offset from the origin
     unsigned cinfo[SLOTS];
@@ -723,7 +732,7 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
     l[axis == 0 ? 1 : 0] = u;
     l[axis == 2 ? 1 : 2] = v;
     const int dcross = side == 0 ? 1 : -1;  // the source n = c - offset lies across the low face when the offset is +1
-    float wf[9];
+    float wf[9], wf2[TWO ? 9 : 1];
     int toff[9];
 #pragma unroll
     for (int q = 0; q < 9; ++q) {
@@ -741,6 +750,7 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
         const bool ok = owned && nz >= 0 && nz < M && ny >= 0 && ny < N && nx >= 0 && nx < K;
         const int t = (d[0] + 1) * 9 + (d[1] + 1) * 3 + (d[2] + 1);
         wf[q] = ok ? w[(size_t)t * tap_stride + ((size_t)nz * N + ny) * K + nx] : 0.0f;
+        if (TWO) wf2[q] = ok ? w2[(size_t)t * tap_stride + ((size_t)nz * N + ny) * K + nx] : 0.0f;
         toff[q] = (l[0] + 1 - d[0]) * 100 + (l[1] + 1 - d[1]) * 10 + (l[2] + 1 - d[2]);
     }
 
@@ -779,13 +789,16 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
     const unsigned nregions = gridDim.x;
 
     const int s0 = blockIdx.y * spc, s1 = min(B, s0 + spc);
-    float pf[SLOTS];
+    float pf[SLOTS], pf2[TWO ? SLOTS : 1];
     auto fetch = [&](int smp) {
         if (smp < s1) {
             const float *src = dsum + (size_t)smp * P + origin;
 #pragma unroll
             for (int j = 0; j < SLOTS; ++j)
-                if (cinfo[j] != 0xffffffffu) pf[j] = ld_pinned(src + (cinfo[j] >> 10));
+                if (cinfo[j] != 0xffffffffu) {
+                    pf[j] = ld_pinned(src + (cinfo[j] >> 10));
+                    if (TWO) pf2[j] = ld_pinned(dsum2 + (size_t)smp * P + origin + (cinfo[j] >> 10));
+                }
         }
     };
     fetch(s0);
@@ -795,9 +808,13 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
     for (int smp = s0; smp < s1; ++smp) {
         const int par = smp & 1;
         float *tl = tile[par];
+        float *tl2 = TWO ? tile2[par] : nullptr;
 #pragma unroll
         for (int j = 0; j < SLOTS; ++j)
-            if (cinfo[j] != 0xffffffffu) tl[cinfo[j] & 0x3ff] = pf[j];
+            if (cinfo[j] != 0xffffffffu) {
+                tl[cinfo[j] & 0x3ff] = pf[j];
+                if (TWO) tl2[cinfo[j] & 0x3ff] = pf2[j];
+            }
         fetch(smp + 1);
         const float gcur = gnext;
         if (active && smp + 1 < s1) gnext = gx[(size_t)(smp + 1) * P + c];
@@ -806,6 +823,10 @@ __global__ void __launch_bounds__(border8::THREADS) bwd_border8_k(const float *_
             float acc = 0.0f;
 #pragma unroll
             for (int q = 0; q < 9; ++q) acc = fmaf(wf[q], tl[toff[q]], acc);
+            if (TWO) {
+#pragma unroll
+                for (int q = 0; q < 9; ++q) acc = fmaf(wf2[q], tl2[toff[q]], acc);
+            }
             part[par][axis][fc] = acc;
         }
         __syncthreads();  // partial sums complete; tile and sums of the other parity are free again
@@ -919,13 +940,17 @@ static void launch_reverse(const BwdParams &p, dim3 grid, int act, cudaStream_t 
 }
 
 int launch_bwd_border8(const float *w, size_t tap_stride, const float *dsum, float *gx, int B, int M, int N, int K,
-                       cudaStream_t st)
+                       cudaStream_t st, const float *w2, const float *dsum2)
 {
     const long long nb = (long long)(M / 8) * (N / 8) * (K / 8);
     const int chunks = pick_batch_chunks_balanced(nb, B, 3, 8.0, 32);
     const int spc = (B + chunks - 1) / chunks;
     dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
-    bwd_border8_k<<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc, nullptr, nullptr, tap_stride);
+    if (w2)
+        bwd_border8_k<true><<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc, nullptr, nullptr, tap_stride, w2, dsum2);
+    else
+        bwd_border8_k<false><<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc, nullptr, nullptr, tap_stride, nullptr,
+                                                                nullptr);
     return check_launch("bwd_border8");
 }
 
@@ -1021,7 +1046,8 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
         const int spc = (B + chunks - 1) / chunks;
         dim3 grid((unsigned)nb, (unsigned)((B + spc - 1) / spc));
         if (block == 4) bwd_halo8_k<4><<<grid, HaloGeo<4>::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc);
-        else bwd_border8_k<<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc, normalize ? hterm : nullptr, x, P);
+        else bwd_border8_k<false><<<grid, border8::THREADS, 0, st>>>(w, dsum, gx, B, M, N, K, spc, normalize ? hterm : nullptr, x, P,
+                                                                     nullptr, nullptr);
     }
     rc = check_launch("bwd_halo8");
     if (rc != GN_OK) return rc;

@@ -14,8 +14,8 @@
 //   wgrad    gated_bwd_wgrad8: dWv[n][t] += x_t[n + o_t] dv_t[n], dWg likewise, plus the two bias gradients,
 //            accumulated in registers over samples and iterations; batch chunks of a block form a thread-block
 //            cluster and add their partial sums through distributed shared memory in rank order;
-//   border   bwd_border8_k (step_bwd_fast.cu) once per branch: the part of grad_x that crosses block borders
-//            needs only the per-neuron sums of dv and dg over the iterations.
+//   border   bwd_border8_k (step_bwd_fast.cu) with both branches in one pass: the part of grad_x that crosses block
+//            borders needs only the per-neuron sums of dv and dg over the iterations.
 // Deterministic: no floating-point atomics. Bounded waits on the bulk tensor copies report through the int at
 // the end of the workspace.
 #include <cooperative_groups.h>
@@ -400,10 +400,9 @@ int launch_gated_bwd_fast8(const float *w, const float *b, const float *x, const
         rc = check_launch("gated_bwd_wgrad8");
         if (rc != GN_OK) return rc;
     }
-    // grad_x across block borders: the value branch (taps at w + 2 t P), then the gate branch (w + (2 t + 1) P)
-    rc = launch_bwd_border8(w, 2 * P, dsum_v, gx, B, M, N, K, st);
-    if (rc != GN_OK) return rc;
-    rc = launch_bwd_border8(w + P, 2 * P, dsum_g, gx, B, M, N, K, st);
+    // grad_x across block borders, both branches in one pass: the value branch (taps at w + 2 t P) and the gate
+    // branch (w + (2 t + 1) P)
+    rc = launch_bwd_border8(w, 2 * P, dsum_v, gx, B, M, N, K, st, w + P, dsum_g);
     if (rc != GN_OK) return rc;
     return launch_propagate_flag(error_flag, st);
 }
