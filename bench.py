@@ -658,6 +658,18 @@ def bench_slab(ctx: Ctx):
     dist.barrier()
     torch.cuda.synchronize()
     ms = ctx.max_over_ranks(e0.elapsed_time(e1))
+    # where a step's time goes (in-place exchange): one more pass with CUDA events between its three launches
+    phases = None
+    if mode == "in-place":
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(outer)]
+        run_in_place(SlabRunner(lay, backend, x, G * G * G, work_buffers=slabs.work_buffers()), outer, slabs, boxes,
+                     probe=lambda k, i: evs[k][i].record())
+        torch.cuda.synchronize()
+        mean = lambda i: sum(evs[k][i].elapsed_time(evs[k][i + 1]) for k in range(1, outer)) / (outer - 1)
+        phases = {"step_kernel_ms": ctx.max_over_ranks(mean(0)), "publish_sums_ms": ctx.max_over_ranks(mean(1)),
+                  "wait_and_finalize_ms": ctx.max_over_ranks(mean(2)),
+                  "note": "CUDA events between the three launches of an outer step, mean over steps 2..32 of one extra pass, "
+                          "max over ranks (the first step has no normalise-on-load)"}
     finite = bool(torch.isfinite(out).all().item())
     chk = out.double().sum().reshape(1)  # the same bits whichever way the faces travel and whatever N is
     dist.all_reduce(chk)
@@ -691,6 +703,8 @@ def bench_slab(ctx: Ctx):
                    "samples_per_sec": B * steps / (ms * 1e-3), "finite": finite, "output_checksum": float(chk.item())},
         "gpu_launches": (outer * 3 + 1) * steps if mode != "nccl" else (outer * 2 + 1) * steps,
     }
+    if phases is not None:
+        rec["phases"] = phases
     rec["full_size_parity"] = {"ok": bool(full_ok[0].item()), "bit_identical": bool(full_ok[1].item()),
                                "max_abs_err": float(worst.item()),
                                "against": "the single-GPU fused loop (gn_outer_forward_f32) on the whole 256^3 grid, run on "

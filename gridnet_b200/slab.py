@@ -535,21 +535,29 @@ class PeerStatsMailboxes:
         return bool(self.error_flag.item())
 
 
-def run_in_place(runner: SlabRunner, outer: int, slabs: "PeerSlabBuffers", mailboxes: "PeerStatsMailboxes") -> torch.Tensor:
+def run_in_place(runner: SlabRunner, outer: int, slabs: "PeerSlabBuffers", mailboxes: "PeerStatsMailboxes",
+                 probe=None) -> torch.Tensor:
     """Drive one rank for ``outer`` steps with the faces stored by the step kernel straight into the neighbours'
     ghost columns (:class:`PeerSlabBuffers`; the runner must have been built on ``slabs.work_buffers()``) and the
     sums exchanged through :class:`PeerStatsMailboxes`: per step the step kernel, the publish kernel and a kernel
     that waits for the sums and finishes the statistics - no unpacking pass, no collective call. A neighbour
     writes a ghost column of the buffer this rank reads NEXT while this rank still writes that buffer's real
-    columns; it cannot write again before this rank has published its next sums, i.e. finished reading."""
+    columns; it cannot write again before this rank has published its next sums, i.e. finished reading.
+    ``probe(k, i)`` (optional) is called before the three launches of step k (i = 0, 1, 2) and after them (3),
+    e.g. to record CUDA events."""
     be, lay = runner.backend, runner.layout
+    mark = probe if probe is not None else (lambda k, i: None)
     for k in range(outer):
         mailboxes.step += 1
         step = mailboxes.step
+        mark(k, 0)
         runner.compute_direct_no_sums(*slabs.targets(runner.next_index()), face_stride=slabs.stride)
+        mark(k, 1)
         be.publish_sums(mailboxes.ptrs, lay.rank, lay.world, step)
+        mark(k, 2)
         runner.stats = be.finalize_unpack(mailboxes.buf, lay.world, step, runner.grid_size, None, None,
                                           runner.bufs[runner.cur], mailboxes.error_flag)
+        mark(k, 3)
     return runner.result()
 
 
