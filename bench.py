@@ -850,8 +850,8 @@ def bench_train(ctx: Ctx, name: str, stash=None, microbatches=None, steps_cap: i
                        "forward_ms": t_fwd / steps, "backward_ms": t_bwd / steps, "finite": finite,
                        "intermediate_results": ("kept from the forward pass" if stash else "recomputed in the backward pass"
                                                 if stash is not None else
-                                                "kept from the forward pass for as many of the last outer steps as fit into three "
-                                                "quarters of the free device memory, recomputed for the others (package default)"),
+                                                "kept from the forward pass for as many of the last outer steps as fit into 70 % "
+                                                "of the free device memory, recomputed for the others (package default)"),
                        "microbatches": nmb,
                        "allocator": {"driver_allocations_in_timed_region": driver_allocs,
                                      "out_of_memory_retries_in_timed_region": alloc_retries,

@@ -49,7 +49,7 @@ def keep_forward_stash(enabled):
     always recomputes. ``True`` / ``False`` force the choice; ``None`` (the default) keeps them whenever they
     take at most a tenth of the device memory that is free at that moment, and recomputes otherwise, call by
     call; the fused training loop (:class:`FusedLoopTrainOp`) decides once per loop how many of its LAST outer
-    steps keep them: as many as fit into three quarters of the free memory. Returns the previous setting."""
+    steps keep them: as many as fit into 70 % of the free memory. Returns the previous setting."""
     global _keep_forward_stash
     previous, _keep_forward_stash = _keep_forward_stash, (None if enabled is None else bool(enabled))
     return previous
@@ -71,7 +71,7 @@ def _stash_wanted(weight, init_activations, inner_iters: int, block_size: int) -
 
 def _stash_steps(weight, x, inner_iters: int, block_size: int, steps: int) -> int:
     """How many of the ``steps`` outer steps of a fused training loop keep their inner iterations: all or none when
-    :func:`keep_forward_stash` forces it; otherwise as many as fit into 75 % of the device memory that is free when
+    :func:`keep_forward_stash` forces it; otherwise as many as fit into 70 % of the device memory that is free when
     the loop starts (a step costs its stash plus the raw output that is saved anyway). Asked once per loop: the
     driver's memory query is not free, and a loop should not change its mind half-way for a few megabytes."""
     if _keep_forward_stash is not None:
@@ -84,7 +84,7 @@ def _stash_steps(weight, x, inner_iters: int, block_size: int, steps: int) -> in
     free, _ = torch.cuda.mem_get_info(dev)
     free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
     per_step = need + x.numel() * 4
-    return max(0, min(steps, int(0.75 * free) // per_step))
+    return max(0, min(steps, int(0.7 * free) // per_step))
 
 
 class GridnetCudaOp(torch.autograd.Function):
