@@ -33,6 +33,7 @@ SIGNATURES = {
     "gn_step_backward_stash_error_flag_offset": (c_size_t, [c_int] * 5),
     "gn_step_forward_stash_f32": (c_int, [_P] * 5 + _geom + [c_int, c_int, c_int, _P, c_size_t, _P]),
     "gn_step_backward_stash_f32": (c_int, [_P] * 9 + _geom + [c_int, c_int, c_int, _P, c_size_t, _P, c_size_t, _P]),
+    "gn_step_backward_fused_in_f32": (c_int, [_P] * 12 + _geom + [c_int, c_int, c_int, _P, c_size_t, _P, c_size_t, _P]),
     "gn_step_backward_ws_f32": (c_int, [_P] * 9 + _geom + [c_int, c_int, c_float, c_int, c_int, _P, c_size_t, _P]),
     "gn_gated_forward_f32": (c_int, [_P] * 4 + _geom + [c_int, c_int, c_int, _P]),
     "gn_gated_forward_f64": (c_int, [_P] * 4 + _geom + [c_int, c_int, c_int, _P]),

@@ -494,6 +494,34 @@ def _fused_loop_forward(plist, norm_weight, norm_bias, x, inner_iters, block_siz
     return y, raws, stats, stashes
 
 
+def _step_backward_fused_in(weight, bias, scale, x_raw, mean_rstd, gamma, beta, gy, dw, db, ds, gx, inner, block,
+                            activation, stash) -> bool:
+    """The tuned step backward on an input given as (raw tensor, statistics, norm parameters); False where the
+    library has no such path (the caller then normalises first)."""
+    from ._lib import GN_ERR_UNSUPPORTED
+
+    if int(block) != 8:
+        return False
+    B, M, N, K = x_raw.shape
+    with torch.cuda.device(x_raw.device):
+        if stash is not None:
+            need = int(lib.gn_step_backward_stash_workspace_bytes(B, M, N, K, int(inner), int(block)))
+        else:
+            need = int(lib.gn_step_backward_workspace_bytes(B, M, N, K, int(inner), int(block), 0, 4))
+        if need <= 0:
+            return False
+        ws = torch.empty(need, dtype=torch.uint8, device=x_raw.device)
+        rc = lib.gn_step_backward_fused_in_f32(
+            weight.data_ptr(), bias.data_ptr(), scale.data_ptr(), x_raw.data_ptr(), mean_rstd.data_ptr(), gamma.data_ptr(),
+            beta.data_ptr(), gy.data_ptr(), dw.data_ptr(), db.data_ptr(), ds.data_ptr(), gx.data_ptr(), B, M, N, K,
+            int(inner), int(block), activation_id(activation), None if stash is None else stash.data_ptr(),
+            0 if stash is None else stash.numel(), ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+    if rc == GN_ERR_UNSUPPORTED:
+        return False
+    check(rc)
+    return True
+
+
 def _fused_loop_backward(plist, gamma, beta, x, raws, stats, stashes, grad_y, inner, block, activation, sink):
     """The reverse walk over the steps of :func:`_fused_loop_forward`: the library's LayerNorm backward with the
     saved statistics, then the tuned step backward on the step's normalised input rebuilt from the saved raw
@@ -520,14 +548,26 @@ def _fused_loop_backward(plist, gamma, beta, x, raws, stats, stashes, grad_y, in
             check(lib.gn_norm_backward_apply_f32(raws[k].data_ptr(), gamma.data_ptr(), g.data_ptr(), stats[k].data_ptr(),
                                                  sums.data_ptr(), P, gs_k.data_ptr(), dg.data_ptr(), dbt.data_ptr(), B, P,
                                                  nws.data_ptr(), nws.numel(), st))
-            # the step's input: x itself for the first step, else the normalised output of the step before
+            dw, db, ds, gx = (torch.empty_like(t) for t in (weight, bias, scale, x))
+            # the step's input: x itself for the first step, else the normalised output of the step before - which
+            # the backward kernels rebuild while loading the raw tensor where they can (block 8), else a pass here
+            if k > 0 and _step_backward_fused_in(weight, bias, scale, raws[k - 1], stats[k - 1], gamma, beta, gs_k, dw, db,
+                                                 ds, gx, inner, block, activation, stashes[k]):
+                stashes[k] = None
+                sink(k, (dw, db, ds))
+                if gg is None:
+                    gg, gbt = dg, dbt
+                else:
+                    gg += dg
+                    gbt += dbt
+                g = gx
+                continue
             if k == 0:
                 xin = x
             else:
                 xin = torch.empty_like(x)
                 check(lib.gn_norm_apply_f32(raws[k - 1].data_ptr(), gamma.data_ptr(), beta.data_ptr(),
                                             stats[k - 1].data_ptr(), xin.data_ptr(), B, P, st))
-            dw, db, ds, gx = (torch.empty_like(t) for t in (weight, bias, scale, x))
             if stashes[k] is not None:
                 gridnet_cuda.backward_with_stash(weight, bias, scale, xin, gs_k, dw, db, ds, gx, inner, block, activation,
                                                  stashes[k])

@@ -442,6 +442,37 @@ GN_API int gn_gated_backward_ws_f32(const float *w, const float *b, const float 
     return api_gated_backward<float>(w, b, x, gy, gw, gb, gx, B, M, N, K, inner, block, act, stream);
 }
 
+GN_API int gn_step_backward_fused_in_f32(const float *w, const float *b, const float *s, const float *x_raw,
+                                         const float *in_mean_rstd, const float *gamma, const float *beta, const float *gy,
+                                         float *gw, float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner,
+                                         int block, int act, const void *stash, size_t stash_bytes, void *workspace,
+                                         size_t workspace_bytes, void *stream)
+{
+    const int rc = check_geometry(B, M, N, K, inner, block, act);
+    if (rc != GN_OK) return rc;
+    if (!w || !b || !s || !gw || !gb || !gs) return GN_ERR_NULL_POINTER;
+    if (B == 0 || block != 8 || inner < 1) return GN_ERR_UNSUPPORTED;
+    if (!x_raw || !in_mean_rstd || !gamma || !beta || !gy || !gx || !workspace) return GN_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(in_mean_rstd) % 8 || reinterpret_cast<uintptr_t>(workspace) % 16) return GN_ERR_WORKSPACE;
+    const size_t need_ws = stash ? gn_step_backward_stash_workspace_bytes(B, M, N, K, inner, block)
+                                 : gn_step_backward_workspace_bytes(B, M, N, K, inner, block, 0, 4);
+    if (need_ws == 0) return GN_ERR_UNSUPPORTED;
+    if (workspace_bytes < need_ws) return GN_ERR_WORKSPACE;
+    if (stash) {
+        const size_t need_stash = gn_step_stash_bytes(B, M, N, K, inner, block);
+        if (need_stash == 0) return GN_ERR_UNSUPPORTED;
+        if (stash_bytes < need_stash || reinterpret_cast<uintptr_t>(stash) % 16) return GN_ERR_WORKSPACE;
+    }
+    // bulk tensor copies are what the normalise-on-load path of the weight-gradient kernel is built on
+    CUtensorMap probe_map;
+    if (!bwd_fast8_applicable(w, b, s, x_raw, gy, gw, gb, gs, gx, B, M, N, K, inner, block, 0) ||
+        !fast8_make_tile_map(&probe_map, x_raw, B, M, N, K))
+        return GN_ERR_UNSUPPORTED;
+    return launch_step_bwd_fast8(w, b, s, x_raw, gy, gw, gb, gs, gx, B, M, N, K, inner, block, act,
+                                 static_cast<const float *>(stash), static_cast<float *>(workspace), (cudaStream_t)stream, 0,
+                                 0.0f, in_mean_rstd, gamma, beta);
+}
+
 GN_API int gn_step_backward_max_inner(int block, int elem_size) { return step_backward_max_inner(block, elem_size); }
 
 GN_API int gn_gated_forward_f32(const float *w, const float *b, const float *x, float *y, int B, int M, int N, int K,

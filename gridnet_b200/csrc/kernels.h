@@ -104,7 +104,8 @@ bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const 
                           int normalize);
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
-                          const float *stash, float *ws, cudaStream_t st, int normalize = 0, float eps = 0.0f);
+                          const float *stash, float *ws, cudaStream_t st, int normalize = 0, float eps = 0.0f,
+                          const float *in_stats = nullptr, const float *gamma = nullptr, const float *beta = nullptr);
 size_t bwd_fast8_norm_extra_floats(int B, int M, int N, int K, int inner);
 
 // ---- step_pair64.cu ("lanes = samples" kernel for large batches; activations in the IL64 layout

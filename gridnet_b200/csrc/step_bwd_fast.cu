@@ -58,6 +58,10 @@ struct BwdParams {
     const float *b;
     const float4 *tile_stats;
     float2 *hterm;
+    // The step input given as the RAW output of the step before plus its whole-grid statistics: the
+    // weight-gradient kernel (and the replay) normalise it while loading, (x - mean) * rstd * gamma + beta.
+    const float2 *in_stats;  // [B] (mean, rstd); nullptr: x is used as it is
+    const float *gamma, *beta;
 };
 
 // ---------------------------------------------------------------------------- reverse sweep
@@ -297,7 +301,9 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_reverse8(const BwdParams
 // NORM (per-block normalisation): the stencil input was (tile - mean_t) / (std_t + eps) and the stored deltas
 // are already divided by (std_t + eps), so the tile mean is subtracted from each window value and the bias
 // gradient multiplies the stored delta by (std_t + eps) again.
-template <int SUB, bool USE_TMA, bool NORM = false>
+// FUSE_IN: x is a raw step output; its tile cells are normalised with the sample's whole-grid statistics on their
+// way from the staging buffer into the tile (as in step_fwd_fast8), so the normalised tensor is never stored.
+template <int SUB, bool USE_TMA, bool NORM = false, bool FUSE_IN = false>
 __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_constant__ CUtensorMap x_map, const BwdParams p)
 {
     using namespace bwd8;
@@ -316,6 +322,8 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
     float(*tiles)[TS] = reinterpret_cast<float(*)[TS]>(pool + STGF);
     __shared__ __align__(8) unsigned long long bars[2];
     __shared__ unsigned ctab[CI_SMEM ? SLOTS * THREADS : 1];
+    static_assert(!FUSE_IN || (SUB == 8 && USE_TMA), "normalise-on-load: block 8 with bulk tensor copies");
+    __shared__ float2 gbtab[FUSE_IN ? SLOTS * THREADS : 1];  // (gamma, beta) per tile cell; 0 outside the grid
     const int tid = threadIdx.x;
     const int xp = tid & 3, yp = (tid >> 2) & 3, z = tid >> 4;
     const int nbx = p.K >> 3, nby = p.N >> 3;
@@ -332,11 +340,16 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
     for (int j = 0; j < SLOTS; ++j) {
         const int i = tid + j * THREADS;
         unsigned ci = 0xffffffffu;
+        if (FUSE_IN && i < SLOTS * THREADS) gbtab[i] = make_float2(0.0f, 0.0f);
         if (i < Geo::CELLS) {
             int soff, cz, cy, cx;
             bool halo;
             Geo::cell(i, soff, cz, cy, cx, halo);
             const int gz = bz * 8 + cz - 1, gy = by * 8 + cy - 1, gx = bx * 8 + cx - 1;
+            if (FUSE_IN && gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K) {
+                const long long rel = origin + ((long long)cz * p.N + cy) * K + cx;
+                gbtab[i] = make_float2(p.gamma[rel], p.beta[rel]);
+            }
             if (USE_TMA)  // every cell comes from the staging buffer; the copy zero-fills what lies outside the grid
                 ci = (unsigned)soff | (halo ? HALO_BIT : 0u) | ((unsigned)((cz * 10 + cy) * 16 + cx + 3) << SRC_SHIFT);
             else if (gz >= 0 && gz < p.M && gy >= 0 && gy < p.N && gx >= 0 && gx < K)
@@ -418,11 +431,16 @@ __global__ void __launch_bounds__(bwd8::THREADS, 3) bwd_wgrad8(const __grid_cons
                 *p.error_flag = 1;
         }
         __syncthreads();  // the previous sample's tiles are no longer read
+        const float2 mr = FUSE_IN ? p.in_stats[smp] : make_float2(0.0f, 1.0f);
 #pragma unroll
         for (int j = 0; j < SLOTS; ++j) {
             const unsigned ci = cell_info(j);
             if (ci != 0xffffffffu) {
-                const float v = USE_TMA ? staging[par][ci >> SRC_SHIFT] : pf[USE_TMA ? 0 : j];
+                float v = USE_TMA ? staging[par][ci >> SRC_SHIFT] : pf[USE_TMA ? 0 : j];
+                if (FUSE_IN) {
+                    const float2 gb = gbtab[tid + j * THREADS];
+                    v = fmaf((v - mr.x) * mr.y, gb.x, gb.y);
+                }
                 tiles[0][ci & SOFF_MASK] = v;
                 if (ci & HALO_BIT) tiles[1][ci & SOFF_MASK] = v;
             }
@@ -890,10 +908,10 @@ bool bwd_fast8_applicable(const float *w, const float *b, const float *s, const 
 
 // wgrad launch for one instantiation: plain when one CTA covers a block's batch, otherwise the
 // batch chunks of a block as one thread-block cluster
-template <int SUB, bool USE_TMA, bool NORM = false>
+template <int SUB, bool USE_TMA, bool NORM = false, bool FUSE_IN = false>
 static int launch_wgrad(const CUtensorMap &map, const BwdParams &p, long long nb, unsigned chunks, cudaStream_t st)
 {
-    auto kern = bwd_wgrad8<SUB, USE_TMA, NORM>;
+    auto kern = bwd_wgrad8<SUB, USE_TMA, NORM, FUSE_IN>;
     if (chunks <= 1) {
         kern<<<(unsigned)nb, bwd8::THREADS, 0, st>>>(map, p);
         return GN_OK;
@@ -956,7 +974,8 @@ int launch_bwd_border8(const float *w, size_t tap_stride, const float *dsum, flo
 
 int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const float *x, const float *gy, float *gw,
                           float *gb, float *gs, float *gx, int B, int M, int N, int K, int inner, int block, int act,
-                          const float *stash, float *ws, cudaStream_t st, int normalize, float eps)
+                          const float *stash, float *ws, cudaStream_t st, int normalize, float eps, const float *in_stats,
+                          const float *gamma, const float *beta)
 {
     // stash != nullptr: the forward pass kept the pre-activations and intermediate activations
     // (launch_step_fwd_fast8 with save_h / save_x), so the replay is skipped
@@ -972,6 +991,7 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     float4 *tile_stats = reinterpret_cast<float4 *>(dsb + BP + 4);
     float2 *hterm = reinterpret_cast<float2 *>(tile_stats + (size_t)inner * B * nregions);
     if (normalize && (stash || block != 8)) return GN_ERR_UNSUPPORTED;
+    if (in_stats && (normalize || block != 8 || !gamma || !beta)) return GN_ERR_UNSUPPORTED;
     if (cudaMemsetAsync(error_flag, 0, sizeof(int), st) != cudaSuccess) {
         record_cuda_error(cudaGetLastError(), "cudaMemsetAsync");
         return GN_ERR_CUDA;
@@ -987,6 +1007,9 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     f.normalize = normalize ? 1 : 0;
     f.norm_eps = eps;
     f.tile_stats = normalize ? tile_stats : nullptr;
+    f.in_stats = reinterpret_cast<const float2 *>(in_stats);  // x is a raw step output: the replay normalises on load
+    f.gamma = gamma;
+    f.beta = beta;
     if (!stash) {
         rc = launch_step_fwd_fast8(f, act, st);
         if (rc != GN_OK) return rc;
@@ -1001,6 +1024,9 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
     p.b = b;
     p.tile_stats = tile_stats;
     p.hterm = hterm;
+    p.in_stats = reinterpret_cast<const float2 *>(in_stats);
+    p.gamma = gamma;
+    p.beta = beta;
     {
         const int chunks = pick_batch_chunks_balanced(nb, B, 3, 1.5, 16);
         p.spc = (B + chunks - 1) / chunks;
@@ -1030,6 +1056,9 @@ int launch_step_bwd_fast8(const float *w, const float *b, const float *s, const 
         if (block == 4) {
             if (!tma) return GN_ERR_UNSUPPORTED;  // excluded by bwd_fast8_applicable
             rc = launch_wgrad<4, true>(map, p, nb, chunks, st);
+        } else if (in_stats) {
+            if (!tma) return GN_ERR_UNSUPPORTED;
+            rc = launch_wgrad<8, true, false, true>(map, p, nb, chunks, st);
         } else if (normalize) {
             rc = tma ? launch_wgrad<8, true, true>(map, p, nb, chunks, st) : launch_wgrad<8, false, true>(map, p, nb, chunks, st);
         } else if (tma) {

@@ -166,6 +166,20 @@ GN_API int gn_step_backward_stash_f32(const float *weight, const float *bias, co
                                int N, int K, int inner, int block, int activation,
                                const void *stash, size_t stash_bytes, void *workspace,
                                size_t workspace_bytes, void *stream);
+/* gn_step_backward_ws_f32 / gn_step_backward_stash_f32 for a step inside the model loop
+ * (gridnet/scripts/train_mnist.py:62-64), whose input is the LayerNorm of the step before: x_raw is that step's RAW
+ * output, in_mean_rstd [B][2] its statistics, norm_weight / norm_bias the LayerNorm parameters; the kernels
+ * normalise x_raw while loading it, so the caller does not rebuild the normalised tensor. grad_x is the gradient
+ * with respect to the NORMALISED input, as in the other entry points. stash: what gn_step_forward_train_f32 kept
+ * (then workspace >= gn_step_backward_stash_workspace_bytes), or NULL (the inner iterations are replayed; workspace
+ * >= gn_step_backward_workspace_bytes(..., normalize 0, elem 4)). Float, block 8, x_raw 16-byte aligned;
+ * GN_ERR_UNSUPPORTED otherwise (normalise with gn_norm_apply_f32 and call the entry points above). */
+GN_API int gn_step_backward_fused_in_f32(const float *weight, const float *bias, const float *scale, const float *x_raw,
+                                  const float *in_mean_rstd, const float *norm_weight, const float *norm_bias,
+                                  const float *grad_y, float *grad_weight, float *grad_bias, float *grad_scale,
+                                  float *grad_x, int B, int M, int N, int K, int inner, int block, int activation,
+                                  const void *stash, size_t stash_bytes, void *workspace, size_t workspace_bytes,
+                                  void *stream);
 /* Largest `inner` the backward entry points accept for this block size and
  * element size (the per-iteration stash lives in shared memory). */
 GN_API int gn_step_backward_max_inner(int block, int elem_size);
