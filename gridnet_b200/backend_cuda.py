@@ -411,16 +411,23 @@ class FusedLoopResidualTrainOp(torch.autograd.Function):
             for k in reversed(range(outer)):
                 weight, bias, scale = plist[k]
                 h, mr = inputs[k], stats[k]
-                n = torch.empty_like(h)  # the step's input, rebuilt from h and its statistics
-                check(lib.gn_norm_apply_f32(h.data_ptr(), gamma.data_ptr(), beta.data_ptr(), mr.data_ptr(), n.data_ptr(), B, P, st))
                 dw, db, ds, gn = (torch.empty_like(t) for t in (weight, bias, scale, h))
-                if stashes[k] is not None:
-                    gridnet_cuda.backward_with_stash(weight, bias, scale, n, g, dw, db, ds, gn, inner, block, activation,
-                                                     stashes[k])
+                # the step's input n = layer_norm(h): rebuilt by the backward kernels while they load h (block 8),
+                # else by a pass here
+                if _step_backward_fused_in(weight, bias, scale, h, mr, gamma, beta, g, dw, db, ds, gn, inner, block,
+                                           activation, stashes[k]):
                     stashes[k] = None
                 else:
-                    gridnet_cuda.backward(weight, bias, scale, n, g, dw, db, ds, gn, inner, block, 1e-5, False, activation)
-                del n
+                    n = torch.empty_like(h)
+                    check(lib.gn_norm_apply_f32(h.data_ptr(), gamma.data_ptr(), beta.data_ptr(), mr.data_ptr(), n.data_ptr(),
+                                                B, P, st))
+                    if stashes[k] is not None:
+                        gridnet_cuda.backward_with_stash(weight, bias, scale, n, g, dw, db, ds, gn, inner, block, activation,
+                                                         stashes[k])
+                        stashes[k] = None
+                    else:
+                        gridnet_cuda.backward(weight, bias, scale, n, g, dw, db, ds, gn, inner, block, 1e-5, False, activation)
+                    del n
                 gn -= g  # h' = h + net(n) - n: n also enters with a minus sign
                 gh, dg, dbt = torch.empty_like(h), torch.empty_like(gamma), torch.empty_like(gamma)
                 check(lib.gn_norm_backward_local_sums_f32(h.data_ptr(), gamma.data_ptr(), gn.data_ptr(), mr.data_ptr(),
