@@ -490,13 +490,16 @@ bool fast8_applicable(const FastFwdParams &p, int block, int normalize)
 
 int g_fast8_spc_override = 0;
 
-int fast8_default_spc(int B, long long nbricks)
+int fast8_default_spc(int B, long long nbricks, int inner)
 {
     if (g_fast8_spc_override > 0) return g_fast8_spc_override;
-    // evenly filled rounds of 3 CTAs per SM; a CTA's fixed work (weight fetch, pipeline fill) is
-    // charged as 1.5 samples, which keeps CTAs long where the batch allows it and still splits
-    // a small batch over the whole GPU
-    const int chunks = pick_batch_chunks_balanced(nbricks, B, fast8::MIN_CTAS, 1.5, B < 64 ? B : 64);
+    // evenly filled rounds of 3 CTAs per SM; a CTA's fixed work (weight fetch, pipeline fill) is charged in
+    // samples: 1.5 of them, or 3.5 where a sample is cheap (one or two inner iterations; measured on a
+    // 256 x 256 x 32 slab with batch 32: one CTA per block, 0.611 ms, beats two, 0.638 ms; with eight inner
+    // iterations at block 4 the larger charge picked a split that was 15 % slower). It keeps CTAs long where the
+    // batch allows it and still splits a small batch over the whole GPU.
+    const double fixed = inner <= 2 ? 3.5 : 1.5;
+    const int chunks = pick_batch_chunks_balanced(nbricks, B, fast8::MIN_CTAS, fixed, B < 64 ? B : 64);
     return (B + chunks - 1) / chunks;
 }
 
@@ -530,7 +533,7 @@ int launch_step_fwd_fast8(FastFwdParams p, int act, cudaStream_t st)
     }
     const long long nbl = (long long)(p.M / 8) * (p.N / 8) * p.kbn;
     (void)nb;
-    if (p.spc <= 0) p.spc = fast8_default_spc(p.B, nbl);
+    if (p.spc <= 0) p.spc = fast8_default_spc(p.B, nbl, p.inner);
     dim3 grid((unsigned)nbl, (unsigned)((p.B + p.spc - 1) / p.spc));
     const bool fin = p.in_stats != nullptr, sout = p.out_partials != nullptr;
     CUtensorMap map;
