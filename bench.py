@@ -661,15 +661,15 @@ def bench_slab(ctx: Ctx):
     # where a step's time goes (in-place exchange): one more pass with CUDA events between its three launches
     phases = None
     if mode == "in-place":
-        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(outer)]
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(outer)]
         run_in_place(SlabRunner(lay, backend, x, G * G * G, work_buffers=slabs.work_buffers()), outer, slabs, boxes,
                      probe=lambda k, i: evs[k][i].record())
         torch.cuda.synchronize()
         mean = lambda i: sum(evs[k][i].elapsed_time(evs[k][i + 1]) for k in range(1, outer)) / (outer - 1)
-        phases = {"step_kernel_ms": ctx.max_over_ranks(mean(0)), "publish_sums_ms": ctx.max_over_ranks(mean(1)),
-                  "wait_and_finalize_ms": ctx.max_over_ranks(mean(2)),
-                  "note": "CUDA events between the three launches of an outer step, mean over steps 2..32 of one extra pass, "
-                          "max over ranks (the first step has no normalise-on-load)"}
+        phases = {"step_kernel_ms": ctx.max_over_ranks(mean(0)), "publish_wait_finalize_ms": ctx.max_over_ranks(mean(1)),
+                  "note": "CUDA events between the two launches of an outer step (the step kernel; the kernel that publishes "
+                          "the sums, waits for the other ranks' and finishes the statistics), mean over steps 2..32 of one "
+                          "extra pass, max over ranks (the first step has no normalise-on-load)"}
     finite = bool(torch.isfinite(out).all().item())
     chk = out.double().sum().reshape(1)  # the same bits whichever way the faces travel and whatever N is
     dist.all_reduce(chk)
@@ -695,13 +695,13 @@ def bench_slab(ctx: Ctx):
                                "LayerNorm, slab-sharded along K", "parallelism": f"slab x{world}",
                    "exchange": ("per outer step: the step kernel stores 2 faces [32,256,256] fp32 straight into the "
                                 "neighbours' ghost columns over NVLink (nothing is unpacked); the [32,2] f64 sums go to every "
-                                "rank's mailbox by peer stores and flags (no collective call)" if mode == "in-place" else
+                                "rank's mailbox by peer stores and flags (no collective call; two launches per step)" if mode == "in-place" else
                                 "per outer step: the step kernel stores 2 faces [32,256,256] fp32 into the neighbours' memory "
                                 "over NVLink; the [32,2] f64 sums go to every rank's mailbox by peer stores and flags "
                                 "(no collective call)" if direct else
                                 "per outer step: 2 faces [32,256,256] fp32 send/recv per neighbour + all-reduce of [32,2] f64"),
                    "samples_per_sec": B * steps / (ms * 1e-3), "finite": finite, "output_checksum": float(chk.item())},
-        "gpu_launches": (outer * 3 + 1) * steps if mode != "nccl" else (outer * 2 + 1) * steps,
+        "gpu_launches": (outer * (2 if mode == "in-place" else 3) + 1) * steps if mode != "nccl" else (outer * 2 + 1) * steps,
     }
     if phases is not None:
         rec["phases"] = phases

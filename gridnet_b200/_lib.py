@@ -71,6 +71,7 @@ SIGNATURES = {
     "gn_slab_unpack_faces_f32": (c_int, [_P] * 3 + _geom + [c_int, c_int, _P]),
     "gn_slab_mailbox_bytes": (c_size_t, [c_int, c_int]),
     "gn_slab_publish_sums_f32": (c_int, [_P, c_int, c_int, c_int, c_int, _P, c_int, c_ulonglong, _P]),
+    "gn_slab_publish_finalize_f32": (c_int, [_P, c_int, c_int, c_int, c_int, _P, c_int, c_ulonglong, c_longlong, c_float, _P, _P, _P]),
     "gn_slab_finalize_unpack_f32": (c_int, [_P, c_int, c_int, c_int, c_ulonglong, c_longlong, c_float, _P, _P, _P, _P,
                                             c_int, c_int, c_int, c_int, c_int, _P, _P]),
     "gn_norm_finalize_f32": (c_int, [_P, c_int, _P, c_int, c_longlong, c_float, _P]),

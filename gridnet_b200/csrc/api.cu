@@ -786,6 +786,18 @@ GN_API int gn_slab_publish_sums_f32(const double *partials, int partials_per_sam
                                     parity, step, (cudaStream_t)stream);
 }
 
+GN_API int gn_slab_publish_finalize_f32(const double *partials, int partials_per_sample, int B, int rank, int world,
+                                        void *const *mailboxes, int parity, unsigned long long step, long long count,
+                                        float eps, float *mean_rstd, int *error_flag, void *stream)
+{
+    if (B <= 0 || partials_per_sample <= 0 || count <= 0 || (parity != 0 && parity != 1) || step == 0) return GN_ERR_BAD_SHAPE;
+    if (!partials || !mailboxes || !mean_rstd) return GN_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(partials) % 16 || reinterpret_cast<uintptr_t>(mean_rstd) % 8) return GN_ERR_UNSUPPORTED;
+    return launch_slab_publish_finalize(reinterpret_cast<const double2 *>(partials), partials_per_sample, B, rank, world,
+                                        mailboxes, parity, step, count, eps, reinterpret_cast<float2 *>(mean_rstd), error_flag,
+                                        (cudaStream_t)stream);
+}
+
 GN_API int gn_slab_finalize_unpack_f32(const void *mailbox, int world, int B, int parity, unsigned long long step,
                                        long long count, float eps, float *mean_rstd, const float *from_left,
                                        const float *from_right, float *x, int M, int N, int K, int col_left, int col_right,

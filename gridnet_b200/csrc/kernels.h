@@ -92,6 +92,9 @@ int launch_slab_unpack_faces(const float *from_left, const float *from_right, fl
 size_t slab_mailbox_bytes(int world, int B);
 int launch_slab_publish_sums(const double2 *partials, int nparts, int B, int rank, int world, void *const *mailboxes,
                              int parity, unsigned long long step, cudaStream_t st);
+int launch_slab_publish_finalize(const double2 *partials, int nparts, int B, int rank, int world, void *const *mailboxes,
+                                 int parity, unsigned long long step, long long count, float eps, float2 *stats,
+                                 int *error_flag, cudaStream_t st);
 int launch_slab_finalize_unpack(const void *mailbox, int world, int B, int parity, unsigned long long step, long long count,
                                 float eps, float2 *stats, const float *from_left, const float *from_right, float *x, int M,
                                 int N, int K, int col_left, int col_right, int *error_flag, cudaStream_t st);

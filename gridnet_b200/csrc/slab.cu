@@ -70,9 +70,14 @@ size_t slab_mailbox_bytes(int world, int B)
 // grid B * kPublishSlices: a CTA adds up one slice of a sample's partials (fixed order); the CTA of a sample that
 // finishes last adds the slice sums in slice order and stores the pair into every mailbox; the CTA that finishes
 // last of all publishes the flags
+// FINALIZE: the CTA that publishes the flags then also waits (with the iteration limit of slab_finalize_unpack_k)
+// for the other ranks' flags and finishes the statistics of all samples, which saves the separate kernel where
+// nothing has to be unpacked. Every other CTA has left by then, so the wait cannot hold anything up.
+template <bool FINALIZE>
 __global__ void __launch_bounds__(256) slab_publish_sums_k(const double2 *__restrict__ partials, int nparts, int B,
                                                            int rank, int world, SlabMailboxes boxes, int parity,
-                                                           unsigned long long step)
+                                                           unsigned long long step, long long count, float eps,
+                                                           float2 *__restrict__ stats, int *error_flag)
 {
     __shared__ double red[33];
     __shared__ bool last_of_sample, last_of_all;
@@ -126,6 +131,37 @@ __global__ void __launch_bounds__(256) slab_publish_sums_k(const double2 *__rest
         unsigned long long *flag = reinterpret_cast<unsigned long long *>(boxes.base[threadIdx.x] + mailbox_flags_offset(world, B)) +
                                    parity * world + rank;
         asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flag), "l"(step) : "memory");
+    }
+    if (FINALIZE && last_of_all) {
+        const unsigned char *box = boxes.base[rank];
+        if (threadIdx.x < world) {  // one thread per rank polls that rank's flag in this rank's own mailbox
+            const unsigned long long *flag =
+                reinterpret_cast<const unsigned long long *>(box + mailbox_flags_offset(world, B)) + parity * world + threadIdx.x;
+            unsigned spins = 0;
+            unsigned long long v;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+                if (v >= step) break;
+                if (++spins > kMailboxSpinLimit) {
+                    if (error_flag) *error_flag = 1;
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        __syncthreads();
+        for (int b2 = threadIdx.x; b2 < B; b2 += blockDim.x) {
+            double ts = 0.0, tq = 0.0;
+            for (int r = 0; r < world; ++r) {  // rank order: the same bits on every rank
+                const double2 v = __ldcg(reinterpret_cast<const double2 *>(box + mailbox_sums_offset(parity, r, world, B)) + b2);
+                ts += v.x;
+                tq += v.y;
+            }
+            const double mean = ts / (double)count;
+            double var = tq / (double)count - mean * mean;
+            if (var < 0.0) var = 0.0;
+            stats[b2] = make_float2((float)mean, (float)(1.0 / sqrt(var + (double)eps)));
+        }
     }
 }
 
@@ -187,8 +223,25 @@ int launch_slab_publish_sums(const double2 *partials, int nparts, int B, int ran
         if (!mailboxes[r]) return GN_ERR_NULL_POINTER;
         boxes.base[r] = static_cast<unsigned char *>(mailboxes[r]);
     }
-    slab_publish_sums_k<<<B * kPublishSlices, 256, 0, st>>>(partials, nparts, B, rank, world, boxes, parity, step);
+    slab_publish_sums_k<false><<<B * kPublishSlices, 256, 0, st>>>(partials, nparts, B, rank, world, boxes, parity, step, 1, 0.0f,
+                                                                   nullptr, nullptr);
     return check_launch("slab_publish_sums");
+}
+
+int launch_slab_publish_finalize(const double2 *partials, int nparts, int B, int rank, int world, void *const *mailboxes,
+                                 int parity, unsigned long long step, long long count, float eps, float2 *stats,
+                                 int *error_flag, cudaStream_t st)
+{
+    if (world < 1 || world > kMaxSlabWorld || rank < 0 || rank >= world) return GN_ERR_BAD_SHAPE;
+    SlabMailboxes boxes;
+    for (int r = 0; r < world; ++r) {
+        if (!mailboxes[r]) return GN_ERR_NULL_POINTER;
+        boxes.base[r] = static_cast<unsigned char *>(mailboxes[r]);
+    }
+    if (!error_flag) error_flag = device_status_ptr();
+    slab_publish_sums_k<true><<<B * kPublishSlices, 256, 0, st>>>(partials, nparts, B, rank, world, boxes, parity, step, count,
+                                                                  eps, stats, error_flag);
+    return check_launch("slab_publish_finalize");
 }
 
 int launch_slab_finalize_unpack(const void *mailbox, int world, int B, int parity, unsigned long long step, long long count,

@@ -178,6 +178,20 @@ class CudaSlabBackend:
         self.check(self.lib.gn_slab_publish_sums_f32(self._partials.data_ptr(), self.nparts, B, rank, world, arr, step & 1,
                                                      step, self._stream()))
 
+    def publish_finalize(self, mailbox_ptrs, rank: int, world: int, step: int, count: int, like, error_flag=None):
+        """:meth:`publish_sums` and the statistics half of :meth:`finalize_unpack` in one launch
+        (``gn_slab_publish_finalize_f32``): for exchanges with nothing to unpack, on one rank per GPU. Returns
+        ``[B, 2]`` (mean, rstd)."""
+        import ctypes
+
+        B = self._partials.shape[0]
+        arr = (ctypes.c_void_p * world)(*mailbox_ptrs)
+        stats = torch.empty(B, 2, dtype=torch.float32, device=like.device)
+        self.check(self.lib.gn_slab_publish_finalize_f32(
+            self._partials.data_ptr(), self.nparts, B, rank, world, arr, step & 1, step, int(count), self.ln_eps,
+            stats.data_ptr(), None if error_flag is None else error_flag.data_ptr(), self._stream()))
+        return stats
+
     def finalize_unpack(self, mailbox, world: int, step: int, count: int, from_left, from_right, x, error_flag=None):
         """Waits (bounded) for the step's sums of all ranks, finishes the statistics and moves the faces into the
         ghost columns of ``x`` (``gn_slab_finalize_unpack_f32``); returns ``[B, 2]`` (mean, rstd)."""
@@ -539,12 +553,12 @@ def run_in_place(runner: SlabRunner, outer: int, slabs: "PeerSlabBuffers", mailb
                  probe=None) -> torch.Tensor:
     """Drive one rank for ``outer`` steps with the faces stored by the step kernel straight into the neighbours'
     ghost columns (:class:`PeerSlabBuffers`; the runner must have been built on ``slabs.work_buffers()``) and the
-    sums exchanged through :class:`PeerStatsMailboxes`: per step the step kernel, the publish kernel and a kernel
-    that waits for the sums and finishes the statistics - no unpacking pass, no collective call. A neighbour
+    sums exchanged through :class:`PeerStatsMailboxes`: per step the step kernel and one kernel that publishes the
+    sums, waits for the other ranks' and finishes the statistics - no unpacking pass, no collective call. A neighbour
     writes a ghost column of the buffer this rank reads NEXT while this rank still writes that buffer's real
     columns; it cannot write again before this rank has published its next sums, i.e. finished reading.
-    ``probe(k, i)`` (optional) is called before the three launches of step k (i = 0, 1, 2) and after them (3),
-    e.g. to record CUDA events."""
+    ``probe(k, i)`` (optional) is called before the two launches of step k (i = 0, 1) and after them (2), e.g. to
+    record CUDA events."""
     be, lay = runner.backend, runner.layout
     mark = probe if probe is not None else (lambda k, i: None)
     for k in range(outer):
@@ -553,11 +567,9 @@ def run_in_place(runner: SlabRunner, outer: int, slabs: "PeerSlabBuffers", mailb
         mark(k, 0)
         runner.compute_direct_no_sums(*slabs.targets(runner.next_index()), face_stride=slabs.stride)
         mark(k, 1)
-        be.publish_sums(mailboxes.ptrs, lay.rank, lay.world, step)
+        runner.stats = be.publish_finalize(mailboxes.ptrs, lay.rank, lay.world, step, runner.grid_size,
+                                           runner.bufs[runner.cur], mailboxes.error_flag)
         mark(k, 2)
-        runner.stats = be.finalize_unpack(mailboxes.buf, lay.world, step, runner.grid_size, None, None,
-                                          runner.bufs[runner.cur], mailboxes.error_flag)
-        mark(k, 3)
     return runner.result()
 
 

@@ -409,6 +409,13 @@ GN_API int gn_slab_unpack_faces_f32(const float *from_left, const float *from_ri
 GN_API size_t gn_slab_mailbox_bytes(int world, int B);
 GN_API int gn_slab_publish_sums_f32(const double *partials, int partials_per_sample, int B, int rank, int world,
                              void *const *mailboxes, int parity, unsigned long long step, void *stream);
+/* gn_slab_publish_sums_f32 and the statistics half of gn_slab_finalize_unpack_f32 in one launch, for exchanges
+ * that have nothing to unpack (faces stored in place): the CTA that publishes this rank's flags then waits, with the
+ * same iteration limit, for the other ranks' flags and writes mean_rstd [B][2]. Same requirement: the other ranks'
+ * kernels must be able to run at the same time (one rank per GPU). */
+GN_API int gn_slab_publish_finalize_f32(const double *partials, int partials_per_sample, int B, int rank, int world,
+                                 void *const *mailboxes, int parity, unsigned long long step, long long count,
+                                 float eps, float *mean_rstd, int *error_flag, void *stream);
 GN_API int gn_slab_finalize_unpack_f32(const void *mailbox, int world, int B, int parity, unsigned long long step,
                                 long long count, float eps, float *mean_rstd, const float *from_left,
                                 const float *from_right, float *x, int M, int N, int K, int col_left,
