@@ -101,7 +101,10 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
     // NORM: bias, scale and weight sum of the thread's four neurons (kept out of the registers: used once per
     // iteration), and per warp the sample's (halo sum, halo sum of squares, fresh interior sum, ... of squares)
     // relative to the pivot, then the pivot
-    __shared__ float4 tconst[3][NORM ? THREADS : 1];
+    // (block 4 keeps bias and scale there too: its variants run out of registers otherwise, and reading them back
+    // once per iteration made its forward pass 9 % faster; at block 8 the registers were there and it cost 1 %)
+    constexpr bool CONST_SMEM = NORM || SUB == 4;
+    __shared__ float4 tconst[3][CONST_SMEM ? THREADS : 1];
     __shared__ float4 wnorm[2][NORM ? 4 : 1];
 
     const int tid = threadIdx.x;
@@ -168,6 +171,10 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
         scl[j][1] = vs.y;
     }
 
+    if (CONST_SMEM && !NORM) {
+        tconst[0][tid] = make_float4(bias[0][0], bias[0][1], bias[1][0], bias[1][1]);
+        tconst[1][tid] = make_float4(scl[0][0], scl[0][1], scl[1][0], scl[1][1]);
+    }
     if (NORM) {
         float wsum[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};  // sum of each neuron's 27 weights
 #pragma unroll
@@ -319,7 +326,13 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
             const bool last = it + 1 == inner;
             const int cur = it & 1;
             const float *tl = tiles[set][cur] + toff;
-            float acc[2][2] = {{bias[0][0], bias[0][1]}, {bias[1][0], bias[1][1]}};
+            float acc[2][2];
+            if (CONST_SMEM) {
+                const float4 cb0 = tconst[0][tid];
+                acc[0][0] = cb0.x, acc[0][1] = cb0.y, acc[1][0] = cb0.z, acc[1][1] = cb0.w;
+            } else {
+                acc[0][0] = bias[0][0], acc[0][1] = bias[0][1], acc[1][0] = bias[1][0], acc[1][1] = bias[1][1];
+            }
             float old[2][2];
             // NORM: the interior sums of this tile relative to the pivot: this lane's share of the 128 partial
             // sums; the five shuffle rounds that add them over the warp sit between the first stencil rows
@@ -389,6 +402,13 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                         acc[j][i] = fmaf(fmaf(-tmean, ww[j][i], acc[j][i]), trs, bb[j][i]);
                         nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), ss[j][i], old[j][i]);
                     }
+            } else if (CONST_SMEM) {
+                const float4 cs0 = tconst[1][tid];
+                const float ss0[2][2] = {{cs0.x, cs0.y}, {cs0.z, cs0.w}};
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) nv[j][i] = fmaf(Act<ACT, float>::fwd(acc[j][i]), ss0[j][i], old[j][i]);
             } else {
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
