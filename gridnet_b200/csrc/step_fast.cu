@@ -28,8 +28,9 @@
 //             prefetch register into shared memory, so the normalised tensor never
 //             exists in HBM.
 //   STATS_OUT per-sample sum and sum of squares of what this step writes are
-//             reduced in double precision per warp and stored as partials for
-//             norm_finalize_k (norm.cu).
+//             reduced over each warp (128 values, in float; at block 8 the shuffle
+//             rounds run inside the next sample's first iteration) and stored as
+//             double partials for norm_finalize_k (norm.cu), which adds them in double.
 //
 // Reference semantics: gridnet/backend_torch.py:61-142; the kernel it stands in
 // for is gridnet_cuda_forward_kernel, src/gridnet_cuda_kernels.cu:101-200.
@@ -289,6 +290,12 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
     __syncthreads();
 
     const int inner = INNER_T > 0 ? INNER_T : p.inner;
+    // STATS_OUT: the (sum, sum of squares) of the four values this thread wrote for the sample before; its five
+    // shuffle rounds over the warp run between the first stencil rows of the NEXT sample's first iteration, where
+    // their latency hides (done at the end of the sample they were 13 % of the kernel at two inner iterations)
+    // (block 8; the block-4 variants, short of registers, reduce at the end of the sample: deferring cost them 6 %)
+    constexpr bool DEFER_STATS = STATS_OUT && SUB == 8;
+    float ps_sum = 0.0f, ps_sq = 0.0f;
     for (int smp = s0; smp < s1; ++smp) {
         const int set = (smp - s0) & 1;
         // TMA: the staging buffer of THIS sample was consumed a whole sample ago (a barrier has passed),
@@ -358,6 +365,13 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                         old[r - 1][0] = v[1];
                         old[r - 1][1] = v[2];
                     }
+                    if (DEFER_STATS && it == 0 && a * 4 + r < 5 && smp > s0) {  // uniform over the CTA
+                        ps_sum += __shfl_xor_sync(0xffffffffu, ps_sum, 16 >> (a * 4 + r));
+                        ps_sq += __shfl_xor_sync(0xffffffffu, ps_sq, 16 >> (a * 4 + r));
+                    }
+                    if (DEFER_STATS && it == 0 && a * 4 + r == 5 && smp > s0 && (tid & 31) == 0)
+                        p.out_partials[(size_t)(smp - 1) * p.nparts + (size_t)blk * 4 + (tid >> 5)] =
+                            make_double2((double)ps_sum, (double)ps_sq);
                     if (NORM) {
 #pragma unroll
                         for (int c = 0; c < 4; ++c) v[c] -= pivot;
@@ -467,23 +481,29 @@ __global__ void __launch_bounds__(fast8::THREADS, fast8::MIN_CTAS)
                     }
                 }
                 if (STATS_OUT) {
-                    double sm = 0.0, sq = 0.0;
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-#pragma unroll
-                        for (int i = 0; i < 2; ++i) {
-                            const double v = (double)nv[j][i];
-                            sm += v;
-                            sq = fma(v, v, sq);
-                        }
-                    sm = warp_sum(sm);
-                    sq = warp_sum(sq);
-                    if ((tid & 31) == 0)
-                        p.out_partials[(size_t)smp * p.nparts + (size_t)blk * 4 + (tid >> 5)] = make_double2(sm, sq);
+                    // the 128 values of a warp are added in float (ten shuffles instead of twenty: the shuffles,
+                    // not the arithmetic, were 13 % of this kernel at two inner iterations); everything above
+                    // the warp - 4 partials per block and sample here, their sum per sample in norm_finalize_k -
+                    // is double. A warp's sum of 128 values carries a relative error of a few 1e-7.
+                    ps_sum = (nv[0][0] + nv[0][1]) + (nv[1][0] + nv[1][1]);
+                    ps_sq = fmaf(nv[0][0], nv[0][0], nv[0][1] * nv[0][1]) + fmaf(nv[1][0], nv[1][0], nv[1][1] * nv[1][1]);
+                    if (!DEFER_STATS) {
+                        ps_sum = warp_sum(ps_sum);
+                        ps_sq = warp_sum(ps_sq);
+                        if ((tid & 31) == 0)
+                            p.out_partials[(size_t)smp * p.nparts + (size_t)blk * 4 + (tid >> 5)] =
+                                make_double2((double)ps_sum, (double)ps_sq);
+                    }
                 }
             }
         }
         __syncthreads();  // next sample's tiles are complete; this sample's tiles are free
+    }
+    if (DEFER_STATS && s0 < s1) {  // the last sample's statistics
+        ps_sum = warp_sum(ps_sum);
+        ps_sq = warp_sum(ps_sq);
+        if ((tid & 31) == 0)
+            p.out_partials[(size_t)(s1 - 1) * p.nparts + (size_t)blk * 4 + (tid >> 5)] = make_double2((double)ps_sum, (double)ps_sq);
     }
 }
 
