@@ -184,18 +184,12 @@ __global__ void __launch_bounds__(small8::THREADS, 2) outer_small_k(const OuterS
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
                         __stcg(reinterpret_cast<float2 *>(ys + (size_t)j * K), make_float2(nv[j][0], nv[j][1]));
-                    double sm = 0.0, sq = 0.0;
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-#pragma unroll
-                        for (int i = 0; i < 2; ++i) {
-                            const double v = (double)nv[j][i];
-                            sm += v;
-                            sq = fma(v, v, sq);
-                        }
+                    // a warp's 128 values in float (ten shuffles, not twenty), doubles above the warp
+                    float sm = (nv[0][0] + nv[0][1]) + (nv[1][0] + nv[1][1]);
+                    float sq = fmaf(nv[0][0], nv[0][0], nv[0][1] * nv[0][1]) + fmaf(nv[1][0], nv[1][0], nv[1][1] * nv[1][1]);
                     sm = warp_sum(sm);
                     sq = warp_sum(sq);
-                    if ((tid & 31) == 0) wsum[smp - s0][tid >> 5] = make_double2(sm, sq);
+                    if ((tid & 31) == 0) wsum[smp - s0][tid >> 5] = make_double2((double)sm, (double)sq);
                 }
             }
         }
