@@ -231,3 +231,36 @@ def test_cuda_slabs_match_single_device(world, shape):
     want = orc.outer_forward(*(t.double().numpy() for t in prob), inner, outer, 8)
     err = np.abs(got.cpu().numpy() - want)
     assert (err <= 1e-5 + 1e-4 * np.abs(want)).all(), err.max()
+
+
+@pytest.mark.gpu
+def test_publish_finalize_in_one_launch_equals_the_two_kernels():
+    """gn_slab_publish_finalize_f32 (publish this rank's sums, wait for all flags, finish the statistics in one
+    launch) against gn_slab_publish_sums_f32 + gn_slab_finalize_unpack_f32, with a world of one rank (the only
+    world whose waits a single GPU can satisfy from inside one kernel), over several steps of both parities."""
+    from gridnet_b200._lib import lib
+    from gridnet_b200.slab import make_cuda_runner
+
+    shape, B, inner = (16, 8, 16), 3, 2
+    prob = [t.float() for t in problem(41, B, shape)]
+    w, b, s, gamma, beta, x = prob
+    lay = SlabLayout(shape[2], 1, 0)
+    stats = {}
+    for tag in ("two kernels", "one kernel"):
+        r = make_cuda_runner(lay, w, b, s, gamma, beta, x, inner)
+        box = torch.zeros((int(lib.gn_slab_mailbox_bytes(1, B)) + 7) // 8, dtype=torch.int64, device="cuda")
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        got = []
+        for step in (1, 2, 3):
+            r.compute_direct_no_sums(0, 0)
+            if tag == "one kernel":
+                r.stats = r.backend.publish_finalize([box.data_ptr()], 0, 1, step, r.grid_size, r.bufs[r.cur], flag)
+            else:
+                r.backend.publish_sums([box.data_ptr()], 0, 1, step)
+                r.stats = r.backend.finalize_unpack(box, 1, step, r.grid_size, None, None, r.bufs[r.cur], flag)
+            got.append(r.stats.clone())
+        assert not bool(flag.item())
+        stats[tag] = (got, r.result())
+    for a, c in zip(stats["two kernels"][0], stats["one kernel"][0]):
+        assert torch.equal(a, c)
+    assert torch.equal(stats["two kernels"][1], stats["one kernel"][1])
