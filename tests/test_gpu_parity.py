@@ -573,3 +573,64 @@ def test_tuned_gated_backward(activation, inner):
     assert lib.gn_gated_backward_workspace_bytes(B, M, N, K, inner, 4, 4) == 0
     assert lib.gn_gated_backward_workspace_bytes(B, M, N, K, inner, 8, 8) == 0
     assert lib.gn_gated_backward_workspace_bytes(B, 12, N, K, inner, 8, 4) == 0
+
+
+@pytest.mark.parametrize("with_stash", [False, True])
+def test_backward_on_a_raw_input_with_statistics(with_stash):
+    """gn_step_backward_fused_in_f32 (the step backward inside the model loop: raw output of the step before, its
+    statistics and the LayerNorm parameters instead of the normalised tensor) against normalising first and calling
+    the ordinary workspace / stash entry points: same bits, with the inner iterations replayed and kept."""
+    from gridnet_b200._lib import lib
+
+    shape, B, inner = (24, 16, 32), 5, 3
+    M, N, K = shape
+    P = M * N * K
+    w, b, s, xraw = rng_inputs(91, B, shape, unit_scale=True)
+    r = np.random.default_rng(92)
+    b = (0.1 * r.standard_normal(shape)).astype(np.float32)
+    gamma = (1 + 0.1 * r.standard_normal(shape)).astype(np.float32)
+    beta = (0.1 * r.standard_normal(shape)).astype(np.float32)
+    xraw = (0.7 * xraw + 0.2).astype(np.float32)
+    gy = r.standard_normal(xraw.shape).astype(np.float32)
+    tw, tb, ts, tx, tgy, tga, tbe = (dev(a) for a in (w, b, s, xraw, gy, gamma, beta))
+    st = torch.cuda.current_stream().cuda_stream
+    # statistics and the normalised tensor through the library's own LayerNorm
+    nws = torch.empty(int(lib.gn_norm_workspace_bytes(B, P)), dtype=torch.uint8, device="cuda")
+    xn, mr = torch.empty_like(tx), torch.empty(B, 2, device="cuda")
+    assert lib.gn_norm_forward_f32(tx.data_ptr(), tga.data_ptr(), tbe.data_ptr(), xn.data_ptr(), mr.data_ptr(), B, P, 1e-5,
+                                   nws.data_ptr(), nws.numel(), st) == 0
+    stash = None
+    if with_stash:
+        stash = torch.empty(int(lib.gn_step_stash_bytes(B, M, N, K, inner, 8)), dtype=torch.uint8, device="cuda")
+        y = torch.empty_like(tx)
+        assert lib.gn_step_forward_stash_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), xn.data_ptr(), y.data_ptr(), B, M, N,
+                                             K, inner, 8, 2, stash.data_ptr(), stash.numel(), st) == 0
+        need = int(lib.gn_step_backward_stash_workspace_bytes(B, M, N, K, inner, 8))
+    else:
+        need = int(lib.gn_step_backward_workspace_bytes(B, M, N, K, inner, 8, 0, 4))
+    outs = {}
+    for tag in ("normalised first", "raw input"):
+        g = [torch.full_like(t, 3.0) for t in (tw, tb, ts, tx)]
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        if tag == "raw input":
+            rc = lib.gn_step_backward_fused_in_f32(
+                tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), mr.data_ptr(), tga.data_ptr(), tbe.data_ptr(),
+                tgy.data_ptr(), *(t.data_ptr() for t in g), B, M, N, K, inner, 8, 2,
+                None if stash is None else stash.data_ptr(), 0 if stash is None else stash.numel(), ws.data_ptr(),
+                ws.numel(), st)
+        elif with_stash:
+            rc = lib.gn_step_backward_stash_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), xn.data_ptr(), tgy.data_ptr(),
+                                                *(t.data_ptr() for t in g), B, M, N, K, inner, 8, 2, stash.data_ptr(),
+                                                stash.numel(), ws.data_ptr(), ws.numel(), st)
+        else:
+            rc = lib.gn_step_backward_ws_f32(tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), xn.data_ptr(), tgy.data_ptr(),
+                                             *(t.data_ptr() for t in g), B, M, N, K, inner, 8, 1e-5, 0, 2, ws.data_ptr(),
+                                             ws.numel(), st)
+        assert rc == 0, lib.gn_status_string(rc)
+        outs[tag] = [t.cpu().numpy() for t in g]
+    for name, a, c in zip(("gw", "gb", "gs", "gx"), outs["normalised first"], outs["raw input"]):
+        assert np.array_equal(a, c), f"{name}: normalising while loading changed the bits"
+    # block 4 has no such path
+    assert lib.gn_step_backward_fused_in_f32(
+        tw.data_ptr(), tb.data_ptr(), ts.data_ptr(), tx.data_ptr(), mr.data_ptr(), tga.data_ptr(), tbe.data_ptr(),
+        tgy.data_ptr(), *(t.data_ptr() for t in g), B, M, N, K, inner, 4, 2, None, 0, ws.data_ptr(), ws.numel(), st) == -8
